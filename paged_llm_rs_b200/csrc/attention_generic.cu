@@ -1,0 +1,233 @@
+// Paged attention for any head size (a multiple of 4 floats / 8 bfloat16 up to
+// 256), any number of heads and groups, any page size, with an optional window:
+// the kernel of the true 32-bit path, and of bfloat16 shapes that the tuned
+// kernels do not take.  Arithmetic in float on the CUDA cores.
+//
+// What it computes is the reference's attention
+// (crates/pagedllm/src/model/attention.rs:198-214 and
+// crates/pagedllm/src/kernels/paged_attention.cu:86-147): for query head h the
+// keys and values of kv head h / group; score = q.k * scale; key j is visible to
+// the query at position p iff j <= p (and, with a window w, j > p - w);
+// softmax in float; weighted sum of values.  Unlike the reference's kernel it
+// keeps no score buffer as long as the context: the softmax runs online over
+// tiles of 32 keys, so the context is bounded by the cache alone.
+//
+// Work comes as a list of items prepared on the host, one CTA per (item, kv
+// head, part of the group):
+//   item = {seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slot, unused}
+// q_count consecutive tokens of one request (token index q_token0.. in the step,
+// positions q_pos0..) attend over keys [kv_begin, kv_end) of the request's block
+// table row `seg`.  part_slot < 0: the item sees all keys its queries may see and
+// writes the normalised output.  part_slot >= 0: the item is one split of a long
+// key range and writes (max, sum, unnormalised output) for attention_reduce.
+#include "common.cuh"
+
+#define ATT_BK 32        // keys per tile
+#define ATT_MAX_ROWS 16  // query rows (token x head of the group) per CTA, one warp each
+#define ATT_MAX_HD 256
+
+struct AttnWork { int seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slot, unused; };
+
+template <typename T>
+__global__ void attention_generic_kernel(
+    const T* __restrict__ q,            // [n_tokens, nh, hd]
+    const T* __restrict__ k_pool, const T* __restrict__ v_pool,  // [pages, nkv, page_size, hd]
+    const int* __restrict__ block_tables,  // [n_segs, table_width]
+    const AttnWork* __restrict__ work, const int* __restrict__ n_work_ptr,
+    T* __restrict__ out,                // [n_tokens, nh, hd]
+    float* __restrict__ part_o,         // [parts, nh, hd]
+    float* __restrict__ part_ml,        // [parts, nh, 2]
+    int nh, int nkv, int hd, int page_size, int n_pages, int table_width, int window, float scale,
+    int heads_per_cta, int* status) {
+    if ((int)blockIdx.x >= *n_work_ptr) return;
+    const AttnWork w = work[blockIdx.x];
+    const int group = nh / nkv;
+    const int gparts = (group + heads_per_cta - 1) / heads_per_cta;
+    const int kh = blockIdx.y / gparts;
+    const int head0 = kh * group + (blockIdx.y % gparts) * heads_per_cta;       // first q head of this CTA
+    const int n_heads = min(heads_per_cta, kh * group + group - head0);
+    const int rows = w.q_count * n_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hdp = hd + 4;  // padded row: conflict-free float4 reads across keys
+
+    extern __shared__ float smem[];
+    float* q_s = smem;                               // [ATT_MAX_ROWS][hd]
+    float* k_s = q_s + ATT_MAX_ROWS * hd;            // [ATT_BK][hdp]
+    float* v_s = k_s + ATT_BK * hdp;                 // [ATT_BK][hdp]
+    __shared__ int page_s[ATT_BK];
+
+    // Row r of the CTA: token r / n_heads of the item, head head0 + r % n_heads.
+    const bool active = warp < rows;
+    const int tq = active ? warp / n_heads : 0;
+    const int head = active ? head0 + warp % n_heads : head0;
+    const int pos = w.q_pos0 + tq;
+    if (active) {
+        const T* qr = q + ((size_t)(w.q_token0 + tq) * nh + head) * hd;
+        for (int e = lane; e < hd; e += 32) q_s[warp * hd + e] = to_f32(qr[e]) * scale;
+    }
+    // Keys this row may see inside the item's range.
+    const int lo = max(w.kv_begin, window > 0 ? pos - window + 1 : 0);
+    const int hi = min(w.kv_end, pos + 1);
+
+    float m = -CUDART_INF_F, l = 0.f;
+    float acc[ATT_MAX_HD / 32];
+#pragma unroll
+    for (int k = 0; k < ATT_MAX_HD / 32; k++) acc[k] = 0.f;
+
+    constexpr int N = Vec16<T>::N;
+    const int vec_per_row = hd / N;
+    const int* table = block_tables + (size_t)w.seg * table_width;
+
+    for (int kv0 = w.kv_begin; kv0 < w.kv_end; kv0 += ATT_BK) {
+        __syncthreads();  // the previous tile is no longer read
+        if (threadIdx.x < ATT_BK) {
+            const int j = kv0 + threadIdx.x;
+            int page = -1;
+            if (j < w.kv_end) {
+                const int b = j / page_size;
+                page = b < table_width ? table[b] : -1;
+                // A freed page of a window layer holds -1 and is never visible to a
+                // query of this item; anything else out of range is a fault.
+                if (page >= n_pages) { atomicOr(status, 8); page = -1; }
+            }
+            page_s[threadIdx.x] = page;
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < ATT_BK * vec_per_row; idx += blockDim.x) {
+            const int j = idx / vec_per_row, c = (idx % vec_per_row) * N;
+            const int page = page_s[j];
+            float fk[N], fv[N];
+            if (page >= 0) {
+                const size_t base = (((size_t)page * nkv + kh) * page_size + (kv0 + j) % page_size) * hd + c;
+                Vec16<T> vk, vv;
+                vk.load(k_pool + base); vv.load(v_pool + base);
+                vk.unpack(fk); vv.unpack(fv);
+            } else {
+#pragma unroll
+                for (int k = 0; k < N; k++) { fk[k] = 0.f; fv[k] = 0.f; }
+            }
+#pragma unroll
+            for (int k = 0; k < N; k++) { k_s[j * hdp + c + k] = fk[k]; v_s[j * hdp + c + k] = fv[k]; }
+        }
+        __syncthreads();
+        if (!active) continue;
+        const int j = kv0 + lane;
+        const bool visible = j >= lo && j < hi;
+        if (!__any_sync(0xffffffffu, visible)) continue;
+        float s = 0.f;
+        {
+            const float4* kr = reinterpret_cast<const float4*>(k_s + lane * hdp);
+            const float4* qr = reinterpret_cast<const float4*>(q_s + warp * hd);
+            for (int c = 0; c < hd / 4; c++) {
+                const float4 a = qr[c], b = kr[c];
+                s = fmaf(a.x, b.x, s); s = fmaf(a.y, b.y, s); s = fmaf(a.z, b.z, s); s = fmaf(a.w, b.w, s);
+            }
+        }
+        s = visible ? s : -CUDART_INF_F;
+        const float m_new = fmaxf(m, warp_max(s));
+        const float p = visible ? expf(s - m_new) : 0.f;
+        const float corr = expf(m - m_new);  // m = -inf on the first visible tile: exp(-inf) = 0
+        l = l * corr + warp_sum(p);
+        m = m_new;
+#pragma unroll
+        for (int k = 0; k < ATT_MAX_HD / 32; k++) acc[k] *= corr;
+        for (int jj = 0; jj < ATT_BK; jj++) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            if (pj == 0.f) continue;  // uniform across the warp
+            const float* vr = v_s + jj * hdp;
+#pragma unroll
+            for (int k = 0; k < ATT_MAX_HD / 32; k++)
+                if (k * 32 + lane < hd) acc[k] = fmaf(pj, vr[k * 32 + lane], acc[k]);
+        }
+    }
+    if (!active) return;
+    if (w.part_slot < 0) {
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        T* o = out + ((size_t)(w.q_token0 + tq) * nh + head) * hd;
+#pragma unroll
+        for (int k = 0; k < ATT_MAX_HD / 32; k++)
+            if (k * 32 + lane < hd) o[k * 32 + lane] = from_f32<T>(acc[k] * inv);
+    } else {
+        const size_t pr = (size_t)(w.part_slot + tq) * nh + head;
+        float* o = part_o + pr * hd;
+#pragma unroll
+        for (int k = 0; k < ATT_MAX_HD / 32; k++)
+            if (k * 32 + lane < hd) o[k * 32 + lane] = acc[k];
+        if (lane == 0) { part_ml[pr * 2] = m; part_ml[pr * 2 + 1] = l; }
+    }
+}
+
+// Combine the splits of a token in their order: for token t with
+// red[t] = {first, count, stride}, its parts are first + s * stride, s < count.
+// count == 0: the token was not split, nothing to do.
+template <typename T>
+__global__ void attention_reduce_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                        const int* __restrict__ red, const int* __restrict__ n_red_ptr,
+                                        T* __restrict__ out, int nh, int hd) {
+    const int t = blockIdx.x;
+    if (t >= *n_red_ptr) return;
+    const int token = red[t * 4], first = red[t * 4 + 1], count = red[t * 4 + 2], stride = red[t * 4 + 3];
+    if (count <= 0) return;
+    for (int head = threadIdx.y; head < nh; head += blockDim.y) {
+        float M = -CUDART_INF_F;
+        for (int s = 0; s < count; s++) M = fmaxf(M, part_ml[((size_t)(first + s * stride) * nh + head) * 2]);
+        float L = 0.f;
+        for (int s = 0; s < count; s++) {
+            const size_t pr = (size_t)(first + s * stride) * nh + head;
+            const float ms = part_ml[pr * 2];
+            L += ms == -CUDART_INF_F ? 0.f : part_ml[pr * 2 + 1] * expf(ms - M);
+        }
+        const float inv = L > 0.f ? 1.0f / L : 0.f;
+        for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+            float o = 0.f;
+            for (int s = 0; s < count; s++) {
+                const size_t pr = (size_t)(first + s * stride) * nh + head;
+                const float ms = part_ml[pr * 2];
+                if (ms != -CUDART_INF_F) o += part_o[pr * hd + d] * expf(ms - M);
+            }
+            out[((size_t)token * nh + head) * hd + d] = from_f32<T>(o * inv);
+        }
+    }
+}
+
+PLLM_EXPORT int pllm_attention_generic(int dtype, const void* q, const void* k_pool, const void* v_pool,
+                                       const int* block_tables, const int* work, const int* n_work_ptr,
+                                       int max_work, void* out, float* part_o, float* part_ml, int nh, int nkv,
+                                       int hd, int page_size, int n_pages, int table_width, int window,
+                                       float scale, int* status, cudaStream_t stream) {
+    if (max_work <= 0) return PLLM_OK;
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0) return PLLM_ERR_SIZE;
+    if (hd <= 0 || hd > ATT_MAX_HD || hd % 8 != 0) return PLLM_ERR_SIZE;
+    const int group = nh / nkv;
+    const int heads_per_cta = group < ATT_MAX_ROWS ? group : ATT_MAX_ROWS;
+    const int gparts = (group + heads_per_cta - 1) / heads_per_cta;
+    const size_t smem = ((size_t)ATT_MAX_ROWS * hd + 2 * (size_t)ATT_BK * (hd + 4)) * sizeof(float);
+    PLLM_DISPATCH_DTYPE(dtype, {
+        cudaFuncSetAttribute(attention_generic_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        dim3 grid(max_work, nkv * gparts);
+        attention_generic_kernel<T><<<grid, ATT_MAX_ROWS * 32, smem, stream>>>(
+            (const T*)q, (const T*)k_pool, (const T*)v_pool, block_tables, (const AttnWork*)work, n_work_ptr,
+            (T*)out, part_o, part_ml, nh, nkv, hd, page_size, n_pages, table_width, window, scale, heads_per_cta,
+            status);
+    });
+    return launch_status();
+}
+
+// The most query tokens one work item may hold for a given group size, so that
+// the host cuts tiles the kernel accepts.
+PLLM_EXPORT int pllm_attention_generic_tile_tokens(int nh, int nkv) {
+    const int group = nh / nkv;
+    const int heads_per_cta = group < ATT_MAX_ROWS ? group : ATT_MAX_ROWS;
+    return ATT_MAX_ROWS / heads_per_cta;
+}
+
+PLLM_EXPORT int pllm_attention_reduce(int dtype, const float* part_o, const float* part_ml, const int* red,
+                                      const int* n_red_ptr, int max_red, void* out, int nh, int hd,
+                                      cudaStream_t stream) {
+    if (max_red <= 0) return PLLM_OK;
+    PLLM_DISPATCH_DTYPE(dtype, {
+        dim3 block(32, 4);
+        attention_reduce_kernel<T><<<max_red, block, 0, stream>>>(part_o, part_ml, red, n_red_ptr, (T*)out, nh, hd);
+    });
+    return launch_status();
+}

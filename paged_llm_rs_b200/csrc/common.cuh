@@ -1,0 +1,104 @@
+// Shared helpers of the sm_100a kernels: element conversion, vector access,
+// warp and block reductions, and the return codes of the C entry points.
+//
+// Every kernel is a template over the element type (float for the true 32-bit
+// path, __nv_bfloat16 for serving) and does its arithmetic in float.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#define PLLM_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Return codes of the C entry points.  0 is success; positive values are
+// cudaError_t from the launch; negative values are refusals of the arguments.
+enum : int {
+    PLLM_OK = 0,
+    PLLM_ERR_DTYPE = -1,      // dtype code not 0 (float32) or 1 (bfloat16)
+    PLLM_ERR_SIZE = -2,       // a size the kernel does not take
+    PLLM_ERR_ALIGN = -3,      // a pointer or stride that is not aligned as required
+    PLLM_ERR_LIMIT = -4,      // a size beyond a stated maximum
+};
+
+enum : int { PLLM_F32 = 0, PLLM_BF16 = 1 };
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` is 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : 0.f;
+    return warp_sum(r);
+}
+
+// 16-byte vectors of elements: 4 floats or 8 bfloat16.
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    float4 raw;
+    __device__ __forceinline__ void load(const float* p) { raw = *reinterpret_cast<const float4*>(p); }
+    __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = raw; }
+    __device__ __forceinline__ void unpack(float* f) const { f[0] = raw.x; f[1] = raw.y; f[2] = raw.z; f[3] = raw.w; }
+    __device__ __forceinline__ void pack(const float* f) { raw = make_float4(f[0], f[1], f[2], f[3]); }
+};
+template <> struct Vec16<bf16> {
+    static constexpr int N = 8;
+    uint4 raw;
+    __device__ __forceinline__ void load(const bf16* p) { raw = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void store(bf16* p) const { *reinterpret_cast<uint4*>(p) = raw; }
+    __device__ __forceinline__ void unpack(float* f) const {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            // a bfloat16 is the upper half of a float
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    __device__ __forceinline__ void pack(const float* f) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        raw = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
+static inline int launch_status() {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? PLLM_OK : (int)e;
+}
+
+#define PLLM_DISPATCH_DTYPE(dtype, ...)                         \
+    do {                                                        \
+        if ((dtype) == PLLM_F32) { typedef float T; __VA_ARGS__; } \
+        else if ((dtype) == PLLM_BF16) { typedef bf16 T; __VA_ARGS__; } \
+        else return PLLM_ERR_DTYPE;                             \
+    } while (0)

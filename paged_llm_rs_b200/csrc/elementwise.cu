@@ -1,0 +1,183 @@
+// Embedding gather, RMSNorm (plain, with the residual add fused in, and over
+// gathered rows), and the SwiGLU activation.
+//
+// Formulas follow the reference: embedding is a plain row gather with no scale
+// (crates/pagedllm/src/model/mod.rs:323-327); RMSNorm is x / sqrt(mean(x^2) + eps)
+// times the gain with the statistic in float (crates/pagedllm/src/model/layers.rs:58-64);
+// SwiGLU is silu(gate) * up with the activation on the gate (layers.rs:93-99).
+// Here the whole norm, gain multiply included, runs in float and rounds once.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+// out[t, :] = table[token[t], :].  A token id outside [0, vocab) writes zeros and
+// raises bit 0 of *status.
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table, T* __restrict__ out,
+                             int hidden, int vocab, int* status) {
+    const int t = blockIdx.x;
+    const int tok = tokens[t];
+    const bool ok = tok >= 0 && tok < vocab;
+    if (!ok && threadIdx.x == 0) atomicOr(status, 1);
+    const T* src = table + (size_t)(ok ? tok : 0) * hidden;
+    T* dst = out + (size_t)t * hidden;
+    constexpr int N = Vec16<T>::N;
+    if (hidden % N == 0) {
+        for (int i = threadIdx.x * N; i < hidden; i += blockDim.x * N) {
+            Vec16<T> v;
+            if (ok) v.load(src + i);
+            else { float z[N] = {}; v.pack(z); }
+            v.store(dst + i);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? src[i] : from_f32<T>(0.f);
+    }
+}
+
+PLLM_EXPORT int pllm_embed(int dtype, const int* tokens, const void* table, void* out, int n_tokens, int hidden,
+                           int vocab, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return PLLM_OK;
+    if (hidden <= 0 || vocab <= 0) return PLLM_ERR_SIZE;
+    PLLM_DISPATCH_DTYPE(dtype, {
+        int threads = min(256, max(32, (hidden / Vec16<T>::N + 31) / 32 * 32));
+        embed_kernel<T><<<n_tokens, threads, 0, stream>>>(tokens, (const T*)table, (T*)out, hidden, vocab, status);
+    });
+    return launch_status();
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// Row i of the launch reads source row r = rows ? rows[i] : i.
+//   v = x[r] (+ delta[r], rounded to T as the residual stream holds it)
+//   if residual_out: residual_out[r] = v         (the fused residual add)
+//   y[i] = v / sqrt(mean(v^2) + eps) * gain
+// x and residual_out may be the same buffer.
+template <typename T>
+__global__ void rmsnorm_kernel(const T* x, const T* __restrict__ delta, T* residual_out,
+                               const float* __restrict__ gain, T* __restrict__ y, const int* __restrict__ rows,
+                               int width, float eps) {
+    __shared__ float scratch[32];
+    const int i = blockIdx.x;
+    const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+    const T* xr = x + r * width;
+    const T* dr = delta ? delta + r * width : nullptr;
+    T* rr = residual_out ? residual_out + r * width : nullptr;
+    T* yr = y + (size_t)i * width;
+    constexpr int N = Vec16<T>::N;
+    const bool vec = (width % N == 0);
+    float ss = 0.f;
+    if (vec) {
+        for (int c = threadIdx.x * N; c < width; c += blockDim.x * N) {
+            Vec16<T> v; v.load(xr + c);
+            float f[N]; v.unpack(f);
+            if (dr) {
+                Vec16<T> d; d.load(dr + c);
+                float g[N]; d.unpack(g);
+#pragma unroll
+                for (int k = 0; k < N; k++) f[k] = to_f32(from_f32<T>(f[k] + g[k]));
+                if (rr) { Vec16<T> o; o.pack(f); o.store(rr + c); }
+            } else if (rr && rr != xr) {
+                v.store(rr + c);
+            }
+#pragma unroll
+            for (int k = 0; k < N; k++) ss += f[k] * f[k];
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) {
+            float f = to_f32(xr[c]);
+            if (dr) { f = to_f32(from_f32<T>(f + to_f32(dr[c]))); if (rr) rr[c] = from_f32<T>(f); }
+            else if (rr && rr != xr) rr[c] = xr[c];
+            ss += f * f;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    // Second pass: the summed row is read back from where it was written, or
+    // recomputed from x and delta when nothing was written (gathered rows).
+    if (vec) {
+        for (int c = threadIdx.x * N; c < width; c += blockDim.x * N) {
+            float f[N];
+            if (rr) { Vec16<T> v; v.load(rr + c); v.unpack(f); }
+            else {
+                Vec16<T> v; v.load(xr + c); v.unpack(f);
+                if (dr) {
+                    Vec16<T> d; d.load(dr + c);
+                    float g[N]; d.unpack(g);
+#pragma unroll
+                    for (int k = 0; k < N; k++) f[k] = to_f32(from_f32<T>(f[k] + g[k]));
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < N; k++) f[k] = f[k] * inv * gain[c + k];
+            Vec16<T> o; o.pack(f); o.store(yr + c);
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) {
+            float f;
+            if (rr) f = to_f32(rr[c]);
+            else { f = to_f32(xr[c]); if (dr) f = to_f32(from_f32<T>(f + to_f32(dr[c]))); }
+            yr[c] = from_f32<T>(f * inv * gain[c]);
+        }
+    }
+}
+
+PLLM_EXPORT int pllm_rmsnorm(int dtype, const void* x, const void* delta, void* residual_out, const float* gain,
+                             void* y, const int* rows, int n_rows, int width, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return PLLM_OK;
+    if (width <= 0) return PLLM_ERR_SIZE;
+    PLLM_DISPATCH_DTYPE(dtype, {
+        int threads = min(1024, max(32, (width / Vec16<T>::N + 31) / 32 * 32));
+        // A thread that wrote residual_out reads the same addresses back in the
+        // second pass (same thread, same columns), so no fence is needed.
+        rmsnorm_kernel<T><<<n_rows, threads, 0, stream>>>((const T*)x, (const T*)delta, (T*)residual_out, gain,
+                                                          (T*)y, rows, width, eps);
+    });
+    return launch_status();
+}
+
+// ------------------------------------------------------------------- SwiGLU
+// in is [n, 2*inter]: the gate in columns [0, inter), up in [inter, 2*inter).
+// out[n, inter] = silu(gate) * up, silu(z) = z / (1 + exp(-z)).
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, long long total_vec,
+                              int vec_per_row) {
+    constexpr int N = Vec16<T>::N;
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total_vec;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long row = idx / vec_per_row;
+        const int c = (int)(idx % vec_per_row) * N;
+        const T* g = in + row * 2 * inter + c;
+        Vec16<T> vg, vu; vg.load(g); vu.load(g + inter);
+        float fg[N], fu[N];
+        vg.unpack(fg); vu.unpack(fu);
+#pragma unroll
+        for (int k = 0; k < N; k++) fg[k] = fg[k] / (1.0f + expf(-fg[k])) * fu[k];
+        Vec16<T> o; o.pack(fg); o.store(out + row * inter + c);
+    }
+}
+template <typename T>
+__global__ void swiglu_scalar_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, long long total) {
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long row = idx / inter;
+        const int c = (int)(idx % inter);
+        const float g = to_f32(in[row * 2 * inter + c]), u = to_f32(in[row * 2 * inter + inter + c]);
+        out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+PLLM_EXPORT int pllm_swiglu(int dtype, const void* in, void* out, int n_rows, int inter, cudaStream_t stream) {
+    if (n_rows <= 0) return PLLM_OK;
+    if (inter <= 0) return PLLM_ERR_SIZE;
+    PLLM_DISPATCH_DTYPE(dtype, {
+        constexpr int N = Vec16<T>::N;
+        if (inter % N == 0) {
+            long long total = (long long)n_rows * (inter / N);
+            int blocks = (int)min((long long)148 * 16, (total + 255) / 256);
+            swiglu_kernel<T><<<blocks, 256, 0, stream>>>((const T*)in, (T*)out, inter, total, inter / N);
+        } else {
+            long long total = (long long)n_rows * inter;
+            int blocks = (int)min((long long)148 * 16, (total + 255) / 256);
+            swiglu_scalar_kernel<T><<<blocks, 256, 0, stream>>>((const T*)in, (T*)out, inter, total);
+        }
+    });
+    return launch_status();
+}

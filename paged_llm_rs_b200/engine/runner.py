@@ -1,0 +1,129 @@
+"""The model on the device with its cache, and the one step function.
+
+``ModelRunner.step`` is the engine's only forward pass
+(crates/pagedllm/src/model/mod.rs:315-352 in the reference): it runs exactly the
+tokens it is given, as one batch, from the cache that earlier steps left, writes
+their keys and values, and returns the logits at the wanted places.  It does not
+advance any length: whoever asked for the step commits it afterwards
+(mod.rs:312-314), so a failed step leaves the bookkeeping untouched.
+Generation, the scheduler and trace replay all go through it.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import models  # noqa: F401  (registers the architectures)
+from ..cache.manager import CacheManager
+from ..config.registry import load_config
+from ..errors import ConfigError, KernelError
+from ..kernels import ops
+from ..parts.base import KVNeed, Runtime
+from ..parts.decoder import DecoderModel
+from ..weights.loader import load_weights
+from .step import GroupPlanConfig, StepCaps, StepEntry, StepPacker
+
+DTYPES = {"float32": torch.float32, "f32": torch.float32, "fp32": torch.float32,
+          "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
+SM_COUNT_TARGET = 2 * 148  # CTAs an attention launch should have before splits stop
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name not in (torch.float32, torch.bfloat16):
+            raise ConfigError(f"dtype {name} is not served; float32 and bfloat16 are")
+        return name
+    try:
+        return DTYPES[str(name).lower()]
+    except KeyError:
+        raise ConfigError(f"dtype {name!r} is not served; float32 and bfloat16 are") from None
+
+
+class ModelRunner:
+    def __init__(self, model_dir: str, dtype="bfloat16", page_size: int = 16, num_pages: Optional[int] = None,
+                 cache_bytes: Optional[int] = None, max_requests: int = 64, device: str = "cuda:0",
+                 prefix_cache: bool = True):
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: this engine has no CPU path")
+        ops.lib()  # build or load the kernels now; fails loudly if that cannot be done
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self.dtype = parse_dtype(dtype)
+        # float32 means float32: no TF32 or other reduced-precision matrix mode
+        torch.backends.cuda.matmul.allow_tf32 = False
+        torch.backends.cudnn.allow_tf32 = False
+        torch.set_float32_matmul_precision("highest")
+        self.arch, self.config = load_config(model_dir)
+        self.spec = self.arch.describe(self.config)
+        self.rt = Runtime(self.device, self.dtype)
+        with torch.no_grad():
+            self.model = DecoderModel(self.spec, self.rt)
+            tensors = load_weights(model_dir, self.model.tensor_specs(), self.dtype, self.device)
+            self.model.bind(tensors)
+            del tensors
+        needs = self.model.cache_needs()
+        group_sizes = []
+        for e, need in zip(self.model.schedule, needs):
+            m = self.model.blocks[e.layer].mixer
+            group_sizes.append(getattr(m, "nh", 1) // max(1, getattr(m, "nkv", 1)) if isinstance(need, KVNeed) else 1)
+        probe = CacheManager(needs, page_size, 1, 1, self.dtype, self.device, allocate_device=False)
+        if num_pages is None:
+            if cache_bytes is None:
+                raise ConfigError("give the cache a size: num_pages or cache_bytes")
+            # pages = budget / bytes per page, at least one (crates/pagedllm/src/batch.rs:53-57)
+            num_pages = max(1, cache_bytes // max(1, page_size * probe.bytes_per_token()))
+        self.cache = CacheManager(needs, page_size, num_pages, max_requests, self.dtype, self.device,
+                                  prefix_cache=prefix_cache, group_sizes=group_sizes)
+        self.caches = self.cache.layer_caches()
+        plans, self._heads = [], []
+        for g in self.cache.groups:
+            nkv = g.need.num_kv_heads
+            nh = nkv * g.max_group_size
+            tile = ops.attention_tile_tokens(nh, nkv)
+            gparts = -(-g.max_group_size // 16)
+            plans.append(GroupPlanConfig(tile, nkv * gparts, g.window))
+            nh_max = max(getattr(self.model.blocks[self.model.schedule[i].layer].mixer, "nh", nh) for i in g.entries)
+            self._heads.append((nh_max, g.need.head_dim))
+        self.packer = StepPacker(self.cache, plans, SM_COUNT_TARGET, self.spec.vocab_size, self.spec.max_positions,
+                                 self.device)
+        self.vocab_size = self.spec.vocab_size
+
+    # -- the step ----------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry], check: bool = True) -> torch.Tensor:
+        """Run one batch.  Returns float32 logits [wanted, vocab] on the device, in
+        the order of the entries and of their ``want`` lists.  Pages for the new
+        tokens must have been reserved; nothing is committed."""
+        if not entries:
+            return torch.zeros((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        host, layout, sizes = self.packer.pack(entries, self._heads)
+        pinned = torch.from_numpy(host).pin_memory()
+        dev = pinned.to(self.device, non_blocking=True)
+        state = self.packer.to_state(dev, layout, sizes, self._heads)
+        with torch.no_grad():
+            logits = self.model.forward(state, self.caches)
+        if check:
+            self.check_status()
+        return logits
+
+    def check_status(self) -> None:
+        code = int(self.rt.status.item())
+        if code:
+            self.rt.status.zero_()
+            what = [name for bit, name in ((1, "a token id outside the vocabulary"), (2, "a cache slot outside the pool"),
+                                          (4, "a position outside the rotary table"), (8, "a page id outside the pool"))
+                    if code & bit]
+            raise KernelError("a kernel met " + ", ".join(what))
+
+    # -- sizes -------------------------------------------------------------------------------
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+        for p in self.model.parts():
+            for v in vars(p).values():
+                if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
+                    seen.add(v.data_ptr())
+                    total += v.numel() * v.element_size()
+        return total

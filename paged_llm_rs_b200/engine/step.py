@@ -1,0 +1,196 @@
+"""The step function's input: a batch of (request, its next tokens) packed for
+the device.
+
+The reference's descriptor is ``Batch`` (crates/pagedllm/src/batch.rs:67-94): a
+rectangle, or one row per token so that a portion of a prompt can ride beside
+decoded tokens, with per-layer uploads of tables on the kernel path
+(crates/pagedllm/src/kernels/paged_attention.rs:114-123).  Here a step is a list
+of segments (the consecutive tokens one request brings), each cut anywhere, and
+everything the kernels need goes to the device in ONE packed int32 buffer:
+token ids, positions, wanted rows, segments, and per cache group the write
+slots, the block tables and the attention work items.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, RequestCache
+from ..errors import CacheError, ConfigError
+from ..kernels import attention_plan
+from ..parts.base import GroupStep, StepState
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens, and the places among them
+    whose logits are wanted (may be empty)."""
+
+    request_id: object
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class GroupPlanConfig:
+    tile_tokens: int      # query tokens per attention work item
+    ctas_per_item: int    # CTAs the kernel launches per item (kv heads x group parts)
+    window: Optional[int]
+
+
+@dataclass
+class StepCaps:
+    """Fixed capacities of a packed step (for steps replayed as CUDA graphs); None
+    where the actual size is used."""
+
+    tokens: int
+    wanted: int
+    segments: int
+    table_width: int
+
+
+class StepPacker:
+    """Lays out and fills the packed buffer of a step."""
+
+    def __init__(self, cache: CacheManager, plans: List[GroupPlanConfig], target_ctas: int, vocab_size: int,
+                 max_positions: int, device):
+        self.cache, self.plans, self.target_ctas = cache, plans, target_ctas
+        self.vocab_size, self.max_positions, self.device = vocab_size, max_positions, device
+        self._scratch: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+    def scratch(self, gi: int, parts: int, nh_hd: Tuple[int, int]) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Partial-result buffers of group gi for at least ``parts`` rows."""
+        nh, hd = nh_hd
+        cur = self._scratch.get(gi)
+        if cur is None or cur[0].shape[0] < parts or cur[0].shape[1] != nh or cur[0].shape[2] != hd:
+            rows = max(parts, 1)
+            cur = (torch.empty((rows, nh, hd), dtype=torch.float32, device=self.device),
+                   torch.empty((rows, nh, 2), dtype=torch.float32, device=self.device))
+            self._scratch[gi] = cur
+        return cur
+
+    def pack(self, entries: Sequence[StepEntry], heads: List[Tuple[int, int]],
+             caps: Optional[StepCaps] = None, work_caps: Optional[List[Tuple[int, int]]] = None):
+        """Returns (host int32 array, layout dict, sizes) for the entries.  Pages
+        must already be reserved for every token."""
+        cache = self.cache
+        toks: List[int] = []
+        pos: List[int] = []
+        rows: List[int] = []
+        segs: List[Tuple[int, int, int, int]] = []
+        rcs: List[RequestCache] = []
+        for e in entries:
+            n = len(e.tokens)
+            if n == 0:
+                raise ConfigError(f"request {e.request_id!r} brings no tokens to the step")
+            rc = cache.get(e.request_id)
+            p0 = rc.tokens
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ConfigError(f"request {e.request_id!r} wants place {w} among {n} tokens")
+                rows.append(len(toks) + w)
+            segs.append((len(toks), n, p0, rc.state_slot))
+            rcs.append(rc)
+            toks.extend(int(t) for t in e.tokens)
+            pos.extend(range(p0, p0 + n))
+        T, n_want, n_seg = len(toks), len(rows), len(segs)
+        tok_a = np.asarray(toks, dtype=np.int64)
+        if T and (tok_a.min() < 0 or tok_a.max() >= self.vocab_size):
+            raise ConfigError(f"a token id lies outside the vocabulary of {self.vocab_size}")
+        if T and max(pos) >= self.max_positions:
+            raise ConfigError(f"position {max(pos)} reaches past max_position_embeddings {self.max_positions}")
+
+        ps = cache.page_size
+        Tc = caps.tokens if caps else T
+        nc = caps.wanted if caps else n_want
+        sc = caps.segments if caps else n_seg
+        if T > Tc or n_want > nc or n_seg > sc:
+            raise ConfigError("the step does not fit the capacities it was given")
+
+        group_parts = []
+        for gi, g in enumerate(cache.groups):
+            slots = np.full(Tc, -1, dtype=np.int32)
+            width = max((len(rc.tables[gi].blocks) for rc in rcs), default=1)
+            W = caps.table_width if caps else max(width, 1)
+            if width > W:
+                raise ConfigError("a block table is wider than the step's capacity")
+            tables = np.full((sc, W), -1, dtype=np.int32)
+            for si, (rc, (t0, n, p0, _)) in enumerate(zip(rcs, segs)):
+                tb = rc.tables[gi]
+                if p0 + n > tb.capacity():
+                    raise CacheError(f"request {rc.request_id!r}: no pages reserved for positions up to {p0 + n - 1}")
+                blocks = np.asarray(tb.blocks, dtype=np.int64)
+                tables[si, :len(blocks)] = blocks
+                pp = np.arange(p0, p0 + n)
+                page = blocks[pp // ps]
+                if (page < 0).any():
+                    raise CacheError(f"request {rc.request_id!r} writes into a page it gave back")
+                slots[t0:t0 + n] = page * ps + pp % ps
+            plan = self.plans[gi]
+            work, red, parts = attention_plan.plan_attention(
+                [(t0, n, p0) for (t0, n, p0, _) in segs], plan.tile_tokens, plan.window, plan.ctas_per_item,
+                self.target_ctas)
+            mw, mr = (work_caps[gi] if work_caps else (len(work), len(red)))
+            if len(work) > mw or len(red) > mr:
+                raise ConfigError("the step's attention work does not fit the capacities it was given")
+            group_parts.append((slots, tables, work, red, parts, mw, mr, W))
+
+        # layout: offsets in int32 units
+        off = 0
+        layout = {}
+
+        def take(name, count):
+            nonlocal off
+            layout[name] = (off, count)
+            off += count
+
+        take("tokens", Tc); take("positions", Tc); take("logit_rows", max(nc, 1)); take("segments", max(sc, 1) * 4)
+        for gi, (slots, tables, work, red, parts, mw, mr, W) in enumerate(group_parts):
+            take(f"g{gi}.slots", Tc); take(f"g{gi}.tables", sc * W)
+            take(f"g{gi}.n_work", 1); take(f"g{gi}.n_red", 1)
+            take(f"g{gi}.work", max(mw, 1) * 8); take(f"g{gi}.red", max(mr, 1) * 4)
+        host = np.zeros(off, dtype=np.int32)
+
+        def put(name, arr):
+            o, _ = layout[name]
+            a = np.asarray(arr, dtype=np.int32).reshape(-1)
+            host[o:o + len(a)] = a
+
+        put("tokens", toks); put("positions", pos); put("logit_rows", rows)
+        put("segments", np.asarray(segs, dtype=np.int32).reshape(-1) if segs else [])
+        for gi, (slots, tables, work, red, parts, mw, mr, W) in enumerate(group_parts):
+            put(f"g{gi}.slots", slots); put(f"g{gi}.tables", tables)
+            put(f"g{gi}.n_work", [len(work)]); put(f"g{gi}.n_red", [len(red)])
+            put(f"g{gi}.work", work); put(f"g{gi}.red", red)
+        sizes = dict(tokens=T, wanted=n_want, segments=n_seg, tokens_cap=Tc, wanted_cap=nc, segments_cap=sc,
+                     groups=[dict(parts=p[4], max_work=p[5], max_red=p[6], table_width=p[7]) for p in group_parts],
+                     host_segments=segs)
+        return host, layout, sizes
+
+    def to_state(self, dev: torch.Tensor, layout, sizes, heads: List[Tuple[int, int]],
+                 full: bool = False) -> StepState:
+        """Views of the packed device buffer as the parts see it.  ``full``: take
+        the capacities rather than the live sizes (graph capture)."""
+
+        def view(name, count=None):
+            o, c = layout[name]
+            return dev[o:o + (c if count is None else count)]
+
+        T = sizes["tokens_cap"] if full else sizes["tokens"]
+        nw = sizes["wanted_cap"] if full else sizes["wanted"]
+        groups = []
+        for gi, gs in enumerate(sizes["groups"]):
+            part_o, part_ml = self.scratch(gi, gs["parts"], heads[gi])
+            groups.append(GroupStep(
+                block_tables=view(f"g{gi}.tables").view(sizes["segments_cap"], gs["table_width"]),
+                slots=view(f"g{gi}.slots", T),
+                work=view(f"g{gi}.work").view(-1, 8), n_work=view(f"g{gi}.n_work"), max_work=gs["max_work"],
+                red=view(f"g{gi}.red").view(-1, 4), n_red=view(f"g{gi}.n_red"), max_red=gs["max_red"],
+                part_o=part_o, part_ml=part_ml))
+        return StepState(n_tokens=T, tokens=view("tokens", T), positions=view("positions", T), groups=groups,
+                         logit_rows=view("logit_rows", nw), n_wanted=nw,
+                         segments=view("segments").view(-1, 4), host_segments=list(sizes["host_segments"]))

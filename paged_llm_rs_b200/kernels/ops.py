@@ -1,0 +1,240 @@
+"""Python side of the CUDA kernels: argument checks, then the C entry point.
+
+Every function takes torch tensors that live on the GPU, checks dtype, shape and
+contiguity, and launches on torch's current stream.  There is no fallback: if
+the kernel library cannot be built or loaded, or a tensor is not on a CUDA
+device, a ``KernelError`` is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..csrc.build import load_library
+from ..errors import KernelError
+
+_F32, _BF16 = 0, 1
+_ERRORS = {
+    -1: "dtype is neither float32 nor bfloat16",
+    -2: "a size the kernel does not take",
+    -3: "a pointer or stride is not aligned as the kernel needs",
+    -4: "a size beyond the kernel's stated maximum",
+}
+
+_lib = None
+c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        L = load_library()
+        P = c_void_p
+        sig = {
+            "pllm_embed": [c_int, P, P, P, c_int, c_int, c_int, P, P],
+            "pllm_rmsnorm": [c_int, P, P, P, P, P, P, c_int, c_int, c_float, P],
+            "pllm_swiglu": [c_int, P, P, c_int, c_int, P],
+            "pllm_qk_norm_rope_kv": [c_int, P, P, P, P, c_float, P, P, c_int, c_int, P, P, P, P,
+                                     c_int, c_int, c_int, c_int, c_int, c_int, P, P],
+            "pllm_attention_generic": [c_int, P, P, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int,
+                                       c_int, c_int, c_int, c_float, P, P],
+            "pllm_attention_generic_tile_tokens": [c_int, c_int],
+            "pllm_attention_reduce": [c_int, P, P, P, P, c_int, P, c_int, c_int, P],
+            "pllm_sample": [P, c_int, c_int, c_ll, P, P, P, P],
+        }
+        for name, args in sig.items():
+            fn = getattr(L, name)
+            fn.argtypes = args
+            fn.restype = c_int
+        _lib = L
+    return _lib
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: refused, {_ERRORS.get(code, code)}")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _F32
+    if t.dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"dtype {t.dtype} is not handled: the kernels take float32 and bfloat16")
+
+
+def _dev(*tensors) -> None:
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise KernelError("a tensor is not on a CUDA device: there is no CPU path")
+        if not t.is_contiguous():
+            raise KernelError("a tensor is not contiguous")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _i32(t: Optional[torch.Tensor], name: str):
+    if t is not None and t.dtype != torch.int32:
+        raise KernelError(f"{name} must be int32, got {t.dtype}")
+
+
+def _f32(t: Optional[torch.Tensor], name: str):
+    if t is not None and t.dtype != torch.float32:
+        raise KernelError(f"{name} must be float32, got {t.dtype}")
+
+
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+    """out[t] = table[tokens[t]]; tokens int32 [T], table [V, H], out [T, H]."""
+    _dev(tokens, table, out, status)
+    _i32(tokens, "tokens")
+    T, (V, H) = tokens.numel(), table.shape
+    if out.shape != (T, H) or out.dtype != table.dtype:
+        raise KernelError(f"embed: out is {tuple(out.shape)} {out.dtype}, expected {(T, H)} {table.dtype}")
+    _check(lib().pllm_embed(_code(table), _ptr(tokens), _ptr(table), _ptr(out), T, H, V, _ptr(status), _stream()),
+           "embed")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
+            delta: Optional[torch.Tensor] = None, residual_out: Optional[torch.Tensor] = None,
+            rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[i] = rmsnorm(x[r] (+ delta[r])) * gain with r = rows[i] or i; when
+    residual_out is given the sum is stored to residual_out[r] (may alias x)."""
+    _dev(x, gain, out, delta, residual_out, rows)
+    _f32(gain, "gain")
+    _i32(rows, "rows")
+    W = x.shape[-1]
+    n = rows.numel() if rows is not None else x.numel() // W
+    if gain.numel() != W:
+        raise KernelError(f"rmsnorm: gain has {gain.numel()} entries for rows of width {W}")
+    if out.numel() != n * W or out.dtype != x.dtype:
+        raise KernelError("rmsnorm: out does not fit")
+    for t in (delta, residual_out):
+        if t is not None and (t.shape != x.shape or t.dtype != x.dtype):
+            raise KernelError("rmsnorm: delta / residual_out must have x's shape and dtype")
+    _check(lib().pllm_rmsnorm(_code(x), _ptr(x), _ptr(delta), _ptr(residual_out), _ptr(gain), _ptr(out),
+                              _ptr(rows), n, W, float(eps), _stream()), "rmsnorm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[n, I] = silu(gate_up[n, :I]) * gate_up[n, I:]."""
+    _dev(gate_up, out)
+    n, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (n, two_i // 2) or out.dtype != gate_up.dtype:
+        raise KernelError("swiglu: out must be [n, I] for an input [n, 2I] of the same dtype")
+    _check(lib().pllm_swiglu(_code(gate_up), _ptr(gate_up), _ptr(out), n, two_i // 2, _stream()), "swiglu")
+    return out
+
+
+def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, q_gain, k_gain, eps: float, cos, sin,
+                    rotary_dim: int, positions: torch.Tensor, slots: torch.Tensor, k_pool, v_pool,
+                    num_heads: int, num_kv_heads: int, head_dim: int, status: torch.Tensor) -> torch.Tensor:
+    """Per-head RMSNorm of q and k, rotation, q to q_out, k and v into the paged
+    pools [pages, kv_heads, page_size, head_dim] at ``slots`` (a negative slot, or
+    k_pool None, writes nothing)."""
+    _dev(qkv, q_out, q_gain, k_gain, cos, sin, positions, slots, k_pool, v_pool, status)
+    _f32(q_gain, "q_gain"); _f32(k_gain, "k_gain"); _f32(cos, "cos"); _f32(sin, "sin")
+    _i32(positions, "positions"); _i32(slots, "slots")
+    T = qkv.shape[0]
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    if qkv.shape != (T, width):
+        raise KernelError(f"qk_norm_rope_kv: qkv is {tuple(qkv.shape)}, expected {(T, width)}")
+    if q_out.numel() != T * num_heads * head_dim or q_out.dtype != qkv.dtype:
+        raise KernelError("qk_norm_rope_kv: q_out does not fit")
+    if positions.numel() < T or slots.numel() < T:
+        raise KernelError("qk_norm_rope_kv: positions / slots shorter than the tokens")
+    max_pos, page_size, n_pages = 0, 1, 0
+    if cos is not None:
+        if cos.shape != sin.shape or cos.shape[1] * 2 != rotary_dim:
+            raise KernelError("qk_norm_rope_kv: cos/sin must be [max_positions, rotary_dim/2]")
+        max_pos = cos.shape[0]
+    if k_pool is not None:
+        if k_pool.shape != v_pool.shape or k_pool.dtype != qkv.dtype or k_pool.dim() != 4 \
+                or k_pool.shape[1] != num_kv_heads or k_pool.shape[3] != head_dim:
+            raise KernelError(f"qk_norm_rope_kv: pools must be [pages, {num_kv_heads}, page_size, {head_dim}] "
+                              f"of {qkv.dtype}, got {tuple(k_pool.shape)} {k_pool.dtype}")
+        n_pages, page_size = k_pool.shape[0], k_pool.shape[2]
+    for g in (q_gain, k_gain):
+        if g is not None and g.numel() != head_dim:
+            raise KernelError("qk_norm_rope_kv: a head gain must have head_dim entries")
+    _check(lib().pllm_qk_norm_rope_kv(_code(qkv), _ptr(qkv), _ptr(q_out), _ptr(q_gain), _ptr(k_gain), float(eps),
+                                      _ptr(cos), _ptr(sin), rotary_dim, max_pos, _ptr(positions), _ptr(slots),
+                                      _ptr(k_pool), _ptr(v_pool), T, num_heads, num_kv_heads, head_dim, page_size,
+                                      n_pages, _ptr(status), _stream()), "qk_norm_rope_kv")
+    return q_out
+
+
+def attention_tile_tokens(num_heads: int, num_kv_heads: int) -> int:
+    """The most query tokens one attention work item may hold."""
+    return lib().pllm_attention_generic_tile_tokens(num_heads, num_kv_heads)
+
+
+def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
+                    work: torch.Tensor, n_work: torch.Tensor, max_work: int, out: torch.Tensor,
+                    part_o: torch.Tensor, part_ml: torch.Tensor, red: torch.Tensor, n_red: torch.Tensor,
+                    max_red: int, num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
+                    status: torch.Tensor) -> torch.Tensor:
+    """Attention of the step's tokens over the paged cache, then the reduction of
+    split items.  ``work`` is int32 [>=max_work, 8], ``red`` int32 [>=max_red, 4];
+    n_work / n_red are int32 scalars on the device saying how many are live."""
+    _dev(q, k_pool, v_pool, block_tables, work, n_work, out, part_o, part_ml, red, n_red, status)
+    for t, n in ((block_tables, "block_tables"), (work, "work"), (n_work, "n_work"), (red, "red"), (n_red, "n_red")):
+        _i32(t, n)
+    _f32(part_o, "part_o"); _f32(part_ml, "part_ml")
+    if k_pool.dtype != q.dtype or out.dtype != q.dtype or k_pool.shape != v_pool.shape:
+        raise KernelError("paged_attention: q, pools and out must share one dtype, pools one shape")
+    if k_pool.dim() != 4 or k_pool.shape[1] != num_kv_heads or k_pool.shape[3] != head_dim:
+        raise KernelError(f"paged_attention: pools must be [pages, {num_kv_heads}, page_size, {head_dim}]")
+    if head_dim % 16 or head_dim > 256:
+        raise KernelError(f"paged_attention: head_dim {head_dim} is not a multiple of 16 up to 256")
+    if num_heads % num_kv_heads:
+        raise KernelError(f"paged_attention: {num_heads} heads do not group over {num_kv_heads} kv heads")
+    if work.numel() < max_work * 8 or red.numel() < max_red * 4:
+        raise KernelError("paged_attention: work / red lists shorter than their maxima")
+    n_pages, page_size = k_pool.shape[0], k_pool.shape[2]
+    L = lib()
+    _check(L.pllm_attention_generic(_code(q), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
+                                    _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml), num_heads,
+                                    num_kv_heads, head_dim, page_size, n_pages, block_tables.shape[-1], int(window),
+                                    float(scale), _ptr(status), _stream()), "paged_attention")
+    _check(L.pllm_attention_reduce(_code(q), _ptr(part_o), _ptr(part_ml), _ptr(red), _ptr(n_red), max_red,
+                                   _ptr(out), num_heads, head_dim, _stream()), "attention_reduce")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+    """tokens[i] = argmax(logits[i]) where temperature[i] <= 0, else a draw from
+    softmax(logits[i] / temperature[i]) at uniform[i], walking ids upward."""
+    _dev(logits, temperature, uniform, tokens)
+    _f32(logits, "logits"); _f32(temperature, "temperature"); _f32(uniform, "uniform"); _i32(tokens, "tokens")
+    n, V = logits.shape
+    if min(temperature.numel(), uniform.numel(), tokens.numel()) < n:
+        raise KernelError("sample: per-row arguments shorter than the rows")
+    _check(lib().pllm_sample(_ptr(logits), n, V, logits.stride(0), _ptr(temperature), _ptr(uniform), _ptr(tokens),
+                             _stream()), "sample")
+    return tokens
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x W^T with W stored [out, in]: the library matrix product (cuBLAS through
+    torch), which is where the reference uses a library too
+    (crates/pagedllm/src/model/layers.rs:27-35).  float32 inputs run in true
+    float32: the engine switches TF32 off."""
+    if not x.is_cuda:
+        raise KernelError("linear: input is not on a CUDA device: there is no CPU path")
+    return torch.matmul(x, weight.t(), out=out) if out is not None else torch.matmul(x, weight.t())

@@ -1,0 +1,74 @@
+"""Grouped-query attention over the paged cache
+(crates/pagedllm/src/model/attention.rs:123-216).
+
+q, k and v come from one matrix product over the stacked projection weights;
+one kernel then norms q and k per head, rotates them and writes k and v into
+the cache pages; the attention kernel reads the pages through the block tables;
+the output projection follows.  Head counts, head size, norm eps, scale, window
+and the position encoding are parameters.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import KVNeed, Mixer, register_mixer
+from .spec import TensorSpec
+
+
+class GQAttention(Mixer):
+    def __init__(self, spec, rt, position_encodings=None):
+        super().__init__(spec, rt)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.nh, self.nkv, self.hd = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"])
+        self.qk_norm_eps = p.get("qk_norm_eps")  # None: no per-head norm
+        self.scale = float(p["scale"])
+        self.window = p.get("window")
+        name = p.get("position_encoding")
+        self.position = (position_encodings or {}).get(name) if name else None
+        if name and self.position is None:
+            raise KeyError(f"position encoding {name!r} is not among the model's")
+        if self.nh % self.nkv:
+            raise ValueError(f"{self.nh} heads do not group over {self.nkv} kv heads")
+        self.w_qkv = self.w_o = self.q_gain = self.k_gain = None
+
+    def tensors(self):
+        H, qw, kw = self.hidden, self.nh * self.hd, self.nkv * self.hd
+        t = [TensorSpec(self._name("q_proj.weight"), (qw, H)), TensorSpec(self._name("k_proj.weight"), (kw, H)),
+             TensorSpec(self._name("v_proj.weight"), (kw, H)), TensorSpec(self._name("o_proj.weight"), (H, qw))]
+        if self.qk_norm_eps is not None:
+            t += [TensorSpec(self._name("q_norm.weight"), (self.hd,), "gain"),
+                  TensorSpec(self._name("k_norm.weight"), (self.hd,), "gain")]
+        return t
+
+    def bind(self, tensors):
+        # one [q; k; v] matrix: a single product makes all three
+        self.w_qkv = torch.cat([tensors[self._name(n)] for n in ("q_proj.weight", "k_proj.weight", "v_proj.weight")], 0)
+        self.w_o = tensors[self._name("o_proj.weight")]
+        if self.qk_norm_eps is not None:
+            self.q_gain, self.k_gain = tensors[self._name("q_norm.weight")], tensors[self._name("k_norm.weight")]
+
+    def cache_need(self):
+        return KVNeed("window" if self.window else "full", self.nkv, self.hd, self.window)
+
+    def forward(self, x, step, cache, writes_cache=True):
+        k_pool, v_pool, gi = cache
+        g = step.groups[gi]
+        T = x.shape[0]
+        qkv = ops.linear(x, self.w_qkv)
+        q = torch.empty((T, self.nh * self.hd), dtype=x.dtype, device=x.device)
+        rot = self.position.rotary() if self.position is not None else None
+        cos, sin, rdim = rot if rot is not None else (None, None, 0)
+        ops.qk_norm_rope_kv(qkv, q, self.q_gain, self.k_gain, self.qk_norm_eps or 0.0, cos, sin, rdim,
+                            step.positions, g.slots, k_pool if writes_cache else None,
+                            v_pool if writes_cache else None, self.nh, self.nkv, self.hd, self.rt.status)
+        o = torch.empty_like(q)
+        ops.paged_attention(q, k_pool, v_pool, g.block_tables, g.work, g.n_work, g.max_work, o, g.part_o, g.part_ml,
+                            g.red, g.n_red, g.max_red, self.nh, self.nkv, self.hd, self.window or 0, self.scale,
+                            self.rt.status)
+        return ops.linear(o, self.w_o)
+
+
+register_mixer("gqa_attention", GQAttention)
