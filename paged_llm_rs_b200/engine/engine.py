@@ -1,0 +1,143 @@
+"""The engine loop: plan a step, run it, choose tokens, commit
+(crates/pagedllm-server/src/engine.rs:180-303 in the reference, without the
+server around it).  Token ids go in and token ids come out.
+
+    engine = Engine("model_dir", dtype="bfloat16")
+    outputs = engine.generate([[1, 2, 3], [4, 5]], max_tokens=16)
+
+Options carry the names and defaults of the reference's command line
+(crates/pagedllm-server/src/main.rs:20-71): block_size 16, cache_mib 3584,
+max_batch 16, chunk 128 (None = "off": prompts run whole), prefix_cache on.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Iterable, List, Optional, Sequence as Seq
+
+import numpy as np
+import torch
+
+from ..errors import ConfigError
+from ..kernels import ops
+from ..sampling.sampler import SamplingParams, sample_host
+from .runner import ModelRunner
+from .scheduler import Finish, Outcome, Plan, Scheduler, Sequence
+
+
+class Engine:
+    def __init__(self, model: str, dtype="bfloat16", block_size: int = 16, cache_mib: int = 3584,
+                 blocks: Optional[int] = None, max_batch: int = 16, chunk: Optional[int] = 128,
+                 prefix_cache: bool = True, device: str = "cuda:0", max_requests: Optional[int] = None):
+        if chunk is not None and chunk < 1:
+            raise ConfigError("chunk 0 would carry nothing")
+        self.runner = ModelRunner(model, dtype=dtype, page_size=block_size, num_pages=blocks,
+                                  cache_bytes=None if blocks is not None else cache_mib << 20,
+                                  max_requests=max_requests or max(256, 2 * max_batch), device=device,
+                                  prefix_cache=prefix_cache)
+        self.scheduler = Scheduler(self.runner.cache, max_batch=max_batch, chunk=chunk,
+                                   max_positions=self.runner.spec.max_positions)
+        self._next_id = 0
+        self._seqs: Dict[int, Sequence] = {}
+        self._finish: Dict[int, Finish] = {}
+        dev = self.runner.device
+        self._tok_dev = torch.empty(4096, dtype=torch.int32, device=dev)
+
+    # -- requests ------------------------------------------------------------------------
+    def submit(self, prompt: Seq[int], max_tokens: int = 512, temperature: float = 0.0,
+               top_k: Optional[int] = None, top_p: Optional[float] = None, seed: int = 0,
+               stop_tokens: Iterable[int] = ()) -> int:
+        if temperature <= 0.0:
+            top_k = top_p = None  # an explicit greedy request drops the nucleus settings (routes.rs:106-126)
+        params = SamplingParams(float(temperature), top_k, top_p)
+        V = self.runner.vocab_size
+        if any((not 0 <= int(t) < V) for t in prompt):
+            raise ConfigError(f"a prompt token lies outside the vocabulary of {V}")
+        rid = self._next_id
+        self._next_id += 1
+        seq = Sequence(rid, prompt, params, max_tokens, stop_tokens, seed)
+        self._seqs[rid] = seq
+        self.scheduler.submit(seq)
+        return rid
+
+    def cancel(self, rid: int) -> None:
+        self.scheduler.cancel(rid)
+
+    # -- one step ------------------------------------------------------------------------
+    def step(self) -> Optional[Outcome]:
+        """Plan, run, sample and commit one step.  None when there is nothing to do."""
+        plan = self.scheduler.plan()
+        if plan.kind == "idle":
+            return None
+        if plan.kind == "refused":
+            out = self.scheduler.commit(plan, [])
+        else:
+            logits = self.runner.step(plan.entries, check=False)
+            tokens = self._sample(plan, logits) if plan.ids else []
+            out = self.scheduler.commit(plan, tokens)
+        for rid, why in out.finished:
+            self._finish[rid] = why
+        return out
+
+    def _sample(self, plan: Plan, logits: torch.Tensor) -> List[int]:
+        n = len(plan.ids)
+        seqs = [self._seqs[rid] for rid in plan.ids]
+        temp = np.zeros(n, dtype=np.float32)
+        uni = np.zeros(n, dtype=np.float32)
+        host_rows = []
+        for i, s in enumerate(seqs):
+            p = s.sampling
+            if not p.on_device:
+                host_rows.append(i)
+            elif not p.is_greedy:
+                temp[i] = p.temperature
+                uni[i] = s.rng.next_f32()
+        dev = self.runner.device
+        packed = torch.from_numpy(np.concatenate([temp, uni])).pin_memory().to(dev, non_blocking=True)
+        if self._tok_dev.numel() < n:
+            self._tok_dev = torch.empty(2 * n, dtype=torch.int32, device=dev)
+        ops.sample(logits, packed[:n], packed[n:], self._tok_dev)
+        status_and_tokens = torch.cat([self.runner.rt.status, self._tok_dev[:n]]).cpu()  # one copy back
+        if int(status_and_tokens[0]):
+            self.runner.check_status()
+        tokens = status_and_tokens[1:].tolist()
+        if host_rows:
+            rows = logits[torch.tensor(host_rows, device=dev)].cpu().numpy()
+            for r, i in zip(rows, host_rows):
+                tokens[i] = sample_host(r, seqs[i].sampling, seqs[i].rng)
+        return tokens
+
+    # -- whole generations -----------------------------------------------------------------
+    def run_until_done(self) -> None:
+        while self.scheduler.has_work():
+            if self.step() is None:
+                if self.scheduler.has_work():
+                    raise RuntimeError("the scheduler is idle with requests left: the cache is too small to run any")
+                break
+
+    def generate(self, prompts: Seq[Seq[int]], max_tokens: int = 512, temperature: float = 0.0,
+                 top_k: Optional[int] = None, top_p: Optional[float] = None, seed: int = 0,
+                 stop_tokens: Iterable[int] = ()) -> List[List[int]]:
+        """Generate for every prompt; returns the produced token ids per prompt
+        (stop tokens are not part of the output)."""
+        stop = tuple(stop_tokens)
+        ids = [self.submit(p, max_tokens, temperature, top_k, top_p, seed, stop) for p in prompts]
+        self.run_until_done()
+        outs = [list(self._seqs[i].output) for i in ids]
+        for i in ids:
+            self._seqs.pop(i, None)
+        return outs
+
+    def finish_reason(self, rid: int) -> Optional[Finish]:
+        return self._finish.get(rid)
+
+    def metrics(self) -> dict:
+        m = self.scheduler.metrics
+        d = dict(vars(m))
+        d["prefix_hit_rate"] = m.prefix_hit_rate()
+        d["mean_batch"] = m.mean_batch()
+        d["pages"] = self.runner.cache.num_pages
+        d["pages_free"] = self.runner.cache.available()
+        for gi, g in enumerate(self.runner.cache.groups):
+            a = g.allocator
+            d[f"group{gi}"] = dict(hits=a.hits, misses=a.misses, evictions=a.evictions, handed_out=a.handed_out)
+        return d

@@ -1,0 +1,240 @@
+"""The scheduler's decisions without a model (the reference's cases:
+crates/pagedllm/src/scheduler.rs:803-1370).  Every row of a step is answered
+with a constant token, as its ``step()`` helper does (scheduler.rs:826-830)."""
+
+import pytest
+import torch
+
+from paged_llm_rs_b200.cache import CacheManager
+from paged_llm_rs_b200.engine.scheduler import Finish, Scheduler, Sequence
+from paged_llm_rs_b200.parts.base import KVNeed, StateNeed
+from paged_llm_rs_b200.sampling import SamplingParams
+
+GREEDY = SamplingParams.greedy()
+
+
+def make(pages, page_size=4, max_batch=16, chunk=None, needs=None, max_requests=16, prefix=True, max_positions=None):
+    cache = CacheManager(needs or [KVNeed("full", 1, 16)], page_size, pages, max_requests, torch.float32, "cpu",
+                         prefix_cache=prefix, allocate_device=False)
+    return Scheduler(cache, max_batch=max_batch, chunk=chunk, max_positions=max_positions), cache
+
+
+def seq(i, n, max_tokens=4, stop=(), start=0):
+    return Sequence(i, [(start + k) % 50 + 1 for k in range(n)], GREEDY, max_tokens, stop)
+
+
+def step(s, token=9):
+    plan = s.plan()
+    out = s.commit(plan, [token] * len(plan.ids))
+    s.cache.check_invariants()
+    return plan, out
+
+
+def test_prompts_are_admitted_in_order_then_decoded_together():
+    s, cache = make(pages=16)
+    for i, n in enumerate((5, 3, 6)):
+        s.submit(seq(i, n, start=10 * i))    # different tokens: nothing to share
+    kinds = []
+    for _ in range(3):
+        plan, _ = step(s)
+        kinds.append((plan.kind, plan.ids, [len(e.tokens) for e in plan.entries]))
+    assert kinds == [("prefill", [0], [5]), ("prefill", [1], [3]), ("prefill", [2], [6])]
+    plan, _ = step(s)
+    assert plan.kind == "decode" and plan.ids == [0, 1, 2] and all(len(e.tokens) == 1 for e in plan.entries)
+    assert s.metrics.prefills == 3 and s.metrics.decode_rows == 3
+
+
+def test_pages_grow_one_at_a_time_and_a_stop_token_frees_them():
+    s, cache = make(pages=8)
+    s.submit(seq(0, 4, max_tokens=10, stop=[7]))
+    step(s)                                 # prefill fills page 0 exactly
+    assert cache.groups[0].allocator.in_use() == 1
+    step(s)                                 # the first decode needs a second page
+    assert cache.groups[0].allocator.in_use() == 2
+    plan, out = step(s, token=7)            # the stop token ends it and is not returned
+    assert out.tokens == [] and out.finished == [(0, Finish.STOP)]
+    assert cache.available() == 8 and not s.has_work()
+
+
+def test_max_tokens_ends_with_length():
+    s, _ = make(pages=8)
+    s.submit(seq(0, 3, max_tokens=2))
+    outs = [step(s)[1] for _ in range(2)]
+    assert [o.tokens for o in outs] == [[(0, 9)], [(0, 9)]] and outs[1].finished == [(0, Finish.LENGTH)]
+
+
+def test_a_prompt_the_pool_can_never_hold_is_refused():
+    s, cache = make(pages=2)
+    s.submit(seq(0, 9))                     # needs 3 pages of 4
+    s.submit(seq(1, 4))
+    plan, out = step(s)
+    assert plan.kind == "refused" and out.finished == [(0, Finish.LENGTH)]
+    assert step(s)[0].ids == [1]
+
+
+def test_admission_waits_for_pages():
+    s, cache = make(pages=3)
+    s.submit(seq(0, 8, max_tokens=1))
+    s.submit(seq(1, 8, max_tokens=1))
+    assert step(s)[0].ids == [0]            # takes 2 pages and finishes at once (max_tokens 1)
+    assert step(s)[0].ids == [1]
+    s.submit(seq(2, 8, max_tokens=50)); step(s)
+    s.submit(seq(3, 8))
+    before = s.metrics.admission_stalls
+    plan, _ = step(s)                       # 1 page left: the newcomer stalls, the resident decodes
+    assert plan.kind == "decode" and plan.ids == [2] and s.metrics.admission_stalls == before + 1
+
+
+def test_pool_dry_evicts_the_newest_never_the_oldest():
+    s, cache = make(pages=4)                # 16 tokens in all
+    s.submit(seq(0, 7, max_tokens=50))
+    s.submit(seq(1, 7, max_tokens=50, start=20))
+    step(s); step(s)                        # both admitted: 2 pages each
+    plan, _ = step(s)                       # token 8 fits in the second page
+    assert plan.ids == [0, 1]
+    plan, _ = step(s)                       # position 8 needs a third page: none left, the newest goes
+    assert plan.kind == "decode" and plan.ids == [0]
+    assert s.metrics.preemptions == 1 and [q.id for q in s.waiting] == [1]
+    victim = s.waiting[0]
+    assert victim.pending == victim.history and len(victim.history) == 9 and victim.preemptions == 1
+    assert s.metrics.recomputed_tokens == 9
+    # tokens already returned stay returned; it is recomputed from prompt plus output when room comes
+    assert victim.output == [9, 9]
+    for _ in range(40):
+        if not s.has_work():
+            break
+        step(s)
+    assert not s.has_work() and cache.available() == 4
+
+
+def test_a_lone_request_that_outgrows_the_pool_stops_the_engine_not_the_process():
+    s, cache = make(pages=1)
+    s.submit(seq(0, 4, max_tokens=50))
+    step(s)
+    assert s.plan().kind == "idle"          # nobody else to evict: it cannot run, and says so
+
+
+def test_budget_covers_decodes_and_one_portion():
+    s, cache = make(pages=64, chunk=8)
+    for i in range(3):
+        s.submit(seq(i, 2, max_tokens=50))
+    for _ in range(3):
+        step(s)
+    assert len(s.running) == 3 and s.cache.available() == 61
+    s.submit(seq(3, 19, max_tokens=50))
+    plan, _ = step(s)                       # 3 decodes + 5 prompt tokens = 8
+    assert plan.kind == "mixed" and plan.ids == [0, 1, 2]
+    assert [len(e.tokens) for e in plan.entries] == [1, 1, 1, 5] and plan.entries[3].want == []
+    assert plan.advanced[-1] == (3, 5)
+    plan, _ = step(s)
+    assert plan.entries[3].tokens == seq(3, 19).history[5:10]      # the portion goes on where the last ended
+    plan, _ = step(s); plan, _ = step(s)                            # 15 done; 4 left
+    assert [len(e.tokens) for e in plan.entries] == [1, 1, 1, 4] and plan.entries[3].want == [3]
+    assert plan.ids == [0, 1, 2, 3]                                 # the last portion brings a token back
+    assert s.metrics.mixed_steps == 7
+
+
+def test_a_prompt_is_admitted_and_gets_a_portion_in_the_same_step():
+    s, _ = make(pages=64, chunk=4)
+    s.submit(seq(0, 6))
+    plan, _ = step(s)
+    assert plan.kind == "mixed" and plan.ids == [] and [len(e.tokens) for e in plan.entries] == [4]
+    plan, _ = step(s)
+    assert plan.ids == [0] and plan.entries[0].want == [1]
+
+
+def test_one_prompt_in_flight_at_a_time():
+    s, _ = make(pages=64, chunk=4)
+    s.submit(seq(0, 10)); s.submit(seq(1, 3))
+    for _ in range(2):
+        plan, _ = step(s)
+        assert [e.request_id for e in plan.entries] == [0]
+    plan, _ = step(s)                       # request 0 finishes its prompt (2 left)
+    assert [e.request_id for e in plan.entries] == [0] and plan.ids == [0]
+    plan, _ = step(s)
+    assert [e.request_id for e in plan.entries] == [0, 1] and [len(e.tokens) for e in plan.entries] == [1, 3]
+
+
+def test_mixed_step_gives_way_to_preemption_when_a_resident_needs_a_page():
+    s, cache = make(pages=4, chunk=8)
+    s.submit(seq(0, 8, max_tokens=50))
+    step(s)
+    s.submit(seq(1, 7, max_tokens=50, start=20))
+    step(s)                                  # request 0 takes a third page for position 8, request 1 starts
+    for _ in range(12):
+        step(s)
+    assert s.metrics.preemptions >= 1 and s.running and s.running[0].id == 0
+
+
+def test_portion_shrinks_to_the_pages_that_are_left():
+    s, cache = make(pages=3, chunk=16)
+    s.submit(seq(0, 4, max_tokens=50)); step(s)
+    s.submit(seq(1, 12, max_tokens=2))
+    plan, _ = step(s)                        # request 0 takes a page for position 4, one page is left
+    assert [len(e.tokens) for e in plan.entries] == [1, 4] and plan.advanced[-1] == (1, 4)
+
+
+def test_prefix_hits_are_counted_and_skip_the_shared_tokens():
+    s, cache = make(pages=32, chunk=None)
+    s.submit(seq(0, 12, max_tokens=1)); step(s)
+    s.submit(seq(1, 12, max_tokens=1))       # the same 12 tokens
+    plan, _ = step(s)
+    assert [len(e.tokens) for e in plan.entries] == [4]      # two pages shared, the last page its own
+    assert s.metrics.cached_tokens == 8 and s.metrics.prefilled_tokens == 16
+    assert s.metrics.prefix_hit_rate() == pytest.approx(8 / 24)
+    s2, _ = make(pages=32, chunk=None, prefix=False)
+    s2.submit(seq(0, 12, max_tokens=1)); step(s2)
+    s2.submit(seq(1, 12, max_tokens=1))
+    assert [len(e.tokens) for e in step(s2)[0].entries] == [12]
+
+
+def test_cancel_frees_waiting_and_running():
+    s, cache = make(pages=8)
+    s.submit(seq(0, 5, max_tokens=50)); s.submit(seq(1, 5, max_tokens=50))
+    step(s)
+    s.cancel(1)
+    assert not s.waiting
+    s.cancel(0)
+    assert not s.running and cache.available() == 8
+
+
+def test_max_batch_caps_decode_rows():
+    s, _ = make(pages=64, max_batch=2)
+    for i in range(3):
+        s.submit(seq(i, 2, max_tokens=50))
+    for _ in range(3):
+        step(s)
+    assert step(s)[0].ids == [0, 1]
+
+
+def test_context_ends_at_the_last_position():
+    s, _ = make(pages=64, max_positions=6)
+    s.submit(seq(0, 4, max_tokens=50))
+    outs = [step(s)[1] for _ in range(2)]
+    assert outs[1].finished == [(0, Finish.LENGTH)]          # 6 tokens seen: the next would sit at position 6
+    s.submit(seq(1, 7))
+    assert step(s)[0].kind == "refused"
+
+
+def test_state_slots_limit_admission_and_come_back_on_preemption():
+    s, cache = make(pages=64, needs=[KVNeed("full", 1, 16), StateNeed((2,))], max_requests=2, chunk=8)
+    for i in range(3):
+        s.submit(seq(i, 2, max_tokens=6, start=10 * i))
+    for _ in range(3):
+        step(s)
+    assert len(s.running) == 2 and len(s.waiting) == 1 and s.metrics.admission_stalls >= 1
+    for _ in range(10):
+        step(s)
+    assert not s.has_work() and cache.slots_free() == 2
+
+
+def test_window_model_runs_a_long_prompt_through_few_pages():
+    win = KVNeed("window", 1, 16, window=8)
+    s, cache = make(pages=6, needs=[win], chunk=4)
+    s.submit(seq(0, 40, max_tokens=5))       # 10 pages of tokens through a pool of 6
+    produced = []
+    for _ in range(30):
+        if not s.has_work():
+            break
+        produced += step(s)[1].tokens
+    assert len(produced) == 5 and cache.available() == 6

@@ -1,0 +1,43 @@
+"""Two tiny Qwen3 configurations that differ in every size and option, and
+helpers that write them as model folders with random weights."""
+
+import os
+
+TINY_A = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_act="silu", attention_bias=False,
+    hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+    head_dim=16, rms_norm_eps=1e-6, vocab_size=256, max_position_embeddings=512, tie_word_embeddings=True,
+    rope_theta=10000.0, sliding_window=None, use_sliding_window=False,
+)
+
+# heads * head_dim != hidden, one kv head (8 query heads share it), sizes that are no
+# power of two, untied head, nested rope_theta, another eps, and a window on two of
+# its three layers.
+TINY_B = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_act="silu",
+    hidden_size=96, intermediate_size=160, num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=1,
+    head_dim=32, rms_norm_eps=1e-5, vocab_size=384, max_position_embeddings=640, tie_word_embeddings=False,
+    rope_parameters=dict(rope_theta=1000000.0, rope_type="default"),
+    use_sliding_window=True, sliding_window=40,
+    layer_types=["sliding_attention", "full_attention", "sliding_attention"],
+)
+
+# a third one for kernels' odd sizes: head_dim 48, 6 heads over 3 kv heads, vocabulary 1000
+TINY_C = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_act="silu",
+    hidden_size=72, intermediate_size=200, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=3,
+    head_dim=48, rms_norm_eps=1e-6, vocab_size=1000, max_position_embeddings=512, tie_word_embeddings=True,
+    rope_theta=50000.0,
+)
+
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
+
+
+def write_model(folder, name, dtype=None):
+    import torch
+    from paged_llm_rs_b200.weights.random_init import write_random_model
+
+    cfg, seed = CONFIGS[name]
+    d = os.path.join(str(folder), f"tiny_{name}")
+    write_random_model(d, cfg, seed, dtype or torch.bfloat16)
+    return d
