@@ -68,7 +68,7 @@ class Engine:
         plan = self.scheduler.plan()
         if plan.kind == "idle":
             return None
-        if plan.kind == "refused":
+        if plan.kind in ("refused", "outgrown"):
             out = self.scheduler.commit(plan, [])
         else:
             logits = self.runner.step(plan.entries, check=False)

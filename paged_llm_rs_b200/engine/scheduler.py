@@ -13,7 +13,9 @@ The policy is the reference's (crates/pagedllm/src/scheduler.rs):
   to the front of the queue and is recomputed from its prompt plus what it had
   produced; tokens already returned stay returned (scheduler.rs:645-661, 700-712).
 * A prompt that the whole pool could never hold is refused and ends with
-  ``Finish.LENGTH`` (scheduler.rs:681-690).
+  ``Finish.LENGTH`` (scheduler.rs:681-690).  A running request that needs a page
+  when nobody is left to evict ends with LENGTH too (the reference idles for good
+  in that case, scheduler.rs:647-650, 663-665).
 * A step is committed only after it ran: lengths advance, full pages get their
   names, sampled tokens are appended, a stop token ends the request and is not
   returned, ``max_tokens`` ends it with LENGTH (scheduler.rs:717-764).
@@ -61,7 +63,7 @@ class Sequence:
 
 @dataclass
 class Plan:
-    kind: str  # "idle", "prefill", "mixed", "decode", "refused"
+    kind: str  # "idle", "prefill", "mixed", "decode", "refused" (a waiting prompt), "outgrown" (a running request)
     ids: List[object] = field(default_factory=list)               # requests a token comes back for, in row order
     advanced: List[Tuple[object, int]] = field(default_factory=list)  # (request, tokens it writes)
     entries: List[StepEntry] = field(default_factory=list)
@@ -269,6 +271,13 @@ class Scheduler:
             if victim < index:
                 index -= 1
         if not chosen:
+            # A request that needs a page when nobody is left to evict has outgrown the
+            # pool.  The reference idles here for good; this scheduler ends the request
+            # with LENGTH, as it does for a prompt the pool can never hold.
+            for s in self.running:
+                if s.finish is None and len(s.pending) == 1 and self.cache.blocks_needed(s.id, 1) > 0:
+                    s.finish = Finish.LENGTH
+                    return Plan("outgrown", refused=s.id)
             return Plan("idle")
         seqs = [self.running[i] for i in chosen]
         self.metrics.steps += 1

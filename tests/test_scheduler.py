@@ -111,7 +111,8 @@ def test_a_lone_request_that_outgrows_the_pool_stops_the_engine_not_the_process(
     s, cache = make(pages=1)
     s.submit(seq(0, 4, max_tokens=50))
     step(s)
-    assert s.plan().kind == "idle"          # nobody else to evict: it cannot run, and says so
+    plan, out = step(s)                     # nobody else to evict: it ends with LENGTH instead of idling for good
+    assert plan.kind == "outgrown" and out.finished == [(0, Finish.LENGTH)] and cache.available() == 1
 
 
 def test_budget_covers_decodes_and_one_portion():
