@@ -162,9 +162,12 @@ def test_mixed_step_gives_way_to_preemption_when_a_resident_needs_a_page():
     step(s)
     s.submit(seq(1, 7, max_tokens=50, start=20))
     step(s)                                  # request 0 takes a third page for position 8, request 1 starts
-    for _ in range(12):
+    assert [e.request_id for e in s.plan().entries] == [0]     # no page for the rest of the prompt: 0 decodes alone
+    for _ in range(4):
         step(s)
-    assert s.metrics.preemptions >= 1 and s.running and s.running[0].id == 0
+    # position 12 of request 0 needs a page: the half-run prompt is the newest and gives its pages back
+    assert s.metrics.preemptions == 1 and [q.id for q in s.running] == [0] and [q.id for q in s.waiting] == [1]
+    assert s.waiting[0].pending == s.waiting[0].history and s.waiting[0].prompt_left == 0
 
 
 def test_portion_shrinks_to_the_pages_that_are_left():
