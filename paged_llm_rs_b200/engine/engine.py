@@ -39,8 +39,7 @@ class Engine:
         self._next_id = 0
         self._seqs: Dict[int, Sequence] = {}
         self._finish: Dict[int, Finish] = {}
-        dev = self.runner.device
-        self._tok_dev = torch.empty(4096, dtype=torch.int32, device=dev)
+        self.bytes_d2h = 0  # bytes the last step copied back to the host
 
     # -- requests ------------------------------------------------------------------------
     def submit(self, prompt: Seq[int], max_tokens: int = 512, temperature: float = 0.0,
@@ -71,16 +70,18 @@ class Engine:
         if plan.kind in ("refused", "outgrown"):
             out = self.scheduler.commit(plan, [])
         else:
-            logits = self.runner.step(plan.entries, check=False)
-            tokens = self._sample(plan, logits) if plan.ids else []
+            tokens = self._run(plan)
             out = self.scheduler.commit(plan, tokens)
         for rid, why in out.finished:
             self._finish[rid] = why
         return out
 
-    def _sample(self, plan: Plan, logits: torch.Tensor) -> List[int]:
-        n = len(plan.ids)
+    def _run(self, plan: Plan) -> List[int]:
+        """The step and the choice of tokens: one packed copy to the device, the
+        model, the sampling kernel, one copy of status word and tokens back.  Rows
+        of requests with top-k or top-p are copied back as logits and drawn on the host."""
         seqs = [self._seqs[rid] for rid in plan.ids]
+        n = len(seqs)
         temp = np.zeros(n, dtype=np.float32)
         uni = np.zeros(n, dtype=np.float32)
         host_rows = []
@@ -90,18 +91,19 @@ class Engine:
                 host_rows.append(i)
             elif not p.is_greedy:
                 temp[i] = p.temperature
-                uni[i] = s.rng.next_f32()
-        dev = self.runner.device
-        packed = torch.from_numpy(np.concatenate([temp, uni])).pin_memory().to(dev, non_blocking=True)
-        if self._tok_dev.numel() < n:
-            self._tok_dev = torch.empty(2 * n, dtype=torch.int32, device=dev)
-        ops.sample(logits, packed[:n], packed[n:], self._tok_dev)
-        status_and_tokens = torch.cat([self.runner.rt.status, self._tok_dev[:n]]).cpu()  # one copy back
-        if int(status_and_tokens[0]):
+                uni[i] = s.rng.next_f32()   # greedy rows leave their generator alone (sampler.rs:119-121)
+        logits, tokens_dev = self.runner.step_and_sample(plan.entries, temp, uni)
+        if tokens_dev is None:
+            self.bytes_d2h = 0
+            return []
+        back = tokens_dev.cpu()
+        self.bytes_d2h = back.numel() * 4
+        if int(back[0]):
             self.runner.check_status()
-        tokens = status_and_tokens[1:].tolist()
+        tokens = back[1:].tolist()
         if host_rows:
-            rows = logits[torch.tensor(host_rows, device=dev)].cpu().numpy()
+            rows = logits[torch.tensor(host_rows, device=self.runner.device)].cpu().numpy()
+            self.bytes_d2h += rows.nbytes
             for r, i in zip(rows, host_rows):
                 tokens[i] = sample_host(r, seqs[i].sampling, seqs[i].rng)
         return tokens

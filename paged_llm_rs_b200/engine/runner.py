@@ -21,7 +21,7 @@ from .. import models  # noqa: F401  (registers the architectures)
 from ..cache.manager import CacheManager
 from ..config.registry import load_config
 from ..errors import ConfigError, KernelError
-from ..kernels import ops
+from ..kernels import attention_plan, ops
 from ..parts.base import KVNeed, Runtime
 from ..parts.decoder import DecoderModel
 from ..weights.loader import load_weights
@@ -43,10 +43,60 @@ def parse_dtype(name) -> torch.dtype:
         raise ConfigError(f"dtype {name!r} is not served; float32 and bfloat16 are") from None
 
 
+class _DecodeGraph:
+    """One captured decode step for up to ``B`` requests whose block tables are at
+    most ``W`` pages wide.  Every launch argument is fixed: the step's data (token
+    ids, positions, slots, tables, work items, sampling numbers) lives in one
+    device buffer that each replay overwrites; what does not fill the capacities
+    is padding that writes nothing (slot -1) and attends to nothing (no work item)."""
+
+    def __init__(self, runner: "ModelRunner", B: int, W: int):
+        self.runner, self.B, self.W = runner, B, W
+        pk = runner.packer
+        self.caps = StepCaps(tokens=B, wanted=B, segments=B, table_width=W)
+        self.work_caps = [attention_plan.plan_limits(B, p.tile_tokens, pk.target_ctas) for p in pk.plans]
+        host, self.layout, self.sizes = pk.pack([], runner._heads, self.caps, self.work_caps)
+        self.pinned = torch.from_numpy(host.copy()).pin_memory()
+        self.dev = self.pinned.to(runner.device)
+        self.nbytes = host.nbytes
+        self.state = pk.to_state(self.dev, self.layout, self.sizes, runner._heads, full=True)
+        self.tokens = torch.zeros(1 + B, dtype=torch.int32, device=runner.device)
+        # Warm up on a side stream (library handles, workspaces), then capture.
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(2):
+                self._body()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        before = ops.LAUNCHES
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph), torch.no_grad():
+            self._body()
+        self.launches = ops.LAUNCHES - before
+
+    def _body(self):
+        r = self.runner
+        self.logits = r.model.forward(self.state, r.caches)
+        ops.sample(self.logits, self.state.temperature, self.state.uniform, self.tokens[1:])
+        self.tokens[:1].copy_(r.rt.status)
+
+    def run(self, entries, temperature, uniform):
+        r = self.runner
+        host, _, _ = r.packer.pack(entries, r._heads, self.caps, self.work_caps, temperature, uniform)
+        self.pinned.numpy()[:] = host
+        self.dev.copy_(self.pinned, non_blocking=True)
+        self.graph.replay()
+        r.bytes_h2d = self.nbytes
+        r.last_launches = self.launches
+        n = len(entries)
+        return self.logits[:n], self.tokens[:1 + n]
+
+
 class ModelRunner:
     def __init__(self, model_dir: str, dtype="bfloat16", page_size: int = 16, num_pages: Optional[int] = None,
                  cache_bytes: Optional[int] = None, max_requests: int = 64, device: str = "cuda:0",
-                 prefix_cache: bool = True):
+                 prefix_cache: bool = True, use_graphs: bool = True, max_graph_batch: int = 256):
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device: this engine has no CPU path")
         ops.lib()  # build or load the kernels now; fails loudly if that cannot be done
@@ -91,23 +141,72 @@ class ModelRunner:
         self.packer = StepPacker(self.cache, plans, SM_COUNT_TARGET, self.spec.vocab_size, self.spec.max_positions,
                                  self.device)
         self.vocab_size = self.spec.vocab_size
+        # A captured step replays fixed launches; a mixer that loops over the step on the
+        # host (it says so by graph_safe = False) keeps the engine on plain launches.
+        self.use_graphs = use_graphs and all(getattr(b.mixer, "graph_safe", False) for b in self.model.blocks)
+        self.max_graph_batch = max_graph_batch
+        self._graphs = {}
+        self.bytes_h2d = 0        # bytes the last step copied to the device
+        self.last_launches = 0    # kernels of this library the last step launched
 
     # -- the step ----------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry], check: bool = True) -> torch.Tensor:
         """Run one batch.  Returns float32 logits [wanted, vocab] on the device, in
         the order of the entries and of their ``want`` lists.  Pages for the new
         tokens must have been reserved; nothing is committed."""
+        logits, _ = self.step_and_sample(entries, None, None, check=check)
+        return logits
+
+    def step_and_sample(self, entries: Sequence[StepEntry], temperature, uniform, check: bool = False):
+        """The step, followed (when ``temperature`` and ``uniform`` are given, one per
+        wanted row) by the sampling kernel.  Returns (logits, tokens): tokens is an
+        int32 device tensor [1 + wanted] whose first entry is the kernels' status
+        word, so one copy brings both back.  A step of single decoded tokens runs
+        as a replayed CUDA graph when graphs are on."""
         if not entries:
-            return torch.zeros((0, self.vocab_size), dtype=torch.float32, device=self.device)
-        host, layout, sizes = self.packer.pack(entries, self._heads)
+            return torch.zeros((0, self.vocab_size), dtype=torch.float32, device=self.device), None
+        self.bytes_h2d = 0
+        if self.use_graphs and temperature is not None and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            g = self._decode_graph(entries)
+            if g is not None:
+                return g.run(entries, temperature, uniform)
+        host, layout, sizes = self.packer.pack(entries, self._heads, temperature=temperature, uniform=uniform)
         pinned = torch.from_numpy(host).pin_memory()
         dev = pinned.to(self.device, non_blocking=True)
+        self.bytes_h2d = host.nbytes
         state = self.packer.to_state(dev, layout, sizes, self._heads)
+        tokens = None
+        before = ops.LAUNCHES
         with torch.no_grad():
             logits = self.model.forward(state, self.caches)
+            if temperature is not None and state.n_wanted:
+                tokens = torch.empty(1 + state.n_wanted, dtype=torch.int32, device=self.device)
+                ops.sample(logits, state.temperature, state.uniform, tokens[1:])
+                tokens[:1].copy_(self.rt.status)
+        self.last_launches = ops.LAUNCHES - before
         if check:
             self.check_status()
-        return logits
+        return logits, tokens
+
+    # -- decode steps as CUDA graphs ------------------------------------------------------
+    def _decode_graph(self, entries):
+        n = len(entries)
+        if n > self.max_graph_batch:
+            return None
+        B = 1
+        while B < n:
+            B *= 2
+        width = max((len(self.cache.get(e.request_id).tables[gi].blocks) for e in entries
+                     for gi in range(len(self.cache.groups))), default=1)
+        W = 64
+        while W < width:
+            W *= 2
+        key = (B, W)
+        g = self._graphs.get(key)
+        if g is None:
+            g = _DecodeGraph(self, B, W)
+            self._graphs[key] = g
+        return g
 
     def check_status(self) -> None:
         code = int(self.rt.status.item())

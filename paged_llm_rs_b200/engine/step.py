@@ -74,9 +74,14 @@ class StepPacker:
         return cur
 
     def pack(self, entries: Sequence[StepEntry], heads: List[Tuple[int, int]],
-             caps: Optional[StepCaps] = None, work_caps: Optional[List[Tuple[int, int]]] = None):
+             caps: Optional[StepCaps] = None, work_caps: Optional[List[Tuple[int, int, int]]] = None,
+             temperature: Optional[Sequence[float]] = None, uniform: Optional[Sequence[float]] = None):
         """Returns (host int32 array, layout dict, sizes) for the entries.  Pages
-        must already be reserved for every token."""
+        must already be reserved for every token.  ``temperature`` / ``uniform``
+        (one per wanted row) ride along for the sampling kernel.  With ``caps`` and
+        ``work_caps`` (max work items, reductions, partial rows per group) the
+        layout depends on them alone, so a captured graph can be fed any step
+        that fits."""
         cache = self.cache
         toks: List[int] = []
         pos: List[int] = []
@@ -134,10 +139,10 @@ class StepPacker:
             work, red, parts = attention_plan.plan_attention(
                 [(t0, n, p0) for (t0, n, p0, _) in segs], plan.tile_tokens, plan.window, plan.ctas_per_item,
                 self.target_ctas)
-            mw, mr = (work_caps[gi] if work_caps else (len(work), len(red)))
-            if len(work) > mw or len(red) > mr:
+            mw, mr, mp = (work_caps[gi] if work_caps else (len(work), len(red), parts))
+            if len(work) > mw or len(red) > mr or parts > mp:
                 raise ConfigError("the step's attention work does not fit the capacities it was given")
-            group_parts.append((slots, tables, work, red, parts, mw, mr, W))
+            group_parts.append((slots, tables, work, red, mp, mw, mr, W))
 
         # layout: offsets in int32 units
         off = 0
@@ -149,6 +154,7 @@ class StepPacker:
             off += count
 
         take("tokens", Tc); take("positions", Tc); take("logit_rows", max(nc, 1)); take("segments", max(sc, 1) * 4)
+        take("temperature", max(nc, 1)); take("uniform", max(nc, 1))
         for gi, (slots, tables, work, red, parts, mw, mr, W) in enumerate(group_parts):
             take(f"g{gi}.slots", Tc); take(f"g{gi}.tables", sc * W)
             take(f"g{gi}.n_work", 1); take(f"g{gi}.n_red", 1)
@@ -161,6 +167,9 @@ class StepPacker:
             host[o:o + len(a)] = a
 
         put("tokens", toks); put("positions", pos); put("logit_rows", rows)
+        if temperature is not None:
+            put("temperature", np.asarray(temperature, dtype=np.float32).view(np.int32))
+            put("uniform", np.asarray(uniform, dtype=np.float32).view(np.int32))
         put("segments", np.asarray(segs, dtype=np.int32).reshape(-1) if segs else [])
         for gi, (slots, tables, work, red, parts, mw, mr, W) in enumerate(group_parts):
             put(f"g{gi}.slots", slots); put(f"g{gi}.tables", tables)
@@ -191,6 +200,9 @@ class StepPacker:
                 work=view(f"g{gi}.work").view(-1, 8), n_work=view(f"g{gi}.n_work"), max_work=gs["max_work"],
                 red=view(f"g{gi}.red").view(-1, 4), n_red=view(f"g{gi}.n_red"), max_red=gs["max_red"],
                 part_o=part_o, part_ml=part_ml))
-        return StepState(n_tokens=T, tokens=view("tokens", T), positions=view("positions", T), groups=groups,
-                         logit_rows=view("logit_rows", nw), n_wanted=nw,
-                         segments=view("segments").view(-1, 4), host_segments=list(sizes["host_segments"]))
+        state = StepState(n_tokens=T, tokens=view("tokens", T), positions=view("positions", T), groups=groups,
+                          logit_rows=view("logit_rows", nw), n_wanted=nw,
+                          segments=view("segments").view(-1, 4), host_segments=list(sizes["host_segments"]))
+        state.temperature = view("temperature", max(nw, 1)).view(torch.float32)
+        state.uniform = view("uniform", max(nw, 1)).view(torch.float32)
+        return state

@@ -25,6 +25,7 @@ _ERRORS = {
 }
 
 _lib = None
+LAUNCHES = 0  # kernels of this library launched so far (library matrix products are not counted)
 c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
 
 
@@ -54,7 +55,9 @@ def lib():
 
 
 def _check(code: int, what: str) -> None:
+    global LAUNCHES
     if code == 0:
+        LAUNCHES += 1
         return
     if code < 0:
         raise KernelError(f"{what}: refused, {_ERRORS.get(code, code)}")

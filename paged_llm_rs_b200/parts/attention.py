@@ -18,6 +18,8 @@ from .spec import TensorSpec
 
 
 class GQAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, spec, rt, position_encodings=None):
         super().__init__(spec, rt)
         p = spec.params

@@ -97,6 +97,9 @@ class StepState:
     # (first token, token count, tokens in the cache before this step, state slot)
     segments: torch.Tensor = None  # int32 [segments, 4]
     host_segments: List[Tuple[int, int, int, int]] = field(default_factory=list)
+    # per wanted row, for the sampling kernel: temperature (<= 0: greedy) and the request's uniform number
+    temperature: torch.Tensor = None
+    uniform: torch.Tensor = None
 
 
 # --- parts ------------------------------------------------------------------------
@@ -145,6 +148,10 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True when forward() only launches kernels whose arguments do not depend on the
+    # step's contents, so that a decode step can be captured once and replayed.
+    graph_safe = False
+
     def cache_need(self):
         """KVNeed, StateNeed or None."""
         return None

@@ -1,0 +1,171 @@
+"""Generation through the Python entry point against the plain implementation:
+greedy (identical tokens in float32), temperature draws, top-k / top-p, a shared
+prefix, preemption in a pool that is too small, and the command line."""
+
+import json
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+from tiny_configs import CONFIGS, write_model
+
+pytestmark = pytest.mark.gpu
+
+
+def prompts_for(vocab, lengths, seed, shared=0):
+    rng = np.random.default_rng(seed)
+    ps = [rng.integers(0, vocab, n).tolist() for n in lengths]
+    if shared:
+        ps[-1][:shared] = ps[-2][:shared]
+    return ps
+
+
+def plain_greedy(model, prompt, n):
+    cfg, w = P.load_model(model, torch.float64)
+    seq, gaps = list(prompt), []
+    for _ in range(n):
+        logits = P.forward(cfg, w, seq)[-1]
+        top2 = torch.topk(logits, 2).values
+        gaps.append(float(top2[0] - top2[1]))
+        seq.append(P.greedy(logits))
+    return seq[len(prompt):], gaps
+
+
+def check_greedy(model, prompts, outs, n, dtype):
+    for p, o in zip(prompts, outs):
+        want, gaps = plain_greedy(model, p, n)
+        assert len(o) == n
+        if dtype == "float32":
+            assert o == want
+        else:
+            # bfloat16 may only differ where the float64 decision was closer than its noise
+            for i, (a, b) in enumerate(zip(o, want)):
+                if a != b:
+                    assert gaps[i] < 0.03, (i, gaps[i])
+                    break
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_tiny_a(tmp_path, dtype):
+    # three requests with prompts of 1, 7 and 19 tokens, 8 greedy tokens each, pages of 16, budget 8
+    from paged_llm_rs_b200 import Engine
+    cfg, seed = CONFIGS["A"]
+    model = write_model(tmp_path, "A")
+    prompts = prompts_for(cfg["vocab_size"], [1, 7, 19], 11)
+    eng = Engine(model, dtype=dtype, block_size=16, blocks=32, chunk=8)
+    outs = eng.generate(prompts, max_tokens=8)
+    check_greedy(model, prompts, outs, 8, dtype)
+    m = eng.metrics()
+    assert m["mixed_steps"] > 0 and m["tokens"] == 24 and m["pages_free"] == 32
+    # whole prompts (chunk off) give the same tokens
+    eng2 = Engine(model, dtype=dtype, block_size=16, blocks=32, chunk=None)
+    assert eng2.generate(prompts, max_tokens=8) == outs or dtype == "bfloat16"
+
+
+def vocab_order_choice(logits64, temperature, u):
+    """The engine's device draw: ids upward, the first id whose running sum reaches u * total."""
+    p = torch.softmax(logits64 / temperature, -1)
+    cdf = torch.cumsum(p, 0)
+    return cdf, float(u)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_temperature_tiny_b(tmp_path, dtype):
+    # five requests, prompts of 3, 11, 24, 40 and 40 tokens (the last two share 32), 12 tokens at
+    # temperature 0.8 with seed 7, pages of 8, budget 16.  Two of this model's layers have a window.
+    from paged_llm_rs_b200 import Engine
+    cfg, seed = CONFIGS["B"]
+    model = write_model(tmp_path, "B")
+    prompts = prompts_for(cfg["vocab_size"], [3, 11, 24, 40, 40], 12, shared=32)
+    eng = Engine(model, dtype=dtype, block_size=8, blocks=64, chunk=16)
+    outs = eng.generate(prompts, max_tokens=12, temperature=0.8, seed=7)
+    assert outs == Engine(model, dtype=dtype, block_size=8, blocks=64, chunk=16).generate(
+        prompts, max_tokens=12, temperature=0.8, seed=7)                      # the same seed, the same tokens
+    c, w = P.load_model(model, torch.float64)
+    slack = 1e-4 if dtype == "float32" else 2e-2
+    for p, o in zip(prompts, outs):
+        assert len(o) == 12
+        rng = P.PlainRng(7)
+        for i, tok in enumerate(o):
+            logits = P.forward(c, w, p + o[:i])[-1]
+            cdf, u = vocab_order_choice(logits, 0.8, rng.next_f32())
+            lo = float(cdf[tok - 1]) if tok > 0 else 0.0
+            assert lo - slack <= u <= float(cdf[tok]) + slack, (i, tok)
+
+
+def test_top_k_top_p_follow_the_reference_order(tmp_path):
+    from paged_llm_rs_b200 import Engine
+    cfg, seed = CONFIGS["A"]
+    model = write_model(tmp_path, "A")
+    prompts = prompts_for(cfg["vocab_size"], [5, 9], 13)
+    eng = Engine(model, dtype="float32", blocks=32)
+    outs = eng.generate(prompts, max_tokens=10, temperature=0.9, top_k=20, top_p=0.9, seed=3)
+    c, w = P.load_model(model, torch.float64)
+    for p, o in zip(prompts, outs):
+        rng = P.PlainRng(3)
+        for i, tok in enumerate(o):
+            logits = P.forward(c, w, p + o[:i])[-1].float()
+            assert tok == P.sample(logits, 0.9, 20, 0.9, rng), i
+
+
+def test_shared_prefix_gives_the_same_tokens(tmp_path):
+    # crates/pagedllm/tests/prefix.rs:88-139: shared equals computed
+    from paged_llm_rs_b200 import Engine
+    cfg, seed = CONFIGS["A"]
+    model = write_model(tmp_path, "A")
+    prompts = prompts_for(cfg["vocab_size"], [50, 50, 50], 14, shared=32)
+    prompts[0][:32] = prompts[1][:32]
+    on = Engine(model, dtype="float32", blocks=64, chunk=16, prefix_cache=True)
+    off = Engine(model, dtype="float32", blocks=64, chunk=16, prefix_cache=False)
+    a, b = on.generate(prompts, max_tokens=6), off.generate(prompts, max_tokens=6)
+    assert a == b
+    assert on.metrics()["cached_tokens"] == 64 and off.metrics()["cached_tokens"] == 0
+    check_greedy(model, prompts, a, 6, "float32")
+
+
+def test_preemption_changes_no_token(tmp_path):
+    from paged_llm_rs_b200 import Engine
+    cfg, seed = CONFIGS["A"]
+    model = write_model(tmp_path, "A")
+    prompts = prompts_for(cfg["vocab_size"], [20, 25, 18, 22], 15)
+    big = Engine(model, dtype="float32", block_size=8, blocks=64, chunk=16, prefix_cache=False)
+    small = Engine(model, dtype="float32", block_size=8, blocks=14, chunk=16, prefix_cache=False)
+    a, b = big.generate(prompts, max_tokens=20), small.generate(prompts, max_tokens=20)
+    assert small.metrics()["preemptions"] > 0 and big.metrics()["preemptions"] == 0
+    assert a == b
+    small.runner.cache.check_invariants()
+    assert small.metrics()["pages_free"] == 14
+
+
+def test_stop_tokens_and_refusal(tmp_path):
+    from paged_llm_rs_b200 import Engine
+    from paged_llm_rs_b200.engine.scheduler import Finish
+    cfg, seed = CONFIGS["A"]
+    model = write_model(tmp_path, "A")
+    eng = Engine(model, dtype="float32", block_size=8, blocks=4)
+    p = prompts_for(cfg["vocab_size"], [6], 16)[0]
+    free = eng.generate([p], max_tokens=6)[0]
+    stop = free[-1]
+    stopped = eng.generate([p], max_tokens=6, stop_tokens=[stop])[0]
+    assert stopped == free[:free.index(stop)]                    # the stop token ends it and is not returned
+    rid = eng.submit(list(range(40)), max_tokens=4)              # 5 pages of 8 can never fit in 4
+    eng.run_until_done()
+    assert eng.finish_reason(rid) == Finish.LENGTH and eng._seqs[rid].output == []
+
+
+def test_command_line(tmp_path):
+    cfg, seed = CONFIGS["A"]
+    model = write_model(tmp_path, "A")
+    r = subprocess.run([sys.executable, "-m", "paged_llm_rs_b200", "generate", "--model", model, "--dtype", "f32",
+                        "--prompt-ids", "5,6,7", "--prompt-ids", "9", "--max-tokens", "5", "--blocks", "16",
+                        "--chunk", "off", "--prefix-cache", "off", "--metrics"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = r.stdout.strip().splitlines()
+    assert len(lines) == 2 and all(len(l.split(",")) == 5 for l in lines)
+    want, _ = plain_greedy(model, [5, 6, 7], 5)
+    assert [int(t) for t in lines[0].split(",")] == want

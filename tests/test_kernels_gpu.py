@@ -1,0 +1,314 @@
+"""Each CUDA kernel alone against a plain float32 PyTorch statement of the same
+operation, at sizes other than the engine's tiny models use: widths and
+vocabularies that are no power of two, head sizes in steps of 16, one kv head
+under many query heads, page sizes 8 to 64.  Where random inputs would hide a
+fault the inputs are made so that it shows: one far key among hundreds that must
+dominate, keys just inside and just outside a window, a value that marks each
+page."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from paged_llm_rs_b200.kernels import attention_plan, ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+def status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,vocab", [(72, 1000), (1024, 50), (33, 7)])
+def test_embed(dtype, hidden, vocab):
+    g = torch.Generator(device=DEV).manual_seed(0)
+    table = torch.randn(vocab, hidden, device=DEV, generator=g).to(dtype)
+    tokens = torch.randint(0, vocab, (37,), device=DEV, generator=g, dtype=torch.int32)
+    out = torch.empty(37, hidden, device=DEV, dtype=dtype)
+    st = status()
+    ops.embed(tokens, table, out, st)
+    assert torch.equal(out, table[tokens.long()]) and st.item() == 0
+    tokens[3] = vocab  # out of range: zeros and a raised status bit, no fault
+    ops.embed(tokens, table, out, st)
+    assert st.item() == 1 and out[3].abs().sum() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width,eps", [(96, 1e-5), (1000, 1e-6), (4096, 1e-6), (50, 1e-3)])
+def test_rmsnorm_plain_fused_and_gathered(dtype, width, eps):
+    g = torch.Generator(device=DEV).manual_seed(1)
+    x = (torch.randn(19, width, device=DEV, generator=g) * 3).to(dtype)
+    d = torch.randn(19, width, device=DEV, generator=g).to(dtype)
+    gain = 1 + 0.1 * torch.randn(width, device=DEV, generator=g)
+
+    def ref(v):
+        v = v.float()
+        return v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * gain
+
+    out = torch.empty_like(x)
+    ops.rmsnorm(x, gain, eps, out)
+    torch.testing.assert_close(out.float(), ref(x), **tol(dtype))
+    # fused residual add: the sum is stored in the stream's dtype and normed from there
+    res = x.clone()
+    ops.rmsnorm(res, gain, eps, out, delta=d, residual_out=res)
+    summed = (x.float() + d.float()).to(dtype)
+    assert torch.equal(res, summed)
+    torch.testing.assert_close(out.float(), ref(summed), **tol(dtype))
+    # gathered rows with a pending add, nothing stored
+    rows = torch.tensor([18, 0, 7], dtype=torch.int32, device=DEV)
+    res2 = x.clone()
+    out3 = torch.empty(3, width, device=DEV, dtype=dtype)
+    ops.rmsnorm(res2, gain, eps, out3, delta=d, rows=rows)
+    assert torch.equal(res2, x)
+    torch.testing.assert_close(out3.float(), ref(summed[rows.long()]), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter", [160, 3072, 77])
+def test_swiglu(dtype, inter):
+    g = torch.Generator(device=DEV).manual_seed(2)
+    gu = (torch.randn(11, 2 * inter, device=DEV, generator=g) * 2).to(dtype)
+    out = torch.empty(11, inter, device=DEV, dtype=dtype)
+    ops.swiglu(gu, out)
+    a, b = gu.float()[:, :inter], gu.float()[:, inter:]
+    torch.testing.assert_close(out.float(), a * torch.sigmoid(a) * b, **tol(dtype))   # the gate carries the activation
+
+
+def rope_ref(x, pos, theta, rotary_dim):
+    half = rotary_dim // 2
+    inv = 1.0 / theta ** (torch.arange(half, dtype=torch.float64) * 2 / rotary_dim)
+    ang = pos.double()[:, None] * inv[None]
+    c, s = ang.cos().float().to(x.device)[:, None], ang.sin().float().to(x.device)[:, None]
+    x1, x2 = x[..., :half], x[..., half:rotary_dim]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, x[..., rotary_dim:]], -1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,rot,page", [(6, 3, 48, 48, 8), (8, 1, 32, 16, 16), (16, 8, 128, 128, 64), (4, 4, 80, 80, 16)])
+def test_qk_norm_rope_kv_write(dtype, nh, nkv, hd, rot, page):
+    from paged_llm_rs_b200.parts.base import Runtime
+    from paged_llm_rs_b200.parts.position import RotaryEncoding
+    from paged_llm_rs_b200.parts.spec import PartSpec
+
+    g = torch.Generator(device=DEV).manual_seed(3)
+    T, pages, eps, theta = 21, 9, 1e-5, 1e6
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV, generator=g).to(dtype)
+    qg = 1 + 0.1 * torch.randn(hd, device=DEV, generator=g)
+    kg = 1 + 0.1 * torch.randn(hd, device=DEV, generator=g)
+    pos = torch.randint(0, 300, (T,), device=DEV, generator=g, dtype=torch.int32)
+    slots = torch.randperm(pages * page, device=DEV, generator=g)[:T].to(torch.int32)
+    slots[5] = -1  # a token that is not to be written
+    enc = RotaryEncoding(PartSpec("rope", dict(head_dim=hd, rotary_dim=rot, theta=theta, max_positions=300)),
+                         Runtime(torch.device(DEV), dtype))
+    cos, sin, rdim = enc.rotary()
+    kp = torch.zeros(pages, nkv, page, hd, device=DEV, dtype=dtype)
+    vp = torch.zeros_like(kp)
+    q = torch.empty(T, nh * hd, device=DEV, dtype=dtype)
+    st = status()
+    ops.qk_norm_rope_kv(qkv, q, qg, kg, eps, cos, sin, rdim, pos, slots, kp, vp, nh, nkv, hd, st)
+    assert st.item() == 0
+
+    x = qkv.float().view(T, nh + 2 * nkv, hd)
+    norm = lambda v, gain: v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * gain
+    q_ref = rope_ref(norm(x[:, :nh], qg), pos.cpu(), theta, rot)       # norm per head, then the rotation
+    k_ref = rope_ref(norm(x[:, nh:nh + nkv], kg), pos.cpu(), theta, rot)
+    v_ref = x[:, nh + nkv:]                                            # values raw
+    torch.testing.assert_close(q.float().view(T, nh, hd), q_ref, **tol(dtype))
+    for t in range(T):
+        s = slots[t].item()
+        if s < 0:
+            continue
+        torch.testing.assert_close(kp[s // page, :, s % page].float(), k_ref[t], **tol(dtype))
+        torch.testing.assert_close(vp[s // page, :, s % page].float(), v_ref[t], **tol(dtype))
+    written = torch.zeros(pages * page, dtype=torch.bool)
+    written[slots[slots >= 0].long().cpu()] = True
+    flat = kp.float().permute(0, 2, 1, 3).reshape(pages * page, -1).abs().sum(-1).cpu()
+    assert (flat[~written] == 0).all()          # nothing else was touched
+
+
+# --- attention -------------------------------------------------------------------------
+
+def attention_ref(q, k, v, scale, window):
+    """q [nq, nh, hd] at positions pos0.., k/v [ctx, nkv, hd]; float64."""
+    nq, nh, hd = q.shape
+    ctx, nkv, _ = k.shape
+    pos0 = ctx - nq
+    g = nh // nkv
+    out = torch.zeros(nq, nh, hd, dtype=torch.float64)
+    for h in range(nh):
+        s = q[:, h].double() @ k[:, h // g].double().T * scale
+        i = torch.arange(nq)[:, None] + pos0
+        j = torch.arange(ctx)[None]
+        hidden = j > i
+        if window:
+            hidden |= j <= i - window
+        s = s.masked_fill(hidden, float("-inf"))
+        out[:, h] = torch.softmax(s, -1) @ v[:, h // g].double()
+    return out
+
+
+def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, craft=None):
+    """reqs: list of (context before the step, query tokens).  Builds a paged cache
+    with shuffled pages, runs the kernel, returns (got, want) per request."""
+    g = torch.Generator().manual_seed(seed)
+    scale = hd ** -0.5
+    n_pages = sum(-(-(c + n) // page) for c, n in reqs) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    kp = torch.zeros(n_pages, nkv, page, hd, dtype=dtype)
+    vp = torch.zeros_like(kp)
+    width = max(-(-(c + n) // page) for c, n in reqs)
+    tables = torch.full((len(reqs), width), -1, dtype=torch.int32)
+    qs, ks, vs, segs = [], [], [], []
+    t0 = 0
+    for r, (c, n) in enumerate(reqs):
+        total = c + n
+        k = torch.randn(total, nkv, hd, generator=g)
+        v = torch.randn(total, nkv, hd, generator=g)
+        q = torch.randn(n, nh, hd, generator=g)
+        if craft:
+            craft(r, q, k, v)
+        k, v, q = k.to(dtype), v.to(dtype), q.to(dtype)
+        for b in range(-(-total // page)):
+            pg = perm.pop()
+            tables[r, b] = pg
+            m = min(page, total - b * page)
+            kp[pg, :, :m] = k[b * page:b * page + m].transpose(0, 1)
+            vp[pg, :, :m] = v[b * page:b * page + m].transpose(0, 1)
+        if window:  # pages the window has passed for every query of the step are given back
+            first_needed = max(0, c - window + 1)
+            for b in range(width):
+                if (b + 1) * page <= first_needed:
+                    tables[r, b] = -1
+        qs.append(q); ks.append(k); vs.append(v)
+        segs.append((t0, n, c))
+        t0 += n
+    tile = ops.attention_tile_tokens(nh, nkv)
+    work, red, parts = attention_plan.plan_attention(segs, tile, window, nkv * (-(-(nh // nkv) // 16)), target_ctas)
+    dev = lambda t: t.to(DEV)
+    workd = dev(torch.from_numpy(np.ascontiguousarray(work)).reshape(-1, 8)) if len(work) else torch.zeros(1, 8, dtype=torch.int32, device=DEV)
+    redd = dev(torch.from_numpy(np.ascontiguousarray(red)).reshape(-1, 4)) if len(red) else torch.zeros(1, 4, dtype=torch.int32, device=DEV)
+    qd = dev(torch.cat(qs).reshape(t0, nh * hd).contiguous())
+    out = torch.zeros_like(qd)
+    part_o = torch.zeros(max(parts, 1), nh, hd, device=DEV)
+    part_ml = torch.zeros(max(parts, 1), nh, 2, device=DEV)
+    st = status()
+    ops.paged_attention(qd, dev(kp), dev(vp), dev(tables), workd, dev(torch.tensor([len(work)], dtype=torch.int32)),
+                        len(work), out, part_o, part_ml, redd, dev(torch.tensor([len(red)], dtype=torch.int32)),
+                        len(red), nh, nkv, hd, window or 0, scale, st)
+    assert st.item() == 0
+    res = []
+    for (a, n, c), q, k, v in zip(segs, qs, ks, vs):
+        want = attention_ref(q.float(), k.float(), v.float(), scale, window)
+        res.append((out[a:a + n].view(n, nh, hd).double().cpu(), want))
+    return res, len(red)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [
+    (6, 3, 48, 8, None), (8, 1, 32, 16, None), (16, 8, 128, 16, None), (4, 4, 80, 64, None),
+    (32, 1, 16, 8, None), (8, 2, 64, 16, 40), (6, 3, 48, 8, 7), (2, 1, 256, 32, None)])
+def test_paged_attention_mixed_batch(dtype, nh, nkv, hd, page, window):
+    # portions beside decoded tokens, contexts that end on and off page edges
+    reqs = [(0, 1), (0, 37), (63, 1), (64, 1), (130, 2), (17, 50), (300, 1), (page * 3 - 1, 3)]
+    for target in (1, 10 ** 6):     # never split / split wherever the range is long enough
+        res, n_red = run_attention(dtype, reqs, nh, nkv, hd, page, window, target)
+        assert (n_red > 0) == (target > 1 and not (window and window < 128))
+        for got, want in res:
+            torch.testing.assert_close(got, want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_far_key_among_hundreds_decides(dtype):
+    # One key early in a long context matches the query; its value is a marker.  A
+    # kernel that loses that key (a wrong page, a range cut short) cannot return the marker.
+    def craft(r, q, k, v):
+        far = 3 + 5 * r
+        k[far] = 0; k[far, :, 0] = 8.0
+        q[:] = 0; q[:, :, 0] = 8.0 * (q.shape[-1] ** 0.5)
+        v[far] = 100.0 + r
+    reqs = [(700, 1), (517, 1), (333, 2)]
+    for target in (1, 10 ** 6):
+        res, _ = run_attention(dtype, reqs, 4, 2, 64, 16, None, target, craft=craft)
+        for r, (got, want) in enumerate(res):
+            assert (got - (100.0 + r)).abs().max() < 0.6
+            torch.testing.assert_close(got, want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_window_edge(dtype):
+    # window 24: the query at position p sees keys p-23..p.  The key at p-23 carries the
+    # answer; the key at p-24, just outside, carries a louder wrong one.
+    W = 24
+
+    def craft(r, q, k, v):
+        p = k.shape[0] - 1
+        q[:] = 0; q[:, :, 1] = 6.0 * (q.shape[-1] ** 0.5)
+        k[:, :, 1] = 0
+        k[p - W + 1, :, 1] = 6.0; v[p - W + 1] = 7.0
+        k[p - W, :, 1] = 12.0; v[p - W] = -50.0
+    res, _ = run_attention(dtype, [(90, 1), (47, 1), (24, 1)], 4, 2, 32, 8, W, 1, craft=craft)
+    for got, want in res:
+        assert (got - 7.0).abs().max() < 0.5
+        torch.testing.assert_close(got, want, **tol(dtype))
+
+
+def test_attention_refuses_sizes_it_does_not_take():
+    from paged_llm_rs_b200.errors import KernelError
+    with pytest.raises(KernelError, match="head_dim"):
+        run_attention(torch.float32, [(3, 1)], 2, 1, 24, 8, None, 1)
+    with pytest.raises(KernelError, match="head_dim"):
+        run_attention(torch.float32, [(3, 1)], 2, 1, 512, 8, None, 1)
+
+
+def test_kernels_refuse_host_tensors():
+    from paged_llm_rs_b200.errors import KernelError
+    with pytest.raises(KernelError, match="no CPU path"):
+        ops.swiglu(torch.zeros(2, 8), torch.zeros(2, 4))
+
+
+# --- sampling ----------------------------------------------------------------------------
+
+@pytest.mark.parametrize("vocab", [1000, 151936, 33])
+def test_sampling_kernel(vocab):
+    g = torch.Generator(device=DEV).manual_seed(5)
+    n = 24
+    logits = torch.randn(n, vocab, device=DEV, generator=g) * 4
+    logits[0, 7] = logits[0, 3] = 99.0              # a tie: the first maximum wins
+    temp = torch.zeros(n, device=DEV)
+    temp[n // 2:] = torch.rand(n - n // 2, device=DEV, generator=g) + 0.3
+    u = torch.rand(n, device=DEV, generator=g)
+    u[n // 2] = 0.0
+    toks = torch.zeros(n, dtype=torch.int32, device=DEV)
+    ops.sample(logits, temp, u, toks)
+    toks = toks.cpu().tolist()
+    lg = logits.cpu().double()
+    assert toks[0] == 3
+    for i in range(n // 2):
+        assert toks[i] == int(lg[i].argmax())
+    for i in range(n // 2, n):
+        p = torch.softmax(lg[i] / temp[i].item(), -1)
+        cdf = torch.cumsum(p, 0)
+        point = u[i].item()
+        # the token whose span of the running sum holds the point, give or take float32 rounding
+        lo = cdf[toks[i] - 1].item() if toks[i] > 0 else 0.0
+        assert lo - 1e-4 <= point <= cdf[toks[i]].item() + 1e-4, i
+
+
+def test_sampling_kernel_follows_the_distribution():
+    probs = torch.tensor([0.5, 0.3, 0.15, 0.05])
+    n = 4000
+    logits = torch.log(probs).repeat(n, 1).to(DEV).contiguous()
+    u = torch.rand(n, device=DEV, generator=torch.Generator(device=DEV).manual_seed(9))
+    toks = torch.zeros(n, dtype=torch.int32, device=DEV)
+    ops.sample(logits, torch.ones(n, device=DEV), u, toks)
+    freq = torch.bincount(toks.long().cpu(), minlength=4).double() / n
+    assert (freq - probs.double()).abs().max() < 0.03
