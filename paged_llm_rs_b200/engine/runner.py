@@ -29,7 +29,7 @@ from .step import GroupPlanConfig, StepCaps, StepEntry, StepPacker
 
 DTYPES = {"float32": torch.float32, "f32": torch.float32, "fp32": torch.float32,
           "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
-SM_COUNT_TARGET = 2 * 148  # CTAs an attention launch should have before splits stop
+SM_COUNT_TARGET = 4 * 148  # CTAs an attention launch should have before splits stop
 
 
 def parse_dtype(name) -> torch.dtype:
@@ -133,7 +133,7 @@ class ModelRunner:
         for g in self.cache.groups:
             nkv = g.need.num_kv_heads
             nh = nkv * g.max_group_size
-            tile = ops.attention_tile_tokens(nh, nkv)
+            tile = ops.attention_tile_tokens(nh, nkv, self.dtype, g.need.head_dim)
             gparts = -(-g.max_group_size // 16)
             plans.append(GroupPlanConfig(tile, nkv * gparts, g.window))
             nh_max = max(getattr(self.model.blocks[self.model.schedule[i].layer].mixer, "nh", nh) for i in g.entries)

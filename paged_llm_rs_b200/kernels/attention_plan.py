@@ -20,7 +20,7 @@ from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
 
-SPLIT_ALIGN = 32   # split boundaries fall on multiples of the kernels' key tile
+SPLIT_ALIGN = 64   # split boundaries fall on multiples of the kernels' key tiles (32 and 64)
 MIN_SPLIT_KEYS = 128
 
 

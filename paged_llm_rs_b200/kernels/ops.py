@@ -45,6 +45,10 @@ def lib():
             "pllm_attention_generic_tile_tokens": [c_int, c_int],
             "pllm_attention_reduce": [c_int, P, P, P, P, c_int, P, c_int, c_int, P],
             "pllm_sample": [P, c_int, c_int, c_ll, P, P, P, P],
+            "pllm_attention_mma_supports": [c_int, c_int, c_int, c_int],
+            "pllm_attention_mma_tile_tokens": [c_int, c_int],
+            "pllm_attention_mma": [P, P, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
+                                   c_int, c_float, P, P],
         }
         for name, args in sig.items():
             fn = getattr(L, name)
@@ -182,8 +186,20 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, q_gain, k_gain, eps:
     return q_out
 
 
-def attention_tile_tokens(num_heads: int, num_kv_heads: int) -> int:
-    """The most query tokens one attention work item may hold."""
+def attention_uses_tensor_cores(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    """Whether paged_attention runs the mma kernel for this shape (bfloat16, head
+    sizes 64 and 128) or the generic one."""
+    if dtype != torch.bfloat16:
+        return False
+    return bool(lib().pllm_attention_mma_supports(_BF16, num_heads, num_kv_heads, head_dim))
+
+
+def attention_tile_tokens(num_heads: int, num_kv_heads: int, dtype: torch.dtype = torch.float32,
+                          head_dim: int = 0) -> int:
+    """The most query tokens one attention work item may hold, for the kernel that
+    paged_attention picks for this dtype and shape."""
+    if attention_uses_tensor_cores(dtype, num_heads, num_kv_heads, head_dim):
+        return lib().pllm_attention_mma_tile_tokens(num_heads, num_kv_heads)
     return lib().pllm_attention_generic_tile_tokens(num_heads, num_kv_heads)
 
 
@@ -211,10 +227,17 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         raise KernelError("paged_attention: work / red lists shorter than their maxima")
     n_pages, page_size = k_pool.shape[0], k_pool.shape[2]
     L = lib()
-    _check(L.pllm_attention_generic(_code(q), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
-                                    _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml), num_heads,
-                                    num_kv_heads, head_dim, page_size, n_pages, block_tables.shape[-1], int(window),
-                                    float(scale), _ptr(status), _stream()), "paged_attention")
+    if attention_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim):
+        _check(L.pllm_attention_mma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work), _ptr(n_work),
+                                    max_work, _ptr(out), _ptr(part_o), _ptr(part_ml), num_heads, num_kv_heads,
+                                    head_dim, page_size, n_pages, block_tables.shape[-1], int(window), float(scale),
+                                    _ptr(status), _stream()), "paged_attention (mma)")
+    else:
+        _check(L.pllm_attention_generic(_code(q), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables),
+                                        _ptr(work), _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml),
+                                        num_heads, num_kv_heads, head_dim, page_size, n_pages,
+                                        block_tables.shape[-1], int(window), float(scale), _ptr(status), _stream()),
+               "paged_attention")
     _check(L.pllm_attention_reduce(_code(q), _ptr(part_o), _ptr(part_ml), _ptr(red), _ptr(n_red), max_red,
                                    _ptr(out), num_heads, head_dim, _stream()), "attention_reduce")
     return out

@@ -191,7 +191,7 @@ def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, c
         qs.append(q); ks.append(k); vs.append(v)
         segs.append((t0, n, c))
         t0 += n
-    tile = ops.attention_tile_tokens(nh, nkv)
+    tile = ops.attention_tile_tokens(nh, nkv, dtype, hd)
     work, red, parts = attention_plan.plan_attention(segs, tile, window, nkv * (-(-(nh // nkv) // 16)), target_ctas)
     dev = lambda t: t.to(DEV)
     workd = dev(torch.from_numpy(np.ascontiguousarray(work)).reshape(-1, 8)) if len(work) else torch.zeros(1, 8, dtype=torch.int32, device=DEV)
@@ -215,7 +215,8 @@ def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, c
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd,page,window", [
     (6, 3, 48, 8, None), (8, 1, 32, 16, None), (16, 8, 128, 16, None), (4, 4, 80, 64, None),
-    (32, 1, 16, 8, None), (8, 2, 64, 16, 40), (6, 3, 48, 8, 7), (2, 1, 256, 32, None)])
+    (32, 1, 16, 8, None), (8, 2, 64, 16, 40), (6, 3, 48, 8, 7), (2, 1, 256, 32, None),
+    (4, 4, 128, 16, None), (8, 1, 64, 8, None), (9, 3, 128, 12, 50), (40, 2, 64, 16, None), (32, 8, 128, 64, None)])
 def test_paged_attention_mixed_batch(dtype, nh, nkv, hd, page, window):
     # portions beside decoded tokens, contexts that end on and off page edges
     reqs = [(0, 1), (0, 37), (63, 1), (64, 1), (130, 2), (17, 50), (300, 1), (page * 3 - 1, 3)]

@@ -121,7 +121,7 @@ def test_attention_part_alone_in_portions(dtype, window):
     w = {k: v.to(dtype) if "norm" not in k else v for k, v in attention_weights(cfg, "a", 10).items()}
     att.bind({k: v.to(DEV) for k, v in w.items()})
     cache = CacheManager([att.cache_need()], 8, 12, 4, dtype, DEV, prefix_cache=False)
-    packer = StepPacker(cache, [GroupPlanConfig(ops.attention_tile_tokens(nh, nkv), nkv, window)], 296, 1000, 64, DEV)
+    packer = StepPacker(cache, [GroupPlanConfig(ops.attention_tile_tokens(nh, nkv, dtype, hd), nkv, window)], 296, 1000, 64, DEV)
     x = rand((40, H), 20).to(dtype)
     cache.open("r")
     outs, p = [], 0
