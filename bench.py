@@ -146,6 +146,8 @@ def main(argv=None) -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the shape has (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one part alone and print a short line (for profiling; not a bench record)")
     args = ap.parse_args(argv)
 
     if args.impl == "reference":
@@ -172,7 +174,7 @@ def main(argv=None) -> int:
     clocks = ClockSampler()
     try:
         model_dir = write_random_model(os.path.join(tmp, "model"), shape, 0, device="cuda")
-        most = 1 if args.no_points else 64
+        most = 1 if (args.no_points or args.only) else 64
         pages = max(most, B) * (ctx // PAGE + 4) + PREFILL_TOKENS // PAGE + 64
         eng = Engine(model_dir, dtype="bfloat16", block_size=PAGE, blocks=pages, max_batch=max(most, B),
                      chunk=PREFILL_TOKENS, prefix_cache=False)
@@ -186,8 +188,24 @@ def main(argv=None) -> int:
         kv_token_bytes = runner.cache.bytes_per_token()
         clocks.start()
 
+        if args.only == "prefill":
+            from paged_llm_rs_b200.engine.step import StepEntry
+            prompt = np.random.default_rng(0).integers(0, V, PREFILL_TOKENS).tolist()
+            for _ in range(warmup + steps):
+                runner.cache.open("prefill")
+                runner.cache.reserve("prefill", PREFILL_TOKENS)
+                runner.step([StepEntry("prefill", prompt, [PREFILL_TOKENS - 1])], check=False)
+                runner.cache.close("prefill")
+            torch.cuda.synchronize()
+            print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "steps": steps}))
+            return 0
+
         # -- decode, on the device -------------------------------------------------------
         ms, launches = decode_point(runner, B, ctx, steps, warmup, clocks)
+        if args.only == "decode":
+            print(json.dumps({"only": "decode", "batch": B, "context": ctx, "ms_per_step": round(ms, 4),
+                              "launches_per_step": launches}))
+            return 0
         value = B / (ms / 1e3)
         step_bytes = weight_bytes + B * ctx * kv_token_bytes
         achieved = step_bytes / (ms / 1e3) / 1e9

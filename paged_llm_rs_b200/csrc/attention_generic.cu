@@ -39,6 +39,8 @@ __global__ void attention_generic_kernel(
     float* __restrict__ part_ml,        // [parts, nh, 2]
     int nh, int nkv, int hd, int page_size, int n_pages, int table_width, int window, float scale,
     int heads_per_cta, int* status) {
+    pdl_launch_dependents();
+    pdl_wait();
     if ((int)blockIdx.x >= *n_work_ptr) return;
     const AttnWork w = work[blockIdx.x];
     const int group = nh / nkv;
@@ -157,36 +159,44 @@ __global__ void attention_generic_kernel(
     }
 }
 
-// Combine the splits of a token in their order: for token t with
-// red[t] = {first, count, stride}, its parts are first + s * stride, s < count.
-// count == 0: the token was not split, nothing to do.
+// Combine the splits of a token in their order: for entry t,
+// red[t] = {token, first, count, stride}: its parts are first + s * stride, s < count.
+// One CTA per (entry, head); the weights exp(m_s - M) are formed once in shared
+// memory, then each thread sums its output dimensions over the splits.
+#define RED_MAX_SPLITS 256
 template <typename T>
 __global__ void attention_reduce_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                         const int* __restrict__ red, const int* __restrict__ n_red_ptr,
                                         T* __restrict__ out, int nh, int hd) {
-    const int t = blockIdx.x;
+    __shared__ float wgt[RED_MAX_SPLITS];
+    __shared__ float inv_s;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, head = blockIdx.y;
     if (t >= *n_red_ptr) return;
-    const int token = red[t * 4], first = red[t * 4 + 1], count = red[t * 4 + 2], stride = red[t * 4 + 3];
+    const int token = red[t * 4], first = red[t * 4 + 1], count = min(red[t * 4 + 2], RED_MAX_SPLITS), stride = red[t * 4 + 3];
     if (count <= 0) return;
-    for (int head = threadIdx.y; head < nh; head += blockDim.y) {
+    if (threadIdx.x < 32) {
         float M = -CUDART_INF_F;
-        for (int s = 0; s < count; s++) M = fmaxf(M, part_ml[((size_t)(first + s * stride) * nh + head) * 2]);
+        for (int s = threadIdx.x; s < count; s += 32) M = fmaxf(M, part_ml[((size_t)(first + s * stride) * nh + head) * 2]);
+        M = warp_max(M);
         float L = 0.f;
-        for (int s = 0; s < count; s++) {
+        for (int s = threadIdx.x; s < count; s += 32) {
             const size_t pr = (size_t)(first + s * stride) * nh + head;
             const float ms = part_ml[pr * 2];
-            L += ms == -CUDART_INF_F ? 0.f : part_ml[pr * 2 + 1] * expf(ms - M);
+            const float f = ms == -CUDART_INF_F ? 0.f : expf(ms - M);
+            wgt[s] = f;
+            L += part_ml[pr * 2 + 1] * f;
         }
-        const float inv = L > 0.f ? 1.0f / L : 0.f;
-        for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-            float o = 0.f;
-            for (int s = 0; s < count; s++) {
-                const size_t pr = (size_t)(first + s * stride) * nh + head;
-                const float ms = part_ml[pr * 2];
-                if (ms != -CUDART_INF_F) o += part_o[pr * hd + d] * expf(ms - M);
-            }
-            out[((size_t)token * nh + head) * hd + d] = from_f32<T>(o * inv);
-        }
+        L = warp_sum(L);
+        if (threadIdx.x == 0) inv_s = L > 0.f ? 1.0f / L : 0.f;
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float o = 0.f;
+        for (int s = 0; s < count; s++) o = fmaf(part_o[((size_t)(first + s * stride) * nh + head) * hd + d], wgt[s], o);
+        out[((size_t)token * nh + head) * hd + d] = from_f32<T>(o * inv);
     }
 }
 
@@ -205,10 +215,10 @@ PLLM_EXPORT int pllm_attention_generic(int dtype, const void* q, const void* k_p
     PLLM_DISPATCH_DTYPE(dtype, {
         cudaFuncSetAttribute(attention_generic_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         dim3 grid(max_work, nkv * gparts);
-        attention_generic_kernel<T><<<grid, ATT_MAX_ROWS * 32, smem, stream>>>(
-            (const T*)q, (const T*)k_pool, (const T*)v_pool, block_tables, (const AttnWork*)work, n_work_ptr,
-            (T*)out, part_o, part_ml, nh, nkv, hd, page_size, n_pages, table_width, window, scale, heads_per_cta,
-            status);
+        launch_chained(attention_generic_kernel<T>, grid, dim3(ATT_MAX_ROWS * 32), smem, stream,
+                       (const T*)q, (const T*)k_pool, (const T*)v_pool, block_tables, (const AttnWork*)work, n_work_ptr,
+                       (T*)out, part_o, part_ml, nh, nkv, hd, page_size, n_pages, table_width, window, scale,
+                       heads_per_cta, status);
     });
     return launch_status();
 }
@@ -226,8 +236,9 @@ PLLM_EXPORT int pllm_attention_reduce(int dtype, const float* part_o, const floa
                                       cudaStream_t stream) {
     if (max_red <= 0) return PLLM_OK;
     PLLM_DISPATCH_DTYPE(dtype, {
-        dim3 block(32, 4);
-        attention_reduce_kernel<T><<<max_red, block, 0, stream>>>(part_o, part_ml, red, n_red_ptr, (T*)out, nh, hd);
+        dim3 grid(max_red, nh);
+        launch_chained(attention_reduce_kernel<T>, grid, dim3(hd >= 128 ? 128 : 64), 0, stream, part_o, part_ml, red,
+                       n_red_ptr, (T*)out, nh, hd);
     });
     return launch_status();
 }

@@ -105,6 +105,8 @@ __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     int nh, int nkv, int page_size, int page_shift, int n_pages, int table_width, int window, float scale_log2,
     int heads_per_cta, int* status) {
+    pdl_launch_dependents();
+    pdl_wait();
     if ((int)blockIdx.x >= *n_work_ptr) return;
     const AttnWork w = work[blockIdx.x];
     const int group = nh / nkv;
@@ -126,30 +128,33 @@ __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
     TileLoader<HD> loader{k_pool, v_pool, block_tables + (size_t)w.seg * table_width, table_width, page_size, page_shift,
                           n_pages, nkv, kh, w.kv_end};
 
-    // ---- q rows into the last stage's buffer, then into A fragments -----------------------
-    {
-        const uint32_t q_s = smem_base + (MMA_STAGES - 1) * STAGE_BYTES;
-        for (int idx = threadIdx.x; idx < MMA_ROWS * CH; idx += 128) {
-            const int row = idx / CH, chunk = idx % CH;
-            const bool valid = row < rows;
-            const int tq = valid ? row / n_heads : 0, hg = valid ? row % n_heads : 0;
-            const bf16* src = q + ((size_t)(w.q_token0 + tq) * nh + head0 + hg) * HD + chunk * 8;
-            cp_async16(q_s + tile_off<HD>(row, chunk), src, valid);
-        }
-        cp_async_commit();
-        cp_async_wait<0>();
-        __syncthreads();
+    // ---- q rows into a buffer of their own; the first key tiles are requested at once --------
+    const uint32_t q_s = smem_base + MMA_STAGES * STAGE_BYTES;
+    for (int idx = threadIdx.x; idx < (decode ? 16 : MMA_ROWS) * CH; idx += 128) {
+        const int row = idx / CH, chunk = idx % CH;
+        const bool valid = row < rows;
+        const int tq = valid ? row / n_heads : 0, hg = valid ? row % n_heads : 0;
+        const bf16* src = q + ((size_t)(w.q_token0 + tq) * nh + head0 + hg) * HD + chunk * 8;
+        cp_async16(q_s + tile_off<HD>(row, chunk), src, valid);
     }
+    cp_async_commit();
+    const int n_tiles = (w.kv_end - w.kv_begin + MMA_BK - 1) / MMA_BK;
+#pragma unroll
+    for (int s = 0; s < MMA_STAGES - 1; s++) {
+        if (s < n_tiles) loader.load(smem_base + s * STAGE_BYTES, smem_base + s * STAGE_BYTES + MMA_BK * HD * 2,
+                                     w.kv_begin + s * MMA_BK, status);
+        cp_async_commit();
+    }
+    cp_async_wait<MMA_STAGES - 1>();   // q has landed; the key tiles may still be in flight
+    __syncthreads();
     uint32_t qf[KSTEPS][4];
     {
-        const uint32_t q_s = smem_base + (MMA_STAGES - 1) * STAGE_BYTES;
         const int rbase = decode ? 0 : warp * 16;
         const int mat = lane >> 3;
         const int row = rbase + (lane & 7) + (mat & 1) * 8;
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ks++) ldmatrix_x4(qf[ks], q_s + tile_off<HD>(row, ks * 2 + (mat >> 1)));
     }
-    __syncthreads();  // the q buffer is free for tile MMA_STAGES-1 from here on
 
     // ---- the two rows of this thread and what they may see -----------------------------------
     const int r0 = (decode ? 0 : warp * 16) + (lane >> 2), r1 = r0 + 8;
@@ -176,13 +181,6 @@ __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
 #pragma unroll
     for (int d = 0; d < DTILES; d++) { o_acc[d][0] = o_acc[d][1] = o_acc[d][2] = o_acc[d][3] = 0.f; }
 
-    const int n_tiles = (w.kv_end - w.kv_begin + MMA_BK - 1) / MMA_BK;
-#pragma unroll
-    for (int s = 0; s < MMA_STAGES - 1; s++) {
-        if (s < n_tiles) loader.load(smem_base + s * STAGE_BYTES, smem_base + s * STAGE_BYTES + MMA_BK * HD * 2,
-                                     w.kv_begin + s * MMA_BK, status);
-        cp_async_commit();
-    }
     // keys of a tile this warp multiplies: all 64 (several query tokens) or its own 16 (decoding)
     const int key_base = decode ? warp * 16 : 0;
     const int NT = decode ? 2 : 8;   // 8-key score tiles per warp and key tile
@@ -376,19 +374,19 @@ PLLM_EXPORT int pllm_attention_mma(const void* q, const void* k_pool, const void
     const float scale_log2 = scale * 1.4426950408889634f;
     dim3 grid(max_work, nkv * gparts);
     if (hd == 128) {
-        const int smem = MMA_STAGES * 2 * MMA_BK * 128 * 2;
+        const int smem = MMA_STAGES * 2 * MMA_BK * 128 * 2 + MMA_ROWS * 128 * 2;
         cudaFuncSetAttribute(attention_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        attention_mma_kernel<128><<<grid, 128, smem, stream>>>(
-            (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work, n_work_ptr,
-            (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width, window, scale_log2,
-            heads_per_cta, status);
+        launch_chained(attention_mma_kernel<128>, grid, dim3(128), (size_t)smem, stream,
+                       (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
+                       n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
+                       window, scale_log2, heads_per_cta, status);
     } else {
-        const int smem = MMA_STAGES * 2 * MMA_BK * 64 * 2;
+        const int smem = MMA_STAGES * 2 * MMA_BK * 64 * 2 + MMA_ROWS * 64 * 2;
         cudaFuncSetAttribute(attention_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        attention_mma_kernel<64><<<grid, 128, smem, stream>>>(
-            (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work, n_work_ptr,
-            (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width, window, scale_log2,
-            heads_per_cta, status);
+        launch_chained(attention_mma_kernel<64>, grid, dim3(128), (size_t)smem, stream,
+                       (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
+                       n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
+                       window, scale_log2, heads_per_cta, status);
     }
     return launch_status();
 }

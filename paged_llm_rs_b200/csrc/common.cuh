@@ -96,6 +96,36 @@ static inline int launch_status() {
     return e == cudaSuccess ? PLLM_OK : (int)e;
 }
 
+// ---- programmatic dependent launch -------------------------------------------------------
+// A decode step is a chain of a few hundred short kernels, each waiting for the one
+// before it.  Launched with the programmatic-serialization attribute, a kernel's CTAs
+// may take their places on the SMs while the kernel before it is still running; they
+// call pdl_wait() before they touch anything an earlier kernel wrote (it returns
+// when every earlier kernel of the stream has finished and its writes are visible),
+// and pdl_launch_dependents() lets the kernel after them do the same.  What does not
+// depend on earlier kernels (reading weights) may come before the wait.
+// Without the attribute both calls do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+
+extern int pllm_pdl_enabled;  // defined in elementwise.cu; set through pllm_set_pdl
+
+template <typename... KArgs, typename... Args>
+static inline void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pllm_pdl_enabled ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 #define PLLM_DISPATCH_DTYPE(dtype, ...)                         \
     do {                                                        \
         if ((dtype) == PLLM_F32) { typedef float T; __VA_ARGS__; } \

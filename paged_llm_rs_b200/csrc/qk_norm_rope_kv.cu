@@ -28,6 +28,8 @@ __global__ void qk_norm_rope_kv_kernel(
     T* __restrict__ k_pool, T* __restrict__ v_pool,  // null: no cache write at all
     int n_tokens, int nh, int nkv, int hd, int page_size, int n_pages, int* status) {
     extern __shared__ float smem[];  // [warps][hd]
+    pdl_launch_dependents();
+    pdl_wait();
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = nh + 2 * nkv;
     const long long item = (long long)blockIdx.x * warps + warp;
@@ -97,9 +99,9 @@ PLLM_EXPORT int pllm_qk_norm_rope_kv(int dtype, const void* qkv, void* q_out, co
     const long long items = (long long)n_tokens * (nh + 2 * nkv);
     const int blocks = (int)((items + warps - 1) / warps);
     PLLM_DISPATCH_DTYPE(dtype, {
-        qk_norm_rope_kv_kernel<T><<<blocks, warps * 32, smem, stream>>>(
-            (const T*)qkv, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, rotary_dim, max_pos, positions, slots,
-            (T*)k_pool, (T*)v_pool, n_tokens, nh, nkv, hd, page_size, n_pages, status);
+        launch_chained(qk_norm_rope_kv_kernel<T>, dim3(blocks), dim3(warps * 32), smem, stream,
+                       (const T*)qkv, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, rotary_dim, max_pos, positions, slots,
+                       (T*)k_pool, (T*)v_pool, n_tokens, nh, nkv, hd, page_size, n_pages, status);
     });
     return launch_status();
 }

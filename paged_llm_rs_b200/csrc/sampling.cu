@@ -9,51 +9,102 @@
 // probability and needs no sort.  (Requests with top-k or top-p go through the
 // host sampler, which keeps the reference's order.)
 //
-// One CTA per row.  Sums are formed in a fixed order (each thread over its own
-// contiguous range, then a scan over threads), so a draw does not depend on
-// timing.
+// Two launches.  The first cuts every row into chunks of 4096 logits, one CTA
+// each, and writes per chunk (max, index of the first max, sum of exp((l - max)/T))
+// to scratch memory.  The second, one CTA per row, combines the chunks in their
+// order, finds the chunk the draw falls into and walks that chunk alone.  All
+// sums are formed in a fixed order, so a draw does not depend on timing.
 #include "common.cuh"
 
-#define SAMPLE_THREADS 1024
+#define SAMPLE_CHUNK 4096
+#define SAMPLE_THREADS 256
+#define SAMPLE_PER_THREAD (SAMPLE_CHUNK / SAMPLE_THREADS)
 
-__global__ void sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
-                              const float* __restrict__ temperature,  // [n]; <= 0: greedy
-                              const float* __restrict__ uniform,      // [n] in [0, 1)
-                              int* __restrict__ tokens) {
-    __shared__ float s_val[32];
-    __shared__ int s_idx[32];
-    __shared__ float s_scan[SAMPLE_THREADS];
+__device__ __forceinline__ void argmax_merge(float& v, int& i, float ov, int oi) {
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+}
+
+// scratch: [rows][chunks][4] floats = (max, index as int bits, sum, unused)
+__global__ void sample_partial_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
+                                      const float* __restrict__ temperature, float* __restrict__ scratch) {
+    __shared__ float s_v[SAMPLE_THREADS / 32];
+    __shared__ int s_i[SAMPLE_THREADS / 32];
+    __shared__ float s_sum[SAMPLE_THREADS / 32];
     __shared__ float s_max;
-    __shared__ int s_arg, s_owner;
-    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.y, chunk = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* l = logits + (size_t)row * row_stride;
-    const int per = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
-    const int c0 = min(vocab, tid * per), c1 = min(vocab, c0 + per);
-
-    // first maximum: larger value wins, equal values keep the smaller id
+    const int base = chunk * SAMPLE_CHUNK;
+    float vals[SAMPLE_PER_THREAD];
     float best = -CUDART_INF_F;
     int arg = 0x7fffffff;
-    for (int i = c0; i < c1; i++) {
-        const float v = l[i];
-        if (arg == 0x7fffffff || v > best) { best = v; arg = i; }
+#pragma unroll
+    for (int j = 0; j < SAMPLE_PER_THREAD; j++) {
+        const int i = base + j * SAMPLE_THREADS + tid;   // neighbouring threads read neighbouring logits
+        vals[j] = i < vocab ? l[i] : -CUDART_INF_F;
+        if (i < vocab && (arg == 0x7fffffff || vals[j] > best)) { best = vals[j]; arg = i; }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, arg, o);
-        if (ov > best || (ov == best && oi < arg)) { best = ov; arg = oi; }
-    }
-    if (lane == 0) { s_val[warp] = best; s_idx[warp] = arg; }
+    for (int o = 16; o > 0; o >>= 1)
+        argmax_merge(best, arg, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, arg, o));
+    if (lane == 0) { s_v[warp] = best; s_i[warp] = arg; }
     __syncthreads();
     if (warp == 0) {
-        best = s_val[lane]; arg = s_idx[lane];
+        best = lane < SAMPLE_THREADS / 32 ? s_v[lane] : -CUDART_INF_F;
+        arg = lane < SAMPLE_THREADS / 32 ? s_i[lane] : 0x7fffffff;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, arg, o);
-            if (ov > best || (ov == best && oi < arg)) { best = ov; arg = oi; }
+        for (int o = 16; o > 0; o >>= 1)
+            argmax_merge(best, arg, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, arg, o));
+        if (lane == 0) {
+            s_max = best;
+            float* out = scratch + ((size_t)row * gridDim.x + chunk) * 4;
+            out[0] = best;
+            out[1] = __int_as_float(arg);
         }
-        if (lane == 0) { s_max = best; s_arg = arg; s_owner = 0x7fffffff; }
+    }
+    __syncthreads();
+    const float temp = temperature[row];
+    if (!(temp > 0.f)) return;
+    const float inv = 1.0f / temp, top = s_max * inv;
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < SAMPLE_PER_THREAD; j++)
+        if (base + j * SAMPLE_THREADS + tid < vocab) sum += expf(vals[j] * inv - top);
+    sum = warp_sum(sum);
+    if (lane == 0) s_sum[warp] = sum;
+    __syncthreads();
+    if (tid == 0) {
+        float total = 0.f;
+        for (int k = 0; k < SAMPLE_THREADS / 32; k++) total += s_sum[k];
+        scratch[((size_t)row * gridDim.x + chunk) * 4 + 2] = total;
+    }
+}
+
+__global__ void sample_final_kernel(const float* __restrict__ logits, int vocab, long long row_stride, int chunks,
+                                    const float* __restrict__ temperature, const float* __restrict__ uniform,
+                                    const float* __restrict__ scratch, int* __restrict__ tokens) {
+    __shared__ float s_v[SAMPLE_THREADS / 32];
+    __shared__ int s_i[SAMPLE_THREADS / 32];
+    __shared__ float s_scan[SAMPLE_THREADS];
+    __shared__ float s_max, s_before, s_point;
+    __shared__ int s_arg, s_chunk, s_owner;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* part = scratch + (size_t)row * chunks * 4;
+    // the first maximum over the chunks
+    float best = -CUDART_INF_F;
+    int arg = 0x7fffffff;
+    for (int c = tid; c < chunks; c += SAMPLE_THREADS) argmax_merge(best, arg, part[c * 4], __float_as_int(part[c * 4 + 1]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        argmax_merge(best, arg, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, arg, o));
+    if (lane == 0) { s_v[warp] = best; s_i[warp] = arg; }
+    __syncthreads();
+    if (tid == 0) {
+        for (int k = 1; k < SAMPLE_THREADS / 32; k++) argmax_merge(best, arg, s_v[k], s_i[k]);
+        s_max = best; s_arg = arg;
     }
     __syncthreads();
     const float temp = temperature[row];
@@ -61,45 +112,56 @@ __global__ void sample_kernel(const float* __restrict__ logits, int vocab, long 
         if (tid == 0) tokens[row] = s_arg;
         return;
     }
-    const float inv = 1.0f / temp;
-    const float top = s_max * inv;
+    const float inv = 1.0f / temp, top = s_max * inv;
+    if (tid == 0) {
+        // chunks in their order: total, then the chunk whose span of the running sum holds the point
+        float total = 0.f;
+        for (int c = 0; c < chunks; c++) total += part[c * 4 + 2] * expf(part[c * 4] * inv - top);
+        const float point = uniform[row] * total;
+        float run = 0.f;
+        int pick = -1;
+        float before = 0.f;
+        for (int c = 0; c < chunks; c++) {
+            const float w = part[c * 4 + 2] * expf(part[c * 4] * inv - top);
+            if (run + w >= point && w > 0.f) { pick = c; before = run; break; }
+            run += w;
+        }
+        s_chunk = pick; s_before = before; s_point = point; s_owner = 0x7fffffff;
+    }
+    __syncthreads();
+    if (s_chunk < 0) {  // rounding left the point past every sum: the most likely token
+        if (tid == 0) tokens[row] = s_arg;
+        return;
+    }
+    const float* l = logits + (size_t)row * row_stride;
+    const int c0 = s_chunk * SAMPLE_CHUNK + tid * SAMPLE_PER_THREAD;   // ids upward: each thread a contiguous run
+    const int c1 = min(vocab, c0 + SAMPLE_PER_THREAD);
     float sum = 0.f;
     for (int i = c0; i < c1; i++) sum += expf(l[i] * inv - top);
-    // inclusive scan over threads, in thread order
     float x = sum;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
         const float y = __shfl_up_sync(0xffffffffu, x, o);
         if (lane >= o) x += y;
     }
-    if (lane == 31) s_val[warp] = x;
+    if (lane == 31) s_v[warp] = x;
     __syncthreads();
-    if (warp == 0) {
-        float w = s_val[lane];
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const float y = __shfl_up_sync(0xffffffffu, w, o);
-            if (lane >= o) w += y;
-        }
-        s_val[lane] = w;
-    }
-    __syncthreads();
-    const float incl = x + (warp > 0 ? s_val[warp - 1] : 0.f);
-    const float total = s_val[31];
+    float offset = s_before;
+    for (int k = 0; k < warp; k++) offset += s_v[k];
+    const float incl = x + offset;
     s_scan[tid] = incl;
     __syncthreads();
-    const float point = uniform[row] * total;
-    // the first thread whose inclusive sum reaches the point owns the draw
-    const float before = tid > 0 ? s_scan[tid - 1] : 0.f;
+    const float point = s_point;
     if (incl >= point && c1 > c0) atomicMin(&s_owner, tid);
     __syncthreads();
     const int owner = s_owner;
-    if (owner == 0x7fffffff) {  // rounding left the point past every sum: take the most likely token
-        if (tid == 0) tokens[row] = s_arg;
+    if (owner == 0x7fffffff) {
+        // the chunk's own sums fell short of what its partial promised: its last token
+        if (tid == 0) tokens[row] = min(vocab, (s_chunk + 1) * SAMPLE_CHUNK) - 1;
         return;
     }
     if (tid == owner) {
-        float run = before;
+        float run = tid > 0 ? s_scan[tid - 1] : s_before;
         int pick = c1 - 1;
         for (int i = c0; i < c1; i++) {
             run += expf(l[i] * inv - top);
@@ -109,10 +171,21 @@ __global__ void sample_kernel(const float* __restrict__ logits, int vocab, long 
     }
 }
 
+// Floats of scratch memory pllm_sample needs for n_rows rows of `vocab` logits.
+PLLM_EXPORT long long pllm_sample_scratch_floats(int n_rows, int vocab) {
+    const long long chunks = (vocab + SAMPLE_CHUNK - 1) / SAMPLE_CHUNK;
+    return (long long)n_rows * chunks * 4;
+}
+
 PLLM_EXPORT int pllm_sample(const float* logits, int n_rows, int vocab, long long row_stride,
-                            const float* temperature, const float* uniform, int* tokens, cudaStream_t stream) {
+                            const float* temperature, const float* uniform, int* tokens, float* scratch,
+                            cudaStream_t stream) {
     if (n_rows <= 0) return PLLM_OK;
     if (vocab <= 0) return PLLM_ERR_SIZE;
-    sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, vocab, row_stride, temperature, uniform, tokens);
+    const int chunks = (vocab + SAMPLE_CHUNK - 1) / SAMPLE_CHUNK;
+    launch_chained(sample_partial_kernel, dim3(chunks, n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, vocab,
+                   row_stride, temperature, scratch);
+    launch_chained(sample_final_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, vocab, row_stride,
+                   chunks, temperature, uniform, (const float*)scratch, tokens);
     return launch_status();
 }

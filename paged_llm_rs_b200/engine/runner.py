@@ -11,6 +11,7 @@ Generation, the scheduler and trace replay all go through it.
 
 from __future__ import annotations
 
+import gc
 import os
 from typing import List, Optional, Sequence
 
@@ -54,7 +55,7 @@ class _DecodeGraph:
         self.runner, self.B, self.W = runner, B, W
         pk = runner.packer
         self.caps = StepCaps(tokens=B, wanted=B, segments=B, table_width=W)
-        self.work_caps = [attention_plan.plan_limits(B, p.tile_tokens, pk.target_ctas) for p in pk.plans]
+        self.work_caps = [attention_plan.plan_limits(B, p.tile_tokens, pk.target_ctas, p.ctas_per_item) for p in pk.plans]
         host, self.layout, self.sizes = pk.pack([], runner._heads, self.caps, self.work_caps)
         self.pinned = torch.from_numpy(host.copy()).pin_memory()
         self.dev = self.pinned.to(runner.device)
@@ -71,8 +72,18 @@ class _DecodeGraph:
         torch.cuda.synchronize()
         before = ops.LAUNCHES
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph), torch.no_grad():
-            self._body()
+        # The collector must not run inside the capture: freeing an older engine's graphs
+        # there (they die in reference cycles, at a time of the collector's choosing) is a
+        # call the capture forbids, and the capture would be invalidated.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph), torch.no_grad():
+                self._body()
+        finally:
+            if collecting:
+                gc.enable()
         self.launches = ops.LAUNCHES - before
 
     def _body(self):

@@ -22,6 +22,7 @@ import numpy as np
 
 SPLIT_ALIGN = 64   # split boundaries fall on multiples of the kernels' key tiles (32 and 64)
 MIN_SPLIT_KEYS = 128
+MAX_SPLITS = 128   # the reduce kernel holds the weights of up to 256 splits in shared memory
 
 
 def plan_attention(segments: Sequence[Tuple[int, int, int]], tile_tokens: int, window: Optional[int],
@@ -47,8 +48,10 @@ def plan_attention(segments: Sequence[Tuple[int, int, int]], tile_tokens: int, w
 
     splits = np.ones(n_tiles, dtype=np.int64)
     if n_tiles * ctas_per_item < target_ctas:
-        want = -(-target_ctas // (n_tiles * ctas_per_item))
-        splits = np.clip(np.minimum(want, keys // MIN_SPLIT_KEYS), 1, None)
+        # as many splits as keep the launch within the target (one or two full waves of
+        # CTAs), rounded down so that the last wave is not a sliver
+        want = max(2, target_ctas // (n_tiles * ctas_per_item))
+        splits = np.clip(np.minimum(want, keys // MIN_SPLIT_KEYS), 1, MAX_SPLITS)
     if (splits == 1).all():
         work = np.stack([seg, q0, qn, p0, kv_begin, kv_end, np.full(n_tiles, -1), np.zeros(n_tiles, np.int64)], 1)
         return work.astype(np.int32), np.zeros((0, 4), np.int32), 0
@@ -74,12 +77,15 @@ def plan_attention(segments: Sequence[Tuple[int, int, int]], tile_tokens: int, w
             np.asarray(red_rows, dtype=np.int32).reshape(-1, 4), parts)
 
 
-def plan_limits(max_step_tokens: int, tile_tokens: int, target_ctas: int) -> Tuple[int, int, int]:
+def plan_limits(max_step_tokens: int, tile_tokens: int, target_ctas: int, ctas_per_item: int = 1) -> Tuple[int, int, int]:
     """Upper bounds (work items, reductions, partial rows) for any step of at most
-    ``max_step_tokens`` tokens, so that buffers can be sized once."""
-    # Unsplit: one item per tile, at most one tile per token.  Split: fewer than
-    # target_ctas tiles, each cut into at most ceil(target / tiles) parts.
-    max_work = max_step_tokens + 2 * target_ctas
+    ``max_step_tokens`` tokens, so that buffers and launch grids can be sized once.
+    Tight, because a captured step launches the bound and the idle CTAs cost time."""
+    # Unsplit: one item per tile, at most one tile per token.  Split: tiles * ctas_per_item
+    # is below the target and each tile is cut into max(2, target // (tiles * ctas_per_item))
+    # parts, which is at most 2 * target / ctas_per_item items in all.
+    split_items = -(-2 * target_ctas // max(1, ctas_per_item))
+    max_work = max(max_step_tokens, split_items)
     max_red = max_step_tokens
-    max_parts = 2 * target_ctas * tile_tokens
+    max_parts = split_items * tile_tokens
     return max_work, max_red, max_parts

@@ -9,6 +9,7 @@ device, a ``KernelError`` is raised.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -44,24 +45,32 @@ def lib():
                                        c_int, c_int, c_int, c_float, P, P],
             "pllm_attention_generic_tile_tokens": [c_int, c_int],
             "pllm_attention_reduce": [c_int, P, P, P, P, c_int, P, c_int, c_int, P],
-            "pllm_sample": [P, c_int, c_int, c_ll, P, P, P, P],
+            "pllm_sample": [P, c_int, c_int, c_ll, P, P, P, P, P],
+            "pllm_sample_scratch_floats": [c_int, c_int],
+            "pllm_skinny_gemm_supports": [c_int, c_int, c_int],
+            "pllm_skinny_gemm": [P, P, P, c_int, c_int, c_int, c_int, c_int, P],
             "pllm_attention_mma_supports": [c_int, c_int, c_int, c_int],
             "pllm_attention_mma_tile_tokens": [c_int, c_int],
             "pllm_attention_mma": [P, P, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                                    c_int, c_float, P, P],
         }
+        sig["pllm_set_pdl"] = [c_int]
         for name, args in sig.items():
             fn = getattr(L, name)
             fn.argtypes = args
             fn.restype = c_int
+        # PAGED_LLM_PDL=1 launches the kernels with programmatic dependent launch (a
+        # kernel's CTAs may take their places while the one before it still runs);
+        # off by default, where it measured slower.
+        L.pllm_set_pdl(1 if os.environ.get("PAGED_LLM_PDL", "0") == "1" else 0)
         _lib = L
     return _lib
 
 
-def _check(code: int, what: str) -> None:
+def _check(code: int, what: str, launches: int = 1) -> None:
     global LAUNCHES
     if code == 0:
-        LAUNCHES += 1
+        LAUNCHES += launches
         return
     if code < 0:
         raise KernelError(f"{what}: refused, {_ERRORS.get(code, code)}")
@@ -251,16 +260,70 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
     n, V = logits.shape
     if min(temperature.numel(), uniform.numel(), tokens.numel()) < n:
         raise KernelError("sample: per-row arguments shorter than the rows")
-    _check(lib().pllm_sample(_ptr(logits), n, V, logits.stride(0), _ptr(temperature), _ptr(uniform), _ptr(tokens),
-                             _stream()), "sample")
+    L = lib()
+    # per chunk of a row (max, first index of it, sum): scratch between the two launches
+    scratch = torch.empty(L.pllm_sample_scratch_floats(n, V), dtype=torch.float32, device=logits.device)
+    _check(L.pllm_sample(_ptr(logits), n, V, logits.stride(0), _ptr(temperature), _ptr(uniform), _ptr(tokens),
+                         _ptr(scratch), _stream()), "sample", launches=2)
     return tokens
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y = x W^T with W stored [out, in]: the library matrix product (cuBLAS through
-    torch), which is where the reference uses a library too
-    (crates/pagedllm/src/model/layers.rs:27-35).  float32 inputs run in true
-    float32: the engine switches TF32 off."""
+SKINNY_GEMM = True  # few rows in bfloat16 go to this library's weight-streaming kernel
+
+
+def skinny_gemm_takes(x: torch.Tensor, weight: torch.Tensor, k: Optional[int] = None) -> bool:
+    """Whether ``linear`` runs the weight-streaming kernel for this product."""
+    if not SKINNY_GEMM or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or x.dim() != 2:
+        return False
+    N, K = weight.shape
+    return bool(lib().pllm_skinny_gemm_supports(x.shape[0], N, K if k is None else k))
+
+
+SKINNY_MAX_N = 32768
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None, gated: bool = False,
+           out_dtype: Optional[torch.dtype] = None, fuse_gate: bool = False) -> torch.Tensor:
+    """y = x W^T with W stored [out, in].
+
+    Few rows (a decode step, up to 64) in bfloat16 run this library's
+    weight-streaming kernel.  With ``gated`` the input is [g | u] of twice W's
+    width and the product is taken of silu(g) * u, the gated feed-forward's
+    activation: by the activation kernel first, or with ``fuse_gate`` inside the
+    weight-streaming kernel.  Everything else is the library
+    matrix product (cuBLAS through torch), which is where the reference uses a
+    library too (crates/pagedllm/src/model/layers.rs:27-35).  float32 inputs run
+    in true float32: the engine switches TF32 off."""
     if not x.is_cuda:
         raise KernelError("linear: input is not on a CUDA device: there is no CPU path")
+    N, K = weight.shape
+    if x.shape[-1] != (2 * K if gated else K):
+        raise KernelError(f"linear: input width {x.shape[-1]} does not fit a weight of {tuple(weight.shape)}")
+    want = out_dtype or x.dtype
+    if gated and not fuse_gate:
+        # Measured on a B200 (batch 8, 3072 -> 1024): forming silu(g) * u inside the product
+        # repeats it in each of the 128 CTAs and costs 31 us against 3.4 + 6 us for a pass
+        # of its own followed by the plain product.
+        act = torch.empty((x.shape[0], K), dtype=x.dtype, device=x.device)
+        swiglu(x, act)
+        x, gated = act, False
+    # The widest products (the output head) stay with the library, which is faster there
+    # (measured 54 us against 66 us at 151936 x 1024, batch 8).
+    if skinny_gemm_takes(x, weight, K) and N <= SKINNY_MAX_N and want in (torch.bfloat16, torch.float32) \
+            and not (gated and want != torch.bfloat16):
+        _dev(x, weight, out)
+        M = x.shape[0]
+        if out is None:
+            out = torch.empty((M, N), dtype=want, device=x.device)
+        elif out.shape != (M, N) or out.dtype != want:
+            raise KernelError("linear: out does not fit")
+        _check(lib().pllm_skinny_gemm(_ptr(x), _ptr(weight), _ptr(out), M, N, K, 1 if gated else 0,
+                                      1 if want == torch.float32 else 0, _stream()), "skinny_gemm")
+        return out
+    if gated:
+        act = torch.empty((x.shape[0], K), dtype=x.dtype, device=x.device)
+        swiglu(x, act)
+        x = act
+    if want != x.dtype:
+        return torch.mm(x, weight.t(), out_dtype=want)
     return torch.matmul(x, weight.t(), out=out) if out is not None else torch.matmul(x, weight.t())

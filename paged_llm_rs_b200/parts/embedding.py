@@ -54,9 +54,7 @@ class LinearHead(Part):
             raise WeightError(f"no {self._name('weight')}, and the config does not tie the embeddings")
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if x.dtype == torch.float32:
-            return ops.linear(x, self.weight)
-        return torch.mm(x, self.weight.t(), out_dtype=torch.float32)
+        return ops.linear(x, self.weight, out_dtype=torch.float32)
 
 
 register_embedding("token_embedding", TokenEmbedding)

@@ -304,6 +304,43 @@ def test_sampling_kernel(vocab):
         assert lo - 1e-4 <= point <= cdf[toks[i]].item() + 1e-4, i
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("N,K", [(1024, 2048), (6144, 1024), (304, 384), (151936, 128), (48, 3072)])
+def test_skinny_gemm(M, N, K):
+    g = torch.Generator(device=DEV).manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    assert ops.skinny_gemm_takes(x, w)
+    ops.SKINNY_MAX_N = 1 << 20      # here also the widest shapes go through the kernel
+    want = x.float() @ w.float().T
+    torch.testing.assert_close(ops.linear(x, w).float(), want, atol=2e-2, rtol=2e-2)
+    y32 = ops.linear(x, w, out_dtype=torch.float32)
+    assert y32.dtype == torch.float32
+    torch.testing.assert_close(y32, want, atol=2e-3, rtol=2e-3)      # float accumulation, no bfloat16 rounding of the sum
+    # the gated form: silu(g) * u on the way in
+    gu = torch.randn(M, 2 * K, device=DEV, generator=g).bfloat16()
+    a = gu.float()[:, :K]
+    act = (a * torch.sigmoid(a) * gu.float()[:, K:]).bfloat16().float()
+    torch.testing.assert_close(ops.linear(gu, w, gated=True).float(), act @ w.float().T, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(ops.linear(gu, w, gated=True, fuse_gate=True).float(), act @ w.float().T, atol=3e-2, rtol=3e-2)
+    ops.SKINNY_MAX_N = 32768
+
+
+def test_linear_falls_back_to_the_library_for_other_shapes():
+    g = torch.Generator(device=DEV).manual_seed(0)
+    for M, N, K, dt in ((100, 256, 256, torch.bfloat16), (4, 250, 256, torch.bfloat16), (4, 256, 200, torch.bfloat16),
+                        (4, 256, 256, torch.float32)):
+        x = torch.randn(M, K, device=DEV, generator=g).to(dt)
+        w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).to(dt)
+        assert not ops.skinny_gemm_takes(x, w)
+        t = dict(atol=2e-2, rtol=2e-2) if dt == torch.bfloat16 else dict(atol=1e-4, rtol=1e-4)
+        torch.testing.assert_close(ops.linear(x, w).float(), x.float() @ w.float().T, **t)
+        gu = torch.randn(M, 2 * K, device=DEV, generator=g).to(dt)
+        a = gu.float()[:, :K]
+        act = (a * torch.sigmoid(a) * gu.float()[:, K:]).to(dt).float()
+        torch.testing.assert_close(ops.linear(gu, w, gated=True).float(), act @ w.float().T, **t)
+
+
 def test_sampling_kernel_follows_the_distribution():
     probs = torch.tensor([0.5, 0.3, 0.15, 0.05])
     n = 4000
