@@ -1,0 +1,377 @@
+// Decode attention over the paged cache in bfloat16, head sizes 64 and 128: one
+// query token per request against its whole context, bound by the bytes of the
+// keys and values.  The reference's decode kernel
+// (crates/pagedllm/src/kernels/paged_attention.cu:42-148) launches one block per
+// (row, query head), re-reads every key once per query head of a group and keeps
+// its scores in a buffer as long as the context; here one CTA serves all query
+// heads of a kv head from one copy of the keys, a long context is split over
+// CTAs, and the softmax runs online.
+//
+// Pages come in with the bulk-copy engine (cp.async.bulk, the untiled TMA): a
+// page's rows for one kv head are contiguous in the cache ([pages, kv_heads,
+// page_size, head_dim]), so one elected thread moves a whole page slab (up to 64
+// rows) with one instruction and an mbarrier counts the bytes.  Nobody computes
+// addresses per 16 bytes.  The cache stores each row's 16-byte chunks XOR-ed
+// with the row's offset in its page (see qk_norm_rope_kv.cu), which is the
+// layout ldmatrix wants in shared memory, so the slab is copied as it lies.
+//
+// A CTA has four consumer warps and one producer warp.  Tiles of 64 keys go round
+// a 3-stage ring; every consumer warp reads every tile in turn and multiplies its
+// own 16 keys of it (a parity wait tells two phases of a barrier apart and no
+// more, so no warp may run a whole turn of the ring ahead of another: taking
+// tiles in turn keeps them within it).  Each warp keeps a running (max, sum, output)
+// of its own over its tiles: q.k^T and p.v on
+// mma.sync.m16n8k16 with the group's heads as the (padded) 16 rows.  The four
+// partial results meet in shared memory at the end.  Every wait on an mbarrier
+// is bounded: a waiter that gives up raises a status bit, tells the others and
+// the CTA returns.
+//
+// It takes items of one query token whose key range starts on a multiple of 64
+// and has no window; other items are the mma kernel's (attention_mma.cu).
+#include "common.cuh"
+
+#define TD_BK 64
+#define TD_STAGES 3
+#define TD_CONSUMERS 4
+#define TD_SPIN_LIMIT (1 << 18)
+
+struct AttnWork { int seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slot, unused; };
+
+namespace {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Waits until the barrier's phase `parity` is over; gives up after a bounded number
+// of polls or when another thread has given up.  Returns false then.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (int spin = 0; spin < TD_SPIN_LIMIT; spin++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 1023) == 1023 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4_t(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+template <int HD> __device__ __forceinline__ uint32_t toff(int row, int chunk) {
+    return (uint32_t)(row * (HD * 2) + ((chunk ^ (row & 7)) << 4));
+}
+
+}  // namespace
+
+template <int HD>
+__global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_tma_kernel(
+    const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+    const int* __restrict__ block_tables, const AttnWork* __restrict__ work, const int* __restrict__ n_work_ptr,
+    bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+    int nh, int nkv, int page_size, int page_shift, int n_pages, int table_width, float scale_log2,
+    int heads_per_cta, int* status) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if ((int)blockIdx.x >= *n_work_ptr) return;
+    const AttnWork w = work[blockIdx.x];
+    if (w.q_count != 1) return;  // the mma kernel's item
+    if (w.kv_begin & (TD_BK - 1)) {  // slabs and the swizzle need the range to start on a tile boundary
+        if (threadIdx.x == 0) atomicOr(status, 32);
+        return;
+    }
+    const int group = nh / nkv;
+    const int gparts = (group + heads_per_cta - 1) / heads_per_cta;
+    const int kh = blockIdx.y / gparts;
+    const int head0 = kh * group + (blockIdx.y % gparts) * heads_per_cta;
+    const int n_heads = min(heads_per_cta, kh * group + group - head0);   // rows of the 16-row block
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int KSTEPS = HD / 16, DTILES = HD / 8, CH = HD / 8;
+    constexpr int TILE_BYTES = TD_BK * HD * 2;          // keys (or values) of one tile
+    constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    const uint32_t base = smem_u32(smem);
+    const uint32_t q_s = base + TD_STAGES * STAGE_BYTES;
+    const uint32_t bars = q_s + 16 * HD * 2;             // full[S], empty[S]
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TD_STAGES * STAGE_BYTES + 16 * HD * 2 + 16 * TD_STAGES);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TD_STAGES; s++) {
+            mbar_init(bars + 8 * s, 1);                      // full: the producer's arrive, plus the bytes
+            mbar_init(bars + 8 * (TD_STAGES + s), TD_CONSUMERS);   // empty: every consumer warp's release
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
+        asm volatile("fence.proxy.async.shared::cta;\n" ::);
+    }
+    // the group's query rows, zero beyond them
+    for (int idx = threadIdx.x; idx < 16 * CH; idx += blockDim.x) {
+        const int row = idx / CH, chunk = idx % CH;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < n_heads) v = *reinterpret_cast<const uint4*>(q + ((size_t)w.q_token0 * nh + head0 + row) * HD + chunk * 8);
+        *reinterpret_cast<uint4*>(smem + TD_STAGES * STAGE_BYTES + toff<HD>(row, chunk)) = v;
+    }
+    __syncthreads();
+
+    const int n_tiles = (w.kv_end - w.kv_begin + TD_BK - 1) / TD_BK;
+    const int slab_rows = page_size < TD_BK ? page_size : TD_BK;
+    const int slabs = TD_BK / slab_rows;
+    const uint32_t slab_bytes = (uint32_t)slab_rows * HD * 2;
+
+    if (warp == TD_CONSUMERS) {
+        // ---- producer: page slabs into the ring ---------------------------------------------
+        const int* table = block_tables + (size_t)w.seg * table_width;
+        for (int t = 0; t < n_tiles; t++) {
+            const int s = t % TD_STAGES;
+            if (t >= TD_STAGES && !mbar_wait(bars + 8 * (TD_STAGES + s), ((t / TD_STAGES) - 1) & 1, abort_flag)) break;
+            const int kv0 = w.kv_begin + t * TD_BK;
+            const uint32_t k_dst = base + s * STAGE_BYTES, v_dst = k_dst + TILE_BYTES;
+            // which slabs exist: a page of the table at or before the range's last key
+            uint32_t have = 0;
+            for (int i = 0; i < slabs; i++) {
+                const int j = kv0 + i * slab_rows;
+                const int b = j >> page_shift;
+                const int page = (j < w.kv_end && b < table_width) ? table[b] : -1;
+                if (page >= n_pages) { if (lane == 0) atomicOr(status, 8); }
+                else if (page >= 0) have |= 1u << i;
+            }
+            // slabs with no page behind them are zeroed by hand: nothing stale or unset is multiplied
+            for (int i = 0; i < slabs; i++) {
+                if (have & (1u << i)) continue;
+                for (int o = lane * 16; o < (int)slab_bytes; o += 32 * 16) {
+                    *reinterpret_cast<uint4*>(smem + s * STAGE_BYTES + i * slab_bytes + o) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(smem + s * STAGE_BYTES + TILE_BYTES + i * slab_bytes + o) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the zeros before the copies
+            __syncwarp();
+            if (lane == 0) {
+                mbar_expect_tx(bars + 8 * s, 2 * slab_bytes * __popc(have));
+                for (int i = 0; i < slabs; i++) {
+                    if (!(have & (1u << i))) continue;
+                    const int j = kv0 + i * slab_rows;
+                    const int page = table[j >> page_shift];
+                    const size_t src = (((size_t)page * nkv + kh) * page_size + (j & (page_size - 1))) * HD;
+                    bulk_copy(k_dst + i * slab_bytes, k_pool + src, slab_bytes, bars + 8 * s);
+                    bulk_copy(v_dst + i * slab_bytes, v_pool + src, slab_bytes, bars + 8 * s);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---- consumers ------------------------------------------------------------------------------
+    uint32_t qf[KSTEPS][4];
+    {
+        const int mat = lane >> 3;
+        const int row = (lane & 7) + (mat & 1) * 8;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++) ldsm4(qf[ks], q_s + toff<HD>(row, ks * 2 + (mat >> 1)));
+    }
+    const int pos = w.q_pos0;
+    const int hi = min(w.kv_end, pos + 1);        // keys [kv_begin, hi) are visible to every row
+    float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_run[2] = {0.f, 0.f};
+    float o_acc[DTILES][4];
+#pragma unroll
+    for (int d = 0; d < DTILES; d++) { o_acc[d][0] = o_acc[d][1] = o_acc[d][2] = o_acc[d][3] = 0.f; }
+    bool alive = true;
+
+    constexpr int KPW = TD_BK / TD_CONSUMERS;     // keys of every tile that one warp multiplies (16)
+    constexpr int NTW = KPW / 8;                  // 8-key score tiles of those
+    const int key_base = warp * KPW;
+    for (int t = 0; t < n_tiles && alive; t++) {
+        const int s = t % TD_STAGES;
+        if (!mbar_wait(bars + 8 * s, (t / TD_STAGES) & 1, abort_flag)) { alive = false; break; }
+        const int kv0 = w.kv_begin + t * TD_BK + key_base;
+        const uint32_t k_s = base + s * STAGE_BYTES, v_s = k_s + TILE_BYTES;
+        if (kv0 < hi) {   // some key of this warp's share is visible
+            float s_acc[NTW][4];
+#pragma unroll
+            for (int n = 0; n < NTW; n++) { s_acc[n][0] = s_acc[n][1] = s_acc[n][2] = s_acc[n][3] = 0.f; }
+            {
+                const int mat = lane >> 3;
+#pragma unroll
+                for (int np = 0; np < NTW / 2; np++) {
+                    const int key = key_base + np * 16 + (lane & 7) + (mat >> 1) * 8;
+#pragma unroll
+                    for (int ks = 0; ks < KSTEPS; ks++) {
+                        uint32_t kf[4];
+                        ldsm4(kf, k_s + toff<HD>(key, ks * 2 + (mat & 1)));
+                        mma(s_acc[np * 2], qf[ks], kf[0], kf[1]);
+                        mma(s_acc[np * 2 + 1], qf[ks], kf[2], kf[3]);
+                    }
+                }
+            }
+            float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
+            const bool whole = kv0 + KPW <= hi;     // every key of the share is visible
+#pragma unroll
+            for (int n = 0; n < NTW; n++) {
+                const int j = kv0 + n * 8 + (lane & 3) * 2;
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float v = (whole || j + (e & 1) < hi) ? s_acc[n][e] * scale_log2 : -CUDART_INF_F;
+                    s_acc[n][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            }
+            float corr[2], m_use[2];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+                const float m_new = fmaxf(m_run[i], mx[i]);
+                m_use[i] = m_new == -CUDART_INF_F ? 0.f : m_new;
+                corr[i] = exp2f(m_run[i] - m_use[i]);
+                m_run[i] = m_new;
+                l_run[i] *= corr[i];
+            }
+            uint32_t pf[NTW / 2][4];
+#pragma unroll
+            for (int n = 0; n < NTW; n++) {
+                const float p0 = exp2f(s_acc[n][0] - m_use[0]), p1 = exp2f(s_acc[n][1] - m_use[0]);
+                const float p2 = exp2f(s_acc[n][2] - m_use[1]), p3 = exp2f(s_acc[n][3] - m_use[1]);
+                l_run[0] += p0 + p1;
+                l_run[1] += p2 + p3;
+                pf[n >> 1][(n & 1) * 2] = pack2(p0, p1);
+                pf[n >> 1][(n & 1) * 2 + 1] = pack2(p2, p3);
+            }
+            // the running maximum seldom moves after the first tiles: rescale only when it did
+            if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
+#pragma unroll
+                for (int d = 0; d < DTILES; d++) {
+                    o_acc[d][0] *= corr[0]; o_acc[d][1] *= corr[0];
+                    o_acc[d][2] *= corr[1]; o_acc[d][3] *= corr[1];
+                }
+            }
+            {
+                const int mat = lane >> 3;
+#pragma unroll
+                for (int kk = 0; kk < NTW / 2; kk++) {
+                    const int key = key_base + kk * 16 + (lane & 7) + (mat & 1) * 8;
+#pragma unroll
+                    for (int dp = 0; dp < DTILES / 2; dp++) {
+                        uint32_t vf[4];
+                        ldsm4_t(vf, v_s + toff<HD>(key, dp * 2 + (mat >> 1)));
+                        mma(o_acc[dp * 2], pf[kk], vf[0], vf[1]);
+                        mma(o_acc[dp * 2 + 1], pf[kk], vf[2], vf[3]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + 8 * (TD_STAGES + s));   // this warp is done with the stage
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    }
+    // ---- the four warps' results meet (named barrier: the producer warp has left) ---------------
+    asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicOr(status, 16);
+        return;
+    }
+    float* o_s = reinterpret_cast<float*>(smem);          // [4][16][HD]; the ring is no longer read
+    float* ml_s = o_s + TD_CONSUMERS * 16 * HD;           // [4][16][2]
+#pragma unroll
+    for (int d = 0; d < DTILES; d++) {
+        const int c = d * 8 + (lane & 3) * 2;
+        float* a = o_s + ((size_t)(warp * 16 + (lane >> 2)) * HD + c);
+        a[0] = o_acc[d][0]; a[1] = o_acc[d][1];
+        a[8 * HD] = o_acc[d][2]; a[8 * HD + 1] = o_acc[d][3];
+    }
+    if ((lane & 3) == 0) {
+        ml_s[(warp * 16 + (lane >> 2)) * 2] = m_run[0]; ml_s[(warp * 16 + (lane >> 2)) * 2 + 1] = l_run[0];
+        ml_s[(warp * 16 + (lane >> 2) + 8) * 2] = m_run[1]; ml_s[(warp * 16 + (lane >> 2) + 8) * 2 + 1] = l_run[1];
+    }
+    asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
+    for (int idx = threadIdx.x; idx < n_heads * HD; idx += TD_CONSUMERS * 32) {
+        const int r = idx / HD, c = idx % HD;
+        float M = -CUDART_INF_F;
+#pragma unroll
+        for (int wi = 0; wi < TD_CONSUMERS; wi++) M = fmaxf(M, ml_s[(wi * 16 + r) * 2]);
+        float L = 0.f, o = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < TD_CONSUMERS; wi++) {
+            const float mw = ml_s[(wi * 16 + r) * 2];
+            const float f = mw == -CUDART_INF_F ? 0.f : exp2f(mw - M);
+            L += ml_s[(wi * 16 + r) * 2 + 1] * f;
+            o += o_s[(size_t)(wi * 16 + r) * HD + c] * f;
+        }
+        const int head = head0 + r;
+        if (w.part_slot < 0) {
+            out[((size_t)w.q_token0 * nh + head) * HD + c] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
+        } else {
+            const size_t pr = (size_t)w.part_slot * nh + head;
+            part_o[pr * HD + c] = o;
+            if (c == 0) { part_ml[pr * 2] = M * 0.6931471805599453f; part_ml[pr * 2 + 1] = L; }   // natural-log units
+        }
+    }
+}
+
+// Whether this kernel takes decode items of this shape and cache layout.
+PLLM_EXPORT int pllm_attention_decode_tma_supports(int dtype, int nh, int nkv, int hd, int page_size, int window) {
+    return dtype == PLLM_BF16 && (hd == 64 || hd == 128) && nkv > 0 && nh % nkv == 0 && window <= 0 && page_size >= 8 &&
+           (page_size & (page_size - 1)) == 0;
+}
+
+template <int HD>
+static int launch_tma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables, const int* work,
+                      const int* n_work_ptr, int max_work, void* out, float* part_o, float* part_ml, int nh, int nkv,
+                      int page_size, int n_pages, int table_width, float scale, int* status, cudaStream_t stream) {
+    const int group = nh / nkv;
+    const int heads_per_cta = group < 16 ? group : 16;
+    const int gparts = (group + heads_per_cta - 1) / heads_per_cta;
+    int page_shift = 0;
+    while ((1 << page_shift) < page_size) page_shift++;
+    const size_t smem = (size_t)TD_STAGES * 2 * TD_BK * HD * 2 + 16 * HD * 2 + 16 * TD_STAGES + 16;
+    cudaFuncSetAttribute(attention_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_chained(attention_decode_tma_kernel<HD>, dim3(max_work, nkv * gparts), dim3((TD_CONSUMERS + 1) * 32), smem, stream,
+                   (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
+                   n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
+                   scale * 1.4426950408889634f, heads_per_cta, status);
+    return launch_status();
+}
+
+PLLM_EXPORT int pllm_attention_decode_tma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables,
+                                          const int* work, const int* n_work_ptr, int max_work, void* out,
+                                          float* part_o, float* part_ml, int nh, int nkv, int hd, int page_size,
+                                          int n_pages, int table_width, float scale, int* status, cudaStream_t stream) {
+    if (max_work <= 0) return PLLM_OK;
+    if (!pllm_attention_decode_tma_supports(PLLM_BF16, nh, nkv, hd, page_size, 0)) return PLLM_ERR_SIZE;
+    if (hd == 128)
+        return launch_tma<128>(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv,
+                               page_size, n_pages, table_width, scale, status, stream);
+    return launch_tma<64>(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv,
+                          page_size, n_pages, table_width, scale, status, stream);
+}

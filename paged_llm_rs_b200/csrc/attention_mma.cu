@@ -73,7 +73,7 @@ struct TileLoader {
     static constexpr int RPP = 128 / CH;          // rows a pass of the CTA covers
     static constexpr int PASSES = MMA_BK / RPP;
     const bf16* k_pool; const bf16* v_pool; const int* table;
-    int table_width, page_size, page_shift, n_pages, nkv, kh, kv_end;
+    int table_width, page_size, page_shift, n_pages, nkv, kh, kv_end, swizzle_mask;  // mask 7: swizzled cache, 0: plain
 
     __device__ __forceinline__ void load(uint32_t k_s, uint32_t v_s, int kv0, int* status) const {
         const int chunk = threadIdx.x % CH, r0 = threadIdx.x / CH;
@@ -89,7 +89,8 @@ struct TileLoader {
                 int page = b < table_width ? table[b] : -1;
                 if (page >= n_pages) { atomicOr(status, 8); page = -1; }
                 valid = page >= 0;
-                base = (((size_t)(valid ? page : 0) * nkv + kh) * page_size + o) * HD + chunk * 8;
+                // a swizzled cache keeps logical chunk c of a row at c ^ (offset in page & 7)
+                base = (((size_t)(valid ? page : 0) * nkv + kh) * page_size + o) * HD + ((chunk ^ (o & swizzle_mask)) * 8);
             }
             const uint32_t off = tile_off<HD>(row, chunk);
             cp_async16(k_s + off, k_pool + base, valid);
@@ -104,7 +105,7 @@ __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
     const int* __restrict__ block_tables, const AttnWork* __restrict__ work, const int* __restrict__ n_work_ptr,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     int nh, int nkv, int page_size, int page_shift, int n_pages, int table_width, int window, float scale_log2,
-    int heads_per_cta, int* status) {
+    int heads_per_cta, int swizzle, int skip_decode, int* status) {
     pdl_launch_dependents();
     pdl_wait();
     if ((int)blockIdx.x >= *n_work_ptr) return;
@@ -126,7 +127,8 @@ __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
     const uint32_t smem_base = smem_u32(smem);
 
     TileLoader<HD> loader{k_pool, v_pool, block_tables + (size_t)w.seg * table_width, table_width, page_size, page_shift,
-                          n_pages, nkv, kh, w.kv_end};
+                          n_pages, nkv, kh, w.kv_end, swizzle ? 7 : 0};
+    if (skip_decode && w.q_count == 1) return;   // the bulk-copy decode kernel takes these items
 
     // ---- q rows into a buffer of their own; the first key tiles are requested at once --------
     const uint32_t q_s = smem_base + MMA_STAGES * STAGE_BYTES;
@@ -363,7 +365,8 @@ PLLM_EXPORT int pllm_attention_mma_tile_tokens(int nh, int nkv) {
 PLLM_EXPORT int pllm_attention_mma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables,
                                    const int* work, const int* n_work_ptr, int max_work, void* out, float* part_o,
                                    float* part_ml, int nh, int nkv, int hd, int page_size, int n_pages,
-                                   int table_width, int window, float scale, int* status, cudaStream_t stream) {
+                                   int table_width, int window, float scale, int swizzle, int skip_decode,
+                                   int* status, cudaStream_t stream) {
     if (max_work <= 0) return PLLM_OK;
     if (!pllm_attention_mma_supports(PLLM_BF16, nh, nkv, hd) || page_size <= 0) return PLLM_ERR_SIZE;
     const int group = nh / nkv;
@@ -379,14 +382,14 @@ PLLM_EXPORT int pllm_attention_mma(const void* q, const void* k_pool, const void
         launch_chained(attention_mma_kernel<128>, grid, dim3(128), (size_t)smem, stream,
                        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
                        n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
-                       window, scale_log2, heads_per_cta, status);
+                       window, scale_log2, heads_per_cta, swizzle, skip_decode, status);
     } else {
         const int smem = MMA_STAGES * 2 * MMA_BK * 64 * 2 + MMA_ROWS * 64 * 2;
         cudaFuncSetAttribute(attention_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         launch_chained(attention_mma_kernel<64>, grid, dim3(128), (size_t)smem, stream,
                        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
                        n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
-                       window, scale_log2, heads_per_cta, status);
+                       window, scale_log2, heads_per_cta, swizzle, skip_decode, status);
     }
     return launch_status();
 }

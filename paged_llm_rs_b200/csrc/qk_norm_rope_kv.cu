@@ -11,7 +11,10 @@
 // formed in double on the host (rope.rs:39-56).
 //
 // Cache layout of one layer: [pages, kv_heads, page_size, head_dim]; slot s of the
-// request's table means page s / page_size, offset s % page_size.
+// request's table means page s / page_size, offset s % page_size.  With `swizzle`
+// the 16-byte chunks of a row are stored at chunk index c ^ (offset & 7): the layout
+// the tensor-core attention kernels read from shared memory without bank conflicts,
+// so that a page can be copied there as it lies.
 #include "common.cuh"
 
 template <typename T>
@@ -26,7 +29,7 @@ __global__ void qk_norm_rope_kv_kernel(
     const int* __restrict__ positions,  // [n_tokens]
     const int* __restrict__ slots,      // [n_tokens]; < 0: do not write this token
     T* __restrict__ k_pool, T* __restrict__ v_pool,  // null: no cache write at all
-    int n_tokens, int nh, int nkv, int hd, int page_size, int n_pages, int* status) {
+    int n_tokens, int nh, int nkv, int hd, int page_size, int n_pages, int swizzle, int* status) {
     extern __shared__ float smem[];  // [warps][hd]
     pdl_launch_dependents();
     pdl_wait();
@@ -57,6 +60,8 @@ __global__ void qk_norm_rope_kv_kernel(
     __syncwarp();
 
     T* dst;
+    int xr = 0;  // what a cache row's 16-byte chunks are XOR-ed with (0: stored as they are)
+    constexpr int EPC = 16 / (int)sizeof(T);
     if (is_q) {
         dst = q_out + (size_t)t * nh * hd + (size_t)h * hd;
     } else {
@@ -66,7 +71,9 @@ __global__ void qk_norm_rope_kv_kernel(
         if (page >= n_pages) { if (lane == 0) atomicOr(status, 2); return; }
         const int kh = is_k ? h - nh : h - nh - nkv;
         dst = (is_k ? k_pool : v_pool) + (((size_t)page * nkv + kh) * page_size + off) * hd;
+        if (swizzle) xr = off & 7;
     }
+    auto at = [&](int e) { return (((e / EPC) ^ xr) * EPC) + (e % EPC); };
 
     if ((is_q || is_k) && cos_t) {
         int pos = positions[t];
@@ -76,12 +83,12 @@ __global__ void qk_norm_rope_kv_kernel(
         const float* s = sin_t + (size_t)pos * half;
         for (int i = lane; i < half; i += 32) {
             const float x1 = buf[i], x2 = buf[i + half];
-            dst[i] = from_f32<T>(x1 * c[i] - x2 * s[i]);
-            dst[i + half] = from_f32<T>(x2 * c[i] + x1 * s[i]);
+            dst[at(i)] = from_f32<T>(x1 * c[i] - x2 * s[i]);
+            dst[at(i + half)] = from_f32<T>(x2 * c[i] + x1 * s[i]);
         }
-        for (int e = rotary_dim + lane; e < hd; e += 32) dst[e] = from_f32<T>(buf[e]);
+        for (int e = rotary_dim + lane; e < hd; e += 32) dst[at(e)] = from_f32<T>(buf[e]);
     } else {
-        for (int e = lane; e < hd; e += 32) dst[e] = from_f32<T>(buf[e]);
+        for (int e = lane; e < hd; e += 32) dst[at(e)] = from_f32<T>(buf[e]);
     }
 }
 
@@ -89,8 +96,10 @@ PLLM_EXPORT int pllm_qk_norm_rope_kv(int dtype, const void* qkv, void* q_out, co
                                      const float* k_gain, float eps, const float* cos_t, const float* sin_t,
                                      int rotary_dim, int max_pos, const int* positions, const int* slots,
                                      void* k_pool, void* v_pool, int n_tokens, int nh, int nkv, int hd,
-                                     int page_size, int n_pages, int* status, cudaStream_t stream) {
+                                     int page_size, int n_pages, int swizzle, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return PLLM_OK;
+    // a swizzled row needs a whole number of 8-chunk groups
+    if (swizzle && (hd * (dtype == PLLM_F32 ? 4 : 2) / 16) % 8 != 0) return PLLM_ERR_SIZE;
     if (nh <= 0 || nkv < 0 || hd <= 0 || page_size <= 0) return PLLM_ERR_SIZE;
     if (cos_t && (rotary_dim <= 0 || rotary_dim > hd || (rotary_dim & 1))) return PLLM_ERR_SIZE;
     const int warps = 4;
@@ -101,7 +110,7 @@ PLLM_EXPORT int pllm_qk_norm_rope_kv(int dtype, const void* qkv, void* q_out, co
     PLLM_DISPATCH_DTYPE(dtype, {
         launch_chained(qk_norm_rope_kv_kernel<T>, dim3(blocks), dim3(warps * 32), smem, stream,
                        (const T*)qkv, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, rotary_dim, max_pos, positions, slots,
-                       (T*)k_pool, (T*)v_pool, n_tokens, nh, nkv, hd, page_size, n_pages, status);
+                       (T*)k_pool, (T*)v_pool, n_tokens, nh, nkv, hd, page_size, n_pages, swizzle, status);
     });
     return launch_status();
 }

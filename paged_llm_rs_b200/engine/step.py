@@ -175,7 +175,10 @@ class StepPacker:
             put(f"g{gi}.slots", slots); put(f"g{gi}.tables", tables)
             put(f"g{gi}.n_work", [len(work)]); put(f"g{gi}.n_red", [len(red)])
             put(f"g{gi}.work", work); put(f"g{gi}.red", red)
-        sizes = dict(tokens=T, wanted=n_want, segments=n_seg, tokens_cap=Tc, wanted_cap=nc, segments_cap=sc,
+        single = sum(1 for s in segs if s[1] == 1)
+        # a step packed to capacities holds single tokens only (a captured decode step)
+        kinds = 1 if (caps is not None or (segs and single == len(segs))) else (2 if single == 0 else 3)
+        sizes = dict(tokens=T, wanted=n_want, segments=n_seg, tokens_cap=Tc, wanted_cap=nc, segments_cap=sc, kinds=kinds,
                      groups=[dict(parts=p[4], max_work=p[5], max_red=p[6], table_width=p[7]) for p in group_parts],
                      host_segments=segs)
         return host, layout, sizes
@@ -199,7 +202,7 @@ class StepPacker:
                 slots=view(f"g{gi}.slots", T),
                 work=view(f"g{gi}.work").view(-1, 8), n_work=view(f"g{gi}.n_work"), max_work=gs["max_work"],
                 red=view(f"g{gi}.red").view(-1, 4), n_red=view(f"g{gi}.n_red"), max_red=gs["max_red"],
-                part_o=part_o, part_ml=part_ml))
+                part_o=part_o, part_ml=part_ml, kinds=sizes["kinds"]))
         state = StepState(n_tokens=T, tokens=view("tokens", T), positions=view("positions", T), groups=groups,
                           logit_rows=view("logit_rows", nw), n_wanted=nw,
                           segments=view("segments").view(-1, 4), host_segments=list(sizes["host_segments"]))

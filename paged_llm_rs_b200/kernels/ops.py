@@ -40,7 +40,7 @@ def lib():
             "pllm_rmsnorm": [c_int, P, P, P, P, P, P, c_int, c_int, c_float, P],
             "pllm_swiglu": [c_int, P, P, c_int, c_int, P],
             "pllm_qk_norm_rope_kv": [c_int, P, P, P, P, c_float, P, P, c_int, c_int, P, P, P, P,
-                                     c_int, c_int, c_int, c_int, c_int, c_int, P, P],
+                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
             "pllm_attention_generic": [c_int, P, P, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int,
                                        c_int, c_int, c_int, c_float, P, P],
             "pllm_attention_generic_tile_tokens": [c_int, c_int],
@@ -52,7 +52,10 @@ def lib():
             "pllm_attention_mma_supports": [c_int, c_int, c_int, c_int],
             "pllm_attention_mma_tile_tokens": [c_int, c_int],
             "pllm_attention_mma": [P, P, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
-                                   c_int, c_float, P, P],
+                                   c_int, c_float, c_int, c_int, P, P],
+            "pllm_attention_decode_tma_supports": [c_int, c_int, c_int, c_int, c_int, c_int],
+            "pllm_attention_decode_tma": [P, P, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          c_float, P, P],
         }
         sig["pllm_set_pdl"] = [c_int]
         for name, args in sig.items():
@@ -159,10 +162,12 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 
 def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, q_gain, k_gain, eps: float, cos, sin,
                     rotary_dim: int, positions: torch.Tensor, slots: torch.Tensor, k_pool, v_pool,
-                    num_heads: int, num_kv_heads: int, head_dim: int, status: torch.Tensor) -> torch.Tensor:
+                    num_heads: int, num_kv_heads: int, head_dim: int, status: torch.Tensor,
+                    swizzled: bool = False) -> torch.Tensor:
     """Per-head RMSNorm of q and k, rotation, q to q_out, k and v into the paged
     pools [pages, kv_heads, page_size, head_dim] at ``slots`` (a negative slot, or
-    k_pool None, writes nothing)."""
+    k_pool None, writes nothing).  ``swizzled``: the pools keep each row's 16-byte
+    chunks at chunk ^ (offset in page & 7), the layout of ``pool_is_swizzled``."""
     _dev(qkv, q_out, q_gain, k_gain, cos, sin, positions, slots, k_pool, v_pool, status)
     _f32(q_gain, "q_gain"); _f32(k_gain, "k_gain"); _f32(cos, "cos"); _f32(sin, "sin")
     _i32(positions, "positions"); _i32(slots, "slots")
@@ -191,7 +196,7 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, q_gain, k_gain, eps:
     _check(lib().pllm_qk_norm_rope_kv(_code(qkv), _ptr(qkv), _ptr(q_out), _ptr(q_gain), _ptr(k_gain), float(eps),
                                       _ptr(cos), _ptr(sin), rotary_dim, max_pos, _ptr(positions), _ptr(slots),
                                       _ptr(k_pool), _ptr(v_pool), T, num_heads, num_kv_heads, head_dim, page_size,
-                                      n_pages, _ptr(status), _stream()), "qk_norm_rope_kv")
+                                      n_pages, 1 if swizzled else 0, _ptr(status), _stream()), "qk_norm_rope_kv")
     return q_out
 
 
@@ -201,6 +206,33 @@ def attention_uses_tensor_cores(dtype: torch.dtype, num_heads: int, num_kv_heads
     if dtype != torch.bfloat16:
         return False
     return bool(lib().pllm_attention_mma_supports(_BF16, num_heads, num_kv_heads, head_dim))
+
+
+DECODE_TMA = True  # single decoded tokens use the bulk-copy kernel where it applies
+
+
+def pool_is_swizzled(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    """Whether the cache pools of such layers keep each row's 16-byte chunks at
+    chunk ^ (offset in page & 7).  True exactly where the tensor-core attention
+    kernels run: they read that layout from shared memory without bank conflicts,
+    and the decode kernel copies whole pages there as they lie."""
+    return attention_uses_tensor_cores(dtype, num_heads, num_kv_heads, head_dim)
+
+
+def swizzle_pool_(pool: torch.Tensor) -> torch.Tensor:
+    """Rearrange a plain pool [pages, kv_heads, page_size, head_dim] into the swizzled
+    layout in place (its own inverse); for tests and tools."""
+    pages, nkv, ps, hd = pool.shape
+    epc = 16 // pool.element_size()
+    ch = hd // epc
+    if ch % 8:
+        raise KernelError("swizzle_pool_: a row must hold a multiple of eight 16-byte chunks")
+    v = pool.view(pages, nkv, ps, ch, epc)
+    o = torch.arange(ps, device=pool.device)[:, None] & 7
+    c = torch.arange(ch, device=pool.device)[None, :]
+    idx = (c ^ o)[None, None, :, :, None].expand_as(v)
+    pool.copy_(torch.gather(v.clone(), 3, idx).view_as(pool))
+    return pool
 
 
 def attention_tile_tokens(num_heads: int, num_kv_heads: int, dtype: torch.dtype = torch.float32,
@@ -216,10 +248,13 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     work: torch.Tensor, n_work: torch.Tensor, max_work: int, out: torch.Tensor,
                     part_o: torch.Tensor, part_ml: torch.Tensor, red: torch.Tensor, n_red: torch.Tensor,
                     max_red: int, num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
-                    status: torch.Tensor) -> torch.Tensor:
+                    status: torch.Tensor, swizzled: bool = False, kinds: int = 3) -> torch.Tensor:
     """Attention of the step's tokens over the paged cache, then the reduction of
     split items.  ``work`` is int32 [>=max_work, 8], ``red`` int32 [>=max_red, 4];
-    n_work / n_red are int32 scalars on the device saying how many are live."""
+    n_work / n_red are int32 scalars on the device saying how many are live.
+    ``swizzled`` says how the pools are laid out (see ``pool_is_swizzled``);
+    ``kinds`` what the work items are: 1 single decoded tokens only, 2 portions of
+    several tokens only, 3 both, so that only the kernels with work are launched."""
     _dev(q, k_pool, v_pool, block_tables, work, n_work, out, part_o, part_ml, red, n_red, status)
     for t, n in ((block_tables, "block_tables"), (work, "work"), (n_work, "n_work"), (red, "red"), (n_red, "n_red")):
         _i32(t, n)
@@ -237,11 +272,24 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     n_pages, page_size = k_pool.shape[0], k_pool.shape[2]
     L = lib()
     if attention_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim):
-        _check(L.pllm_attention_mma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work), _ptr(n_work),
-                                    max_work, _ptr(out), _ptr(part_o), _ptr(part_ml), num_heads, num_kv_heads,
-                                    head_dim, page_size, n_pages, block_tables.shape[-1], int(window), float(scale),
-                                    _ptr(status), _stream()), "paged_attention (mma)")
+        # single decoded tokens go to the bulk-copy kernel where the cache layout allows it
+        tma = swizzled and bool(kinds & 1) and DECODE_TMA and bool(L.pllm_attention_decode_tma_supports(
+            _BF16, num_heads, num_kv_heads, head_dim, page_size, int(window)))
+        if tma:
+            _check(L.pllm_attention_decode_tma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
+                                               _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml),
+                                               num_heads, num_kv_heads, head_dim, page_size, n_pages,
+                                               block_tables.shape[-1], float(scale), _ptr(status), _stream()),
+                   "paged_attention (decode)")
+        if not tma or (kinds & 2):
+            _check(L.pllm_attention_mma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
+                                        _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml), num_heads,
+                                        num_kv_heads, head_dim, page_size, n_pages, block_tables.shape[-1], int(window),
+                                        float(scale), 1 if swizzled else 0, 1 if tma else 0, _ptr(status), _stream()),
+                   "paged_attention (mma)")
     else:
+        if swizzled:
+            raise KernelError("paged_attention: the generic kernel reads plain pools, not swizzled ones")
         _check(L.pllm_attention_generic(_code(q), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables),
                                         _ptr(work), _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml),
                                         num_heads, num_kv_heads, head_dim, page_size, n_pages,

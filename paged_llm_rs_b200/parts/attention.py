@@ -35,6 +35,7 @@ class GQAttention(Mixer):
         if self.nh % self.nkv:
             raise ValueError(f"{self.nh} heads do not group over {self.nkv} kv heads")
         self.w_qkv = self.w_o = self.q_gain = self.k_gain = None
+        self._need = None
 
     def tensors(self):
         H, qw, kw = self.hidden, self.nh * self.hd, self.nkv * self.hd
@@ -53,7 +54,10 @@ class GQAttention(Mixer):
             self.q_gain, self.k_gain = tensors[self._name("q_norm.weight")], tensors[self._name("k_norm.weight")]
 
     def cache_need(self):
-        return KVNeed("window" if self.window else "full", self.nkv, self.hd, self.window)
+        if self._need is None:
+            swizzled = self.rt.device.type == "cuda" and ops.pool_is_swizzled(self.rt.dtype, self.nh, self.nkv, self.hd)
+            self._need = KVNeed("window" if self.window else "full", self.nkv, self.hd, self.window, swizzled)
+        return self._need
 
     def forward(self, x, step, cache, writes_cache=True):
         k_pool, v_pool, gi = cache
@@ -63,13 +67,15 @@ class GQAttention(Mixer):
         q = torch.empty((T, self.nh * self.hd), dtype=x.dtype, device=x.device)
         rot = self.position.rotary() if self.position is not None else None
         cos, sin, rdim = rot if rot is not None else (None, None, 0)
+        swizzled = self.cache_need().swizzled
         ops.qk_norm_rope_kv(qkv, q, self.q_gain, self.k_gain, self.qk_norm_eps or 0.0, cos, sin, rdim,
                             step.positions, g.slots, k_pool if writes_cache else None,
-                            v_pool if writes_cache else None, self.nh, self.nkv, self.hd, self.rt.status)
+                            v_pool if writes_cache else None, self.nh, self.nkv, self.hd, self.rt.status,
+                            swizzled=swizzled)
         o = torch.empty_like(q)
         ops.paged_attention(q, k_pool, v_pool, g.block_tables, g.work, g.n_work, g.max_work, o, g.part_o, g.part_ml,
                             g.red, g.n_red, g.max_red, self.nh, self.nkv, self.hd, self.window or 0, self.scale,
-                            self.rt.status)
+                            self.rt.status, swizzled=swizzled, kinds=g.kinds)
         return ops.linear(o, self.w_o)
 
 

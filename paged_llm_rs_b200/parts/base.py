@@ -50,9 +50,12 @@ class KVNeed:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    # rows stored with their 16-byte chunks XOR-ed by the offset in the page (what the
+    # tensor-core attention kernels read); the mixer that reads the pool decides
+    swizzled: bool = False
 
     def group_key(self) -> tuple:
-        return (self.kind, self.window, self.num_kv_heads, self.head_dim)
+        return (self.kind, self.window, self.num_kv_heads, self.head_dim, self.swizzled)
 
 
 @dataclass(frozen=True)
@@ -81,6 +84,7 @@ class GroupStep:
     max_red: int
     part_o: torch.Tensor        # float32 scratch for split items
     part_ml: torch.Tensor
+    kinds: int = 3              # what the work items are: 1 single tokens only, 2 portions only, 3 both
 
 
 @dataclass

@@ -66,6 +66,22 @@ def test_greedy_tiny_a(tmp_path, dtype):
     assert eng2.generate(prompts, max_tokens=8) == outs or dtype == "bfloat16"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_tiny_d_tensor_core_kernels(tmp_path, dtype):
+    # head_dim 64: in bfloat16 the prompts run through the mma kernel, decoding through the
+    # bulk-copy kernel over the swizzled cache, and decode steps replay as CUDA graphs
+    from paged_llm_rs_b200 import Engine
+    cfg, seed = CONFIGS["D"]
+    model = write_model(tmp_path, "D")
+    prompts = prompts_for(cfg["vocab_size"], [90, 3, 130, 64], 21)
+    eng = Engine(model, dtype=dtype, block_size=16, blocks=64, chunk=48)
+    outs = eng.generate(prompts, max_tokens=24)
+    check_greedy(model, prompts, outs, 24, dtype)
+    plain = Engine(model, dtype=dtype, block_size=16, blocks=64, chunk=48)
+    plain.runner.use_graphs = False
+    assert plain.generate(prompts, max_tokens=24) == outs          # captured and plain launches agree
+
+
 def vocab_order_choice(logits64, temperature, u):
     """The engine's device draw: ids upward, the first id whose running sum reaches u * total."""
     p = torch.softmax(logits64 / temperature, -1)

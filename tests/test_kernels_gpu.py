@@ -156,7 +156,7 @@ def attention_ref(q, k, v, scale, window):
     return out
 
 
-def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, craft=None):
+def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, craft=None, kinds=3):
     """reqs: list of (context before the step, query tokens).  Builds a paged cache
     with shuffled pages, runs the kernel, returns (got, want) per request."""
     g = torch.Generator().manual_seed(seed)
@@ -201,9 +201,14 @@ def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, c
     part_o = torch.zeros(max(parts, 1), nh, hd, device=DEV)
     part_ml = torch.zeros(max(parts, 1), nh, 2, device=DEV)
     st = status()
-    ops.paged_attention(qd, dev(kp), dev(vp), dev(tables), workd, dev(torch.tensor([len(work)], dtype=torch.int32)),
+    # the tensor-core kernels read pools whose rows are stored swizzled (as the cache-write kernel stores them)
+    swz = ops.pool_is_swizzled(dtype, nh, nkv, hd)
+    kpd, vpd = dev(kp), dev(vp)
+    if swz:
+        ops.swizzle_pool_(kpd); ops.swizzle_pool_(vpd)
+    ops.paged_attention(qd, kpd, vpd, dev(tables), workd, dev(torch.tensor([len(work)], dtype=torch.int32)),
                         len(work), out, part_o, part_ml, redd, dev(torch.tensor([len(red)], dtype=torch.int32)),
-                        len(red), nh, nkv, hd, window or 0, scale, st)
+                        len(red), nh, nkv, hd, window or 0, scale, st, swizzled=swz, kinds=kinds)
     assert st.item() == 0
     res = []
     for (a, n, c), q, k, v in zip(segs, qs, ks, vs):
@@ -225,6 +230,43 @@ def test_paged_attention_mixed_batch(dtype, nh, nkv, hd, page, window):
         assert (n_red > 0) == (target > 1 and not (window and window < 128))
         for got, want in res:
             torch.testing.assert_close(got, want, **tol(dtype))
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page", [(16, 8, 128, 16), (8, 1, 64, 8), (32, 8, 128, 64), (40, 2, 64, 16),
+                                            (4, 4, 128, 128), (6, 3, 64, 32)])
+def test_decode_only_steps_take_the_bulk_copy_kernel(nh, nkv, hd, page):
+    # single decoded tokens: contexts that end on and off tile and page edges, one of a single key
+    reqs = [(0, 1), (63, 1), (64, 1), (127, 1), (128, 1), (700, 1), (1023, 1), (15, 1), (page * 3, 1), (331, 1)]
+    assert ops.lib().pllm_attention_decode_tma_supports(1, nh, nkv, hd, page, 0)
+    for target in (1, 10 ** 6):
+        res, n_red = run_attention(torch.bfloat16, reqs, nh, nkv, hd, page, None, target, kinds=1)
+        assert (n_red > 0) == (target > 1)
+        for got, want in res:
+            torch.testing.assert_close(got, want, **tol(torch.bfloat16))
+    # and beside portions of several tokens, where both kernels share one work list
+    res, _ = run_attention(torch.bfloat16, [(100, 1), (40, 9), (513, 1), (0, 70)], nh, nkv, hd, page, None, 10 ** 6, kinds=3)
+    for got, want in res:
+        torch.testing.assert_close(got, want, **tol(torch.bfloat16))
+
+
+def test_swizzled_cache_rows():
+    from paged_llm_rs_b200.parts.base import Runtime
+    g = torch.Generator(device=DEV).manual_seed(4)
+    T, nh, nkv, hd, page, pages = 40, 4, 2, 128, 16, 5
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV, generator=g).bfloat16()
+    pos = torch.arange(T, device=DEV, dtype=torch.int32)
+    slots = torch.randperm(pages * page, device=DEV, generator=g)[:T].to(torch.int32)
+    pools = {}
+    for swz in (False, True):
+        kp = torch.zeros(pages, nkv, page, hd, device=DEV, dtype=torch.bfloat16)
+        vp = torch.zeros_like(kp)
+        q = torch.empty(T, nh * hd, device=DEV, dtype=torch.bfloat16)
+        ops.qk_norm_rope_kv(qkv, q, None, None, 0.0, None, None, 0, pos, slots, kp, vp, nh, nkv, hd, status(), swizzled=swz)
+        pools[swz] = (kp, vp, q)
+    assert torch.equal(pools[False][2], pools[True][2])                       # q is never swizzled
+    assert not torch.equal(pools[False][0], pools[True][0])
+    assert torch.equal(ops.swizzle_pool_(pools[False][0].clone()), pools[True][0])
+    assert torch.equal(ops.swizzle_pool_(pools[False][1].clone()), pools[True][1])
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -91,7 +91,8 @@ def err(got, want):
     return float(np.abs(got - want).max() / max(1.0, np.abs(want).max()))
 
 
-@pytest.fixture(scope="module", params=[("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16")],
+@pytest.fixture(scope="module", params=[("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16"),
+                                        ("D", "float32"), ("D", "bfloat16")],
                 ids=lambda p: f"{p[0]}-{p[1]}")
 def run(request, tmp_path_factory):
     name, dtype = request.param

@@ -30,7 +30,17 @@ TINY_C = dict(
     rope_theta=50000.0,
 )
 
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
+# a fourth one at the sizes the tensor-core kernels take: head_dim 64, widths that are
+# multiples of 128, a window on its middle layer
+TINY_D = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_act="silu",
+    hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+    head_dim=64, rms_norm_eps=1e-6, vocab_size=512, max_position_embeddings=1024, tie_word_embeddings=True,
+    rope_theta=1000000.0, use_sliding_window=True, sliding_window=70,
+    layer_types=["full_attention", "sliding_attention", "full_attention"],
+)
+
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
 
 
 def write_model(folder, name, dtype=None):
