@@ -133,54 +133,61 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
         asm volatile("fence.proxy.async.shared::cta;\n" ::);
     }
-    // the group's query rows, zero beyond them
-    for (int idx = threadIdx.x; idx < 16 * CH; idx += blockDim.x) {
-        const int row = idx / CH, chunk = idx % CH;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < n_heads) v = *reinterpret_cast<const uint4*>(q + ((size_t)w.q_token0 * nh + head0 + row) * HD + chunk * 8);
-        *reinterpret_cast<uint4*>(smem + TD_STAGES * STAGE_BYTES + toff<HD>(row, chunk)) = v;
-    }
-    __syncthreads();
+    __syncthreads();   // the barriers are set up; the producer goes its own way from here
 
     const int n_tiles = (w.kv_end - w.kv_begin + TD_BK - 1) / TD_BK;
     const int slab_rows = page_size < TD_BK ? page_size : TD_BK;
-    const int slabs = TD_BK / slab_rows;
+    const int slabs = TD_BK / slab_rows;          // at most 8 (pages of at least 8 tokens)
     const uint32_t slab_bytes = (uint32_t)slab_rows * HD * 2;
 
     if (warp == TD_CONSUMERS) {
         // ---- producer: page slabs into the ring ---------------------------------------------
         const int* table = block_tables + (size_t)w.seg * table_width;
+        // the table entries of the key range, 32 at a time, one in each lane: no tile waits for a lookup
+        int win0 = w.kv_begin >> page_shift;
+        int tbl = (win0 + lane < table_width) ? table[win0 + lane] : -1;
         for (int t = 0; t < n_tiles; t++) {
             const int s = t % TD_STAGES;
-            if (t >= TD_STAGES && !mbar_wait(bars + 8 * (TD_STAGES + s), ((t / TD_STAGES) - 1) & 1, abort_flag)) break;
             const int kv0 = w.kv_begin + t * TD_BK;
+            if (((kv0 + TD_BK - 1) >> page_shift) >= win0 + 32) {
+                win0 = kv0 >> page_shift;
+                tbl = (win0 + lane < table_width) ? table[win0 + lane] : -1;
+            }
+            if (t >= TD_STAGES && !mbar_wait(bars + 8 * (TD_STAGES + s), ((t / TD_STAGES) - 1) & 1, abort_flag)) break;
             const uint32_t k_dst = base + s * STAGE_BYTES, v_dst = k_dst + TILE_BYTES;
             // which slabs exist: a page of the table at or before the range's last key
             uint32_t have = 0;
-            for (int i = 0; i < slabs; i++) {
+            int pg[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                pg[i] = -1;
+                if (i >= slabs) continue;
                 const int j = kv0 + i * slab_rows;
-                const int b = j >> page_shift;
-                const int page = (j < w.kv_end && b < table_width) ? table[b] : -1;
-                if (page >= n_pages) { if (lane == 0) atomicOr(status, 8); }
-                else if (page >= 0) have |= 1u << i;
+                int page = __shfl_sync(0xffffffffu, tbl, ((j >> page_shift) - win0) & 31);
+                if (j >= w.kv_end) page = -1;
+                if (page >= n_pages) { if (lane == 0) atomicOr(status, 8); page = -1; }
+                pg[i] = page;
+                if (page >= 0) have |= 1u << i;
             }
             // slabs with no page behind them are zeroed by hand: nothing stale or unset is multiplied
-            for (int i = 0; i < slabs; i++) {
-                if (have & (1u << i)) continue;
-                for (int o = lane * 16; o < (int)slab_bytes; o += 32 * 16) {
-                    *reinterpret_cast<uint4*>(smem + s * STAGE_BYTES + i * slab_bytes + o) = make_uint4(0, 0, 0, 0);
-                    *reinterpret_cast<uint4*>(smem + s * STAGE_BYTES + TILE_BYTES + i * slab_bytes + o) = make_uint4(0, 0, 0, 0);
+            if (have != (1u << slabs) - 1) {
+                for (int i = 0; i < slabs; i++) {
+                    if (have & (1u << i)) continue;
+                    for (int o = lane * 16; o < (int)slab_bytes; o += 32 * 16) {
+                        *reinterpret_cast<uint4*>(smem + s * STAGE_BYTES + i * slab_bytes + o) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(smem + s * STAGE_BYTES + TILE_BYTES + i * slab_bytes + o) = make_uint4(0, 0, 0, 0);
+                    }
                 }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the zeros before the copies
+                __syncwarp();
             }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the zeros before the copies
-            __syncwarp();
             if (lane == 0) {
                 mbar_expect_tx(bars + 8 * s, 2 * slab_bytes * __popc(have));
-                for (int i = 0; i < slabs; i++) {
-                    if (!(have & (1u << i))) continue;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    if (i >= slabs || pg[i] < 0) continue;
                     const int j = kv0 + i * slab_rows;
-                    const int page = table[j >> page_shift];
-                    const size_t src = (((size_t)page * nkv + kh) * page_size + (j & (page_size - 1))) * HD;
+                    const size_t src = (((size_t)pg[i] * nkv + kh) * page_size + (j & (page_size - 1))) * HD;
                     bulk_copy(k_dst + i * slab_bytes, k_pool + src, slab_bytes, bars + 8 * s);
                     bulk_copy(v_dst + i * slab_bytes, v_pool + src, slab_bytes, bars + 8 * s);
                 }
@@ -188,6 +195,15 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
         }
         return;
     }
+
+    // the group's query rows, zero beyond them (the first tiles are on their way meanwhile)
+    for (int idx = threadIdx.x; idx < 16 * CH; idx += TD_CONSUMERS * 32) {
+        const int row = idx / CH, chunk = idx % CH;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < n_heads) v = *reinterpret_cast<const uint4*>(q + ((size_t)w.q_token0 * nh + head0 + row) * HD + chunk * 8);
+        *reinterpret_cast<uint4*>(smem + TD_STAGES * STAGE_BYTES + toff<HD>(row, chunk)) = v;
+    }
+    asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
 
     // ---- consumers ------------------------------------------------------------------------------
     uint32_t qf[KSTEPS][4];

@@ -30,7 +30,7 @@ from .step import GroupPlanConfig, StepCaps, StepEntry, StepPacker
 
 DTYPES = {"float32": torch.float32, "f32": torch.float32, "fp32": torch.float32,
           "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
-SM_COUNT_TARGET = 4 * 148  # CTAs an attention launch should have before splits stop
+SM_COUNT_TARGET = 2 * 148  # CTAs an attention launch should have before splits stop: one full wave at two CTAs an SM
 
 
 def parse_dtype(name) -> torch.dtype:
