@@ -189,3 +189,63 @@ PLLM_EXPORT int pllm_sample(const float* logits, int n_rows, int vocab, long lon
                    chunks, temperature, uniform, (const float*)scratch, tokens);
     return launch_status();
 }
+
+// ---- sampling without any allocation (declared in sampling_static.h) ------------------------
+// This entry point has no counterpart in the reference.  It is for callers that may not
+// allocate device memory at all when they ask for a token: code running inside a
+// section where cudaMalloc is forbidden or would stall every stream (a real-time
+// control loop that holds the device, a plugin loaded into a host process that gave it
+// a fixed memory budget at start-up and hands it no allocator), or code that must not
+// touch torch's allocator from its thread.  pllm_sample needs scratch memory between
+// its two launches and leaves it to the caller to provide; here that scratch is a fixed
+// array in the library's own device image, so the call needs nothing but its inputs
+// and outputs.
+//
+// The price: the array is there on every GPU that loads this library, from load to exit,
+// whether or not this entry point is ever called (PLLM_STATIC_SAMPLE_FLOATS * 4 bytes =
+// 256 KiB), and it bounds what one call may ask for: at most PLLM_STATIC_SAMPLE_MAX_ROWS
+// rows of at most PLLM_STATIC_SAMPLE_MAX_VOCAB logits.  Larger requests are refused
+// with PLLM_ERR_LIMIT and nothing is launched.
+//
+// All calls share the one array.  Every entry a call reads it has written itself
+// earlier in the same call, so nothing has to be cleared between calls and what an
+// earlier call left behind is never seen; but two calls whose kernels overlap on the GPU
+// (different streams, no ordering between them) write the same entries and race.
+// Keep calls of this entry point ordered on one stream, or order them with events.
+//
+// The first call on a device looks up the array's device address
+// (cudaGetSymbolAddress, with that device current) and keeps it; make that first call
+// outside any stream capture.  Nothing here calls cudaMalloc, cudaFree or any
+// allocating routine of a library.
+#include "sampling_static.h"
+
+static __device__ __align__(256) float g_static_sample_scratch[PLLM_STATIC_SAMPLE_FLOATS];
+
+// In host code the array's name stands for a host-side shadow, not for device memory;
+// the device address is asked for once per device and kept here.
+#define PLLM_MAX_DEVICES 64
+static float* g_static_sample_ptr[PLLM_MAX_DEVICES];
+
+PLLM_EXPORT int pllm_sample_static(const float* logits, int n_rows, int vocab, long long row_stride,
+                                   const float* temperature, const float* uniform, int* tokens, cudaStream_t stream) {
+    if (n_rows <= 0) return PLLM_OK;
+    if (vocab <= 0) return PLLM_ERR_SIZE;
+    if (n_rows > PLLM_STATIC_SAMPLE_MAX_ROWS || vocab > PLLM_STATIC_SAMPLE_MAX_VOCAB) return PLLM_ERR_LIMIT;
+    const int chunks = (vocab + SAMPLE_CHUNK - 1) / SAMPLE_CHUNK;
+    if ((long long)n_rows * chunks * 4 > PLLM_STATIC_SAMPLE_FLOATS) return PLLM_ERR_LIMIT;
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= PLLM_MAX_DEVICES) return PLLM_ERR_LIMIT;
+    float* scratch = g_static_sample_ptr[device];
+    if (scratch == nullptr) {
+        e = cudaGetSymbolAddress((void**)&scratch, g_static_sample_scratch);
+        if (e != cudaSuccess) return (int)e;
+        g_static_sample_ptr[device] = scratch;   // the same value whoever stores it first
+    }
+    launch_chained(sample_partial_kernel, dim3(chunks, n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, vocab,
+                   row_stride, temperature, scratch);
+    launch_chained(sample_final_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, vocab, row_stride,
+                   chunks, temperature, uniform, (const float*)scratch, tokens);
+    return launch_status();
+}
