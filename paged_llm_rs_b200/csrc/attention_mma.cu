@@ -108,12 +108,12 @@ __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
     int heads_per_cta, int swizzle, int skip_decode, int* status) {
     pdl_launch_dependents();
     pdl_wait();
-    if ((int)blockIdx.x >= *n_work_ptr) return;
-    const AttnWork w = work[blockIdx.x];
+    if ((int)blockIdx.y >= *n_work_ptr) return;
+    const AttnWork w = work[blockIdx.y];
     const int group = nh / nkv;
     const int gparts = (group + heads_per_cta - 1) / heads_per_cta;
-    const int kh = blockIdx.y / gparts;
-    const int head0 = kh * group + (blockIdx.y % gparts) * heads_per_cta;
+    const int kh = blockIdx.x / gparts;
+    const int head0 = kh * group + (blockIdx.x % gparts) * heads_per_cta;
     const int n_heads = min(heads_per_cta, kh * group + group - head0);
     const int rows = w.q_count * n_heads;          // <= MMA_ROWS
     const bool decode = w.q_count == 1;            // one token: the warps split the keys, not the rows
@@ -207,17 +207,23 @@ __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
 #pragma unroll
         for (int n = 0; n < 8; n++) { s_acc[n][0] = s_acc[n][1] = s_acc[n][2] = s_acc[n][3] = 0.f; }
         {
+            // The asm statements run in the order written.  One k-step at a time over all
+            // key tiles: the fragments of a step are fetched together, and neighbouring
+            // mma write different accumulators, so none waits for the one before it.
             const int mat = lane >> 3;
+            const int np_count = NT / 2;
+            const int key0 = key_base + (lane & 7) + (mat >> 1) * 8;
 #pragma unroll
-            for (int np = 0; np < 4; np++) {          // pairs of 8-key tiles
-                if (np * 2 >= NT) break;
-                const int key = key_base + np * 16 + (lane & 7) + (mat >> 1) * 8;
+            for (int ks = 0; ks < KSTEPS; ks++) {
+                uint32_t kf[4][4];
 #pragma unroll
-                for (int ks = 0; ks < KSTEPS; ks++) {
-                    uint32_t kf[4];
-                    ldmatrix_x4(kf, k_s + tile_off<HD>(key, ks * 2 + (mat & 1)));
-                    mma_bf16(s_acc[np * 2], qf[ks], kf[0], kf[1]);
-                    mma_bf16(s_acc[np * 2 + 1], qf[ks], kf[2], kf[3]);
+                for (int np = 0; np < 4; np++)
+                    if (np < np_count) ldmatrix_x4(kf[np], k_s + tile_off<HD>(key0 + np * 16, ks * 2 + (mat & 1)));
+#pragma unroll
+                for (int np = 0; np < 4; np++) {
+                    if (np >= np_count) break;
+                    mma_bf16(s_acc[np * 2], qf[ks], kf[np][0], kf[np][1]);
+                    mma_bf16(s_acc[np * 2 + 1], qf[ks], kf[np][2], kf[np][3]);
                 }
             }
         }
@@ -269,12 +275,18 @@ __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
             for (int kk = 0; kk < 4; kk++) {          // 16 keys a step
                 if (kk * 2 >= NT) break;
                 const int key = key_base + kk * 16 + (lane & 7) + (mat & 1) * 8;
+                // four fragment loads in flight, then their eight mma
 #pragma unroll
-                for (int dp = 0; dp < DTILES / 2; dp++) {
-                    uint32_t vf[4];
-                    ldmatrix_x4_trans(vf, v_s + tile_off<HD>(key, dp * 2 + (mat >> 1)));
-                    mma_bf16(o_acc[dp * 2], pf[kk], vf[0], vf[1]);
-                    mma_bf16(o_acc[dp * 2 + 1], pf[kk], vf[2], vf[3]);
+                for (int d4 = 0; d4 < DTILES / 2; d4 += 4) {
+                    uint32_t vf[4][4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        ldmatrix_x4_trans(vf[i], v_s + tile_off<HD>(key, (d4 + i) * 2 + (mat >> 1)));
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        mma_bf16(o_acc[(d4 + i) * 2], pf[kk], vf[i][0], vf[i][1]);
+                        mma_bf16(o_acc[(d4 + i) * 2 + 1], pf[kk], vf[i][2], vf[i][3]);
+                    }
                 }
             }
         }
@@ -375,7 +387,7 @@ PLLM_EXPORT int pllm_attention_mma(const void* q, const void* k_pool, const void
     int page_shift = -1;
     if ((page_size & (page_size - 1)) == 0) { page_shift = 0; while ((1 << page_shift) < page_size) page_shift++; }
     const float scale_log2 = scale * 1.4426950408889634f;
-    dim3 grid(max_work, nkv * gparts);
+    dim3 grid(nkv * gparts, max_work);   // heads fastest: the items are dealt to the SMs in the order of the work list
     if (hd == 128) {
         const int smem = MMA_STAGES * 2 * MMA_BK * 128 * 2 + MMA_ROWS * 128 * 2;
         cudaFuncSetAttribute(attention_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

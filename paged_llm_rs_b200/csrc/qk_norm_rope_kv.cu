@@ -92,6 +92,86 @@ __global__ void qk_norm_rope_kv_kernel(
     }
 }
 
+// The same, sixteen bytes a lane: LPH lanes share a head (its LPH chunks of 16 bytes), so a
+// warp does 32 / LPH heads at once.  The rotation's partner of chunk c is chunk
+// c ^ (LPH / 2), one shuffle away; the swizzle is an XOR on the chunk index.  Takes head
+// sizes of 8, 16 or 32 chunks that are rotated over their whole width (or not at all).
+template <typename T, int LPH>
+__global__ void qk_norm_rope_kv_vec_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ q_gain,
+    const float* __restrict__ k_gain, float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+    int max_pos, const int* __restrict__ positions, const int* __restrict__ slots, T* __restrict__ k_pool,
+    T* __restrict__ v_pool, int n_tokens, int nh, int nkv, int page_size, int n_pages, int swizzle, int* status) {
+    constexpr int N = Vec16<T>::N, HD = LPH * N, HPW = 32 / LPH;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, sub = lane / LPH, c = lane % LPH;
+    const int heads = nh + 2 * nkv;
+    const long long total = (long long)n_tokens * heads;
+    long long item = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * HPW + sub;
+    const bool live = item < total;
+    if (!live) item = total - 1;               // idle lanes still take part in the shuffles
+    const int t = (int)(item / heads), h = (int)(item % heads);
+    const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
+    const float* gain = is_q ? q_gain : (is_k ? k_gain : nullptr);
+
+    Vec16<T> v;
+    v.load(qkv + (size_t)t * heads * HD + (size_t)h * HD + c * N);
+    float f[N];
+    v.unpack(f);
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < N; k++) ss += f[k] * f[k];
+#pragma unroll
+    for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (gain) {
+        const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+        for (int k = 0; k < N; k++) f[k] = f[k] * inv * gain[c * N + k];
+    }
+    if (cos_t) {
+        int pos = positions[t];
+        if (pos < 0 || pos >= max_pos) { if (c == 0 && live) atomicOr(status, 4); pos = 0; }
+        constexpr int HALF = HD / 2;
+        const bool upper = c >= LPH / 2;
+        const float* cs = cos_t + (size_t)pos * HALF + (upper ? c - LPH / 2 : c) * N;
+        const float* sn = sin_t + (size_t)pos * HALF + (upper ? c - LPH / 2 : c) * N;
+#pragma unroll
+        for (int k = 0; k < N; k++) {
+            const float other = __shfl_xor_sync(0xffffffffu, f[k], LPH / 2);
+            if (is_q || is_k) f[k] = upper ? f[k] * cs[k] + other * sn[k] : f[k] * cs[k] - other * sn[k];
+        }
+    }
+    if (!live) return;
+    T* dst;
+    int xr = 0;
+    if (is_q) {
+        dst = q_out + (size_t)t * nh * HD + (size_t)h * HD;
+    } else {
+        const int slot = slots[t];
+        if (!k_pool || slot < 0) return;
+        const int page = slot / page_size, off = slot % page_size;
+        if (page >= n_pages) { if (c == 0) atomicOr(status, 2); return; }
+        const int kh = is_k ? h - nh : h - nh - nkv;
+        dst = (is_k ? k_pool : v_pool) + (((size_t)page * nkv + kh) * page_size + off) * HD;
+        if (swizzle) xr = off & 7;
+    }
+    v.pack(f);
+    v.store(dst + (c ^ xr) * N);
+}
+
+template <typename T, int LPH>
+static void launch_qk_vec(const void* qkv, void* q_out, const float* q_gain, const float* k_gain, float eps,
+                          const float* cos_t, const float* sin_t, int max_pos, const int* positions, const int* slots,
+                          void* k_pool, void* v_pool, int n_tokens, int nh, int nkv, int page_size, int n_pages,
+                          int swizzle, int* status, cudaStream_t stream) {
+    const long long items = (long long)n_tokens * (nh + 2 * nkv);
+    const int per_block = 4 * (32 / LPH);
+    launch_chained(qk_norm_rope_kv_vec_kernel<T, LPH>, dim3((unsigned)((items + per_block - 1) / per_block)), dim3(128), 0,
+                   stream, (const T*)qkv, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, max_pos, positions, slots,
+                   (T*)k_pool, (T*)v_pool, n_tokens, nh, nkv, page_size, n_pages, swizzle, status);
+}
+
 PLLM_EXPORT int pllm_qk_norm_rope_kv(int dtype, const void* qkv, void* q_out, const float* q_gain,
                                      const float* k_gain, float eps, const float* cos_t, const float* sin_t,
                                      int rotary_dim, int max_pos, const int* positions, const int* slots,
@@ -102,6 +182,21 @@ PLLM_EXPORT int pllm_qk_norm_rope_kv(int dtype, const void* qkv, void* q_out, co
     if (swizzle && (hd * (dtype == PLLM_F32 ? 4 : 2) / 16) % 8 != 0) return PLLM_ERR_SIZE;
     if (nh <= 0 || nkv < 0 || hd <= 0 || page_size <= 0) return PLLM_ERR_SIZE;
     if (cos_t && (rotary_dim <= 0 || rotary_dim > hd || (rotary_dim & 1))) return PLLM_ERR_SIZE;
+    // sixteen bytes a lane where the head is 8, 16 or 32 chunks wide and rotated over its whole width
+    const int chunks = hd * (dtype == PLLM_F32 ? 4 : 2) / 16;
+    if ((dtype == PLLM_F32 || dtype == PLLM_BF16) && (chunks == 8 || chunks == 16 || chunks == 32) &&
+        hd * (dtype == PLLM_F32 ? 4 : 2) % 16 == 0 && (!cos_t || rotary_dim == hd)) {
+#define PLLM_QK_VEC(T, LPH)                                                                                        \
+    launch_qk_vec<T, LPH>(qkv, q_out, q_gain, k_gain, eps, cos_t, sin_t, max_pos, positions, slots, k_pool, v_pool, \
+                          n_tokens, nh, nkv, page_size, n_pages, swizzle, status, stream)
+        if (dtype == PLLM_F32) {
+            if (chunks == 8) PLLM_QK_VEC(float, 8); else if (chunks == 16) PLLM_QK_VEC(float, 16); else PLLM_QK_VEC(float, 32);
+        } else {
+            if (chunks == 8) PLLM_QK_VEC(bf16, 8); else if (chunks == 16) PLLM_QK_VEC(bf16, 16); else PLLM_QK_VEC(bf16, 32);
+        }
+#undef PLLM_QK_VEC
+        return launch_status();
+    }
     const int warps = 4;
     const size_t smem = (size_t)warps * hd * sizeof(float);
     if (smem > 48 * 1024) return PLLM_ERR_LIMIT;

@@ -33,7 +33,9 @@ def plan_attention(segments: Sequence[Tuple[int, int, int]], tile_tokens: int, w
     for si, (tok0, count, pos0) in enumerate(segments):
         if count <= 0:
             continue
-        starts = np.arange(0, count, tile_tokens, dtype=np.int64)
+        # last tile first: it has the longest key range, and the kernels deal items to the
+        # SMs in list order, so the long ones start early and the short ones fill the end
+        starts = np.arange(0, count, tile_tokens, dtype=np.int64)[::-1]
         seg_ids.append(np.full(len(starts), si, dtype=np.int64))
         q0s.append(tok0 + starts)
         qns.append(np.minimum(tile_tokens, count - starts))

@@ -93,7 +93,8 @@ def rope_ref(x, pos, theta, rotary_dim):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nh,nkv,hd,rot,page", [(6, 3, 48, 48, 8), (8, 1, 32, 16, 16), (16, 8, 128, 128, 64), (4, 4, 80, 80, 16)])
+@pytest.mark.parametrize("nh,nkv,hd,rot,page", [(6, 3, 48, 48, 8), (8, 1, 32, 16, 16), (16, 8, 128, 128, 64), (4, 4, 80, 80, 16),
+                                                (4, 2, 64, 64, 16), (3, 1, 256, 256, 8), (5, 5, 32, 32, 16)])
 def test_qk_norm_rope_kv_write(dtype, nh, nkv, hd, rot, page):
     from paged_llm_rs_b200.parts.base import Runtime
     from paged_llm_rs_b200.parts.position import RotaryEncoding
