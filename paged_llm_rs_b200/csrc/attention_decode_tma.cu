@@ -1,38 +1,43 @@
-// Decode attention over the paged cache in bfloat16, head sizes 64 and 128: one
-// query token per request against its whole context, bound by the bytes of the
-// keys and values.  The reference's decode kernel
+// Attention over the paged cache in bfloat16, head sizes 64 and 128, with the pages
+// brought in by the bulk-copy engine: the serving kernel for decoding (one query
+// token per request against its whole context, bound by the bytes of the keys and
+// values) and for portions of prompts.  The reference's decode kernel
 // (crates/pagedllm/src/kernels/paged_attention.cu:42-148) launches one block per
 // (row, query head), re-reads every key once per query head of a group and keeps
-// its scores in a buffer as long as the context; here one CTA serves all query
-// heads of a kv head from one copy of the keys, a long context is split over
-// CTAs, and the softmax runs online.
+// its scores in a buffer as long as the context; its prefill gathers the pages
+// into a rectangle first (crates/pagedllm/src/model/attention.rs:190-214).  Here
+// one CTA serves all query heads of a kv head from one copy of the keys, a long
+// context is split over CTAs, nothing is gathered, and the softmax runs online.
 //
-// Pages come in with the bulk-copy engine (cp.async.bulk, the untiled TMA): a
-// page's rows for one kv head are contiguous in the cache ([pages, kv_heads,
-// page_size, head_dim]), so one elected thread moves a whole page slab (up to 64
-// rows) with one instruction and an mbarrier counts the bytes.  Nobody computes
-// addresses per 16 bytes.  The cache stores each row's 16-byte chunks XOR-ed
-// with the row's offset in its page (see qk_norm_rope_kv.cu), which is the
-// layout ldmatrix wants in shared memory, so the slab is copied as it lies.
+// Pages come in with cp.async.bulk (the untiled TMA): a page's rows for one kv head
+// are contiguous in the cache ([pages, kv_heads, page_size, head_dim]), so one
+// elected thread moves a whole page slab (up to 64 rows) with one instruction and
+// an mbarrier counts the bytes.  Nobody computes addresses per 16 bytes.  The
+// cache stores each row's 16-byte chunks XOR-ed with the row's offset in its page
+// (see qk_norm_rope_kv.cu), which is the layout ldmatrix wants in shared memory,
+// so the slab is copied as it lies.
 //
 // A CTA has four consumer warps and one producer warp.  Tiles of 64 keys go round
-// a 3-stage ring; every consumer warp reads every tile in turn and multiplies its
-// own 16 keys of it (a parity wait tells two phases of a barrier apart and no
-// more, so no warp may run a whole turn of the ring ahead of another: taking
-// tiles in turn keeps them within it).  Each warp keeps a running (max, sum, output)
-// of its own over its tiles: q.k^T and p.v on
-// mma.sync.m16n8k16 with the group's heads as the (padded) 16 rows.  The four
-// partial results meet in shared memory at the end.  Every wait on an mbarrier
-// is bounded: a waiter that gives up raises a status bit, tells the others and
-// the CTA returns.
+// a 3-stage ring; every consumer warp reads every tile in turn (a parity wait tells
+// two phases of a barrier apart and no more, so no warp may run a whole turn of the
+// ring ahead of another: taking tiles in turn keeps them within it).  q.k^T and p.v
+// run on mma.sync.m16n8k16.  For one query token the group's heads are the (padded)
+// 16 rows of one block, each warp multiplies its own 16 keys of every tile and keeps
+// a running (max, sum, output) of its own; the four meet in shared memory at the
+// end.  For several query tokens the rows (token, head) are spread over the warps,
+// 16 each, and every warp multiplies whole tiles.  Every wait on an mbarrier is
+// bounded: a waiter that gives up raises a status bit, tells the others and the
+// CTA returns.
 //
-// It takes items of one query token whose key range starts on a multiple of 64
-// and has no window; other items are the mma kernel's (attention_mma.cu).
+// It takes items whose key range starts on a multiple of 64 and has no window, in
+// caches whose pages hold a power of two of at least 8 tokens; the rest is the
+// cp.async kernel's (attention_mma.cu).
 #include "common.cuh"
 
 #define TD_BK 64
 #define TD_STAGES 3
 #define TD_CONSUMERS 4
+#define TD_QROWS 64      // query rows (token, head) a CTA may hold
 #define TD_SPIN_LIMIT (1 << 18)
 
 struct AttnWork { int seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slot, unused; };
@@ -98,21 +103,23 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
     const int* __restrict__ block_tables, const AttnWork* __restrict__ work, const int* __restrict__ n_work_ptr,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     int nh, int nkv, int page_size, int page_shift, int n_pages, int table_width, float scale_log2,
-    int heads_per_cta, int* status) {
+    int heads_per_cta, int kinds_mask, int* status) {
     pdl_launch_dependents();
     pdl_wait();
-    if ((int)blockIdx.x >= *n_work_ptr) return;
-    const AttnWork w = work[blockIdx.x];
-    if (w.q_count != 1) return;  // the mma kernel's item
+    if ((int)blockIdx.y >= *n_work_ptr) return;
+    const AttnWork w = work[blockIdx.y];
+    if (!(kinds_mask & (w.q_count == 1 ? 1 : 2))) return;   // another kernel's item
     if (w.kv_begin & (TD_BK - 1)) {  // slabs and the swizzle need the range to start on a tile boundary
         if (threadIdx.x == 0) atomicOr(status, 32);
         return;
     }
     const int group = nh / nkv;
     const int gparts = (group + heads_per_cta - 1) / heads_per_cta;
-    const int kh = blockIdx.y / gparts;
-    const int head0 = kh * group + (blockIdx.y % gparts) * heads_per_cta;
-    const int n_heads = min(heads_per_cta, kh * group + group - head0);   // rows of the 16-row block
+    const int kh = blockIdx.x / gparts;
+    const int head0 = kh * group + (blockIdx.x % gparts) * heads_per_cta;
+    const int n_heads = min(heads_per_cta, kh * group + group - head0);
+    const int rows = w.q_count * n_heads;          // <= 64: (token, head) pairs
+    const bool decode = w.q_count == 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int KSTEPS = HD / 16, DTILES = HD / 8, CH = HD / 8;
     constexpr int TILE_BYTES = TD_BK * HD * 2;          // keys (or values) of one tile
@@ -121,8 +128,8 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
     extern __shared__ __align__(128) unsigned char smem[];
     const uint32_t base = smem_u32(smem);
     const uint32_t q_s = base + TD_STAGES * STAGE_BYTES;
-    const uint32_t bars = q_s + 16 * HD * 2;             // full[S], empty[S]
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TD_STAGES * STAGE_BYTES + 16 * HD * 2 + 16 * TD_STAGES);
+    const uint32_t bars = q_s + TD_QROWS * HD * 2;       // full[S], empty[S]
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TD_STAGES * STAGE_BYTES + TD_QROWS * HD * 2 + 16 * TD_STAGES);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TD_STAGES; s++) {
@@ -196,65 +203,83 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
         return;
     }
 
-    // the group's query rows, zero beyond them (the first tiles are on their way meanwhile)
-    for (int idx = threadIdx.x; idx < 16 * CH; idx += TD_CONSUMERS * 32) {
+    // the query rows, zero beyond them (the first tiles are on their way meanwhile)
+    for (int idx = threadIdx.x; idx < (decode ? 16 : TD_QROWS) * CH; idx += TD_CONSUMERS * 32) {
         const int row = idx / CH, chunk = idx % CH;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < n_heads) v = *reinterpret_cast<const uint4*>(q + ((size_t)w.q_token0 * nh + head0 + row) * HD + chunk * 8);
+        if (row < rows)
+            v = *reinterpret_cast<const uint4*>(q + ((size_t)(w.q_token0 + row / n_heads) * nh + head0 + row % n_heads) * HD + chunk * 8);
         *reinterpret_cast<uint4*>(smem + TD_STAGES * STAGE_BYTES + toff<HD>(row, chunk)) = v;
     }
     asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
 
     // ---- consumers ------------------------------------------------------------------------------
+    // One query token: the group's heads are ONE 16-row block and the warps share each tile's
+    // keys (16 each).  Several query tokens: the rows (token, head) are spread over the warps,
+    // 16 each, and every warp multiplies all 64 keys of a tile.
+    const int rbase = decode ? 0 : warp * 16;
     uint32_t qf[KSTEPS][4];
     {
         const int mat = lane >> 3;
-        const int row = (lane & 7) + (mat & 1) * 8;
+        const int row = rbase + (lane & 7) + (mat & 1) * 8;
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ks++) ldsm4(qf[ks], q_s + toff<HD>(row, ks * 2 + (mat >> 1)));
     }
-    const int pos = w.q_pos0;
-    const int hi = min(w.kv_end, pos + 1);        // keys [kv_begin, hi) are visible to every row
+    // the two rows of this thread and the keys they may see
+    const int r0 = rbase + (lane >> 2), r1 = r0 + 8;
+    int hi[2];
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const int r = i ? r1 : r0;
+        hi[i] = r < rows ? min(w.kv_end, w.q_pos0 + r / n_heads + 1) : 0;
+    }
+    int warp_hi = max(hi[0], hi[1]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) warp_hi = max(warp_hi, __shfl_xor_sync(0xffffffffu, warp_hi, o));
     float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_run[2] = {0.f, 0.f};
     float o_acc[DTILES][4];
 #pragma unroll
     for (int d = 0; d < DTILES; d++) { o_acc[d][0] = o_acc[d][1] = o_acc[d][2] = o_acc[d][3] = 0.f; }
     bool alive = true;
 
-    constexpr int KPW = TD_BK / TD_CONSUMERS;     // keys of every tile that one warp multiplies (16)
-    constexpr int NTW = KPW / 8;                  // 8-key score tiles of those
-    const int key_base = warp * KPW;
+    const int key_base = decode ? warp * (TD_BK / TD_CONSUMERS) : 0;
+    const int np_count = decode ? TD_BK / TD_CONSUMERS / 16 : TD_BK / 16;   // pairs of 8-key score tiles: 1 or 4
     for (int t = 0; t < n_tiles && alive; t++) {
         const int s = t % TD_STAGES;
         if (!mbar_wait(bars + 8 * s, (t / TD_STAGES) & 1, abort_flag)) { alive = false; break; }
         const int kv0 = w.kv_begin + t * TD_BK + key_base;
         const uint32_t k_s = base + s * STAGE_BYTES, v_s = k_s + TILE_BYTES;
-        if (kv0 < hi) {   // some key of this warp's share is visible
-            float s_acc[NTW][4];
+        if (kv0 < warp_hi) {   // some key of this warp's share is visible to one of its rows
+            float s_acc[8][4];
 #pragma unroll
-            for (int n = 0; n < NTW; n++) { s_acc[n][0] = s_acc[n][1] = s_acc[n][2] = s_acc[n][3] = 0.f; }
+            for (int n = 0; n < 8; n++) { s_acc[n][0] = s_acc[n][1] = s_acc[n][2] = s_acc[n][3] = 0.f; }
             {
+                // one k-step at a time over all key tiles: neighbouring mma write different accumulators
                 const int mat = lane >> 3;
+                const int key0 = key_base + (lane & 7) + (mat >> 1) * 8;
 #pragma unroll
-                for (int np = 0; np < NTW / 2; np++) {
-                    const int key = key_base + np * 16 + (lane & 7) + (mat >> 1) * 8;
+                for (int ks = 0; ks < KSTEPS; ks++) {
+                    uint32_t kf[4][4];
 #pragma unroll
-                    for (int ks = 0; ks < KSTEPS; ks++) {
-                        uint32_t kf[4];
-                        ldsm4(kf, k_s + toff<HD>(key, ks * 2 + (mat & 1)));
-                        mma(s_acc[np * 2], qf[ks], kf[0], kf[1]);
-                        mma(s_acc[np * 2 + 1], qf[ks], kf[2], kf[3]);
+                    for (int np = 0; np < 4; np++)
+                        if (np < np_count) ldsm4(kf[np], k_s + toff<HD>(key0 + np * 16, ks * 2 + (mat & 1)));
+#pragma unroll
+                    for (int np = 0; np < 4; np++) {
+                        if (np >= np_count) break;
+                        mma(s_acc[np * 2], qf[ks], kf[np][0], kf[np][1]);
+                        mma(s_acc[np * 2 + 1], qf[ks], kf[np][2], kf[np][3]);
                     }
                 }
             }
             float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
-            const bool whole = kv0 + KPW <= hi;     // every key of the share is visible
+            const bool whole = kv0 + np_count * 16 <= min(hi[0], hi[1]);   // every key visible to both rows
 #pragma unroll
-            for (int n = 0; n < NTW; n++) {
+            for (int n = 0; n < 8; n++) {
+                if (n >= np_count * 2) break;
                 const int j = kv0 + n * 8 + (lane & 3) * 2;
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
-                    const float v = (whole || j + (e & 1) < hi) ? s_acc[n][e] * scale_log2 : -CUDART_INF_F;
+                    const float v = (whole || j + (e & 1) < hi[e >> 1]) ? s_acc[n][e] * scale_log2 : -CUDART_INF_F;
                     s_acc[n][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }
@@ -270,9 +295,10 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
                 m_run[i] = m_new;
                 l_run[i] *= corr[i];
             }
-            uint32_t pf[NTW / 2][4];
+            uint32_t pf[4][4];
 #pragma unroll
-            for (int n = 0; n < NTW; n++) {
+            for (int n = 0; n < 8; n++) {
+                if (n >= np_count * 2) break;
                 const float p0 = exp2f(s_acc[n][0] - m_use[0]), p1 = exp2f(s_acc[n][1] - m_use[0]);
                 const float p2 = exp2f(s_acc[n][2] - m_use[1]), p3 = exp2f(s_acc[n][3] - m_use[1]);
                 l_run[0] += p0 + p1;
@@ -291,14 +317,20 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
             {
                 const int mat = lane >> 3;
 #pragma unroll
-                for (int kk = 0; kk < NTW / 2; kk++) {
+                for (int kk = 0; kk < 4; kk++) {
+                    if (kk >= np_count) break;
                     const int key = key_base + kk * 16 + (lane & 7) + (mat & 1) * 8;
+                    // four fragment loads in flight, then their eight mma
 #pragma unroll
-                    for (int dp = 0; dp < DTILES / 2; dp++) {
-                        uint32_t vf[4];
-                        ldsm4_t(vf, v_s + toff<HD>(key, dp * 2 + (mat >> 1)));
-                        mma(o_acc[dp * 2], pf[kk], vf[0], vf[1]);
-                        mma(o_acc[dp * 2 + 1], pf[kk], vf[2], vf[3]);
+                    for (int d4 = 0; d4 < DTILES / 2; d4 += 4) {
+                        uint32_t vf[4][4];
+#pragma unroll
+                        for (int i = 0; i < 4; i++) ldsm4_t(vf[i], v_s + toff<HD>(key, (d4 + i) * 2 + (mat >> 1)));
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            mma(o_acc[(d4 + i) * 2], pf[kk], vf[i][0], vf[i][1]);
+                            mma(o_acc[(d4 + i) * 2 + 1], pf[kk], vf[i][2], vf[i][3]);
+                        }
                     }
                 }
             }
@@ -310,6 +342,33 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
     for (int i = 0; i < 2; i++) {
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    }
+    if (!decode) {
+        // ---- several query tokens: every warp owns its rows' results ----------------------------
+        if (!alive || *abort_flag) {
+            if (lane == 0) atomicOr(status, 16);
+            return;
+        }
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int r = i ? r1 : r0;
+            if (r >= rows) continue;
+            const int tq = r / n_heads, head = head0 + r % n_heads;
+            if (w.part_slot < 0) {
+                const float inv = l_run[i] > 0.f ? 1.0f / l_run[i] : 0.f;
+                bf16* o = out + ((size_t)(w.q_token0 + tq) * nh + head) * HD + (lane & 3) * 2;
+#pragma unroll
+                for (int d = 0; d < DTILES; d++)
+                    *reinterpret_cast<uint32_t*>(o + d * 8) = pack2(o_acc[d][i * 2] * inv, o_acc[d][i * 2 + 1] * inv);
+            } else {
+                const size_t pr = (size_t)(w.part_slot + tq) * nh + head;
+                float* o = part_o + pr * HD + (lane & 3) * 2;
+#pragma unroll
+                for (int d = 0; d < DTILES; d++) { o[d * 8] = o_acc[d][i * 2]; o[d * 8 + 1] = o_acc[d][i * 2 + 1]; }
+                if ((lane & 3) == 0) { part_ml[pr * 2] = m_run[i] * 0.6931471805599453f; part_ml[pr * 2 + 1] = l_run[i]; }
+            }
+        }
+        return;
     }
     // ---- the four warps' results meet (named barrier: the producer warp has left) ---------------
     asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
@@ -331,7 +390,7 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
         ml_s[(warp * 16 + (lane >> 2) + 8) * 2] = m_run[1]; ml_s[(warp * 16 + (lane >> 2) + 8) * 2 + 1] = l_run[1];
     }
     asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
-    for (int idx = threadIdx.x; idx < n_heads * HD; idx += TD_CONSUMERS * 32) {
+    for (int idx = threadIdx.x; idx < rows * HD; idx += TD_CONSUMERS * 32) {
         const int r = idx / HD, c = idx % HD;
         float M = -CUDART_INF_F;
 #pragma unroll
@@ -364,30 +423,32 @@ PLLM_EXPORT int pllm_attention_decode_tma_supports(int dtype, int nh, int nkv, i
 template <int HD>
 static int launch_tma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables, const int* work,
                       const int* n_work_ptr, int max_work, void* out, float* part_o, float* part_ml, int nh, int nkv,
-                      int page_size, int n_pages, int table_width, float scale, int* status, cudaStream_t stream) {
+                      int page_size, int n_pages, int table_width, float scale, int kinds_mask, int* status,
+                      cudaStream_t stream) {
     const int group = nh / nkv;
     const int heads_per_cta = group < 16 ? group : 16;
     const int gparts = (group + heads_per_cta - 1) / heads_per_cta;
     int page_shift = 0;
     while ((1 << page_shift) < page_size) page_shift++;
-    const size_t smem = (size_t)TD_STAGES * 2 * TD_BK * HD * 2 + 16 * HD * 2 + 16 * TD_STAGES + 16;
+    const size_t smem = (size_t)TD_STAGES * 2 * TD_BK * HD * 2 + TD_QROWS * HD * 2 + 16 * TD_STAGES + 16;
     cudaFuncSetAttribute(attention_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_chained(attention_decode_tma_kernel<HD>, dim3(max_work, nkv * gparts), dim3((TD_CONSUMERS + 1) * 32), smem, stream,
+    launch_chained(attention_decode_tma_kernel<HD>, dim3(nkv * gparts, max_work), dim3((TD_CONSUMERS + 1) * 32), smem, stream,
                    (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
                    n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
-                   scale * 1.4426950408889634f, heads_per_cta, status);
+                   scale * 1.4426950408889634f, heads_per_cta, kinds_mask, status);
     return launch_status();
 }
 
 PLLM_EXPORT int pllm_attention_decode_tma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables,
                                           const int* work, const int* n_work_ptr, int max_work, void* out,
                                           float* part_o, float* part_ml, int nh, int nkv, int hd, int page_size,
-                                          int n_pages, int table_width, float scale, int* status, cudaStream_t stream) {
+                                          int n_pages, int table_width, float scale, int kinds_mask, int* status,
+                                          cudaStream_t stream) {
     if (max_work <= 0) return PLLM_OK;
     if (!pllm_attention_decode_tma_supports(PLLM_BF16, nh, nkv, hd, page_size, 0)) return PLLM_ERR_SIZE;
     if (hd == 128)
         return launch_tma<128>(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv,
-                               page_size, n_pages, table_width, scale, status, stream);
+                               page_size, n_pages, table_width, scale, kinds_mask, status, stream);
     return launch_tma<64>(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv,
-                          page_size, n_pages, table_width, scale, status, stream);
+                          page_size, n_pages, table_width, scale, kinds_mask, status, stream);
 }

@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
     const int* __restrict__ block_tables, const AttnWork* __restrict__ work, const int* __restrict__ n_work_ptr,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     int nh, int nkv, int page_size, int page_shift, int n_pages, int table_width, int window, float scale_log2,
-    int heads_per_cta, int swizzle, int skip_decode, int* status) {
+    int heads_per_cta, int swizzle, int kinds_mask, int* status) {
     pdl_launch_dependents();
     pdl_wait();
     if ((int)blockIdx.y >= *n_work_ptr) return;
@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
 
     TileLoader<HD> loader{k_pool, v_pool, block_tables + (size_t)w.seg * table_width, table_width, page_size, page_shift,
                           n_pages, nkv, kh, w.kv_end, swizzle ? 7 : 0};
-    if (skip_decode && w.q_count == 1) return;   // the bulk-copy decode kernel takes these items
+    if (!(kinds_mask & (w.q_count == 1 ? 1 : 2))) return;   // the bulk-copy kernel takes these items
 
     // ---- q rows into a buffer of their own; the first key tiles are requested at once --------
     const uint32_t q_s = smem_base + MMA_STAGES * STAGE_BYTES;
@@ -377,7 +377,7 @@ PLLM_EXPORT int pllm_attention_mma_tile_tokens(int nh, int nkv) {
 PLLM_EXPORT int pllm_attention_mma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables,
                                    const int* work, const int* n_work_ptr, int max_work, void* out, float* part_o,
                                    float* part_ml, int nh, int nkv, int hd, int page_size, int n_pages,
-                                   int table_width, int window, float scale, int swizzle, int skip_decode,
+                                   int table_width, int window, float scale, int swizzle, int kinds_mask,
                                    int* status, cudaStream_t stream) {
     if (max_work <= 0) return PLLM_OK;
     if (!pllm_attention_mma_supports(PLLM_BF16, nh, nkv, hd) || page_size <= 0) return PLLM_ERR_SIZE;
@@ -394,14 +394,14 @@ PLLM_EXPORT int pllm_attention_mma(const void* q, const void* k_pool, const void
         launch_chained(attention_mma_kernel<128>, grid, dim3(128), (size_t)smem, stream,
                        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
                        n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
-                       window, scale_log2, heads_per_cta, swizzle, skip_decode, status);
+                       window, scale_log2, heads_per_cta, swizzle, kinds_mask, status);
     } else {
         const int smem = MMA_STAGES * 2 * MMA_BK * 64 * 2 + MMA_ROWS * 64 * 2;
         cudaFuncSetAttribute(attention_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         launch_chained(attention_mma_kernel<64>, grid, dim3(128), (size_t)smem, stream,
                        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
                        n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
-                       window, scale_log2, heads_per_cta, swizzle, skip_decode, status);
+                       window, scale_log2, heads_per_cta, swizzle, kinds_mask, status);
     }
     return launch_status();
 }

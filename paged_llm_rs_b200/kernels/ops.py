@@ -55,7 +55,7 @@ def lib():
                                    c_int, c_float, c_int, c_int, P, P],
             "pllm_attention_decode_tma_supports": [c_int, c_int, c_int, c_int, c_int, c_int],
             "pllm_attention_decode_tma": [P, P, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
-                                          c_float, P, P],
+                                          c_float, c_int, P, P],
         }
         sig["pllm_set_pdl"] = [c_int]
         for name, args in sig.items():
@@ -208,7 +208,7 @@ def attention_uses_tensor_cores(dtype: torch.dtype, num_heads: int, num_kv_heads
     return bool(lib().pllm_attention_mma_supports(_BF16, num_heads, num_kv_heads, head_dim))
 
 
-DECODE_TMA = True  # single decoded tokens use the bulk-copy kernel where it applies
+TMA_KINDS = int(os.environ.get("PAGED_LLM_TMA_KINDS", "3"))  # which items the bulk-copy attention kernel takes where it applies: 1 single tokens, 2 portions, 3 both
 
 
 def pool_is_swizzled(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
@@ -272,20 +272,24 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     n_pages, page_size = k_pool.shape[0], k_pool.shape[2]
     L = lib()
     if attention_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim):
-        # single decoded tokens go to the bulk-copy kernel where the cache layout allows it
-        tma = swizzled and bool(kinds & 1) and DECODE_TMA and bool(L.pllm_attention_decode_tma_supports(
-            _BF16, num_heads, num_kv_heads, head_dim, page_size, int(window)))
-        if tma:
+        # The bulk-copy kernel where the cache layout allows it (swizzled rows, pages of a power
+        # of two tokens, no window); TMA_KINDS says which items it takes there: 1 single decoded
+        # tokens, 2 portions of several tokens, 3 both.  The cp.async kernel takes the rest.
+        tma_ok = swizzled and bool(L.pllm_attention_decode_tma_supports(_BF16, num_heads, num_kv_heads, head_dim,
+                                                                        page_size, int(window)))
+        take = (kinds & TMA_KINDS) if tma_ok else 0
+        rest = kinds & ~take
+        if take:
             _check(L.pllm_attention_decode_tma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
                                                _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml),
                                                num_heads, num_kv_heads, head_dim, page_size, n_pages,
-                                               block_tables.shape[-1], float(scale), _ptr(status), _stream()),
-                   "paged_attention (decode)")
-        if not tma or (kinds & 2):
+                                               block_tables.shape[-1], float(scale), take, _ptr(status), _stream()),
+                   "paged_attention (bulk copy)")
+        if rest:
             _check(L.pllm_attention_mma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
                                         _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml), num_heads,
                                         num_kv_heads, head_dim, page_size, n_pages, block_tables.shape[-1], int(window),
-                                        float(scale), 1 if swizzled else 0, 1 if tma else 0, _ptr(status), _stream()),
+                                        float(scale), 1 if swizzled else 0, rest, _ptr(status), _stream()),
                    "paged_attention (mma)")
     else:
         if swizzled:
