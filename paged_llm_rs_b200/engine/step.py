@@ -175,9 +175,15 @@ class StepPacker:
             put(f"g{gi}.slots", slots); put(f"g{gi}.tables", tables)
             put(f"g{gi}.n_work", [len(work)]); put(f"g{gi}.n_red", [len(red)])
             put(f"g{gi}.work", work); put(f"g{gi}.red", red)
-        single = sum(1 for s in segs if s[1] == 1)
-        # a step packed to capacities holds single tokens only (a captured decode step)
-        kinds = 1 if (caps is not None or (segs and single == len(segs))) else (2 if single == 0 else 3)
+        # What the work items are: bit 0 items of one query token (decoded tokens, but also the
+        # last tile of a portion of 33 tokens), bit 1 items of several.  Read off the items, not
+        # the segments.  A step packed to capacities is a captured decode step: single tokens only.
+        kinds = 0
+        for p in group_parts:
+            counts = p[2][:, 2] if len(p[2]) else np.zeros(0, np.int32)
+            kinds |= (1 if (counts == 1).any() else 0) | (2 if (counts > 1).any() else 0)
+        if caps is not None:
+            kinds = 1
         sizes = dict(tokens=T, wanted=n_want, segments=n_seg, tokens_cap=Tc, wanted_cap=nc, segments_cap=sc, kinds=kinds,
                      groups=[dict(parts=p[4], max_work=p[5], max_red=p[6], table_width=p[7]) for p in group_parts],
                      host_segments=segs)
