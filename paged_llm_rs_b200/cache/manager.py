@@ -55,6 +55,17 @@ class BlockTable:
     def live_blocks(self) -> List[int]:
         return [b for b in self.blocks if b >= 0]
 
+    def array(self):
+        """The table as an int32 numpy array, rebuilt only when pages were added or
+        given back since the last call (a page is added every page_size tokens, and
+        the step packer asks every step)."""
+        sig = (len(self.blocks), self.first_live)
+        if getattr(self, "_arr_sig", None) != sig:
+            import numpy as np
+            self._arr = np.asarray(self.blocks, dtype=np.int32)
+            self._arr_sig = sig
+        return self._arr
+
 
 @dataclass
 class CacheGroup:

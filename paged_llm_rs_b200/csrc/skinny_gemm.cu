@@ -152,6 +152,14 @@ __global__ void __launch_bounds__(512) skinny_gemm_kernel(const bf16* __restrict
     }
 }
 
+// For tuning runs: a number of warps a CTA to use instead of the heuristic's (0: the heuristic).
+static int g_skinny_warps_override = 0;
+PLLM_EXPORT int pllm_skinny_gemm_set_warps(int warps) {
+    const int was = g_skinny_warps_override;
+    g_skinny_warps_override = warps;
+    return was;
+}
+
 // Whether this kernel takes the product; the library takes the rest.
 PLLM_EXPORT int pllm_skinny_gemm_supports(int M, int N, int K) {
     return M >= 1 && M <= 64 && N % 16 == 0 && K % 128 == 0 && N >= 16 && K >= 128;
@@ -187,8 +195,14 @@ PLLM_EXPORT int pllm_skinny_gemm(const void* x, const void* w, void* y, int M, i
     // K is split over the warps of a CTA in slices of at least 128.
     const int nt = (N / 16 >= 2 * 148) ? 2 : 1;
     const int ctas = N / (8 * nt);
+    // A warp's loads of 128 values of k are all issued before the first is used, so a slice
+    // of 128 costs one trip to memory: as many warps as give each such a slice (at most 16,
+    // and K must divide evenly into slices that are multiples of 32), unless the launch
+    // would then exceed what the SMs hold at once several times over.
     int warps = 1;
-    while (warps < 16 && K % (warps * 2 * 128) == 0 && ctas * warps < 148 * 12) warps *= 2;
+    for (int wv = 2; wv <= 16; wv++)
+        if (K % (wv * 32) == 0 && K / wv >= 128 && (long long)ctas * wv <= 148LL * 64) warps = wv;
+    if (g_skinny_warps_override > 0 && K % (g_skinny_warps_override * 32) == 0) warps = g_skinny_warps_override;
     if (out_f32) {
         if (act) return PLLM_ERR_SIZE;
         return nt == 2 ? pick_mt<2, 0, float>(x, w, y, M, N, K, ldx, warps, stream)

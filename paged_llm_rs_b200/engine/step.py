@@ -100,8 +100,12 @@ class StepPacker:
                 rows.append(len(toks) + w)
             segs.append((len(toks), n, p0, rc.state_slot))
             rcs.append(rc)
-            toks.extend(int(t) for t in e.tokens)
-            pos.extend(range(p0, p0 + n))
+            if n == 1:
+                toks.append(int(e.tokens[0]))
+                pos.append(p0)
+            else:
+                toks.extend(int(t) for t in e.tokens)
+                pos.extend(range(p0, p0 + n))
         T, n_want, n_seg = len(toks), len(rows), len(segs)
         tok_a = np.asarray(toks, dtype=np.int64)
         if T and (tok_a.min() < 0 or tok_a.max() >= self.vocab_size):
@@ -117,6 +121,7 @@ class StepPacker:
             raise ConfigError("the step does not fit the capacities it was given")
 
         group_parts = []
+        planned = {}
         for gi, g in enumerate(cache.groups):
             slots = np.full(Tc, -1, dtype=np.int32)
             width = max((len(rc.tables[gi].blocks) for rc in rcs), default=1)
@@ -128,17 +133,27 @@ class StepPacker:
                 tb = rc.tables[gi]
                 if p0 + n > tb.capacity():
                     raise CacheError(f"request {rc.request_id!r}: no pages reserved for positions up to {p0 + n - 1}")
-                blocks = np.asarray(tb.blocks, dtype=np.int64)
+                blocks = tb.array()          # cached; rebuilt only when a page came or went
                 tables[si, :len(blocks)] = blocks
-                pp = np.arange(p0, p0 + n)
-                page = blocks[pp // ps]
-                if (page < 0).any():
-                    raise CacheError(f"request {rc.request_id!r} writes into a page it gave back")
-                slots[t0:t0 + n] = page * ps + pp % ps
+                if n == 1:
+                    page = int(blocks[p0 // ps])
+                    if page < 0:
+                        raise CacheError(f"request {rc.request_id!r} writes into a page it gave back")
+                    slots[t0] = page * ps + p0 % ps
+                else:
+                    pp = np.arange(p0, p0 + n)
+                    page = blocks[pp // ps].astype(np.int64)
+                    if (page < 0).any():
+                        raise CacheError(f"request {rc.request_id!r} writes into a page it gave back")
+                    slots[t0:t0 + n] = page * ps + pp % ps
             plan = self.plans[gi]
-            work, red, parts = attention_plan.plan_attention(
-                [(t0, n, p0) for (t0, n, p0, _) in segs], plan.tile_tokens, plan.window, plan.ctas_per_item,
-                self.target_ctas)
+            # groups that cut their work alike (same tile, window, CTAs an item) share one plan
+            key = (plan.tile_tokens, plan.window, plan.ctas_per_item)
+            if key not in planned:
+                planned[key] = attention_plan.plan_attention(
+                    [(t0, n, p0) for (t0, n, p0, _) in segs], plan.tile_tokens, plan.window, plan.ctas_per_item,
+                    self.target_ctas)
+            work, red, parts = planned[key]
             mw, mr, mp = (work_caps[gi] if work_caps else (len(work), len(red), parts))
             if len(work) > mw or len(red) > mr or parts > mp:
                 raise ConfigError("the step's attention work does not fit the capacities it was given")

@@ -30,6 +30,11 @@ def plan_attention(segments: Sequence[Tuple[int, int, int]], tile_tokens: int, w
     """segments: (first token index, token count, position of the first token) per
     segment, in step order.  Returns (work [n, 8], red [m, 4], partial rows used)."""
     seg_ids, q0s, qns, p0s = [], [], [], []
+    if segments and all(c == 1 for _, c, _ in segments):
+        # a decode step: one tile per segment, no per-segment array work
+        a = np.asarray(segments, dtype=np.int64)
+        seg_ids, q0s, qns, p0s = [np.arange(len(a))], [a[:, 0]], [a[:, 1]], [a[:, 2]]
+        segments = ()
     for si, (tok0, count, pos0) in enumerate(segments):
         if count <= 0:
             continue
@@ -58,25 +63,26 @@ def plan_attention(segments: Sequence[Tuple[int, int, int]], tile_tokens: int, w
         work = np.stack([seg, q0, qn, p0, kv_begin, kv_end, np.full(n_tiles, -1), np.zeros(n_tiles, np.int64)], 1)
         return work.astype(np.int32), np.zeros((0, 4), np.int32), 0
 
-    work_rows: List[Tuple[int, ...]] = []
-    red_rows: List[Tuple[int, ...]] = []
-    parts = 0
-    for i in range(n_tiles):
-        s = int(splits[i])
-        if s == 1:
-            work_rows.append((seg[i], q0[i], qn[i], p0[i], kv_begin[i], kv_end[i], -1, 0))
-            continue
-        chunk = -(-int(keys[i]) // s)
-        chunk = -(-chunk // SPLIT_ALIGN) * SPLIT_ALIGN
-        begins = list(range(int(kv_begin[i]), int(kv_end[i]), chunk))
-        base = parts
-        for k, b in enumerate(begins):
-            work_rows.append((seg[i], q0[i], qn[i], p0[i], b, min(b + chunk, int(kv_end[i])), base + k * int(qn[i]), 0))
-        for t in range(int(qn[i])):
-            red_rows.append((int(q0[i]) + t, base + t, len(begins), int(qn[i])))
-        parts += len(begins) * int(qn[i])
-    return (np.asarray(work_rows, dtype=np.int32).reshape(-1, 8),
-            np.asarray(red_rows, dtype=np.int32).reshape(-1, 4), parts)
+    # every tile into its splits, without a Python loop over tiles
+    chunk = -(-keys // splits)
+    chunk = -(-chunk // SPLIT_ALIGN) * SPLIT_ALIGN
+    n_split = np.where(splits > 1, -(-keys // chunk), 1)           # splits that really hold keys
+    total = int(n_split.sum())
+    tile_of = np.repeat(np.arange(n_tiles), n_split)
+    first = np.cumsum(n_split) - n_split
+    k = np.arange(total) - first[tile_of]                          # which split of its tile
+    is_split = n_split > 1
+    begin = kv_begin[tile_of] + k * chunk[tile_of]
+    end = np.where(is_split[tile_of], np.minimum(begin + chunk[tile_of], kv_end[tile_of]), kv_end[tile_of])
+    rows_of = np.where(is_split, n_split * qn, 0)                  # partial rows a tile uses
+    base = np.cumsum(rows_of) - rows_of
+    part = np.where(is_split[tile_of], base[tile_of] + k * qn[tile_of], -1)
+    work = np.stack([seg[tile_of], q0[tile_of], qn[tile_of], p0[tile_of], begin, end, part, np.zeros(total, np.int64)], 1)
+    st = np.nonzero(is_split)[0]
+    tile_r = np.repeat(st, qn[st])                                 # one reduction per token of a split tile
+    t_in = np.arange(len(tile_r)) - np.repeat(np.cumsum(qn[st]) - qn[st], qn[st])
+    red = np.stack([q0[tile_r] + t_in, base[tile_r] + t_in, n_split[tile_r], qn[tile_r]], 1)
+    return work.astype(np.int32), red.astype(np.int32).reshape(-1, 4), int(rows_of.sum())
 
 
 def plan_limits(max_step_tokens: int, tile_tokens: int, target_ctas: int, ctas_per_item: int = 1) -> Tuple[int, int, int]:

@@ -328,9 +328,15 @@ def skinny_gemm_takes(x: torch.Tensor, weight: torch.Tensor, k: Optional[int] = 
     if not SKINNY_GEMM or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or x.dim() != 2:
         return False
     N, K = weight.shape
-    return bool(lib().pllm_skinny_gemm_supports(x.shape[0], N, K if k is None else k))
+    return x.shape[0] <= SKINNY_MAX_M and bool(lib().pllm_skinny_gemm_supports(x.shape[0], N, K if k is None else k))
 
 
+# Measured on a B200 inside a captured step (0.6B shapes, microseconds, skinny / cuBLAS):
+#   rows 1-8:  qkv 3.5-3.8 / 5.0   o 3.1 / 6.4-7.5   gate_up 4.6-4.8 / 5.1   down 3.9-4.2 / 8.9-9.6
+#   rows 64:   qkv 12.3 / 4.9      o 6.3 / 5.4        gate_up 12.6 / 5.3      down 8.4 / 6.6
+# so the kernel (which takes up to 64 rows) is used up to 16, and up to a width where the
+# library's head product is the faster one (151936 x 1024: 66 / 54).
+SKINNY_MAX_M = 16
 SKINNY_MAX_N = 32768
 
 

@@ -353,8 +353,9 @@ def test_skinny_gemm(M, N, K):
     g = torch.Generator(device=DEV).manual_seed(M * 1000 + N)
     x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
     w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    ops.SKINNY_MAX_M = 64
     assert ops.skinny_gemm_takes(x, w)
-    ops.SKINNY_MAX_N = 1 << 20      # here also the widest shapes go through the kernel
+    ops.SKINNY_MAX_N, ops.SKINNY_MAX_M = 1 << 20, 64      # here also the widest and tallest shapes go through the kernel
     want = x.float() @ w.float().T
     torch.testing.assert_close(ops.linear(x, w).float(), want, atol=2e-2, rtol=2e-2)
     y32 = ops.linear(x, w, out_dtype=torch.float32)
@@ -366,7 +367,7 @@ def test_skinny_gemm(M, N, K):
     act = (a * torch.sigmoid(a) * gu.float()[:, K:]).bfloat16().float()
     torch.testing.assert_close(ops.linear(gu, w, gated=True).float(), act @ w.float().T, atol=3e-2, rtol=3e-2)
     torch.testing.assert_close(ops.linear(gu, w, gated=True, fuse_gate=True).float(), act @ w.float().T, atol=3e-2, rtol=3e-2)
-    ops.SKINNY_MAX_N = 32768
+    ops.SKINNY_MAX_N, ops.SKINNY_MAX_M = 32768, 16
 
 
 def test_linear_falls_back_to_the_library_for_other_shapes():
