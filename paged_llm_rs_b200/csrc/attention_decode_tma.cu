@@ -104,7 +104,6 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     int nh, int nkv, int page_size, int page_shift, int n_pages, int table_width, float scale_log2,
     int heads_per_cta, int kinds_mask, int* status) {
-    pdl_launch_dependents();
     pdl_wait();
     if ((int)blockIdx.y >= *n_work_ptr) return;
     const AttnWork w = work[blockIdx.y];
@@ -343,6 +342,7 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
     }
+    pdl_launch_dependents();   // the key tiles are done: the next kernel's CTAs may take their places
     if (!decode) {
         // ---- several query tokens: every warp owns its rows' results ----------------------------
         if (!alive || *abort_flag) {

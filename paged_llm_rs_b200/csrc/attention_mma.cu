@@ -106,7 +106,6 @@ __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     int nh, int nkv, int page_size, int page_shift, int n_pages, int table_width, int window, float scale_log2,
     int heads_per_cta, int swizzle, int kinds_mask, int* status) {
-    pdl_launch_dependents();
     pdl_wait();
     if ((int)blockIdx.y >= *n_work_ptr) return;
     const AttnWork w = work[blockIdx.y];
@@ -292,6 +291,7 @@ __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
         }
     }
     cp_async_wait<0>();
+    pdl_launch_dependents();   // the key tiles are done: the next kernel's CTAs may take their places
     // row sums live spread over the four lanes of a quad
 #pragma unroll
     for (int i = 0; i < 2; i++) {

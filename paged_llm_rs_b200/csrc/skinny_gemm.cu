@@ -47,7 +47,6 @@ template <int MT, int NT, int ACT, typename OutT>
 __global__ void __launch_bounds__(512) skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                           OutT* __restrict__ y, int M, int N, int K, int ldx) {
     constexpr int U = MT == 1 ? 4 : (MT == 2 ? 2 : 1);  // k blocks of 32 whose loads are issued together
-    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, ks_count = blockDim.x >> 5;
     const int n0 = blockIdx.x * (8 * NT);
     const int k_per = K / ks_count;
@@ -116,6 +115,7 @@ __global__ void __launch_bounds__(512) skinny_gemm_kernel(const bf16* __restrict
         }
     }
 
+    pdl_launch_dependents();   // the weights are read: the next kernel may start on its own
     // ---- the warps' partial sums over their slices of K meet in shared memory ---------------
     extern __shared__ float red[];  // [warps][MT*16][NT*8]
     constexpr int ROWS = MT * 16, COLS = NT * 8;
