@@ -99,12 +99,16 @@ template <int HD> __device__ __forceinline__ uint32_t toff(int row, int chunk) {
 
 template <int HD>
 __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_tma_kernel(
-    const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+    const bf16* q, const bf16* k_pool, const bf16* v_pool,   // written by the kernels before this one: no __restrict__
     const int* __restrict__ block_tables, const AttnWork* __restrict__ work, const int* __restrict__ n_work_ptr,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     int nh, int nkv, int page_size, int page_shift, int n_pages, int table_width, float scale_log2,
     int heads_per_cta, int kinds_mask, int* status) {
-    pdl_wait();
+    // The work items and block tables came from the host before the step, and the cache below
+    // the step's own positions was written by earlier steps: neither depends on the kernels
+    // just before this one.  So nobody waits for those kernels yet: the producer starts the
+    // first tiles of old keys on their way at once, and waits only before a tile that may hold
+    // a key of this step; the consumers wait before they read the queries.
     if ((int)blockIdx.y >= *n_work_ptr) return;
     const AttnWork w = work[blockIdx.y];
     if (!(kinds_mask & (w.q_count == 1 ? 1 : 2))) return;   // another kernel's item
@@ -152,9 +156,13 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
         // the table entries of the key range, 32 at a time, one in each lane: no tile waits for a lookup
         int win0 = w.kv_begin >> page_shift;
         int tbl = (win0 + lane < table_width) ? table[win0 + lane] : -1;
+        bool waited = false;
         for (int t = 0; t < n_tiles; t++) {
             const int s = t % TD_STAGES;
             const int kv0 = w.kv_begin + t * TD_BK;
+            // A decoded token's own key is the only one this step writes for its request; a
+            // portion's tiles read keys that other tiles of the portion bring, so they wait first.
+            if (!waited && (!decode || kv0 + TD_BK > w.q_pos0)) { pdl_wait(); waited = true; }
             if (((kv0 + TD_BK - 1) >> page_shift) >= win0 + 32) {
                 win0 = kv0 >> page_shift;
                 tbl = (win0 + lane < table_width) ? table[win0 + lane] : -1;
@@ -203,6 +211,7 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
     }
 
     // the query rows, zero beyond them (the first tiles are on their way meanwhile)
+    pdl_wait(KID_ATT_TMA);
     for (int idx = threadIdx.x; idx < (decode ? 16 : TD_QROWS) * CH; idx += TD_CONSUMERS * 32) {
         const int row = idx / CH, chunk = idx % CH;
         uint4 v = make_uint4(0, 0, 0, 0);
@@ -452,3 +461,5 @@ PLLM_EXPORT int pllm_attention_decode_tma(const void* q, const void* k_pool, con
     return launch_tma<64>(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv,
                           page_size, n_pages, table_width, scale, kinds_mask, status, stream);
 }
+
+PLLM_TRACE_EXPORT(attention_decode_tma)

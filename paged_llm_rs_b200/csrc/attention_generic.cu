@@ -30,8 +30,10 @@ struct AttnWork { int seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slo
 
 template <typename T>
 __global__ void attention_generic_kernel(
-    const T* __restrict__ q,            // [n_tokens, nh, hd]
-    const T* __restrict__ k_pool, const T* __restrict__ v_pool,  // [pages, nkv, page_size, hd]
+    // q and the pools are written by the kernels before this one: not __restrict__, so that they are
+    // read with coherent loads after the wait and never through the read-only cache
+    const T* q,            // [n_tokens, nh, hd]
+    const T* k_pool, const T* v_pool,  // [pages, nkv, page_size, hd]
     const int* __restrict__ block_tables,  // [n_segs, table_width]
     const AttnWork* __restrict__ work, const int* __restrict__ n_work_ptr,
     T* __restrict__ out,                // [n_tokens, nh, hd]
@@ -40,7 +42,7 @@ __global__ void attention_generic_kernel(
     int nh, int nkv, int hd, int page_size, int n_pages, int table_width, int window, float scale,
     int heads_per_cta, int* status) {
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(KID_ATT_GENERIC);
     if ((int)blockIdx.x >= *n_work_ptr) return;
     const AttnWork w = work[blockIdx.x];
     const int group = nh / nkv;
@@ -165,13 +167,13 @@ __global__ void attention_generic_kernel(
 // memory, then each thread sums its output dimensions over the splits.
 #define RED_MAX_SPLITS 256
 template <typename T>
-__global__ void attention_reduce_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+__global__ void attention_reduce_kernel(const float* part_o, const float* part_ml,   // just written: no __restrict__
                                         const int* __restrict__ red, const int* __restrict__ n_red_ptr,
                                         T* __restrict__ out, int nh, int hd) {
     __shared__ float wgt[RED_MAX_SPLITS];
     __shared__ float inv_s;
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(KID_ATT_REDUCE);
     const int t = blockIdx.x, head = blockIdx.y;
     if (t >= *n_red_ptr) return;
     const int token = red[t * 4], first = red[t * 4 + 1], count = min(red[t * 4 + 2], RED_MAX_SPLITS), stride = red[t * 4 + 3];
@@ -242,3 +244,5 @@ PLLM_EXPORT int pllm_attention_reduce(int dtype, const float* part_o, const floa
     });
     return launch_status();
 }
+
+PLLM_TRACE_EXPORT(attention_generic)

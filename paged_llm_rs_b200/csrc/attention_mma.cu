@@ -101,12 +101,12 @@ struct TileLoader {
 
 template <int HD>
 __global__ void __launch_bounds__(128, 2) attention_mma_kernel(
-    const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+    const bf16* q, const bf16* k_pool, const bf16* v_pool,   // written by the kernels before this one: no __restrict__
     const int* __restrict__ block_tables, const AttnWork* __restrict__ work, const int* __restrict__ n_work_ptr,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     int nh, int nkv, int page_size, int page_shift, int n_pages, int table_width, int window, float scale_log2,
     int heads_per_cta, int swizzle, int kinds_mask, int* status) {
-    pdl_wait();
+    pdl_wait(KID_ATT_MMA);
     if ((int)blockIdx.y >= *n_work_ptr) return;
     const AttnWork w = work[blockIdx.y];
     const int group = nh / nkv;
@@ -405,3 +405,5 @@ PLLM_EXPORT int pllm_attention_mma(const void* q, const void* k_pool, const void
     }
     return launch_status();
 }
+
+PLLM_TRACE_EXPORT(attention_mma)

@@ -37,6 +37,11 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
 ]
 
+# PAGED_LLM_NVCC_DEFINES="A=1 B" adds -DA=1 -DB to every compile (a build of its own, named by
+# its own hash): PLLM_TRACE=1 makes the kernels stamp the time around their wait for the kernel
+# before them, for a timeline of a step (read with pllm_trace_read_<file>).
+NVCC_FLAGS += [f"-D{d}" for d in os.environ.get("PAGED_LLM_NVCC_DEFINES", "").split()]
+
 _lock = threading.Lock()
 _lib: Optional[ctypes.CDLL] = None
 

@@ -104,8 +104,56 @@ static inline int launch_status() {
 // when every earlier kernel of the stream has finished and its writes are visible),
 // and pdl_launch_dependents() lets the kernel after them do the same.  What does not
 // depend on earlier kernels (reading weights) may come before the wait.
+// One rule follows for every kernel here: a pointer to data that a kernel shortly before it in
+// the stream writes (activations, partial results, this step's cache rows) is never
+// `const __restrict__` and never read with __ldg.  Those make the compiler use the SM's
+// read-only cache, which is only right for data that does not change while the kernel is
+// resident, and a kernel launched early is resident while its input is still being written:
+// it can then hit a line that an older kernel left on the same SM at the same (recycled)
+// address.  It showed as wrong tokens with a tiny model, whose kernels are all resident
+// at once.  Weights, tables and the host's step buffer may use the read-only path.
 // Without the attribute both calls do nothing.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+#ifndef PLLM_TRACE
+__device__ __forceinline__ void pdl_wait(int kernel_id = 0) { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+#define PLLM_TRACE_EXPORT(file)
+#else
+// A build for timelines (-DPLLM_TRACE=1): thread 0 of block (0, 0) of every kernel stamps the
+// global timer before and after its wait for the kernel before it, with the kernel's id, into a
+// buffer of this source file.  The time between two kernels' "after" stamps is what the earlier
+// one costs in the chain; "before" shows how early a kernel's CTAs were in place.
+#define PLLM_TRACE_SLOTS 8192
+static __device__ unsigned long long g_trace[PLLM_TRACE_SLOTS * 3];
+static __device__ unsigned int g_trace_n;
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void pdl_wait(int kernel_id = 0) {
+    const bool me = (threadIdx.x | threadIdx.y | blockIdx.x | blockIdx.y | blockIdx.z) == 0;
+    const unsigned long long t0 = me ? global_ns() : 0;
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    if (me) {
+        const unsigned int i = atomicAdd(&g_trace_n, 1u);
+        if (i < PLLM_TRACE_SLOTS) { g_trace[3 * i] = (unsigned long long)kernel_id; g_trace[3 * i + 1] = t0; g_trace[3 * i + 2] = global_ns(); }
+    }
+}
+// Copies the stamps out (3 x 64-bit each: id, before, after), empties the buffer, returns the count.
+#define PLLM_TRACE_EXPORT(file)                                                                              \
+    PLLM_EXPORT int pllm_trace_read_##file(unsigned long long* out, int max_records) {                       \
+        unsigned int n = 0, zero = 0;                                                                        \
+        cudaDeviceSynchronize();                                                                             \
+        cudaMemcpyFromSymbol(&n, g_trace_n, sizeof(n));                                                      \
+        if (n > PLLM_TRACE_SLOTS) n = PLLM_TRACE_SLOTS;                                                      \
+        if ((int)n > max_records) n = max_records;                                                           \
+        if (n) cudaMemcpyFromSymbol(out, g_trace, (size_t)n * 3 * sizeof(unsigned long long));               \
+        cudaMemcpyToSymbol(g_trace_n, &zero, sizeof(zero));                                                  \
+        return (int)n;                                                                                       \
+    }
+#endif
+// Kernel ids of the timeline.
+enum : int { KID_EMBED = 1, KID_RMSNORM, KID_SWIGLU, KID_QK, KID_ATT_GENERIC, KID_ATT_REDUCE, KID_ATT_MMA, KID_ATT_TMA,
+             KID_GEMM, KID_SAMPLE_PART, KID_SAMPLE_FINAL };
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 
 extern int pllm_pdl_enabled;  // defined in elementwise.cu; set through pllm_set_pdl

@@ -29,7 +29,7 @@ template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table, T* __restrict__ out,
                              int hidden, int vocab, int* status) {
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(KID_EMBED);
     const int t = blockIdx.x;
     const int tok = tokens[t];
     const bool ok = tok >= 0 && tok < vocab;
@@ -68,12 +68,12 @@ PLLM_EXPORT int pllm_embed(int dtype, const int* tokens, const void* table, void
 //   y[i] = v / sqrt(mean(v^2) + eps) * gain
 // x and residual_out may be the same buffer.
 template <typename T>
-__global__ void rmsnorm_kernel(const T* x, const T* __restrict__ delta, T* residual_out,
+__global__ void rmsnorm_kernel(const T* x, const T* delta, T* residual_out,   // x, delta: just written, no __restrict__
                                const float* __restrict__ gain, T* __restrict__ y, const int* __restrict__ rows,
                                int width, float eps) {
     __shared__ float scratch[32];
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(KID_RMSNORM);
     const int i = blockIdx.x;
     const size_t r = rows ? (size_t)rows[i] : (size_t)i;
     const T* xr = x + r * width;
@@ -156,11 +156,11 @@ PLLM_EXPORT int pllm_rmsnorm(int dtype, const void* x, const void* delta, void* 
 // in is [n, 2*inter]: the gate in columns [0, inter), up in [inter, 2*inter).
 // out[n, inter] = silu(gate) * up, silu(z) = z / (1 + exp(-z)).
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, long long total_vec,
+__global__ void swiglu_kernel(const T* in, T* __restrict__ out, int inter, long long total_vec,
                               int vec_per_row) {
     constexpr int N = Vec16<T>::N;
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(KID_SWIGLU);
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total_vec;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long row = idx / vec_per_row;
@@ -175,9 +175,9 @@ __global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int
     }
 }
 template <typename T>
-__global__ void swiglu_scalar_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, long long total) {
+__global__ void swiglu_scalar_kernel(const T* in, T* __restrict__ out, int inter, long long total) {
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(KID_SWIGLU);
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long row = idx / inter;
@@ -206,3 +206,5 @@ PLLM_EXPORT int pllm_swiglu(int dtype, const void* in, void* out, int n_rows, in
     });
     return launch_status();
 }
+
+PLLM_TRACE_EXPORT(elementwise)

@@ -19,7 +19,7 @@
 
 template <typename T>
 __global__ void qk_norm_rope_kv_kernel(
-    const T* __restrict__ qkv,        // [n_tokens, (nh + 2*nkv) * hd]
+    const T* qkv,        // [n_tokens, (nh + 2*nkv) * hd]; just written by the projection: no __restrict__
     T* __restrict__ q_out,            // [n_tokens, nh * hd]
     const float* __restrict__ q_gain, // [hd] or null: no q norm
     const float* __restrict__ k_gain, // [hd] or null: no k norm
@@ -32,7 +32,7 @@ __global__ void qk_norm_rope_kv_kernel(
     int n_tokens, int nh, int nkv, int hd, int page_size, int n_pages, int swizzle, int* status) {
     extern __shared__ float smem[];  // [warps][hd]
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(KID_QK);
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = nh + 2 * nkv;
     const long long item = (long long)blockIdx.x * warps + warp;
@@ -98,13 +98,13 @@ __global__ void qk_norm_rope_kv_kernel(
 // sizes of 8, 16 or 32 chunks that are rotated over their whole width (or not at all).
 template <typename T, int LPH>
 __global__ void qk_norm_rope_kv_vec_kernel(
-    const T* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ q_gain,
+    const T* qkv, T* __restrict__ q_out, const float* __restrict__ q_gain,
     const float* __restrict__ k_gain, float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
     int max_pos, const int* __restrict__ positions, const int* __restrict__ slots, T* __restrict__ k_pool,
     T* __restrict__ v_pool, int n_tokens, int nh, int nkv, int page_size, int n_pages, int swizzle, int* status) {
     constexpr int N = Vec16<T>::N, HD = LPH * N, HPW = 32 / LPH;
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(KID_QK);
     const int lane = threadIdx.x & 31, sub = lane / LPH, c = lane % LPH;
     const int heads = nh + 2 * nkv;
     const long long total = (long long)n_tokens * heads;
@@ -209,3 +209,5 @@ PLLM_EXPORT int pllm_qk_norm_rope_kv(int dtype, const void* qkv, void* q_out, co
     });
     return launch_status();
 }
+
+PLLM_TRACE_EXPORT(qk_norm_rope_kv)

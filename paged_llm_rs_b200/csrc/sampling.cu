@@ -25,14 +25,14 @@ __device__ __forceinline__ void argmax_merge(float& v, int& i, float ov, int oi)
 }
 
 // scratch: [rows][chunks][4] floats = (max, index as int bits, sum, unused)
-__global__ void sample_partial_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
+__global__ void sample_partial_kernel(const float* logits, int vocab, long long row_stride,
                                       const float* __restrict__ temperature, float* __restrict__ scratch) {
     __shared__ float s_v[SAMPLE_THREADS / 32];
     __shared__ int s_i[SAMPLE_THREADS / 32];
     __shared__ float s_sum[SAMPLE_THREADS / 32];
     __shared__ float s_max;
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(KID_SAMPLE_PART);
     const int row = blockIdx.y, chunk = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* l = logits + (size_t)row * row_stride;
     const int base = chunk * SAMPLE_CHUNK;
@@ -81,16 +81,16 @@ __global__ void sample_partial_kernel(const float* __restrict__ logits, int voca
     }
 }
 
-__global__ void sample_final_kernel(const float* __restrict__ logits, int vocab, long long row_stride, int chunks,
+__global__ void sample_final_kernel(const float* logits, int vocab, long long row_stride, int chunks,
                                     const float* __restrict__ temperature, const float* __restrict__ uniform,
-                                    const float* __restrict__ scratch, int* __restrict__ tokens) {
+                                    const float* scratch, int* __restrict__ tokens) {
     __shared__ float s_v[SAMPLE_THREADS / 32];
     __shared__ int s_i[SAMPLE_THREADS / 32];
     __shared__ float s_scan[SAMPLE_THREADS];
     __shared__ float s_max, s_before, s_point;
     __shared__ int s_arg, s_chunk, s_owner;
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(KID_SAMPLE_FINAL);
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* part = scratch + (size_t)row * chunks * 4;
     // the first maximum over the chunks
@@ -249,3 +249,5 @@ PLLM_EXPORT int pllm_sample_static(const float* logits, int n_rows, int vocab, l
                    chunks, temperature, uniform, (const float*)scratch, tokens);
     return launch_status();
 }
+
+PLLM_TRACE_EXPORT(sampling)

@@ -1,4 +1,4 @@
-// y[M, N] = act(x)[M, K] . W[N, K]^T for few rows (M <= 64, a decode step) in
+// y[M, N] = x[M, K] . W[N, K]^T for few rows (M <= 64, a decode step) in
 // bfloat16 with float accumulation: a weight-streaming kernel, bound by the bytes
 // of W.  Where the reference calls a library product for every projection
 // (crates/pagedllm/src/model/layers.rs:27-35), a library kernel chosen for large
@@ -14,11 +14,28 @@
 // deliver them: lane t (mod 4) holds k = 8t .. 8t+7 of both operands.
 // The warps of a CTA split K; their partial sums meet in shared memory.
 //
-// act = 1: the A operand is silu(g) * u formed on the fly from x = [g | u]
-// ([M, 2K]), the gated feed-forward's activation
-// (crates/pagedllm/src/model/layers.rs:93-99), so the activation needs no pass
-// of its own.
+// Two things a decode step does around its products are folded in, because at a
+// few rows every kernel costs its launch and a round trip through memory, not
+// its arithmetic:
+//   PRO = 1: x is the residual stream; the product is taken of
+//     rmsnorm(x + delta) * gain (crates/pagedllm/src/model/layers.rs:40-65 after
+//     the residual add of crates/pagedllm/src/model/mod.rs:131-132).  A warp's
+//     slice of K is then exactly 128 (K / 128 warps, so K <= 2048), and the step
+//     has at most 8 rows (the upper half of the 16-row operand is zero): with its
+//     weight loads in flight it forms h = x + delta (rounded to bfloat16, as the
+//     residual stream holds it) in registers and sums h^2; the warps exchange
+//     their sums through shared memory, and each then multiplies by
+//     h * (1/rms) * gain rounded to bfloat16, the very operand a norm kernel
+//     would have stored.  The first CTA stores h to residual_out, which must be
+//     a buffer of its own: the other CTAs still read x and delta.
+//   EPI = 1: W is [gate rows | up rows] of a gated feed-forward and y = silu(g) * u
+//     (crates/pagedllm/src/model/layers.rs:93-99): a CTA takes the same columns
+//     of both halves, so the activation needs neither a pass nor a buffer.
 #include "common.cuh"
+
+#ifndef PLLM_SKINNY_EARLY
+#define PLLM_SKINNY_EARLY 1
+#endif
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     uint4 r;
@@ -26,7 +43,14 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
                  : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
     return r;
 }
-__device__ __forceinline__ uint4 ld_cached16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+// x comes from the kernel before this one, which may still run while this kernel's CTAs take their
+// places: a load from L2 after the wait, never the read-only path (L1 may hold the line as an
+// earlier kernel on this SM saw it).
+__device__ __forceinline__ uint4 ld_cached16(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+    return r;
+}
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -35,20 +59,42 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint32_t silu_mul2(uint32_t g, uint32_t u) {
-    // two bfloat16 in each word: silu(g) * u in float, rounded once
-    const float g0 = __uint_as_float(g << 16), g1 = __uint_as_float(g & 0xffff0000u);
-    const float u0 = __uint_as_float(u << 16), u1 = __uint_as_float(u & 0xffff0000u);
-    __nv_bfloat162 h = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
-    return *reinterpret_cast<uint32_t*>(&h);
+// Two bfloat16 in each word.  h = x + d rounded to bfloat16 (x itself without d); its
+// squares are added to ss.
+__device__ __forceinline__ uint32_t add2(uint32_t x, uint32_t d, bool add, float& ss) {
+    float h0 = __uint_as_float(x << 16), h1 = __uint_as_float(x & 0xffff0000u);
+    if (add) {
+        h0 = __bfloat162float(__float2bfloat16_rn(h0 + __uint_as_float(d << 16)));
+        h1 = __bfloat162float(__float2bfloat16_rn(h1 + __uint_as_float(d & 0xffff0000u)));
+    }
+    ss += h0 * h0 + h1 * h1;
+    return (__float_as_uint(h0) >> 16) | (__float_as_uint(h1) & 0xffff0000u);
+}
+// h * inv * gain for the two values of a word, each rounded once.
+__device__ __forceinline__ uint32_t scale2(uint32_t h, float inv, float g0, float g1) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(__uint_as_float(h << 16) * inv * g0,
+                                             __uint_as_float(h & 0xffff0000u) * inv * g1);
+    return *reinterpret_cast<uint32_t*>(&a);
 }
 
-template <int MT, int NT, int ACT, typename OutT>
-__global__ void __launch_bounds__(512) skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
-                                                          OutT* __restrict__ y, int M, int N, int K, int ldx) {
-    constexpr int U = MT == 1 ? 4 : (MT == 2 ? 2 : 1);  // k blocks of 32 whose loads are issued together
+// WMAX: the most warps a launch may have (16, or 8 with the promise of three CTAs to an SM,
+// which the forms with the norm need: a launch that fills the SMs only in a second wave
+// cannot start its weights while the kernel before it drains).
+template <int MT, int NT, int PRO, int EPI, typename OutT, int WMAX = 16>
+__global__ void __launch_bounds__(WMAX * 32, WMAX == 8 ? 3 : 1) skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w,
+                                                          OutT* __restrict__ y, int M, int N, int K,
+                                                          const bf16* delta, bf16* __restrict__ residual_out,
+                                                          const float* __restrict__ gain, float eps) {
+    static_assert(PRO == 0 || MT == 1, "the norm prologue is for up to 16 rows");
+    // PRO = 2 (the form that is launched): at most 8 rows, so that the upper half of the A
+    // operand is zero and costs no registers
+    constexpr int HS = PRO == 2 ? 1 : 2;
+    static_assert(!EPI || NT % 2 == 0, "the gated epilogue pairs tiles of gate and up");
+    // k blocks of 32 whose loads are issued together
+    constexpr int U = MT == 1 ? 4 : (MT == 2 ? 2 : 1);
+    constexpr int ROWS = MT * 16, COLS = NT * 8, OUT_COLS = EPI ? COLS / 2 : COLS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, ks_count = blockDim.x >> 5;
-    const int n0 = blockIdx.x * (8 * NT);
+    const int n0 = blockIdx.x * OUT_COLS;
     const int k_per = K / ks_count;
     const int k_begin = warp * k_per, k_end = k_begin + k_per;
     const int r = lane >> 2, t = lane & 3;
@@ -61,7 +107,11 @@ __global__ void __launch_bounds__(512) skinny_gemm_kernel(const bf16* __restrict
 
     const bf16* wrow[NT];
 #pragma unroll
-    for (int b = 0; b < NT; b++) wrow[b] = w + (size_t)(n0 + b * 8 + r) * K + t * 8;
+    for (int b = 0; b < NT; b++) {
+        // gated: the first half of the tiles are gate rows, the second the same columns of up
+        const int row = (EPI && b >= NT / 2) ? N + n0 + (b - NT / 2) * 8 + r : n0 + b * 8 + r;
+        wrow[b] = w + (size_t)row * K + t * 8;
+    }
     const bf16* xrow[MT][2];
     bool xok[MT][2];
 #pragma unroll
@@ -70,9 +120,81 @@ __global__ void __launch_bounds__(512) skinny_gemm_kernel(const bf16* __restrict
         for (int h = 0; h < 2; h++) {
             const int m = a * 16 + h * 8 + r;
             xok[a][h] = m < M;
-            xrow[a][h] = x + (size_t)(xok[a][h] ? m : 0) * ldx + t * 8;
+            xrow[a][h] = x + (size_t)(xok[a][h] ? m : 0) * K + t * 8;
         }
+    extern __shared__ float red[];  // [warps][MT*16][NT*8]
+    __shared__ float ssq[16][16];   // [warp][row]: sums of h^2 over the warp's slice of K
 
+    if constexpr (PRO) {
+        // ---- one group of 128 values of k a warp: add, norm and product -------------------------
+        const bool add = delta != nullptr;
+        const bool keep = residual_out != nullptr && blockIdx.x == 0;
+        uint4 wf[4][NT], hf[4][HS];
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+#pragma unroll
+            for (int b = 0; b < NT; b++) wf[u][b] = ld_stream16(wrow[b] + k_begin + 32 * u);
+        if (PLLM_SKINNY_EARLY) pdl_launch_dependents();
+        pdl_wait(KID_GEMM);   // the weights do not depend on the kernel before this one; x and delta do
+        float ss[HS];
+        {
+            uint4 df[4][HS];
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int h = 0; h < HS; h++) {
+                    hf[u][h] = df[u][h] = make_uint4(0, 0, 0, 0);
+                    if (xok[0][h]) {
+                        hf[u][h] = ld_cached16(xrow[0][h] + k_begin + 32 * u);
+                        if (add) df[u][h] = ld_cached16(delta + (xrow[0][h] - x) + k_begin + 32 * u);
+                    }
+                }
+#pragma unroll
+            for (int h = 0; h < HS; h++) ss[h] = 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int h = 0; h < HS; h++) {
+                    hf[u][h] = make_uint4(add2(hf[u][h].x, df[u][h].x, add, ss[h]), add2(hf[u][h].y, df[u][h].y, add, ss[h]),
+                                          add2(hf[u][h].z, df[u][h].z, add, ss[h]), add2(hf[u][h].w, df[u][h].w, add, ss[h]));
+                    if (keep && xok[0][h])
+                        *reinterpret_cast<uint4*>(residual_out + (size_t)(h * 8 + r) * K + k_begin + 32 * u + t * 8) = hf[u][h];
+                }
+        }
+#pragma unroll
+        for (int h = 0; h < HS; h++) {
+            float v = ss[h];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            if (t == 0) ssq[warp][h * 8 + r] = v;
+        }
+        __syncthreads();
+        float inv[HS];
+#pragma unroll
+        for (int h = 0; h < HS; h++) {
+            float tot = 0.f;
+            for (int wi = 0; wi < ks_count; wi++) tot += ssq[wi][h * 8 + r];  // fixed order
+            inv[h] = 1.0f / sqrtf(tot / (float)K + eps);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            // the gain is fetched only now (it is in L1 or L2): held across the barrier it would
+            // cost the registers that let a fourth CTA onto the SM
+            const float4 g0 = __ldg(reinterpret_cast<const float4*>(gain + k_begin + 32 * u + t * 8));
+            const float4 g1 = __ldg(reinterpret_cast<const float4*>(gain + k_begin + 32 * u + t * 8 + 4));
+            const uint4 xa = make_uint4(scale2(hf[u][0].x, inv[0], g0.x, g0.y), scale2(hf[u][0].y, inv[0], g0.z, g0.w),
+                                        scale2(hf[u][0].z, inv[0], g1.x, g1.y), scale2(hf[u][0].w, inv[0], g1.z, g1.w));
+            uint4 xb = make_uint4(0, 0, 0, 0);
+            if (HS == 2)
+                xb = make_uint4(scale2(hf[u][HS - 1].x, inv[HS - 1], g0.x, g0.y), scale2(hf[u][HS - 1].y, inv[HS - 1], g0.z, g0.w),
+                                scale2(hf[u][HS - 1].z, inv[HS - 1], g1.x, g1.y), scale2(hf[u][HS - 1].w, inv[HS - 1], g1.z, g1.w));
+#pragma unroll
+            for (int b = 0; b < NT; b++) {
+                mma16816(acc[0][b], xa.x, xb.x, xa.y, xb.y, wf[u][b].x, wf[u][b].y);
+                mma16816(acc[0][b], xa.z, xb.z, xa.w, xb.w, wf[u][b].z, wf[u][b].w);
+            }
+        }
+    } else {
     for (int kb = k_begin; kb < k_end; kb += 32 * U) {
         // every load of the group is issued before the first is used: one trip to memory, not U
         uint4 wf[U][NT], xf[U][MT][2];
@@ -82,7 +204,7 @@ __global__ void __launch_bounds__(512) skinny_gemm_kernel(const bf16* __restrict
             for (int b = 0; b < NT; b++)
                 if (kb + 32 * u < k_end) wf[u][b] = ld_stream16(wrow[b] + kb + 32 * u);
         // The weights do not depend on the kernel before this one; x does.
-        if (kb == k_begin) pdl_wait();
+        if (kb == k_begin) { if (PLLM_SKINNY_EARLY) pdl_launch_dependents(); pdl_wait(KID_GEMM); }
 #pragma unroll
         for (int u = 0; u < U; u++)
 #pragma unroll
@@ -95,17 +217,9 @@ __global__ void __launch_bounds__(512) skinny_gemm_kernel(const bf16* __restrict
 #pragma unroll
         for (int u = 0; u < U; u++) {
             if (kb + 32 * u >= k_end) break;
-            const int k = kb + 32 * u;
 #pragma unroll
             for (int a = 0; a < MT; a++) {
-                uint4 xa = xf[u][a][0], xb = xf[u][a][1];
-                if (ACT == 1) {
-                    uint4 ua = make_uint4(0, 0, 0, 0), ub = make_uint4(0, 0, 0, 0);
-                    if (xok[a][0]) ua = ld_cached16(xrow[a][0] + K + k);
-                    if (xok[a][1]) ub = ld_cached16(xrow[a][1] + K + k);
-                    xa = make_uint4(silu_mul2(xa.x, ua.x), silu_mul2(xa.y, ua.y), silu_mul2(xa.z, ua.z), silu_mul2(xa.w, ua.w));
-                    xb = make_uint4(silu_mul2(xb.x, ub.x), silu_mul2(xb.y, ub.y), silu_mul2(xb.z, ub.z), silu_mul2(xb.w, ub.w));
-                }
+                const uint4 xa = xf[u][a][0], xb = xf[u][a][1];
 #pragma unroll
                 for (int b = 0; b < NT; b++) {
                     mma16816(acc[a][b], xa.x, xb.x, xa.y, xb.y, wf[u][b].x, wf[u][b].y);
@@ -114,12 +228,11 @@ __global__ void __launch_bounds__(512) skinny_gemm_kernel(const bf16* __restrict
             }
         }
     }
+    }
 
-    pdl_launch_dependents();   // the weights are read: the next kernel may start on its own
+    if (!PLLM_SKINNY_EARLY) pdl_launch_dependents();   // the weights are read: the next kernel may start on its own
     // ---- the warps' partial sums over their slices of K meet in shared memory ---------------
-    extern __shared__ float red[];  // [warps][MT*16][NT*8]
-    constexpr int ROWS = MT * 16, COLS = NT * 8;
-    if (ks_count > 1) {
+    if (ks_count > 1 || EPI) {
         float* mine = red + (size_t)warp * ROWS * COLS;
 #pragma unroll
         for (int a = 0; a < MT; a++)
@@ -132,11 +245,19 @@ __global__ void __launch_bounds__(512) skinny_gemm_kernel(const bf16* __restrict
                 mine[(a * 16 + 8 + r) * COLS + c + 1] = acc[a][b][3];
             }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < ROWS * COLS; idx += blockDim.x) {
-            const int m = idx / COLS, c = idx % COLS;
+        for (int idx = threadIdx.x; idx < ROWS * OUT_COLS; idx += blockDim.x) {
+            const int m = idx / OUT_COLS, c = idx % OUT_COLS;
             if (m >= M) continue;
             float s = 0.f;
-            for (int wi = 0; wi < ks_count; wi++) s += red[(size_t)wi * ROWS * COLS + idx];  // fixed order
+            for (int wi = 0; wi < ks_count; wi++) s += red[(size_t)wi * ROWS * COLS + m * COLS + c];  // fixed order
+            if (EPI) {
+                float u = 0.f;
+                for (int wi = 0; wi < ks_count; wi++) u += red[(size_t)wi * ROWS * COLS + m * COLS + OUT_COLS + c];
+                // gate and up are rounded as a product of their own would leave them
+                const float g = __bfloat162float(__float2bfloat16_rn(s));
+                u = __bfloat162float(__float2bfloat16_rn(u));
+                s = g / (1.0f + expf(-g)) * u;
+            }
             y[(size_t)m * N + n0 + c] = from_f32<OutT>(s);
         }
     } else {
@@ -164,53 +285,86 @@ PLLM_EXPORT int pllm_skinny_gemm_set_warps(int warps) {
 PLLM_EXPORT int pllm_skinny_gemm_supports(int M, int N, int K) {
     return M >= 1 && M <= 64 && N % 16 == 0 && K % 128 == 0 && N >= 16 && K >= 128;
 }
+// The same for the forms with the norm before or the gate after (N: columns of y).
+// With the norm every warp holds a slice of exactly 128 values of k, so K is at most 16 x 128;
+// and at most 8 rows, since with 16 the operand's registers leave too few CTAs on an SM
+// (measured 10.3 us against 6.6 us for the norm kernel followed by the plain product).
+PLLM_EXPORT int pllm_skinny_gemm_fused_supports(int M, int N, int K, int normed) {
+    return M >= 1 && M <= 16 && N % 16 == 0 && K % 128 == 0 && N >= 16 && K >= 128 && (!normed || (K <= 2048 && M <= 8));
+}
 
-template <int MT, int NT, int ACT, typename OutT>
-static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, int ldx, int warps,
-                         cudaStream_t stream) {
-    const size_t smem = warps > 1 ? (size_t)warps * MT * 16 * NT * 8 * sizeof(float) : 0;
+template <int MT, int NT, int PRO, int EPI, typename OutT, int WMAX = 16>
+static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, int warps, const void* delta,
+                         void* residual_out, const float* gain, float eps, cudaStream_t stream) {
+    const size_t smem = (warps > 1 || EPI) ? (size_t)warps * MT * 16 * NT * 8 * sizeof(float) : 0;
     if (smem > 48 * 1024)
-        cudaFuncSetAttribute(skinny_gemm_kernel<MT, NT, ACT, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_chained(skinny_gemm_kernel<MT, NT, ACT, OutT>, dim3(N / (8 * NT)), dim3(warps * 32), smem, stream,
-                   (const bf16*)x, (const bf16*)w, (OutT*)y, M, N, K, ldx);
+        cudaFuncSetAttribute(skinny_gemm_kernel<MT, NT, PRO, EPI, OutT, WMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem);
+    constexpr int out_cols = EPI ? 4 * NT : 8 * NT;
+    launch_chained(skinny_gemm_kernel<MT, NT, PRO, EPI, OutT, WMAX>, dim3(N / out_cols), dim3(warps * 32), smem, stream,
+                   (const bf16*)x, (const bf16*)w, (OutT*)y, M, N, K, (const bf16*)delta, (bf16*)residual_out, gain, eps);
     return launch_status();
 }
 
-template <int NT, int ACT, typename OutT>
-static int pick_mt(const void* x, const void* w, void* y, int M, int N, int K, int ldx, int warps, cudaStream_t s) {
-    if (M <= 16) return launch_skinny<1, NT, ACT, OutT>(x, w, y, M, N, K, ldx, warps, s);
-    if (M <= 32) return launch_skinny<2, NT, ACT, OutT>(x, w, y, M, N, K, ldx, warps, s);
-    if (M <= 48) return launch_skinny<3, NT, ACT, OutT>(x, w, y, M, N, K, ldx, warps, s);
-    return launch_skinny<4, NT, ACT, OutT>(x, w, y, M, N, K, ldx, warps, s);
+template <int NT, typename OutT>
+static int pick_mt(const void* x, const void* w, void* y, int M, int N, int K, int warps, cudaStream_t s) {
+    if (M <= 16) return launch_skinny<1, NT, 0, 0, OutT>(x, w, y, M, N, K, warps, nullptr, nullptr, nullptr, 0.f, s);
+    if (M <= 32) return launch_skinny<2, NT, 0, 0, OutT>(x, w, y, M, N, K, warps, nullptr, nullptr, nullptr, 0.f, s);
+    if (M <= 48) return launch_skinny<3, NT, 0, 0, OutT>(x, w, y, M, N, K, warps, nullptr, nullptr, nullptr, 0.f, s);
+    return launch_skinny<4, NT, 0, 0, OutT>(x, w, y, M, N, K, warps, nullptr, nullptr, nullptr, 0.f, s);
 }
 
-// x: [M, K] (act 0) or [M, 2K] (act 1: silu(x[:, :K]) * x[:, K:]); w: [N, K]; y: [M, N]
-// bfloat16 (out_f32 0) or float (out_f32 1).
-PLLM_EXPORT int pllm_skinny_gemm(const void* x, const void* w, void* y, int M, int N, int K, int act, int out_f32,
-                                 cudaStream_t stream) {
-    if (!pllm_skinny_gemm_supports(M, N, K) || act < 0 || act > 1) return PLLM_ERR_SIZE;
-    if (((uintptr_t)x | (uintptr_t)w) & 15) return PLLM_ERR_ALIGN;
-    const int ldx = act ? 2 * K : K;
-    // Tiles of 16 rows of W while that still gives every SM several CTAs, else of 8;
-    // K is split over the warps of a CTA in slices of at least 128.
-    const int nt = (N / 16 >= 2 * 148) ? 2 : 1;
-    const int ctas = N / (8 * nt);
-    // A warp's loads of 128 values of k are all issued before the first is used, so a slice
-    // of 128 costs one trip to memory: as many warps as give each such a slice (at most 16,
-    // and K must divide evenly into slices that are multiples of 32), unless the launch
-    // would then exceed what the SMs hold at once several times over.
+// K is split over the warps of a CTA.  A warp's loads of ``slice`` values of k are all
+// issued before the first is used, so a slice costs one trip to memory: as many warps as
+// give each such a slice (at most 16, and K must divide evenly into slices that are
+// multiples of 32), unless the launch would then exceed what the SMs hold at once
+// several times over.
+static int pick_warps(int K, int ctas, int slice) {
     int warps = 1;
     for (int wv = 2; wv <= 16; wv++)
-        if (K % (wv * 32) == 0 && K / wv >= 128 && (long long)ctas * wv <= 148LL * 64) warps = wv;
-    if (g_skinny_warps_override > 0 && K % (g_skinny_warps_override * 32) == 0) warps = g_skinny_warps_override;
-    if (out_f32) {
-        if (act) return PLLM_ERR_SIZE;
-        return nt == 2 ? pick_mt<2, 0, float>(x, w, y, M, N, K, ldx, warps, stream)
-                       : pick_mt<1, 0, float>(x, w, y, M, N, K, ldx, warps, stream);
-    }
-    if (act)
-        return nt == 2 ? pick_mt<2, 1, bf16>(x, w, y, M, N, K, ldx, warps, stream)
-                       : pick_mt<1, 1, bf16>(x, w, y, M, N, K, ldx, warps, stream);
-    return nt == 2 ? pick_mt<2, 0, bf16>(x, w, y, M, N, K, ldx, warps, stream)
-                   : pick_mt<1, 0, bf16>(x, w, y, M, N, K, ldx, warps, stream);
+        if (K % (wv * 32) == 0 && K / wv >= slice && (long long)ctas * wv <= 148LL * 64) warps = wv;
+    if (g_skinny_warps_override > 0 && g_skinny_warps_override <= 16 && K % (g_skinny_warps_override * 32) == 0)
+        warps = g_skinny_warps_override;
+    return warps;
 }
+
+// x: [M, K]; w: [N, K]; y: [M, N] bfloat16 (out_f32 0) or float (out_f32 1).
+PLLM_EXPORT int pllm_skinny_gemm(const void* x, const void* w, void* y, int M, int N, int K, int out_f32,
+                                 cudaStream_t stream) {
+    if (!pllm_skinny_gemm_supports(M, N, K)) return PLLM_ERR_SIZE;
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return PLLM_ERR_ALIGN;
+    // Tiles of 16 rows of W while that still gives every SM several CTAs, else of 8.
+    const int nt = (N / 16 >= 2 * 148) ? 2 : 1;
+    const int warps = pick_warps(K, N / (8 * nt), 128);
+    if (out_f32)
+        return nt == 2 ? pick_mt<2, float>(x, w, y, M, N, K, warps, stream) : pick_mt<1, float>(x, w, y, M, N, K, warps, stream);
+    return nt == 2 ? pick_mt<2, bf16>(x, w, y, M, N, K, warps, stream) : pick_mt<1, bf16>(x, w, y, M, N, K, warps, stream);
+}
+
+// The forms with work folded in, for up to 16 rows, all bfloat16:
+//   gain != null (up to 8 rows, K <= 2048): y = (rmsnorm(x + delta) * gain) . W^T; delta may be null (no add);
+//     residual_out (may be null) receives x + delta and must not overlap x or delta.
+//   glu != 0: w is [2N, K], gate rows then up rows, and y[M, N] = silu(gate) * up.
+PLLM_EXPORT int pllm_skinny_gemm_fused(const void* x, const void* delta, void* residual_out, const float* gain, float eps,
+                                       const void* w, void* y, int M, int N, int K, int glu, cudaStream_t stream) {
+    if (!pllm_skinny_gemm_fused_supports(M, N, K, gain != nullptr)) return PLLM_ERR_SIZE;
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)delta | (uintptr_t)residual_out | (uintptr_t)gain) & 15)
+        return PLLM_ERR_ALIGN;
+    if (residual_out && (residual_out == x || residual_out == delta)) return PLLM_ERR_ALIGN;
+    const int pro = gain != nullptr;
+    if (!pro && !glu) return pllm_skinny_gemm(x, w, y, M, N, K, 0, stream);
+    // With the norm a CTA needs more registers and three fit an SM: tiles of 16 rows of W as
+    // soon as tiles of 8 would not all be resident at once.
+    const int nt = glu ? 2 : ((pro ? N / 8 > 3 * 148 : N / 16 >= 2 * 148) ? 2 : 1);
+    const int ctas = glu ? N / 8 : N / (8 * nt);
+    const int warps = pro ? K / 128 : pick_warps(K, ctas, 128);
+    if (!pro) return launch_skinny<1, 2, 0, 1, bf16>(x, w, y, M, N, K, warps, nullptr, nullptr, nullptr, 0.f, stream);
+#define PLLM_SKINNY_PRO(NT_, EPI_)                                                                                     \
+    (warps <= 8 ? launch_skinny<1, NT_, 2, EPI_, bf16, 8>(x, w, y, M, N, K, warps, delta, residual_out, gain, eps, stream) \
+                : launch_skinny<1, NT_, 2, EPI_, bf16>(x, w, y, M, N, K, warps, delta, residual_out, gain, eps, stream))
+    if (glu) return PLLM_SKINNY_PRO(2, 1);
+    return nt == 2 ? PLLM_SKINNY_PRO(2, 0) : PLLM_SKINNY_PRO(1, 0);
+#undef PLLM_SKINNY_PRO
+}
+
+PLLM_TRACE_EXPORT(skinny_gemm)

@@ -48,7 +48,9 @@ def lib():
             "pllm_sample": [P, c_int, c_int, c_ll, P, P, P, P, P],
             "pllm_sample_scratch_floats": [c_int, c_int],
             "pllm_skinny_gemm_supports": [c_int, c_int, c_int],
-            "pllm_skinny_gemm": [P, P, P, c_int, c_int, c_int, c_int, c_int, P],
+            "pllm_skinny_gemm": [P, P, P, c_int, c_int, c_int, c_int, P],
+            "pllm_skinny_gemm_fused_supports": [c_int, c_int, c_int, c_int],
+            "pllm_skinny_gemm_fused": [P, P, P, P, c_float, P, P, c_int, c_int, c_int, c_int, P],
             "pllm_attention_mma_supports": [c_int, c_int, c_int, c_int],
             "pllm_attention_mma_tile_tokens": [c_int, c_int],
             "pllm_attention_mma": [P, P, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -323,6 +325,12 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
 
 
 SKINNY_GEMM = True  # few rows in bfloat16 go to this library's weight-streaming kernel
+# ... which can also take the residual add and the norm before it (PAGED_LLM_FUSE_NORM=1).  Off: in a
+# captured step of the 0.6B shape it saves two launches a layer but its CTAs need more registers, and
+# the step was no faster (batch 1: 0.956 against 0.950 ms, batch 4: 1.200 against 1.141, batch 8: 1.527
+# against 1.524).
+FUSE_NORM = os.environ.get("PAGED_LLM_FUSE_NORM", "0") == "1"
+FUSE_GLU = os.environ.get("PAGED_LLM_FUSE_GLU", "1") != "0"     # ... and the gated activation after it
 
 
 def skinny_gemm_takes(x: torch.Tensor, weight: torch.Tensor, k: Optional[int] = None) -> bool:
@@ -342,48 +350,144 @@ SKINNY_MAX_M = 16
 SKINNY_MAX_N = 32768
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None, gated: bool = False,
-           out_dtype: Optional[torch.dtype] = None, fuse_gate: bool = False) -> torch.Tensor:
+class NormedInput:
+    """rmsnorm(residual + delta) * gain, not yet formed: what a norm hands to a part
+    whose first operation is a product (``linear`` or ``linear_glu``), so that the
+    add, the norm and the product can be one kernel.  ``residual_out`` is where
+    residual + delta is stored (a buffer of its own, or ``residual`` itself when
+    there is no delta); it is valid once the input was consumed or ``tensor()``
+    was called."""
+
+    def __init__(self, residual: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor, eps: float):
+        self.residual, self.delta, self.gain, self.eps = residual, delta, gain, float(eps)
+        self.residual_out = residual if delta is None else torch.empty_like(residual)
+        self.consumed = False
+        self._tensor: Optional[torch.Tensor] = None
+
+    @property
+    def shape(self):
+        return self.residual.shape
+
+    @property
+    def dtype(self):
+        return self.residual.dtype
+
+    @property
+    def device(self):
+        return self.residual.device
+
+    def tensor(self) -> torch.Tensor:
+        """The normed rows as a tensor (the norm kernel runs now, once)."""
+        if self._tensor is None:
+            out = torch.empty_like(self.residual)
+            rmsnorm(self.residual, self.gain, self.eps, out, delta=self.delta,
+                    residual_out=self.residual_out if self.delta is not None else None)
+            self._tensor, self.consumed = out, True
+        return self._tensor
+
+
+def deferred_norm_pays(rows: int, width: int, dtype: torch.dtype) -> bool:
+    """Whether a product's kernel would take the add and the norm for rows of this
+    shape (few rows of a decode step in bfloat16); otherwise the norm kernel is
+    the better route and the norm should run at once."""
+    return SKINNY_GEMM and FUSE_NORM and dtype == torch.bfloat16 \
+        and bool(lib().pllm_skinny_gemm_fused_supports(rows, 16, width, 1))
+
+
+def as_tensor(x) -> torch.Tensor:
+    """A part that does anything but a product with its input first calls this."""
+    return x.tensor() if isinstance(x, NormedInput) else x
+
+
+def fused_linear_takes(x, weight: torch.Tensor, n_out: int) -> bool:
+    """Whether the product's kernel can take the norm before it or the gate after."""
+    if not SKINNY_GEMM or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or len(x.shape) != 2:
+        return False
+    normed = isinstance(x, NormedInput) and x._tensor is None
+    return n_out <= SKINNY_MAX_N and bool(lib().pllm_skinny_gemm_fused_supports(x.shape[0], n_out, weight.shape[1],
+                                                                                1 if normed else 0))
+
+
+def _fused(x, weight: torch.Tensor, n_out: int, glu: bool) -> torch.Tensor:
+    M, K = x.shape
+    out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
+    if isinstance(x, NormedInput) and x._tensor is None:
+        _dev(x.residual, x.delta, x.gain, weight)
+        _f32(x.gain, "gain")
+        res_out = x.residual_out if x.delta is not None else None
+        _check(lib().pllm_skinny_gemm_fused(_ptr(x.residual), _ptr(x.delta), _ptr(res_out), _ptr(x.gain), x.eps,
+                                            _ptr(weight), _ptr(out), M, n_out, K, 1 if glu else 0, _stream()),
+               "skinny_gemm_fused")
+        x.consumed = True
+    else:
+        x = as_tensor(x)
+        _dev(x, weight)
+        _check(lib().pllm_skinny_gemm_fused(_ptr(x), None, None, None, 0.0, _ptr(weight), _ptr(out), M, n_out, K,
+                                            1 if glu else 0, _stream()), "skinny_gemm_fused")
+    return out
+
+
+def linear(x, weight: torch.Tensor, out: Optional[torch.Tensor] = None, gated: bool = False,
+           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """y = x W^T with W stored [out, in].
 
-    Few rows (a decode step, up to 64) in bfloat16 run this library's
-    weight-streaming kernel.  With ``gated`` the input is [g | u] of twice W's
-    width and the product is taken of silu(g) * u, the gated feed-forward's
-    activation: by the activation kernel first, or with ``fuse_gate`` inside the
-    weight-streaming kernel.  Everything else is the library
-    matrix product (cuBLAS through torch), which is where the reference uses a
-    library too (crates/pagedllm/src/model/layers.rs:27-35).  float32 inputs run
-    in true float32: the engine switches TF32 off."""
+    Few rows (a decode step) in bfloat16 run this library's weight-streaming
+    kernel, which also takes a ``NormedInput`` (add, norm and product in one
+    kernel).  With ``gated`` the input is [g | u] of twice W's width and the
+    product is taken of silu(g) * u, formed by the activation kernel first.
+    Everything else is the library matrix product (cuBLAS through torch), which
+    is where the reference uses a library too
+    (crates/pagedllm/src/model/layers.rs:27-35).  float32 inputs run in true
+    float32: the engine switches TF32 off."""
+    N, K = weight.shape
+    if isinstance(x, NormedInput):
+        if not gated and out is None and out_dtype in (None, torch.bfloat16) and fused_linear_takes(x, weight, N) \
+                and x.shape[-1] == K:
+            return _fused(x, weight, N, glu=False)
+        x = x.tensor()
     if not x.is_cuda:
         raise KernelError("linear: input is not on a CUDA device: there is no CPU path")
-    N, K = weight.shape
     if x.shape[-1] != (2 * K if gated else K):
         raise KernelError(f"linear: input width {x.shape[-1]} does not fit a weight of {tuple(weight.shape)}")
     want = out_dtype or x.dtype
-    if gated and not fuse_gate:
-        # Measured on a B200 (batch 8, 3072 -> 1024): forming silu(g) * u inside the product
-        # repeats it in each of the 128 CTAs and costs 31 us against 3.4 + 6 us for a pass
-        # of its own followed by the plain product.
+    if gated:
+        # Forming silu(g) * u inside the product that consumes it repeats it in every CTA
+        # (measured 31 us against 3.4 + 6 us at batch 8, 3072 -> 1024): a pass of its own here,
+        # or the epilogue of the product that makes [g | u] (linear_glu).
         act = torch.empty((x.shape[0], K), dtype=x.dtype, device=x.device)
         swiglu(x, act)
-        x, gated = act, False
+        x = act
     # The widest products (the output head) stay with the library, which is faster there
     # (measured 54 us against 66 us at 151936 x 1024, batch 8).
-    if skinny_gemm_takes(x, weight, K) and N <= SKINNY_MAX_N and want in (torch.bfloat16, torch.float32) \
-            and not (gated and want != torch.bfloat16):
+    if skinny_gemm_takes(x, weight, K) and N <= SKINNY_MAX_N and want in (torch.bfloat16, torch.float32):
         _dev(x, weight, out)
         M = x.shape[0]
         if out is None:
             out = torch.empty((M, N), dtype=want, device=x.device)
         elif out.shape != (M, N) or out.dtype != want:
             raise KernelError("linear: out does not fit")
-        _check(lib().pllm_skinny_gemm(_ptr(x), _ptr(weight), _ptr(out), M, N, K, 1 if gated else 0,
+        _check(lib().pllm_skinny_gemm(_ptr(x), _ptr(weight), _ptr(out), M, N, K,
                                       1 if want == torch.float32 else 0, _stream()), "skinny_gemm")
         return out
-    if gated:
-        act = torch.empty((x.shape[0], K), dtype=x.dtype, device=x.device)
-        swiglu(x, act)
-        x = act
     if want != x.dtype:
         return torch.mm(x, weight.t(), out_dtype=want)
     return torch.matmul(x, weight.t(), out=out) if out is not None else torch.matmul(x, weight.t())
+
+
+def linear_glu(x, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) for W = [Wg; Wu] stacked [2I, K]: the gated
+    feed-forward's first half (crates/pagedllm/src/model/layers.rs:93-99).  Few
+    rows in bfloat16: one kernel whose CTAs hold the same columns of both halves
+    (and which takes a ``NormedInput``); otherwise the product, then the
+    activation kernel."""
+    two_i, K = w_gate_up.shape
+    if two_i % 2:
+        raise KernelError("linear_glu: the stacked weight needs an even number of rows")
+    inter = two_i // 2
+    if x.shape[-1] != K:
+        raise KernelError(f"linear_glu: input width {x.shape[-1]} does not fit a weight of {tuple(w_gate_up.shape)}")
+    if FUSE_GLU and fused_linear_takes(x, w_gate_up, inter):
+        return _fused(x, w_gate_up, inter, glu=True)
+    gu = linear(x, w_gate_up)
+    act = torch.empty((gu.shape[0], inter), dtype=gu.dtype, device=gu.device)
+    return swiglu(gu, act)

@@ -59,6 +59,8 @@ class GQAttention(Mixer):
             self._need = KVNeed("window" if self.window else "full", self.nkv, self.hd, self.window, swizzled)
         return self._need
 
+    takes_normed_input = True
+
     def forward(self, x, step, cache, writes_cache=True):
         k_pool, v_pool, gi = cache
         g = step.groups[gi]

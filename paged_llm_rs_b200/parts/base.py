@@ -141,6 +141,13 @@ class Norm(Part):
                 return self.forward(residual.index_select(0, rows.long()) + delta.index_select(0, rows.long()))
         return self.forward(residual, rows)
 
+    def add_norm_deferred(self, residual: torch.Tensor, delta: Optional[torch.Tensor]):
+        """The same as ``add_norm`` but not yet run: an object that the kernels'
+        products take in place of a tensor (ops.NormedInput), whose ``residual_out``
+        is the new residual stream; or None when this norm has no such form for
+        these rows.  Only handed to parts with ``takes_normed_input``."""
+        return None
+
 
 class PositionEncoding(Part):
     """Built once per model and handed to the mixers that name it."""
@@ -152,6 +159,9 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True when forward() hands x straight to a product (ops.linear / ops.linear_glu), so
+    # that the block may pass a norm that is not yet formed (ops.NormedInput) instead of a tensor.
+    takes_normed_input = False
     # True when forward() only launches kernels whose arguments do not depend on the
     # step's contents, so that a decode step can be captured once and replayed.
     graph_safe = False
@@ -168,6 +178,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_normed_input = False   # as for Mixer
+
     def forward(self, x: torch.Tensor, step: StepState) -> torch.Tensor:
         raise NotImplementedError
 

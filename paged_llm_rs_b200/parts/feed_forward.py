@@ -1,6 +1,7 @@
 """The gated feed-forward, down(silu(gate(x)) * up(x))
 (crates/pagedllm/src/model/layers.rs:67-106).  gate and up are one matrix
-product over the stacked weights; the activation kernel reads both halves."""
+product over the stacked weights, with the activation in its epilogue for the
+few rows of a decode step and as a kernel of its own otherwise."""
 
 from __future__ import annotations
 
@@ -27,10 +28,10 @@ class SwiGLUMLP(FeedForward):
         self.w_gate_up = torch.cat([tensors[self._name("gate_proj.weight")], tensors[self._name("up_proj.weight")]], 0)
         self.w_down = tensors[self._name("down_proj.weight")]
 
+    takes_normed_input = True
+
     def forward(self, x, step):
-        gu = ops.linear(x, self.w_gate_up)
-        # silu(gate) * up: inside the down projection's kernel for a decode step, a pass of its own otherwise
-        return ops.linear(gu, self.w_down, gated=True)
+        return ops.linear(ops.linear_glu(x, self.w_gate_up), self.w_down)
 
 
 register_feed_forward("swiglu_mlp", SwiGLUMLP)

@@ -1,6 +1,7 @@
 """RMSNorm (crates/pagedllm/src/model/layers.rs:40-65): x / sqrt(mean(x^2) + eps)
 times a gain, the statistic in float.  ``add_norm`` fuses the residual add that
-precedes it (crates/pagedllm/src/model/mod.rs:131-132) into the same kernel."""
+precedes it (crates/pagedllm/src/model/mod.rs:131-132) into the same kernel;
+``add_norm_deferred`` leaves both to the product that follows (a decode step)."""
 
 from __future__ import annotations
 
@@ -35,6 +36,12 @@ class RMSNorm(Norm):
         # With rows the sum is formed for those rows only and not stored.
         return ops.rmsnorm(residual, self.gain, self.eps, out, delta=delta,
                            residual_out=residual if (delta is not None and rows is None) else None, rows=rows)
+
+    def add_norm_deferred(self, residual, delta):
+        # the few rows of a decode step in bfloat16: the product that follows does the add and the norm
+        if not ops.deferred_norm_pays(residual.shape[0], self.width, residual.dtype):
+            return None
+        return ops.NormedInput(residual, delta, self.gain, self.eps)
 
 
 register_norm("rmsnorm", RMSNorm)

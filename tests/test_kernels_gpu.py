@@ -366,8 +366,83 @@ def test_skinny_gemm(M, N, K):
     a = gu.float()[:, :K]
     act = (a * torch.sigmoid(a) * gu.float()[:, K:]).bfloat16().float()
     torch.testing.assert_close(ops.linear(gu, w, gated=True).float(), act @ w.float().T, atol=3e-2, rtol=3e-2)
-    torch.testing.assert_close(ops.linear(gu, w, gated=True, fuse_gate=True).float(), act @ w.float().T, atol=3e-2, rtol=3e-2)
     ops.SKINNY_MAX_N, ops.SKINNY_MAX_M = 32768, 16
+
+
+def _rms_ref(h, gain, eps):
+    return h * torch.rsqrt((h * h).mean(-1, keepdim=True) + eps) * gain
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 16])
+@pytest.mark.parametrize("N,K", [(1024, 1024), (4096, 1024), (304, 384), (48, 3072), (16, 128), (4096, 2048)])
+@pytest.mark.parametrize("with_delta", [True, False])
+def test_product_with_the_add_and_the_norm_folded_in(M, N, K, with_delta):
+    g = torch.Generator(device=DEV).manual_seed(M * 77 + N + K)
+    res = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    delta = torch.randn(M, K, device=DEV, generator=g).bfloat16() if with_delta else None
+    gain = 1 + 0.2 * torch.randn(K, device=DEV, generator=g)
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    eps = 1e-5
+    res0, delta0 = res.clone(), (delta.clone() if with_delta else None)
+    h = (res.float() + delta.float()).bfloat16().float() if with_delta else res.float()
+    want = _rms_ref(h, gain, eps).bfloat16().float() @ w.float().T
+    x = ops.NormedInput(res, delta, gain, eps)
+    assert ops.fused_linear_takes(x, w, N) == (M <= 8 and K <= 2048)     # else the norm kernel, then the product
+    y = ops.linear(x, w)
+    assert x.consumed and y.dtype == torch.bfloat16
+    torch.testing.assert_close(y.float(), want, atol=2e-2, rtol=2e-2)
+    # the new residual stream is the rounded sum, bit for bit; the inputs are untouched
+    assert torch.equal(x.residual_out.float(), h)
+    assert torch.equal(res, res0) and (not with_delta or torch.equal(delta, delta0))
+    if with_delta:
+        assert x.residual_out.data_ptr() not in (res.data_ptr(), delta.data_ptr())
+    # the unfused route gives the same within rounding
+    x2 = ops.NormedInput(res, delta, gain, eps)
+    y2 = ops.linear(x2.tensor(), w)
+    torch.testing.assert_close(y.float(), y2.float(), atol=2e-2, rtol=2e-2)
+    assert torch.equal(x2.residual_out, x.residual_out)
+
+
+@pytest.mark.parametrize("M", [1, 7, 16])
+@pytest.mark.parametrize("I,K", [(3072, 1024), (304, 384), (16, 128), (1000, 256)])
+@pytest.mark.parametrize("normed", [True, False])
+def test_gate_and_up_product_with_the_activation_folded_in(M, I, K, normed):
+    g = torch.Generator(device=DEV).manual_seed(M * 31 + I + K)
+    res = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    delta = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    gain = 1 + 0.2 * torch.randn(K, device=DEV, generator=g)
+    w = (torch.randn(2 * I, K, device=DEV, generator=g) * 0.05).bfloat16()
+    if normed:
+        h = (res.float() + delta.float()).bfloat16().float()
+        xin = _rms_ref(h, gain, 1e-6).bfloat16().float()
+        x = ops.NormedInput(res, delta, gain, 1e-6)
+    else:
+        xin, x = res.float(), res
+    gu = (xin @ w.float().T).bfloat16().float()
+    want = gu[:, :I] * torch.sigmoid(gu[:, :I]) * gu[:, I:]
+    if I % 16 == 0 and (M <= 8 or not normed):
+        assert ops.fused_linear_takes(x, w, I)
+    y = ops.linear_glu(x, w)
+    assert y.shape == (M, I)
+    torch.testing.assert_close(y.float(), want, atol=2e-2, rtol=3e-2)
+    if normed:
+        assert x.consumed and torch.equal(x.residual_out.float(), h)
+
+
+def test_deferred_norm_falls_back_for_shapes_the_kernel_refuses():
+    g = torch.Generator(device=DEV).manual_seed(5)
+    for M, N, K, dt in ((40, 256, 256, torch.bfloat16), (4, 250, 256, torch.bfloat16), (4, 256, 200, torch.bfloat16),
+                        (4, 256, 256, torch.float32)):
+        res = torch.randn(M, K, device=DEV, generator=g).to(dt)
+        delta = torch.randn(M, K, device=DEV, generator=g).to(dt)
+        gain = 1 + 0.2 * torch.randn(K, device=DEV, generator=g)
+        w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).to(dt)
+        h = (res.float() + delta.float()).to(dt).float()
+        want = _rms_ref(h, gain, 1e-6).to(dt).float() @ w.float().T
+        x = ops.NormedInput(res, delta, gain, 1e-6)
+        t = dict(atol=2e-2, rtol=2e-2) if dt == torch.bfloat16 else dict(atol=1e-4, rtol=1e-4)
+        torch.testing.assert_close(ops.linear(x, w).float(), want, **t)
+        assert x.consumed and torch.equal(x.residual_out.float(), h)
 
 
 def test_linear_falls_back_to_the_library_for_other_shapes():
