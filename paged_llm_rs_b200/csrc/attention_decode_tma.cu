@@ -40,7 +40,7 @@
 #define TD_QROWS 64      // query rows (token, head) a CTA may hold
 #define TD_SPIN_LIMIT (1 << 18)
 
-struct AttnWork { int seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slot, unused; };
+struct AttnWork { int seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slot, split; };   // split: count << 16 | index
 
 namespace {
 
@@ -103,7 +103,7 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
     const int* __restrict__ block_tables, const AttnWork* __restrict__ work, const int* __restrict__ n_work_ptr,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     int nh, int nkv, int page_size, int page_shift, int n_pages, int table_width, float scale_log2,
-    int heads_per_cta, int kinds_mask, int* status) {
+    int heads_per_cta, int kinds_mask, int* counters, int* status) {
     // The work items and block tables came from the host before the step, and the cache below
     // the step's own positions was written by earlier steps: neither depends on the kernels
     // just before this one.  So nobody waits for those kernels yet: the producer starts the
@@ -352,12 +352,14 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
     }
     pdl_launch_dependents();   // the key tiles are done: the next kernel's CTAs may take their places
+    // (named barriers from here on: the producer warp has left)
+    asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
+    if (*abort_flag) {   // set before the warp that gave up reached the barrier: all see it alike
+        if (threadIdx.x == 0) atomicOr(status, 16);
+        return;
+    }
     if (!decode) {
         // ---- several query tokens: every warp owns its rows' results ----------------------------
-        if (!alive || *abort_flag) {
-            if (lane == 0) atomicOr(status, 16);
-            return;
-        }
 #pragma unroll
         for (int i = 0; i < 2; i++) {
             const int r = i ? r1 : r0;
@@ -377,14 +379,8 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
                 if ((lane & 3) == 0) { part_ml[pr * 2] = m_run[i] * 0.6931471805599453f; part_ml[pr * 2 + 1] = l_run[i]; }
             }
         }
-        return;
-    }
-    // ---- the four warps' results meet (named barrier: the producer warp has left) ---------------
-    asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
-    if (*abort_flag) {
-        if (threadIdx.x == 0) atomicOr(status, 16);
-        return;
-    }
+    } else {
+    // ---- one query token: the four warps' results meet ---------------------------------------
     float* o_s = reinterpret_cast<float*>(smem);          // [4][16][HD]; the ring is no longer read
     float* ml_s = o_s + TD_CONSUMERS * 16 * HD;           // [4][16][2]
 #pragma unroll
@@ -421,6 +417,73 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
             if (c == 0) { part_ml[pr * 2] = M * 0.6931471805599453f; part_ml[pr * 2 + 1] = L; }   // natural-log units
         }
     }
+    }
+
+    // ---- the splits of a tile are combined by whichever of their CTAs finishes last ----------------
+    // (no kernel of its own for it, and no CTA waits for another: each adds one to the tile's
+    // counter after its partial results are out, and the one that brings it to the number of
+    // splits reads them all back, in the order of the splits whoever it is, with the arithmetic
+    // of attention_reduce_kernel.  It leaves the counter at zero for the next launch.)
+    if (counters == nullptr || w.part_slot < 0) return;
+    const int n_split = w.split >> 16, k_split = w.split & 0xffff;
+    int* last_s = reinterpret_cast<int*>(const_cast<int*>(abort_flag)) + 2;
+    __threadfence();
+    asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
+    if (threadIdx.x == 0) {
+        int* c = counters + (size_t)((int)blockIdx.y - k_split) * gridDim.x + blockIdx.x;
+        const int last = atomicAdd(c, 1) == n_split - 1;
+        if (last) *c = 0;
+        *last_s = last;
+    }
+    asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
+    if (!*last_s) return;
+    __threadfence();
+    float* wgt = reinterpret_cast<float*>(smem) + TD_CONSUMERS * 16 * HD + TD_CONSUMERS * 16 * 2 + warp * 128;   // [4][128]
+    const int first = w.part_slot - k_split * w.q_count, stride = w.q_count;
+    for (int r = warp; r < rows; r += TD_CONSUMERS) {
+        const int tq = r / n_heads, head = head0 + r % n_heads;
+        float M = -CUDART_INF_F;
+        for (int sp = lane; sp < n_split; sp += 32) M = fmaxf(M, __ldcg(part_ml + ((size_t)(first + sp * stride + tq) * nh + head) * 2));
+        M = warp_max(M);
+        float L = 0.f;
+        for (int sp = lane; sp < n_split; sp += 32) {
+            const size_t pr = (size_t)(first + sp * stride + tq) * nh + head;
+            const float ms = __ldcg(part_ml + pr * 2);
+            const float f = ms == -CUDART_INF_F ? 0.f : expf(ms - M);
+            wgt[sp] = f;
+            L += __ldcg(part_ml + pr * 2 + 1) * f;
+        }
+        L = warp_sum(L);
+        const float inv = L > 0.f ? 1.0f / L : 0.f;
+        __syncwarp();
+        // every lane owns HD / 32 outputs; the partial results of eight splits are fetched
+        // together (they come from L2, written by other SMs) and then added in the splits' order
+        constexpr int DPL = HD / 32;
+        float o[DPL];
+#pragma unroll
+        for (int j = 0; j < DPL; j++) o[j] = 0.f;
+        const float* po = part_o + ((size_t)(first + tq) * nh + head) * HD + lane;
+        const size_t sp_stride = (size_t)stride * nh * HD;
+        for (int sp0 = 0; sp0 < n_split; sp0 += 8) {
+            float v[8][DPL];
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < DPL; j++)
+                    v[i][j] = sp0 + i < n_split ? __ldcg(po + (size_t)(sp0 + i) * sp_stride + 32 * j) : 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                if (sp0 + i >= n_split) break;
+                const float f = wgt[sp0 + i];
+#pragma unroll
+                for (int j = 0; j < DPL; j++) o[j] = fmaf(v[i][j], f, o[j]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < DPL; j++)
+            out[((size_t)(w.q_token0 + tq) * nh + head) * HD + lane + 32 * j] = __float2bfloat16_rn(o[j] * inv);
+        __syncwarp();
+    }
 }
 
 // Whether this kernel takes decode items of this shape and cache layout.
@@ -432,7 +495,7 @@ PLLM_EXPORT int pllm_attention_decode_tma_supports(int dtype, int nh, int nkv, i
 template <int HD>
 static int launch_tma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables, const int* work,
                       const int* n_work_ptr, int max_work, void* out, float* part_o, float* part_ml, int nh, int nkv,
-                      int page_size, int n_pages, int table_width, float scale, int kinds_mask, int* status,
+                      int page_size, int n_pages, int table_width, float scale, int kinds_mask, int* counters, int* status,
                       cudaStream_t stream) {
     const int group = nh / nkv;
     const int heads_per_cta = group < 16 ? group : 16;
@@ -444,22 +507,22 @@ static int launch_tma(const void* q, const void* k_pool, const void* v_pool, con
     launch_chained(attention_decode_tma_kernel<HD>, dim3(nkv * gparts, max_work), dim3((TD_CONSUMERS + 1) * 32), smem, stream,
                    (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
                    n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
-                   scale * 1.4426950408889634f, heads_per_cta, kinds_mask, status);
+                   scale * 1.4426950408889634f, heads_per_cta, kinds_mask, counters, status);
     return launch_status();
 }
 
 PLLM_EXPORT int pllm_attention_decode_tma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables,
                                           const int* work, const int* n_work_ptr, int max_work, void* out,
                                           float* part_o, float* part_ml, int nh, int nkv, int hd, int page_size,
-                                          int n_pages, int table_width, float scale, int kinds_mask, int* status,
-                                          cudaStream_t stream) {
+                                          int n_pages, int table_width, float scale, int kinds_mask, int* counters,
+                                          int* status, cudaStream_t stream) {
     if (max_work <= 0) return PLLM_OK;
     if (!pllm_attention_decode_tma_supports(PLLM_BF16, nh, nkv, hd, page_size, 0)) return PLLM_ERR_SIZE;
     if (hd == 128)
         return launch_tma<128>(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv,
-                               page_size, n_pages, table_width, scale, kinds_mask, status, stream);
+                               page_size, n_pages, table_width, scale, kinds_mask, counters, status, stream);
     return launch_tma<64>(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv,
-                          page_size, n_pages, table_width, scale, kinds_mask, status, stream);
+                          page_size, n_pages, table_width, scale, kinds_mask, counters, status, stream);
 }
 
 PLLM_TRACE_EXPORT(attention_decode_tma)

@@ -14,7 +14,7 @@
 //
 // Work comes as a list of items prepared on the host, one CTA per (item, kv
 // head, part of the group):
-//   item = {seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slot, unused}
+//   item = {seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slot, split}
 // q_count consecutive tokens of one request (token index q_token0.. in the step,
 // positions q_pos0..) attend over keys [kv_begin, kv_end) of the request's block
 // table row `seg`.  part_slot < 0: the item sees all keys its queries may see and
@@ -26,7 +26,7 @@
 #define ATT_MAX_ROWS 16  // query rows (token x head of the group) per CTA, one warp each
 #define ATT_MAX_HD 256
 
-struct AttnWork { int seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slot, unused; };
+struct AttnWork { int seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slot, split; };   // split: count << 16 | index (0: not split)
 
 template <typename T>
 __global__ void attention_generic_kernel(

@@ -29,7 +29,7 @@
 #define MMA_STAGES 3
 #define MMA_ROWS 64
 
-struct AttnWork { int seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slot, unused; };
+struct AttnWork { int seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slot, split; };   // split: count << 16 | index (0: not split)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

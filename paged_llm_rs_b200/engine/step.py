@@ -61,6 +61,7 @@ class StepPacker:
         self.cache, self.plans, self.target_ctas = cache, plans, target_ctas
         self.vocab_size, self.max_positions, self.device = vocab_size, max_positions, device
         self._scratch: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self._counters: Dict[int, torch.Tensor] = {}
 
     def scratch(self, gi: int, parts: int, nh_hd: Tuple[int, int]) -> Tuple[torch.Tensor, torch.Tensor]:
         """Partial-result buffers of group gi for at least ``parts`` rows."""
@@ -71,6 +72,16 @@ class StepPacker:
             cur = (torch.empty((rows, nh, hd), dtype=torch.float32, device=self.device),
                    torch.empty((rows, nh, 2), dtype=torch.float32, device=self.device))
             self._scratch[gi] = cur
+        return cur
+
+    def counters(self, gi: int, max_work: int) -> torch.Tensor:
+        """Zeros for the kernel that combines split items itself (one per work item and CTA of
+        it); the kernel leaves them zero, so they are made once and grown when needed."""
+        n = max(max_work, 1) * self.plans[gi].ctas_per_item
+        cur = self._counters.get(gi)
+        if cur is None or cur.numel() < n:
+            cur = torch.zeros(n, dtype=torch.int32, device=self.device)
+            self._counters[gi] = cur
         return cur
 
     def pack(self, entries: Sequence[StepEntry], heads: List[Tuple[int, int]],
@@ -223,7 +234,7 @@ class StepPacker:
                 slots=view(f"g{gi}.slots", T),
                 work=view(f"g{gi}.work").view(-1, 8), n_work=view(f"g{gi}.n_work"), max_work=gs["max_work"],
                 red=view(f"g{gi}.red").view(-1, 4), n_red=view(f"g{gi}.n_red"), max_red=gs["max_red"],
-                part_o=part_o, part_ml=part_ml, kinds=sizes["kinds"]))
+                part_o=part_o, part_ml=part_ml, kinds=sizes["kinds"], counters=self.counters(gi, gs["max_work"])))
         state = StepState(n_tokens=T, tokens=view("tokens", T), positions=view("positions", T), groups=groups,
                           logit_rows=view("logit_rows", nw), n_wanted=nw,
                           segments=view("segments").view(-1, 4), host_segments=list(sizes["host_segments"]))

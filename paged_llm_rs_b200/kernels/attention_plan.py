@@ -9,7 +9,8 @@ combined by the reduce kernel, always in the same order.
 
 Item layout (int32 x 8): seg, first query token (index in the step), query
 tokens, position of the first query token, first key, one past the last key,
-first partial row or -1 when not split, unused.
+first partial row or -1 when not split, (splits << 16 | index of this split)
+or 0 when not split.  The splits of a tile are consecutive items.
 Reduction layout (int32 x 4): token index, first partial row, splits, stride
 between the token's partial rows.
 """
@@ -77,7 +78,9 @@ def plan_attention(segments: Sequence[Tuple[int, int, int]], tile_tokens: int, w
     rows_of = np.where(is_split, n_split * qn, 0)                  # partial rows a tile uses
     base = np.cumsum(rows_of) - rows_of
     part = np.where(is_split[tile_of], base[tile_of] + k * qn[tile_of], -1)
-    work = np.stack([seg[tile_of], q0[tile_of], qn[tile_of], p0[tile_of], begin, end, part, np.zeros(total, np.int64)], 1)
+    # which split of how many: the kernel that combines a tile's splits itself counts them off
+    split = np.where(is_split[tile_of], (n_split[tile_of] << 16) | k, 0)
+    work = np.stack([seg[tile_of], q0[tile_of], qn[tile_of], p0[tile_of], begin, end, part, split], 1)
     st = np.nonzero(is_split)[0]
     tile_r = np.repeat(st, qn[st])                                 # one reduction per token of a split tile
     t_in = np.arange(len(tile_r)) - np.repeat(np.cumsum(qn[st]) - qn[st], qn[st])

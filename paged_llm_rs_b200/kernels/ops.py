@@ -57,7 +57,7 @@ def lib():
                                    c_int, c_float, c_int, c_int, P, P],
             "pllm_attention_decode_tma_supports": [c_int, c_int, c_int, c_int, c_int, c_int],
             "pllm_attention_decode_tma": [P, P, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
-                                          c_float, c_int, P, P],
+                                          c_float, c_int, P, P, P],
         }
         sig["pllm_set_pdl"] = [c_int]
         for name, args in sig.items():
@@ -252,13 +252,17 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     work: torch.Tensor, n_work: torch.Tensor, max_work: int, out: torch.Tensor,
                     part_o: torch.Tensor, part_ml: torch.Tensor, red: torch.Tensor, n_red: torch.Tensor,
                     max_red: int, num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
-                    status: torch.Tensor, swizzled: bool = False, kinds: int = 3) -> torch.Tensor:
+                    status: torch.Tensor, swizzled: bool = False, kinds: int = 3,
+                    counters: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of the step's tokens over the paged cache, then the reduction of
     split items.  ``work`` is int32 [>=max_work, 8], ``red`` int32 [>=max_red, 4];
     n_work / n_red are int32 scalars on the device saying how many are live.
     ``swizzled`` says how the pools are laid out (see ``pool_is_swizzled``);
     ``kinds`` what the work items are: 1 single decoded tokens only, 2 portions of
-    several tokens only, 3 both, so that only the kernels with work are launched."""
+    several tokens only, 3 both, so that only the kernels with work are launched.
+    ``counters`` (int32 zeros, max_work x CTAs an item, left zero): with them the
+    bulk-copy kernel, where it takes all the work, combines the splits itself and
+    the reduction kernel is not launched."""
     _dev(q, k_pool, v_pool, block_tables, work, n_work, out, part_o, part_ml, red, n_red, status)
     for t, n in ((block_tables, "block_tables"), (work, "work"), (n_work, "n_work"), (red, "red"), (n_red, "n_red")):
         _i32(t, n)
@@ -283,11 +287,19 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                                                                         page_size, int(window)))
         take = (kinds & TMA_KINDS) if tma_ok else 0
         rest = kinds & ~take
+        group = num_heads // num_kv_heads
+        ctas_per_item = num_kv_heads * -(-group // min(group, 16))
+        fused = bool(FUSE_REDUCE and take and not rest and counters is not None
+                     and counters.numel() >= max_work * ctas_per_item)
+        if fused:
+            _dev(counters)
+            _i32(counters, "counters")
         if take:
             _check(L.pllm_attention_decode_tma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
                                                _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml),
                                                num_heads, num_kv_heads, head_dim, page_size, n_pages,
-                                               block_tables.shape[-1], float(scale), take, _ptr(status), _stream()),
+                                               block_tables.shape[-1], float(scale), take,
+                                               _ptr(counters) if fused else None, _ptr(status), _stream()),
                    "paged_attention (bulk copy)")
         if rest:
             _check(L.pllm_attention_mma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
@@ -295,6 +307,8 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                                         num_kv_heads, head_dim, page_size, n_pages, block_tables.shape[-1], int(window),
                                         float(scale), 1 if swizzled else 0, rest, _ptr(status), _stream()),
                    "paged_attention (mma)")
+        if fused:
+            return out
     else:
         if swizzled:
             raise KernelError("paged_attention: the generic kernel reads plain pools, not swizzled ones")
@@ -324,6 +338,11 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
     return tokens
 
 
+# Split items combined by the last CTA of each tile inside the bulk-copy kernel instead of by the
+# reduction kernel (PAGED_LLM_FUSE_REDUCE=1).  Off: the combining CTA's round trips to L2 come after
+# the attention instead of beside it, and a captured step of the 0.6B shape at 4096 tokens of context
+# was slower (batch 1: 1.011 against 0.948 ms, batch 8: 1.564 against 1.537; batch 64: 6.44 against 6.47).
+FUSE_REDUCE = os.environ.get("PAGED_LLM_FUSE_REDUCE", "0") == "1"
 SKINNY_GEMM = True  # few rows in bfloat16 go to this library's weight-streaming kernel
 # ... which can also take the residual add and the norm before it (PAGED_LLM_FUSE_NORM=1).  Off: in a
 # captured step of the 0.6B shape it saves two launches a layer but its CTAs need more registers, and

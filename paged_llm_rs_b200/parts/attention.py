@@ -77,7 +77,7 @@ class GQAttention(Mixer):
         o = torch.empty_like(q)
         ops.paged_attention(q, k_pool, v_pool, g.block_tables, g.work, g.n_work, g.max_work, o, g.part_o, g.part_ml,
                             g.red, g.n_red, g.max_red, self.nh, self.nkv, self.hd, self.window or 0, self.scale,
-                            self.rt.status, swizzled=swizzled, kinds=g.kinds)
+                            self.rt.status, swizzled=swizzled, kinds=g.kinds, counters=g.counters)
         return ops.linear(o, self.w_o)
 
 

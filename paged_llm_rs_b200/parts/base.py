@@ -85,6 +85,8 @@ class GroupStep:
     part_o: torch.Tensor        # float32 scratch for split items
     part_ml: torch.Tensor
     kinds: int = 3              # what the work items are: 1 single tokens only, 2 portions only, 3 both
+    counters: Optional[torch.Tensor] = None   # int32 zeros [max_work * CTAs an item]: a kernel that combines
+                                              # the splits itself counts them off here and leaves zeros
 
 
 @dataclass

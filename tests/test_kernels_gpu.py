@@ -157,7 +157,8 @@ def attention_ref(q, k, v, scale, window):
     return out
 
 
-def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, craft=None, kinds=3):
+def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, craft=None, kinds=3, counters=None,
+                  raw=False):
     """reqs: list of (context before the step, query tokens).  Builds a paged cache
     with shuffled pages, runs the kernel, returns (got, want) per request."""
     g = torch.Generator().manual_seed(seed)
@@ -209,8 +210,10 @@ def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, c
         ops.swizzle_pool_(kpd); ops.swizzle_pool_(vpd)
     ops.paged_attention(qd, kpd, vpd, dev(tables), workd, dev(torch.tensor([len(work)], dtype=torch.int32)),
                         len(work), out, part_o, part_ml, redd, dev(torch.tensor([len(red)], dtype=torch.int32)),
-                        len(red), nh, nkv, hd, window or 0, scale, st, swizzled=swz, kinds=kinds)
+                        len(red), nh, nkv, hd, window or 0, scale, st, swizzled=swz, kinds=kinds, counters=counters)
     assert st.item() == 0
+    if raw:
+        return out, len(red)
     res = []
     for (a, n, c), q, k, v in zip(segs, qs, ks, vs):
         want = attention_ref(q.float(), k.float(), v.float(), scale, window)
@@ -248,6 +251,25 @@ def test_decode_only_steps_take_the_bulk_copy_kernel(nh, nkv, hd, page):
     res, _ = run_attention(torch.bfloat16, [(100, 1), (40, 9), (513, 1), (0, 70)], nh, nkv, hd, page, None, 10 ** 6, kinds=3)
     for got, want in res:
         torch.testing.assert_close(got, want, **tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page", [(16, 8, 128, 16), (8, 1, 64, 8), (40, 2, 64, 16), (6, 3, 64, 32)])
+def test_bulk_copy_kernel_combines_its_splits_itself(nh, nkv, hd, page):
+    # the same steps with the reduction kernel and with the last CTA of each tile combining: equal
+    # bit for bit (same arithmetic, same order), twice in a row (the counters are left at zero)
+    decode = [(63, 1), (700, 1), (1023, 1), (15, 1), (331, 1), (2000, 1)]
+    mixed = [(100, 1), (400, 9), (513, 1), (0, 70), (900, 33)]
+    counters = torch.zeros(1 << 16, dtype=torch.int32, device=DEV)
+    for reqs, kinds in ((decode, 1), (mixed, 3)):
+        base, n_red = run_attention(torch.bfloat16, reqs, nh, nkv, hd, page, None, 10 ** 6, kinds=kinds, raw=True)
+        assert n_red > 0
+        launches = ops.LAUNCHES
+        for _ in range(2):
+            got, _ = run_attention(torch.bfloat16, reqs, nh, nkv, hd, page, None, 10 ** 6, kinds=kinds, counters=counters,
+                                   raw=True)
+            assert torch.equal(got, base)
+            assert int(counters.abs().sum()) == 0
+        assert ops.LAUNCHES - launches == 2          # one kernel a step: no reduction kernel
 
 
 def test_swizzled_cache_rows():
