@@ -136,6 +136,75 @@ def decode_point(runner, batch, context, steps, warmup, clocks):
     return ms, launches
 
 
+TRACE_KERNELS = {1: "embed", 2: "rmsnorm", 3: "swiglu", 4: "qk_norm_rope_kv", 5: "attention_generic", 6: "attention_reduce",
+                 7: "attention_mma", 8: "attention_tma", 9: "skinny_gemm", 10: "sample_partial", 11: "sample_final"}
+TRACE_FILES = ["elementwise", "qk_norm_rope_kv", "attention_generic", "attention_mma", "attention_decode_tma", "sampling",
+               "skinny_gemm"]
+
+
+def timeline(runner, batch, context, layers) -> int:
+    """One replay of the captured decode step, clocked by the kernels themselves (thread 0 of
+    each kernel's first CTA reads the global timer before and after its wait for the kernel
+    before it).  "to next" is the time from a kernel's wait ending to the next kernel's wait
+    ending: what the kernel costs in the chain.  "in place" is how long its first CTA sat on an
+    SM before its wait ended.  Library kernels (the output head) carry no stamps: their time
+    shows in the "to next" of the kernel before them."""
+    import ctypes
+    import numpy as np
+    import torch
+    from paged_llm_rs_b200.engine.step import StepEntry
+    from paged_llm_rs_b200.kernels import ops
+
+    lib = ops.lib()
+    buf = (ctypes.c_ulonglong * (8192 * 3))()
+
+    def read():
+        recs = []
+        for f in TRACE_FILES:
+            fn = getattr(lib, f"pllm_trace_read_{f}")
+            fn.restype = ctypes.c_int
+            n = fn(buf, 8192)
+            recs += [(buf[3 * i + 2], buf[3 * i + 1], int(buf[3 * i])) for i in range(n)]
+        return sorted(recs)
+
+    cache = runner.cache
+    ids = [f"t{b}" for b in range(batch)]
+    for r in ids:
+        cache.open(r)
+        assert cache.reserve(r, context)
+        cache.commit(r, context - 1)
+    entries = [StepEntry(r, [1 + i], [0]) for i, r in enumerate(ids)]
+    zeros = np.zeros(batch, dtype=np.float32)
+    runner.step_and_sample(entries, zeros, zeros)
+    graph = runner._decode_graph(entries)
+    for _ in range(5):
+        graph.graph.replay()
+    torch.cuda.synchronize()
+    read()
+    graph.graph.replay()
+    torch.cuda.synchronize()
+    recs = read()
+    rows = []
+    for i, (after, before, kid) in enumerate(recs):
+        nxt = recs[i + 1][0] if i + 1 < len(recs) else after
+        rows.append((TRACE_KERNELS.get(kid, str(kid)), (after - recs[0][0]) / 1e3, (nxt - after) / 1e3, (after - before) / 1e3))
+    per_layer = max(1, (len(rows) - 4) // max(1, layers))
+    start = min(len(rows), 2 + per_layer * (layers // 2))
+    print(f"decode step, batch {batch}, context {context}, {layers} layers: {len(rows)} kernels stamped, "
+          f"{(recs[-1][0] - recs[0][0]) / 1e3:.1f} us from first to last")
+    print(f"one layer from the middle:\n{'kernel':18s} {'at us':>9s} {'to next':>8s} {'in place':>8s}")
+    for name, t, d, w in rows[start:start + per_layer]:
+        print(f"{name:18s} {t:9.2f} {d:8.2f} {w:8.2f}")
+    tot = {}
+    for name, t, d, w in rows:
+        a = tot.setdefault(name, [0, 0.0, 0.0])
+        a[0] += 1; a[1] += d; a[2] += w
+    print(f"whole step by kernel:\n{'kernel':18s} {'count':>5s} {'sum us':>9s} {'mean':>7s} {'in place':>8s}")
+    for k, (n, d, w) in sorted(tot.items(), key=lambda kv: -kv[1][1]):
+        print(f"{k:18s} {n:5d} {d:9.1f} {d / n:7.2f} {w / n:8.2f}")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -146,8 +215,9 @@ def main(argv=None) -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the shape has (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
-    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
-                    help="run one part alone and print a short line (for profiling; not a bench record)")
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline"], default=None,
+                    help="run one part alone and print a short line (for profiling; not a bench record); "
+                         "timeline: one captured decode step as the kernels themselves clocked it")
     args = ap.parse_args(argv)
 
     if args.impl == "reference":
@@ -159,6 +229,9 @@ def main(argv=None) -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     steps, warmup = args.steps, max(3, args.warmup)
+    if args.only == "timeline":
+        # a build of the kernels that stamps the global timer around each kernel's wait for its predecessor
+        os.environ["PAGED_LLM_NVCC_DEFINES"] = (os.environ.get("PAGED_LLM_NVCC_DEFINES", "") + " PLLM_TRACE=1").strip()
 
     import numpy as np
     import torch
@@ -199,6 +272,9 @@ def main(argv=None) -> int:
             torch.cuda.synchronize()
             print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "steps": steps}))
             return 0
+
+        if args.only == "timeline":
+            return timeline(runner, B, ctx, L)
 
         # -- decode, on the device -------------------------------------------------------
         ms, launches = decode_point(runner, B, ctx, steps, warmup, clocks)

@@ -22,12 +22,15 @@ from typing import List, Optional, Sequence, Tuple
 import numpy as np
 
 SPLIT_ALIGN = 64   # split boundaries fall on multiples of the kernels' key tiles (32 and 64)
-MIN_SPLIT_KEYS = 128
+# A split shorter than this costs more in the reduction than it saves in the attention (a captured
+# step of the 0.6B shape, batch 1, context 4096: 0.927 ms with 256, 0.947 with 128, 1.011 with 512).
+MIN_SPLIT_KEYS = 256
 MAX_SPLITS = 128   # the reduce kernel holds the weights of up to 256 splits in shared memory
 
 
 def plan_attention(segments: Sequence[Tuple[int, int, int]], tile_tokens: int, window: Optional[int],
-                   ctas_per_item: int, target_ctas: int) -> Tuple[np.ndarray, np.ndarray, int]:
+                   ctas_per_item: int, target_ctas: int,
+                   min_split_keys: int = MIN_SPLIT_KEYS) -> Tuple[np.ndarray, np.ndarray, int]:
     """segments: (first token index, token count, position of the first token) per
     segment, in step order.  Returns (work [n, 8], red [m, 4], partial rows used)."""
     seg_ids, q0s, qns, p0s = [], [], [], []
@@ -59,7 +62,7 @@ def plan_attention(segments: Sequence[Tuple[int, int, int]], tile_tokens: int, w
         # as many splits as keep the launch within the target (one or two full waves of
         # CTAs), rounded down so that the last wave is not a sliver
         want = max(2, target_ctas // (n_tiles * ctas_per_item))
-        splits = np.clip(np.minimum(want, keys // MIN_SPLIT_KEYS), 1, MAX_SPLITS)
+        splits = np.clip(np.minimum(want, keys // min_split_keys), 1, MAX_SPLITS)
     if (splits == 1).all():
         work = np.stack([seg, q0, qn, p0, kv_begin, kv_end, np.full(n_tiles, -1), np.zeros(n_tiles, np.int64)], 1)
         return work.astype(np.int32), np.zeros((0, 4), np.int32), 0

@@ -194,7 +194,9 @@ def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, c
         segs.append((t0, n, c))
         t0 += n
     tile = ops.attention_tile_tokens(nh, nkv, dtype, hd)
-    work, red, parts = attention_plan.plan_attention(segs, tile, window, nkv * (-(-(nh // nkv) // 16)), target_ctas)
+    # (splits from 128 keys on, shorter than the engine cuts them, so that the short contexts here have some)
+    work, red, parts = attention_plan.plan_attention(segs, tile, window, nkv * (-(-(nh // nkv) // 16)), target_ctas,
+                                                     min_split_keys=128)
     dev = lambda t: t.to(DEV)
     workd = dev(torch.from_numpy(np.ascontiguousarray(work)).reshape(-1, 8)) if len(work) else torch.zeros(1, 8, dtype=torch.int32, device=DEV)
     redd = dev(torch.from_numpy(np.ascontiguousarray(red)).reshape(-1, 4)) if len(red) else torch.zeros(1, 4, dtype=torch.int32, device=DEV)
@@ -260,8 +262,18 @@ def test_bulk_copy_kernel_combines_its_splits_itself(nh, nkv, hd, page):
     decode = [(63, 1), (700, 1), (1023, 1), (15, 1), (331, 1), (2000, 1)]
     mixed = [(100, 1), (400, 9), (513, 1), (0, 70), (900, 33)]
     counters = torch.zeros(1 << 16, dtype=torch.int32, device=DEV)
-    for reqs, kinds in ((decode, 1), (mixed, 3)):
-        base, n_red = run_attention(torch.bfloat16, reqs, nh, nkv, hd, page, None, 10 ** 6, kinds=kinds, raw=True)
+    was, ops.FUSE_REDUCE = ops.FUSE_REDUCE, False
+    bases = [run_attention(torch.bfloat16, reqs, nh, nkv, hd, page, None, 10 ** 6, kinds=kinds, raw=True)
+             for reqs, kinds in ((decode, 1), (mixed, 3))]
+    ops.FUSE_REDUCE = True        # (off by default: it measured slower in a whole step)
+    try:
+        _check_fused_combine(((decode, 1), (mixed, 3)), bases, counters, nh, nkv, hd, page)
+    finally:
+        ops.FUSE_REDUCE = was
+
+
+def _check_fused_combine(cases, bases, counters, nh, nkv, hd, page):
+    for (reqs, kinds), (base, n_red) in zip(cases, bases):
         assert n_red > 0
         launches = ops.LAUNCHES
         for _ in range(2):
