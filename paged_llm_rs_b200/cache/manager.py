@@ -63,8 +63,14 @@ class BlockTable:
         if getattr(self, "_arr_sig", None) != sig:
             import numpy as np
             self._arr = np.asarray(self.blocks, dtype=np.int32)
+            self._arr_ptr = self._arr.ctypes.data
             self._arr_sig = sig
         return self._arr
+
+    def pointer(self):
+        """(address, entries) of ``array()``: what the native step packer reads."""
+        arr = self.array()
+        return self._arr_ptr, len(arr)
 
 
 @dataclass

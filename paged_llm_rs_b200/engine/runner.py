@@ -26,7 +26,7 @@ from ..kernels import attention_plan, ops
 from ..parts.base import KVNeed, Runtime
 from ..parts.decoder import DecoderModel
 from ..weights.loader import load_weights
-from .step import GroupPlanConfig, StepCaps, StepEntry, StepPacker
+from .step import GroupPlanConfig, NativeDecodePacker, StepCaps, StepEntry, StepPacker
 
 DTYPES = {"float32": torch.float32, "f32": torch.float32, "fp32": torch.float32,
           "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
@@ -58,6 +58,7 @@ class _DecodeGraph:
         self.work_caps = [attention_plan.plan_limits(B, p.tile_tokens, pk.target_ctas, p.ctas_per_item) for p in pk.plans]
         host, self.layout, self.sizes = pk.pack([], runner._heads, self.caps, self.work_caps)
         self.pinned = torch.from_numpy(host.copy()).pin_memory()
+        self.native = NativeDecodePacker(pk, self.caps, self.work_caps, self.layout, self.pinned.numpy())
         self.dev = self.pinned.to(runner.device)
         self.nbytes = host.nbytes
         self.state = pk.to_state(self.dev, self.layout, self.sizes, runner._heads, full=True)
@@ -94,8 +95,7 @@ class _DecodeGraph:
 
     def run(self, entries, temperature, uniform):
         r = self.runner
-        host, _, _ = r.packer.pack(entries, r._heads, self.caps, self.work_caps, temperature, uniform)
-        self.pinned.numpy()[:] = host
+        self.native.pack(entries, temperature, uniform)     # straight into the pinned buffer
         self.dev.copy_(self.pinned, non_blocking=True)
         self.graph.replay()
         r.bytes_h2d = self.nbytes

@@ -13,6 +13,7 @@ slots, the block tables and the attention work items.
 
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -241,3 +242,89 @@ class StepPacker:
         state.temperature = view("temperature", max(nw, 1)).view(torch.float32)
         state.uniform = view("uniform", max(nw, 1)).view(torch.float32)
         return state
+
+
+class _GroupPack(ctypes.Structure):
+    """csrc/step_pack.cu: PllmGroupPack."""
+    _fields_ = [("tables", ctypes.POINTER(ctypes.c_void_p)), ("table_len", ctypes.POINTER(ctypes.c_int)),
+                ("window", ctypes.c_int), ("ctas_per_item", ctypes.c_int),
+                ("max_work", ctypes.c_int), ("max_red", ctypes.c_int), ("max_parts", ctypes.c_int),
+                ("off_slots", ctypes.c_int), ("off_tables", ctypes.c_int), ("off_n_work", ctypes.c_int),
+                ("off_n_red", ctypes.c_int), ("off_work", ctypes.c_int), ("off_red", ctypes.c_int)]
+
+
+class NativeDecodePacker:
+    """The packer of the captured decode step: every request brings one token and
+    wants its logits.  Same buffer as ``StepPacker.pack`` with capacities makes
+    (the tests compare them word for word), written by native code
+    (csrc/step_pack.cu) straight into the pinned buffer the step is copied from."""
+
+    _ERRORS = {
+        -10: (ConfigError, "a token id lies outside the vocabulary of {vocab}"),
+        -11: (ConfigError, "request {rid!r}: its position reaches past max_position_embeddings {maxpos}"),
+        -12: (CacheError, "request {rid!r}: no pages reserved for its next position"),
+        -13: (CacheError, "request {rid!r} writes into a page it gave back"),
+        -14: (ConfigError, "the step's attention work does not fit the capacities it was given"),
+        -15: (ConfigError, "a block table is wider than the step's capacity"),
+        -16: (ConfigError, "the step does not fit the capacities it was given"),
+    }
+
+    def __init__(self, packer: StepPacker, caps: StepCaps, work_caps: List[Tuple[int, int, int]], layout, out: np.ndarray):
+        from ..kernels import ops
+        self.packer, self.caps, self.out = packer, caps, out
+        self.fn = ops.lib().pllm_pack_decode_step
+        B = caps.tokens
+        self.tokens = (ctypes.c_int * B)()
+        self.positions = (ctypes.c_int * B)()
+        self.state_slots = (ctypes.c_int * B)()
+        self.temperature = (ctypes.c_float * B)()
+        self.uniform = (ctypes.c_float * B)()
+        self.err = ctypes.c_int(-1)
+        n_groups = len(packer.cache.groups)
+        self.groups = (_GroupPack * max(n_groups, 1))()
+        self.ptrs, self.lens = [], []
+        for gi in range(n_groups):
+            ptrs, lens = (ctypes.c_void_p * B)(), (ctypes.c_int * B)()
+            self.ptrs.append(ptrs); self.lens.append(lens)
+            g, plan = self.groups[gi], packer.plans[gi]
+            g.tables = ctypes.cast(ptrs, ctypes.POINTER(ctypes.c_void_p))
+            g.table_len = ctypes.cast(lens, ctypes.POINTER(ctypes.c_int))
+            g.window, g.ctas_per_item = int(plan.window or 0), plan.ctas_per_item
+            g.max_work, g.max_red, g.max_parts = work_caps[gi]
+            for name in ("slots", "tables", "n_work", "n_red", "work", "red"):
+                setattr(g, f"off_{name}", layout[f"g{gi}.{name}"][0])
+        self.n_groups = n_groups
+        self.fixed = (caps.tokens, caps.wanted, caps.segments, caps.table_width, packer.cache.page_size, packer.vocab_size,
+                      packer.max_positions, packer.target_ctas, attention_plan.MIN_SPLIT_KEYS,
+                      layout["tokens"][0], layout["positions"][0], layout["logit_rows"][0], layout["segments"][0],
+                      layout["temperature"][0], layout["uniform"][0], n_groups)
+        self.out_ptr = out.ctypes.data
+
+    def pack(self, entries: Sequence[StepEntry], temperature, uniform) -> None:
+        cache = self.packer.cache
+        n = len(entries)
+        if n > self.caps.tokens:
+            raise ConfigError("the step does not fit the capacities it was given")
+        tables = []
+        for i, e in enumerate(entries):
+            rc = cache.get(e.request_id)
+            self.tokens[i] = int(e.tokens[0])
+            self.positions[i] = rc.tokens
+            self.state_slots[i] = rc.state_slot
+            tables.append(rc.tables)
+        for gi in range(self.n_groups):
+            ptrs, lens = self.ptrs[gi], self.lens[gi]
+            for i, tbs in enumerate(tables):
+                ptrs[i], lens[i] = tbs[gi].pointer()
+        have = temperature is not None
+        if have:
+            self.temperature[:n] = [float(t) for t in temperature]
+            self.uniform[:n] = [float(u) for u in uniform]
+        code = self.fn(self.out_ptr, len(self.out), n, self.tokens, self.positions, self.state_slots,
+                       self.temperature if have else None, self.uniform if have else None, *self.fixed,
+                       self.groups, ctypes.byref(self.err))
+        if code != 0:
+            kind, msg = self._ERRORS.get(code, (ConfigError, f"the native step packer refused the step (code {code})"))
+            i = self.err.value
+            raise kind(msg.format(vocab=self.packer.vocab_size, maxpos=self.packer.max_positions,
+                                  rid=entries[i].request_id if 0 <= i < n else None))

@@ -60,6 +60,7 @@ def lib():
                                           c_float, c_int, P, P, P],
         }
         sig["pllm_set_pdl"] = [c_int]
+        sig["pllm_pack_decode_step"] = [P, c_int, c_int, P, P, P, P, P] + [c_int] * 16 + [P, P]
         for name, args in sig.items():
             fn = getattr(L, name)
             fn.argtypes = args
