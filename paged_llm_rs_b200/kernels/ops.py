@@ -60,6 +60,8 @@ def lib():
                                           c_float, c_int, P, P, P],
         }
         sig["pllm_set_pdl"] = [c_int]
+        sig["pllm_gemm_tcgen05_supports"] = [c_int, c_int, c_int, c_int]
+        sig["pllm_gemm_tcgen05"] = [P, P, P, c_int, c_int, c_int, c_int, P, P]
         sig["pllm_pack_decode_step"] = [P, c_int, c_int, P, P, P, P, P] + [c_int] * 16 + [P, P]
         for name, args in sig.items():
             fn = getattr(L, name)
@@ -368,6 +370,43 @@ def skinny_gemm_takes(x: torch.Tensor, weight: torch.Tensor, k: Optional[int] = 
 # library's head product is the faster one (151936 x 1024: 66 / 54).
 SKINNY_MAX_M = 16
 SKINNY_MAX_N = 32768
+
+
+# The many rows of a prompt portion in bfloat16: this library's tcgen05 product (csrc/gemm_tcgen05.cu)
+# instead of the library's (PAGED_LLM_TCGEN05=0 turns it off).
+TCGEN05_GEMM = os.environ.get("PAGED_LLM_TCGEN05", "0") == "1"
+_gemm_status: dict = {}
+
+
+def gemm_status(device) -> torch.Tensor:
+    """The status word the tcgen05 product raises bit 64 in when one of its bounded waits
+    ran out (one int32 per device; the engine reads it with its own status word)."""
+    key = str(device)
+    if key not in _gemm_status:
+        _gemm_status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _gemm_status[key]
+
+
+def gemm_tcgen05_takes(x, weight: torch.Tensor, n_out: int, glu: bool) -> bool:
+    if not isinstance(x, torch.Tensor) or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or x.dim() != 2:
+        return False
+    return x.is_contiguous() and weight.is_contiguous() and bool(
+        lib().pllm_gemm_tcgen05_supports(x.shape[0], n_out, weight.shape[1], 1 if glu else 0))
+
+
+def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, glu: bool = False, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x W^T on the tcgen05 tensor cores (bfloat16, float accumulation); with ``glu`` W is
+    [gate rows; up rows] and the result is silu(x Wg^T) * (x Wu^T)."""
+    M, K = x.shape
+    n_out = weight.shape[0] // 2 if glu else weight.shape[0]
+    if weight.shape[1] != K or not gemm_tcgen05_takes(x, weight, n_out, glu):
+        raise KernelError(f"gemm_tcgen05: does not take x {tuple(x.shape)} {x.dtype}, W {tuple(weight.shape)} {weight.dtype}")
+    _dev(x, weight)
+    out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
+    st = status if status is not None else gemm_status(x.device)
+    _check(lib().pllm_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), M, n_out, K, 1 if glu else 0, _ptr(st), _stream()),
+           "gemm_tcgen05")
+    return out
 
 
 class NormedInput:
