@@ -224,9 +224,12 @@ class ModelRunner:
         if code:
             self.rt.status.zero_()
             what = [name for bit, name in ((1, "a token id outside the vocabulary"), (2, "a cache slot outside the pool"),
-                                          (4, "a position outside the rotary table"), (8, "a page id outside the pool"))
+                                          (4, "a position outside the rotary table"), (8, "a page id outside the pool"),
+                                          (16, "a wait for a copy that ran out (attention)"),
+                                          (32, "a key range that does not start on a tile boundary"),
+                                          (64, "a wait that ran out in the tcgen05 product"))
                     if code & bit]
-            raise KernelError("a kernel met " + ", ".join(what))
+            raise KernelError("a kernel met " + (", ".join(what) or f"status {code}"))
 
     # -- sizes -------------------------------------------------------------------------------
     def weight_bytes(self) -> int:

@@ -373,8 +373,14 @@ SKINNY_MAX_N = 32768
 
 
 # The many rows of a prompt portion in bfloat16: this library's tcgen05 product (csrc/gemm_tcgen05.cu)
-# instead of the library's (PAGED_LLM_TCGEN05=0 turns it off).
-TCGEN05_GEMM = os.environ.get("PAGED_LLM_TCGEN05", "0") == "1"
+# where it is the faster one.  Measured on a B200 at 2048 rows (us, this kernel / cuBLAS):
+#   gate/up 6144 x 1024 with silu(gate)*up in the epilogue 25.2 / 24.3 + 10.8 for the activation's own pass
+#   qkv 4096 x 1024   18.5 / 17.7      o 1024 x 2048   17.4 / 10.7      down 1024 x 3072   19.5 / 12.6
+# so the gated product takes it and the plain ones stay with the library (PAGED_LLM_TCGEN05=0: none,
+# =2: the plain ones too).  One CTA's tcgen05.mma reads both operands from shared memory, whose
+# bandwidth bounds a 128 x 256 tile at two thirds of the tensor peak; pairs of CTAs are the next step.
+TCGEN05_GEMM = int(os.environ.get("PAGED_LLM_TCGEN05", "1"))
+TCGEN05_MIN_M = 64     # below this the tiles of 128 rows are mostly padding
 _gemm_status: dict = {}
 
 
@@ -487,7 +493,7 @@ def _fused(x, weight: torch.Tensor, n_out: int, glu: bool) -> torch.Tensor:
 
 
 def linear(x, weight: torch.Tensor, out: Optional[torch.Tensor] = None, gated: bool = False,
-           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+           out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y = x W^T with W stored [out, in].
 
     Few rows (a decode step) in bfloat16 run this library's weight-streaming
@@ -528,12 +534,15 @@ def linear(x, weight: torch.Tensor, out: Optional[torch.Tensor] = None, gated: b
         _check(lib().pllm_skinny_gemm(_ptr(x), _ptr(weight), _ptr(out), M, N, K,
                                       1 if want == torch.float32 else 0, _stream()), "skinny_gemm")
         return out
+    if TCGEN05_GEMM >= 2 and out is None and want == torch.bfloat16 and x.shape[0] >= TCGEN05_MIN_M \
+            and gemm_tcgen05_takes(x, weight, N, False):
+        return gemm_tcgen05(x, weight, status=status)
     if want != x.dtype:
         return torch.mm(x, weight.t(), out_dtype=want)
     return torch.matmul(x, weight.t(), out=out) if out is not None else torch.matmul(x, weight.t())
 
 
-def linear_glu(x, w_gate_up: torch.Tensor) -> torch.Tensor:
+def linear_glu(x, w_gate_up: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """silu(x Wg^T) * (x Wu^T) for W = [Wg; Wu] stacked [2I, K]: the gated
     feed-forward's first half (crates/pagedllm/src/model/layers.rs:93-99).  Few
     rows in bfloat16: one kernel whose CTAs hold the same columns of both halves
@@ -547,6 +556,8 @@ def linear_glu(x, w_gate_up: torch.Tensor) -> torch.Tensor:
         raise KernelError(f"linear_glu: input width {x.shape[-1]} does not fit a weight of {tuple(w_gate_up.shape)}")
     if FUSE_GLU and fused_linear_takes(x, w_gate_up, inter):
         return _fused(x, w_gate_up, inter, glu=True)
+    if TCGEN05_GEMM >= 1 and x.shape[0] >= TCGEN05_MIN_M and gemm_tcgen05_takes(as_tensor(x), w_gate_up, inter, True):
+        return gemm_tcgen05(as_tensor(x), w_gate_up, glu=True, status=status)
     gu = linear(x, w_gate_up)
     act = torch.empty((gu.shape[0], inter), dtype=gu.dtype, device=gu.device)
     return swiglu(gu, act)

@@ -65,7 +65,7 @@ class GQAttention(Mixer):
         k_pool, v_pool, gi = cache
         g = step.groups[gi]
         T = x.shape[0]
-        qkv = ops.linear(x, self.w_qkv)
+        qkv = ops.linear(x, self.w_qkv, status=self.rt.status)
         q = torch.empty((T, self.nh * self.hd), dtype=x.dtype, device=x.device)
         rot = self.position.rotary() if self.position is not None else None
         cos, sin, rdim = rot if rot is not None else (None, None, 0)
@@ -78,7 +78,7 @@ class GQAttention(Mixer):
         ops.paged_attention(q, k_pool, v_pool, g.block_tables, g.work, g.n_work, g.max_work, o, g.part_o, g.part_ml,
                             g.red, g.n_red, g.max_red, self.nh, self.nkv, self.hd, self.window or 0, self.scale,
                             self.rt.status, swizzled=swizzled, kinds=g.kinds, counters=g.counters)
-        return ops.linear(o, self.w_o)
+        return ops.linear(o, self.w_o, status=self.rt.status)
 
 
 register_mixer("gqa_attention", GQAttention)

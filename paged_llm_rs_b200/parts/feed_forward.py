@@ -31,7 +31,7 @@ class SwiGLUMLP(FeedForward):
     takes_normed_input = True
 
     def forward(self, x, step):
-        return ops.linear(ops.linear_glu(x, self.w_gate_up), self.w_down)
+        return ops.linear(ops.linear_glu(x, self.w_gate_up, status=self.rt.status), self.w_down, status=self.rt.status)
 
 
 register_feed_forward("swiglu_mlp", SwiGLUMLP)

@@ -479,6 +479,53 @@ def test_deferred_norm_falls_back_for_shapes_the_kernel_refuses():
         assert x.consumed and torch.equal(x.residual_out.float(), h)
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (1, 128, 64), (77, 256, 1024), (200, 384, 72), (300, 512, 320),
+                                   (2048, 4096, 1024), (640, 1024, 2048), (129, 1280, 136)])
+def test_tcgen05_product(M, N, K):
+    # tiles of 128 x 128 and 128 x 256, rows and k that end off a tile's edge, several tiles a CTA
+    g = torch.Generator(device=DEV).manual_seed(M + N + K)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    st = status()
+    y = ops.gemm_tcgen05(x, w, status=st)
+    assert st.item() == 0 and y.shape == (M, N) and y.dtype == torch.bfloat16
+    torch.testing.assert_close(y.float(), x.float() @ w.float().T, atol=3e-2, rtol=2e-2)
+    # one far entry of W decides a column: a wrong k block or swizzle would lose it
+    w2 = w.clone(); w2[N - 1, K - 1] = 100.0
+    y2 = ops.gemm_tcgen05(x, w2, status=st)
+    torch.testing.assert_close(y2.float()[:, N - 1], (x.float() @ w2.float().T)[:, N - 1], atol=0.5, rtol=2e-2)
+    assert torch.equal(y2[:, :N - 1], y[:, :N - 1])
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 64, 64), (5, 64, 128), (300, 192, 320), (2048, 3072, 1024), (200, 640, 72)])
+def test_tcgen05_product_with_the_gated_activation(M, I, K):
+    g = torch.Generator(device=DEV).manual_seed(M + I + K)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(2 * I, K, device=DEV, generator=g) * 0.05).bfloat16()
+    st = status()
+    y = ops.gemm_tcgen05(x, w, glu=True, status=st)
+    assert st.item() == 0 and y.shape == (M, I)
+    gu = (x.float() @ w.float().T).bfloat16().float()
+    want = gu[:, :I] * torch.sigmoid(gu[:, :I]) * gu[:, I:]
+    # gate and up are rounded to bfloat16 before the activation on both sides; sums that differ in
+    # the last place flip a rounding now and then, which the activation scales by the other factor
+    scale = 1 + gu[:, :I].abs() + gu[:, I:].abs()
+    assert ((y.float() - want).abs() / scale).max().item() < 2e-2
+    # the engine's route for a prompt portion gives the same
+    was, ops.TCGEN05_GEMM = ops.TCGEN05_GEMM, 1
+    try:
+        if M >= ops.TCGEN05_MIN_M:
+            assert torch.equal(ops.linear_glu(x, w, status=st), y)
+    finally:
+        ops.TCGEN05_GEMM = was
+    ops.TCGEN05_GEMM = 0
+    try:
+        lib_route = ops.linear_glu(x, w)
+    finally:
+        ops.TCGEN05_GEMM = was
+    assert ((y.float() - lib_route.float()).abs() / scale).max().item() < 2e-2
+
+
 def test_linear_falls_back_to_the_library_for_other_shapes():
     g = torch.Generator(device=DEV).manual_seed(0)
     for M, N, K, dt in ((100, 256, 256, torch.bfloat16), (4, 250, 256, torch.bfloat16), (4, 256, 200, torch.bfloat16),
