@@ -50,6 +50,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--prefix-cache", type=_on_off, default=True, metavar="on|off")
     g.add_argument("--chunk", type=_chunk, default=128, metavar="N|off",
                    help="most tokens one step may carry; off runs a prompt whole")
+    g.add_argument("--max-prefill-seqs", type=int, default=1,
+                   help="prompts that may share one pass in chunked mode (1: one joins per pass, as in the reference)")
     g.add_argument("--prompt-ids", action="append", default=[], metavar="1,2,3",
                    help="one prompt as comma-separated token ids; may be given several times")
     g.add_argument("--prompts-file", help="JSON file with a list of prompts, each a list of token ids")
@@ -107,7 +109,8 @@ def main(argv=None) -> int:
     top_p = args.top_p if args.top_p is not None else defaults.top_p
     stop = [int(x) for x in args.stop_ids.split(",") if x.strip()] or list(defaults.eos_token_ids)
     engine = Engine(args.model, dtype=dtype, block_size=args.block_size, cache_mib=args.cache_mib, blocks=args.blocks,
-                    max_batch=args.max_batch, chunk=args.chunk, prefix_cache=args.prefix_cache)
+                    max_batch=args.max_batch, chunk=args.chunk, prefix_cache=args.prefix_cache,
+                    max_prefill_seqs=args.max_prefill_seqs)
     cache = engine.runner.cache
     print(f"model {args.model}  dtype {dtype}  cache {cache.num_pages} pages of {cache.page_size} tokens, "
           f"{cache.bytes_per_token()} bytes a token  chunk {args.chunk or 'off'}  "

@@ -83,6 +83,47 @@ __global__ void rmsnorm_kernel(const T* x, const T* delta, T* residual_out,   //
     constexpr int N = Vec16<T>::N;
     const bool vec = (width % N == 0);
     float ss = 0.f;
+    // Rows of up to RMS_HELD vectors a thread stay in registers between the two passes; wider rows
+    // (and rows that are not whole vectors) are read back.
+    constexpr int RMS_HELD = 4;
+    if (vec && width <= (int)blockDim.x * N * RMS_HELD) {
+        float f[RMS_HELD][N];
+#pragma unroll
+        for (int j = 0; j < RMS_HELD; j++) {
+            const int c = (threadIdx.x + j * blockDim.x) * N;
+            if (c >= width) break;
+            Vec16<T> v; v.load(xr + c);
+            v.unpack(f[j]);
+            if (dr) {
+                Vec16<T> d; d.load(dr + c);
+                float g[N]; d.unpack(g);
+#pragma unroll
+                for (int k = 0; k < N; k++) f[j][k] = to_f32(from_f32<T>(f[j][k] + g[k]));
+                if (rr) { Vec16<T> o; o.pack(f[j]); o.store(rr + c); }
+            } else if (rr && rr != xr) {
+                v.store(rr + c);
+            }
+#pragma unroll
+            for (int k = 0; k < N; k++) ss += f[j][k] * f[j][k];
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+#pragma unroll
+        for (int j = 0; j < RMS_HELD; j++) {
+            const int c = (threadIdx.x + j * blockDim.x) * N;
+            if (c >= width) break;
+            const float4 g0 = *reinterpret_cast<const float4*>(gain + c);
+            float gg[8] = {g0.x, g0.y, g0.z, g0.w, 0.f, 0.f, 0.f, 0.f};
+            if (N == 8) {
+                const float4 g1 = *reinterpret_cast<const float4*>(gain + c + 4);
+                gg[4] = g1.x; gg[5] = g1.y; gg[6] = g1.z; gg[7] = g1.w;
+            }
+#pragma unroll
+            for (int k = 0; k < N; k++) f[j][k] = f[j][k] * inv * gg[k];
+            Vec16<T> o; o.pack(f[j]); o.store(yr + c);
+        }
+        return;
+    }
     if (vec) {
         for (int c = threadIdx.x * N; c < width; c += blockDim.x * N) {
             Vec16<T> v; v.load(xr + c);

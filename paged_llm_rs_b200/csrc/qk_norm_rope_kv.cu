@@ -160,6 +160,94 @@ __global__ void qk_norm_rope_kv_vec_kernel(
     v.store(dst + (c ^ xr) * N);
 }
 
+// The same for the many tokens of a prompt portion: one warp takes a whole token, 32 / LPH
+// heads at a time, so that the token's rotation angles and the two gains are fetched once a
+// warp and not once a head, and four heads' loads are in flight together.
+template <typename T, int LPH>
+__global__ void __launch_bounds__(128) qk_norm_rope_kv_token_kernel(
+    const T* qkv, T* __restrict__ q_out, const float* __restrict__ q_gain,
+    const float* __restrict__ k_gain, float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+    int max_pos, const int* __restrict__ positions, const int* __restrict__ slots, T* __restrict__ k_pool,
+    T* __restrict__ v_pool, int n_tokens, int nh, int nkv, int page_size, int n_pages, int swizzle, int* status) {
+    constexpr int N = Vec16<T>::N, HD = LPH * N, HPW = 32 / LPH, UNR = 4;
+    pdl_launch_dependents();
+    pdl_wait(KID_QK);
+    const int lane = threadIdx.x & 31, sub = lane / LPH, c = lane % LPH;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= n_tokens) return;
+    const int heads = nh + 2 * nkv;
+    float cs[N], sn[N], gq[N], gk[N];
+    const bool upper = c >= LPH / 2;
+    if (cos_t) {
+        int pos = positions[t];
+        if (pos < 0 || pos >= max_pos) { if (lane == 0) atomicOr(status, 4); pos = 0; }
+        const size_t o = (size_t)pos * (HD / 2) + (upper ? c - LPH / 2 : c) * N;
+#pragma unroll
+        for (int k = 0; k < N; k++) { cs[k] = cos_t[o + k]; sn[k] = upper ? sin_t[o + k] : -sin_t[o + k]; }
+    }
+#pragma unroll
+    for (int k = 0; k < N; k++) { gq[k] = q_gain ? q_gain[c * N + k] : 1.f; gk[k] = k_gain ? k_gain[c * N + k] : 1.f; }
+    // where this token's keys and values go
+    const int slot = slots[t];
+    const bool write_kv = k_pool && slot >= 0;
+    int page = 0, off = 0;
+    if (write_kv) {
+        page = slot / page_size; off = slot % page_size;
+        if (page >= n_pages) { if (lane == 0) atomicOr(status, 2); return; }
+    }
+    const int xr = swizzle ? (off & 7) : 0;
+    const T* src = qkv + (size_t)t * heads * HD + c * N;
+    for (int h0 = 0; h0 < heads; h0 += HPW * UNR) {
+        Vec16<T> v[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; u++) {
+            const int h = h0 + u * HPW + sub;
+            v[u].load(src + (size_t)(h < heads ? h : heads - 1) * HD);
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; u++) {
+            const int h = h0 + u * HPW + sub;
+            if (h0 + u * HPW >= heads) break;          // the whole warp is past the last head
+            const bool live = h < heads;
+            const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
+            float f[N];
+            v[u].unpack(f);
+            float ss = 0.f;
+#pragma unroll
+            for (int k = 0; k < N; k++) ss += f[k] * f[k];
+#pragma unroll
+            for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if ((is_q && q_gain) || (is_k && k_gain)) {
+                const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+                for (int k = 0; k < N; k++) f[k] = f[k] * inv * (is_q ? gq[k] : gk[k]);
+            }
+            if (cos_t) {
+#pragma unroll
+                for (int k = 0; k < N; k++) {
+                    const float other = __shfl_xor_sync(0xffffffffu, f[k], LPH / 2);
+                    // upper half: x cos + partner sin; lower half: x cos - partner sin (the sign is in sn)
+                    if (is_q || is_k) f[k] = f[k] * cs[k] + other * sn[k];
+                }
+            }
+            if (!live) continue;
+            T* dst;
+            int x = 0;
+            if (is_q) {
+                dst = q_out + (size_t)t * nh * HD + (size_t)h * HD;
+            } else {
+                if (!write_kv) continue;
+                const int kh = is_k ? h - nh : h - nh - nkv;
+                dst = (is_k ? k_pool : v_pool) + (((size_t)page * nkv + kh) * page_size + off) * HD;
+                x = xr;
+            }
+            Vec16<T> o;
+            o.pack(f);
+            o.store(dst + (c ^ x) * N);
+        }
+    }
+}
+
 template <typename T, int LPH>
 static void launch_qk_vec(const void* qkv, void* q_out, const float* q_gain, const float* k_gain, float eps,
                           const float* cos_t, const float* sin_t, int max_pos, const int* positions, const int* slots,
@@ -167,6 +255,13 @@ static void launch_qk_vec(const void* qkv, void* q_out, const float* q_gain, con
                           int swizzle, int* status, cudaStream_t stream) {
     const long long items = (long long)n_tokens * (nh + 2 * nkv);
     const int per_block = 4 * (32 / LPH);
+    if (n_tokens >= 256) {
+        // enough tokens to fill the GPU with a warp each
+        launch_chained(qk_norm_rope_kv_token_kernel<T, LPH>, dim3((unsigned)((n_tokens + 3) / 4)), dim3(128), 0, stream,
+                       (const T*)qkv, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, max_pos, positions, slots, (T*)k_pool,
+                       (T*)v_pool, n_tokens, nh, nkv, page_size, n_pages, swizzle, status);
+        return;
+    }
     launch_chained(qk_norm_rope_kv_vec_kernel<T, LPH>, dim3((unsigned)((items + per_block - 1) / per_block)), dim3(128), 0,
                    stream, (const T*)qkv, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, max_pos, positions, slots,
                    (T*)k_pool, (T*)v_pool, n_tokens, nh, nkv, page_size, n_pages, swizzle, status);

@@ -27,7 +27,8 @@ from .scheduler import Finish, Outcome, Plan, Scheduler, Sequence
 class Engine:
     def __init__(self, model: str, dtype="bfloat16", block_size: int = 16, cache_mib: int = 3584,
                  blocks: Optional[int] = None, max_batch: int = 16, chunk: Optional[int] = 128,
-                 prefix_cache: bool = True, device: str = "cuda:0", max_requests: Optional[int] = None):
+                 prefix_cache: bool = True, device: str = "cuda:0", max_requests: Optional[int] = None,
+                 max_prefill_seqs: int = 1):
         if chunk is not None and chunk < 1:
             raise ConfigError("chunk 0 would carry nothing")
         self.runner = ModelRunner(model, dtype=dtype, page_size=block_size, num_pages=blocks,
@@ -35,7 +36,7 @@ class Engine:
                                   max_requests=max_requests or max(256, 2 * max_batch), device=device,
                                   prefix_cache=prefix_cache)
         self.scheduler = Scheduler(self.runner.cache, max_batch=max_batch, chunk=chunk,
-                                   max_positions=self.runner.spec.max_positions)
+                                   max_positions=self.runner.spec.max_positions, max_prefill_seqs=max_prefill_seqs)
         self._next_id = 0
         self._seqs: Dict[int, Sequence] = {}
         self._finish: Dict[int, Finish] = {}

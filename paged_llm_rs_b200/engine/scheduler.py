@@ -102,8 +102,13 @@ class Metrics:
 
 class Scheduler:
     def __init__(self, cache: CacheManager, max_batch: int = 16, chunk: Optional[int] = 128,
-                 max_positions: Optional[int] = None):
+                 max_positions: Optional[int] = None, max_prefill_seqs: int = 1):
         self.cache = cache
+        # Prompts that may share one pass in chunked mode.  1 is the reference's behaviour (one
+        # prompt joins per pass, scheduler.rs:388-447, which its README names as what inflates the
+        # time to the first token when many requests arrive at once); more lets a prompt that
+        # ends inside the budget be followed by the next one's first portion in the same pass.
+        self.max_prefill_seqs = max(1, int(max_prefill_seqs))
         self.max_batch = max(1, int(max_batch))
         self.chunk = None if chunk is None else max(1, int(chunk))
         self.max_positions = max_positions
@@ -147,21 +152,20 @@ class Scheduler:
         head.finish = Finish.LENGTH
         return Plan("refused", refused=head.id)
 
-    def _prompt_in_flight(self) -> Optional[int]:
+    def _prompt_in_flight(self, skip=()) -> Optional[int]:
         for i, s in enumerate(self.running):
-            if s.prompt_left > 0 and s.finish is None:
+            if s.prompt_left > 0 and s.finish is None and s.id not in skip:
                 return i
         return None
 
     def _mixed(self) -> Optional[Plan]:
         budget = self.chunk
-        index = self._prompt_in_flight()
         ids, advanced, entries = [], [], []
         cap = min(self.max_batch, budget)
-        for row, s in enumerate(self.running):
+        for s in self.running:
             if len(entries) >= cap:
                 break
-            if row == index or s.finish is not None or len(s.pending) != 1:
+            if s.prompt_left > 0 or s.finish is not None or len(s.pending) != 1:
                 continue
             if self.cache.blocks_needed(s.id, 1) > 0 and not self.cache.reserve(s.id, 1):
                 # A resident that needs a page from a dry pool is a preemption, and
@@ -174,22 +178,31 @@ class Scheduler:
         room = budget - decodes
         if room <= 0:
             return None
-        if index is None:
-            self._start_next_prompt()
-            index = self._prompt_in_flight()
-        if index is None:
+        taken = []
+        while room > 0 and len(taken) < self.max_prefill_seqs:
+            index = self._prompt_in_flight(taken)
+            if index is None:
+                self._start_next_prompt()
+                index = self._prompt_in_flight(taken)
+            if index is None:
+                break
+            s = self.running[index]
+            done = len(s.history) - s.prompt_left
+            want = min(room, s.prompt_left)
+            take = self.cache.reserve_up_to(s.id, want)
+            if take <= 0:
+                break
+            last = take == s.prompt_left
+            if last:
+                ids.append(s.id)
+            advanced.append((s.id, take))
+            entries.append(StepEntry(s.id, s.history[done:done + take], [take - 1] if last else []))
+            taken.append(s.id)
+            room -= take
+            if not last:
+                break           # a part-run prompt finishes before the next is started
+        if not taken:
             return None
-        s = self.running[index]
-        done = len(s.history) - s.prompt_left
-        want = min(room, s.prompt_left)
-        take = self.cache.reserve_up_to(s.id, want)
-        if take <= 0:
-            return None
-        last = take == s.prompt_left
-        if last:
-            ids.append(s.id)
-        advanced.append((s.id, take))
-        entries.append(StepEntry(s.id, s.history[done:done + take], [take - 1] if last else []))
         self.metrics.steps += 1
         self.metrics.mixed_steps += 1
         self.metrics.decode_rows += decodes

@@ -64,6 +64,14 @@ def test_greedy_tiny_a(tmp_path, dtype):
     # whole prompts (chunk off) give the same tokens
     eng2 = Engine(model, dtype=dtype, block_size=16, blocks=32, chunk=None)
     assert eng2.generate(prompts, max_tokens=8) == outs or dtype == "bfloat16"
+    # several prompts in one pass: fewer steps, and in float32 the same tokens
+    eng3 = Engine(model, dtype=dtype, block_size=16, blocks=32, chunk=24, max_prefill_seqs=3)
+    outs3 = eng3.generate(prompts, max_tokens=8)
+    check_greedy(model, prompts, outs3, 8, dtype)
+    assert outs3 == outs or dtype == "bfloat16"
+    eng4 = Engine(model, dtype=dtype, block_size=16, blocks=32, chunk=24)
+    eng4.generate(prompts, max_tokens=8)
+    assert eng3.metrics()["steps"] < eng4.metrics()["steps"]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

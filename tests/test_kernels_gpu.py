@@ -95,13 +95,14 @@ def rope_ref(x, pos, theta, rotary_dim):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd,rot,page", [(6, 3, 48, 48, 8), (8, 1, 32, 16, 16), (16, 8, 128, 128, 64), (4, 4, 80, 80, 16),
                                                 (4, 2, 64, 64, 16), (3, 1, 256, 256, 8), (5, 5, 32, 32, 16)])
-def test_qk_norm_rope_kv_write(dtype, nh, nkv, hd, rot, page):
+@pytest.mark.parametrize("T", [21, 301])     # few tokens: a lane a chunk; many: a warp a token
+def test_qk_norm_rope_kv_write(dtype, nh, nkv, hd, rot, page, T):
     from paged_llm_rs_b200.parts.base import Runtime
     from paged_llm_rs_b200.parts.position import RotaryEncoding
     from paged_llm_rs_b200.parts.spec import PartSpec
 
     g = torch.Generator(device=DEV).manual_seed(3)
-    T, pages, eps, theta = 21, 9, 1e-5, 1e6
+    pages, eps, theta = -(-T // page) + 7, 1e-5, 1e6
     qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV, generator=g).to(dtype)
     qg = 1 + 0.1 * torch.randn(hd, device=DEV, generator=g)
     kg = 1 + 0.1 * torch.randn(hd, device=DEV, generator=g)

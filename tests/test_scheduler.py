@@ -13,10 +13,12 @@ from paged_llm_rs_b200.sampling import SamplingParams
 GREEDY = SamplingParams.greedy()
 
 
-def make(pages, page_size=4, max_batch=16, chunk=None, needs=None, max_requests=16, prefix=True, max_positions=None):
+def make(pages, page_size=4, max_batch=16, chunk=None, needs=None, max_requests=16, prefix=True, max_positions=None,
+         max_prefill_seqs=1):
     cache = CacheManager(needs or [KVNeed("full", 1, 16)], page_size, pages, max_requests, torch.float32, "cpu",
                          prefix_cache=prefix, allocate_device=False)
-    return Scheduler(cache, max_batch=max_batch, chunk=chunk, max_positions=max_positions), cache
+    return Scheduler(cache, max_batch=max_batch, chunk=chunk, max_positions=max_positions,
+                     max_prefill_seqs=max_prefill_seqs), cache
 
 
 def seq(i, n, max_tokens=4, stop=(), start=0):
@@ -154,6 +156,33 @@ def test_one_prompt_in_flight_at_a_time():
     assert [e.request_id for e in plan.entries] == [0] and plan.ids == [0]
     plan, _ = step(s)
     assert [e.request_id for e in plan.entries] == [0, 1] and [len(e.tokens) for e in plan.entries] == [1, 3]
+
+
+def test_several_prompts_may_share_a_pass_when_asked():
+    # three short prompts and a long one under a budget of 16: with max_prefill_seqs 3 the first
+    # pass holds the three short ones whole; the long one starts in the next and, part-run, keeps
+    # the following passes to itself; a decoded token rides along from the second pass on
+    s, _ = make(pages=64, chunk=16, max_prefill_seqs=3)
+    for i, n in enumerate((3, 5, 4, 30)):
+        s.submit(seq(i, n, max_tokens=8, start=10 * i))
+    plan, _ = step(s)
+    assert [(e.request_id, len(e.tokens), list(e.want)) for e in plan.entries] == [(0, 3, [2]), (1, 5, [4]), (2, 4, [3])]
+    assert plan.ids == [0, 1, 2]
+    plan, _ = step(s)
+    assert [(e.request_id, len(e.tokens)) for e in plan.entries] == [(0, 1), (1, 1), (2, 1), (3, 13)]
+    assert plan.ids == [0, 1, 2]                      # the long prompt's portion wants no logits yet
+    plan, _ = step(s)
+    assert [(e.request_id, len(e.tokens)) for e in plan.entries] == [(0, 1), (1, 1), (2, 1), (3, 13)]
+    plan, _ = step(s)
+    assert [(e.request_id, len(e.tokens)) for e in plan.entries] == [(0, 1), (1, 1), (2, 1), (3, 4)]
+    assert plan.ids == [0, 1, 2, 3]
+    # the budget bounds the pass: two prompts of 10 under 16 tokens are 10 + 6, then 4
+    s, _ = make(pages=64, chunk=16, max_prefill_seqs=4)
+    s.submit(seq(0, 10)); s.submit(seq(1, 10, start=20))
+    plan, _ = step(s)
+    assert [(e.request_id, len(e.tokens), list(e.want)) for e in plan.entries] == [(0, 10, [9]), (1, 6, [])]
+    plan, _ = step(s)
+    assert [(e.request_id, len(e.tokens), list(e.want)) for e in plan.entries] == [(0, 1, [0]), (1, 4, [3])]
 
 
 def test_mixed_step_gives_way_to_preemption_when_a_resident_needs_a_page():
