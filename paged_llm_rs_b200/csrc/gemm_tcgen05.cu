@@ -25,88 +25,16 @@
 //              the tensor cores are on the next tile meanwhile
 // Every wait is bounded: a thread that gives up raises a flag that the others see, the
 // CTA frees its tensor memory and leaves, and the status word says so (bit 64).
-#include <cuda.h>
+#include "tcgen05.cuh"
 
-#include <map>
-#include <mutex>
-#include <tuple>
-
-#include "common.cuh"
+using namespace tc;
 
 namespace {
 
 constexpr int G_BM = 128, G_BK = 64;
 constexpr int G_TILE_A = G_BM * G_BK * 2;           // 16 KB
 constexpr int G_SMEM_TILES = 192 * 1024;            // what the stages may fill
-constexpr int G_SPIN_LIMIT = 1 << 22;
 constexpr int G_THREADS = 192;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Waits until the barrier's phase `parity` is over; gives up after a bounded number of polls
-// or when another thread has given up.  Returns false then.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (int spin = 0; spin < G_SPIN_LIMIT; spin++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 255) == 255 && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16),
-// stored with the 128-byte swizzle in groups of 8 rows (1024 bytes): start address, leading
-// byte offset 1 (unused with a swizzle), stride byte offset 1024, version 1, layout 2.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    return (uint64_t)((addr >> 4) & 0x3fff) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor: float accumulator, bfloat16 A and B, both K-major, M x N.
-__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
-                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(addr));
-}
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
 }  // namespace
 
@@ -263,49 +191,6 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tcgen05_kernel(const __grid
 
 // ---- host side ----------------------------------------------------------------------------------
 
-namespace {
-
-struct MapKey {
-    const void* ptr; int rows, cols, box_rows;
-    bool operator<(const MapKey& o) const { return std::tie(ptr, rows, cols, box_rows) < std::tie(o.ptr, o.rows, o.cols, o.box_rows); }
-};
-std::map<MapKey, CUtensorMap> g_maps;
-std::mutex g_maps_lock;
-
-// A [rows, cols] bfloat16 row-major matrix cut into boxes of box_rows x 64 with the 128-byte swizzle.
-int tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
-    std::lock_guard<std::mutex> hold(g_maps_lock);
-    const MapKey key{ptr, rows, cols, box_rows};
-    auto it = g_maps.find(key);
-    if (it != g_maps.end()) { *out = it->second; return 0; }
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {(cuuint32_t)G_BK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    // the driver's encoder is looked up at run time: the library then loads on a machine without a
-    // driver too (where only its host-side functions are used)
-    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    static EncodeFn encode = nullptr;
-    if (encode == nullptr) {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult found;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found) != cudaSuccess || fn == nullptr)
-            return -1;
-        encode = (EncodeFn)fn;
-    }
-    const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return (int)r;
-    if (g_maps.size() > 4096) g_maps.clear();     // activations come and go; weights come back
-    g_maps[key] = *out;
-    return 0;
-}
-
-}  // namespace
-
 // Whether this kernel takes the product (n_out: columns of y).
 PLLM_EXPORT int pllm_gemm_tcgen05_supports(int M, int n_out, int K, int glu) {
     return M >= 1 && K >= 64 && K % 8 == 0 && n_out >= 64 && n_out % (glu ? 64 : 128) == 0;
@@ -320,8 +205,12 @@ int launch_gemm(const void* x, const void* w, void* y, int M, int n_out, int K, 
     constexpr int OUT_BN = GLU ? BN / 2 : BN;
     constexpr int STAGE = G_TILE_A + BN * G_BK * 2, STAGES = G_SMEM_TILES / STAGE;
     CUtensorMap map_a, map_b;
-    if (tensor_map(x, M, K, G_BM, &map_a) != 0) return PLLM_ERR_SIZE;
-    if (tensor_map(w, GLU ? 2 * n_out : n_out, K, OUT_BN, &map_b) != 0) return PLLM_ERR_SIZE;
+    {
+        const long long da[2] = {K, M}, db[2] = {K, GLU ? 2LL * n_out : n_out}, st[1] = {2LL * K};
+        const int ba[2] = {G_BK, G_BM}, bb[2] = {G_BK, OUT_BN};
+        if (tensor_map(x, 2, da, st, ba, true, &map_a) != 0) return PLLM_ERR_SIZE;
+        if (tensor_map(w, 2, db, st, bb, true, &map_b) != 0) return PLLM_ERR_SIZE;
+    }
     if (g_sm_count == 0) {
         int dev = 0;
         cudaGetDevice(&dev);

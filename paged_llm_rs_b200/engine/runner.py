@@ -144,7 +144,7 @@ class ModelRunner:
         for g in self.cache.groups:
             nkv = g.need.num_kv_heads
             nh = nkv * g.max_group_size
-            tile = ops.attention_tile_tokens(nh, nkv, self.dtype, g.need.head_dim)
+            tile = ops.attention_tile_tokens(nh, nkv, self.dtype, g.need.head_dim, page_size, g.window or 0)
             gparts = -(-g.max_group_size // 16)
             plans.append(GroupPlanConfig(tile, nkv * gparts, g.window))
             nh_max = max(getattr(self.model.blocks[self.model.schedule[i].layer].mixer, "nh", nh) for i in g.entries)
@@ -227,7 +227,8 @@ class ModelRunner:
                                           (4, "a position outside the rotary table"), (8, "a page id outside the pool"),
                                           (16, "a wait for a copy that ran out (attention)"),
                                           (32, "a key range that does not start on a tile boundary"),
-                                          (64, "a wait that ran out in the tcgen05 product"))
+                                          (64, "a wait that ran out in the tcgen05 product"),
+                                          (128, "a wait that ran out in the tcgen05 attention"))
                     if code & bit]
             raise KernelError("a kernel met " + (", ".join(what) or f"status {code}"))
 

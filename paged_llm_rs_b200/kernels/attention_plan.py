@@ -60,8 +60,12 @@ def plan_attention(segments: Sequence[Tuple[int, int, int]], tile_tokens: int, w
     splits = np.ones(n_tiles, dtype=np.int64)
     if n_tiles * ctas_per_item < target_ctas:
         # as many splits as keep the launch within the target (one or two full waves of
-        # CTAs), rounded down so that the last wave is not a sliver
-        want = max(2, target_ctas // (n_tiles * ctas_per_item))
+        # CTAs), rounded down so that the last wave is not a sliver.  A step of single tokens that
+        # falls short of the target is cut in two at least; tiles of many tokens are not (their
+        # partial results are large, and a portion that nearly fills the GPU is better left whole).
+        want = target_ctas // (n_tiles * ctas_per_item)
+        if want < 2:
+            want = 2 if int(qn.max()) == 1 else 1
         splits = np.clip(np.minimum(want, keys // min_split_keys), 1, MAX_SPLITS)
     if (splits == 1).all():
         work = np.stack([seg, q0, qn, p0, kv_begin, kv_end, np.full(n_tiles, -1), np.zeros(n_tiles, np.int64)], 1)

@@ -60,6 +60,9 @@ def lib():
                                           c_float, c_int, P, P, P],
         }
         sig["pllm_set_pdl"] = [c_int]
+        sig["pllm_attention_prefill_tcgen05_tile_tokens"] = [c_int, c_int]
+        sig["pllm_attention_prefill_tcgen05_supports"] = [c_int] * 6
+        sig["pllm_attention_prefill_tcgen05"] = [P] * 10 + [c_int] * 7 + [c_float, P, P]
         sig["pllm_gemm_tcgen05_supports"] = [c_int, c_int, c_int, c_int]
         sig["pllm_gemm_tcgen05"] = [P, P, P, c_int, c_int, c_int, c_int, P, P]
         sig["pllm_pack_decode_step"] = [P, c_int, c_int, P, P, P, P, P] + [c_int] * 16 + [P, P]
@@ -242,10 +245,25 @@ def swizzle_pool_(pool: torch.Tensor) -> torch.Tensor:
     return pool
 
 
+# Prompt portions (work items of several tokens) in bfloat16 over swizzled pages: the tcgen05 kernel
+# (csrc/attention_prefill_tcgen05.cu), 128 rows an item (PAGED_LLM_TCGEN05_ATTN=0: the mma.sync kernels).
+TCGEN05_ATTN = os.environ.get("PAGED_LLM_TCGEN05_ATTN", "1") != "0"
+
+
+def attention_prefill_uses_tcgen05(dtype, num_heads: int, num_kv_heads: int, head_dim: int, page_size: Optional[int],
+                                   window: int) -> bool:
+    if not TCGEN05_ATTN or page_size is None or not pool_is_swizzled(dtype, num_heads, num_kv_heads, head_dim):
+        return False
+    return bool(lib().pllm_attention_prefill_tcgen05_supports(_BF16, num_heads, num_kv_heads, head_dim, int(page_size),
+                                                              int(window or 0)))
+
+
 def attention_tile_tokens(num_heads: int, num_kv_heads: int, dtype: torch.dtype = torch.float32,
-                          head_dim: int = 0) -> int:
+                          head_dim: int = 0, page_size: Optional[int] = None, window: int = 0) -> int:
     """The most query tokens one attention work item may hold, for the kernel that
-    paged_attention picks for this dtype and shape."""
+    paged_attention picks for this dtype, shape and (when given) cache layout."""
+    if attention_prefill_uses_tcgen05(dtype, num_heads, num_kv_heads, head_dim, page_size, window):
+        return lib().pllm_attention_prefill_tcgen05_tile_tokens(num_heads, num_kv_heads)
     if attention_uses_tensor_cores(dtype, num_heads, num_kv_heads, head_dim):
         return lib().pllm_attention_mma_tile_tokens(num_heads, num_kv_heads)
     return lib().pllm_attention_generic_tile_tokens(num_heads, num_kv_heads)
@@ -288,11 +306,21 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         # tokens, 2 portions of several tokens, 3 both.  The cp.async kernel takes the rest.
         tma_ok = swizzled and bool(L.pllm_attention_decode_tma_supports(_BF16, num_heads, num_kv_heads, head_dim,
                                                                         page_size, int(window)))
+        # portions of several tokens go to the tcgen05 kernel where the layout allows it
+        multi_tc = bool(kinds & 2) and swizzled and attention_prefill_uses_tcgen05(q.dtype, num_heads, num_kv_heads, head_dim,
+                                                                                   page_size, int(window))
+        if multi_tc:
+            _check(L.pllm_attention_prefill_tcgen05(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
+                                                    _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml),
+                                                    q.shape[0], num_heads, num_kv_heads, head_dim, page_size, n_pages,
+                                                    block_tables.shape[-1], float(scale), _ptr(status), _stream()),
+                   "paged_attention (tcgen05)")
+            kinds &= ~2
         take = (kinds & TMA_KINDS) if tma_ok else 0
         rest = kinds & ~take
         group = num_heads // num_kv_heads
         ctas_per_item = num_kv_heads * -(-group // min(group, 16))
-        fused = bool(FUSE_REDUCE and take and not rest and counters is not None
+        fused = bool(FUSE_REDUCE and take and not rest and not multi_tc and counters is not None
                      and counters.numel() >= max_work * ctas_per_item)
         if fused:
             _dev(counters)

@@ -194,7 +194,7 @@ def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, c
         qs.append(q); ks.append(k); vs.append(v)
         segs.append((t0, n, c))
         t0 += n
-    tile = ops.attention_tile_tokens(nh, nkv, dtype, hd)
+    tile = ops.attention_tile_tokens(nh, nkv, dtype, hd, page, window or 0)
     # (splits from 128 keys on, shorter than the engine cuts them, so that the short contexts here have some)
     work, red, parts = attention_plan.plan_attention(segs, tile, window, nkv * (-(-(nh // nkv) // 16)), target_ctas,
                                                      min_split_keys=128)
@@ -264,13 +264,14 @@ def test_bulk_copy_kernel_combines_its_splits_itself(nh, nkv, hd, page):
     mixed = [(100, 1), (400, 9), (513, 1), (0, 70), (900, 33)]
     counters = torch.zeros(1 << 16, dtype=torch.int32, device=DEV)
     was, ops.FUSE_REDUCE = ops.FUSE_REDUCE, False
-    bases = [run_attention(torch.bfloat16, reqs, nh, nkv, hd, page, None, 10 ** 6, kinds=kinds, raw=True)
-             for reqs, kinds in ((decode, 1), (mixed, 3))]
-    ops.FUSE_REDUCE = True        # (off by default: it measured slower in a whole step)
+    was_tc, ops.TCGEN05_ATTN = ops.TCGEN05_ATTN, False     # the portions too go to the bulk-copy kernel here
     try:
+        bases = [run_attention(torch.bfloat16, reqs, nh, nkv, hd, page, None, 10 ** 6, kinds=kinds, raw=True)
+                 for reqs, kinds in ((decode, 1), (mixed, 3))]
+        ops.FUSE_REDUCE = True        # (off by default: it measured slower in a whole step)
         _check_fused_combine(((decode, 1), (mixed, 3)), bases, counters, nh, nkv, hd, page)
     finally:
-        ops.FUSE_REDUCE = was
+        ops.FUSE_REDUCE, ops.TCGEN05_ATTN = was, was_tc
 
 
 def _check_fused_combine(cases, bases, counters, nh, nkv, hd, page):
@@ -283,6 +284,31 @@ def _check_fused_combine(cases, bases, counters, nh, nkv, hd, page):
             assert torch.equal(got, base)
             assert int(counters.abs().sum()) == 0
         assert ops.LAUNCHES - launches == 2          # one kernel a step: no reduction kernel
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page", [(16, 8, 128, 16), (8, 1, 64, 8), (4, 4, 128, 64), (6, 3, 64, 32), (40, 2, 64, 16),
+                                            (5, 1, 128, 16)])
+def test_prompt_portions_take_the_tcgen05_kernel(nh, nkv, hd, page):
+    # portions of many tokens, with and without context before them, ending on and off the edges of
+    # the 64-key tiles and of the 128-row items; beside single decoded tokens (the bulk-copy kernel's)
+    assert ops.attention_prefill_uses_tcgen05(torch.bfloat16, nh, nkv, hd, page, 0)
+    reqs = [(0, 300), (1000, 200), (37, 129), (63, 2), (500, 1), (0, 64), (64, 65), (0, 1)]
+    launches = ops.LAUNCHES
+    for target in (1, 10 ** 6):
+        res, _ = run_attention(torch.bfloat16, reqs, nh, nkv, hd, page, None, target)
+        for got, want in res:
+            torch.testing.assert_close(got, want, **tol(torch.bfloat16))
+    assert ops.LAUNCHES - launches >= 6        # tcgen05 + bulk-copy + reduction, twice
+    # one key far back decides the row: its score stands out, and its value is unlike the others
+    def craft(r, q, k, v):
+        if r == 0:
+            q[250] *= 0; q[250, :, 3] = 16.0
+            k[:, :, 3] = -1.0; k[41, :, 3] = 16.0
+            v[41] = 5.0
+    res, _ = run_attention(torch.bfloat16, [(0, 300)], nh, nkv, hd, page, None, 1, craft=craft)
+    got, want = res[0]
+    assert (got[250] - 5.0).abs().max() < 0.1
+    torch.testing.assert_close(got, want, **tol(torch.bfloat16))
 
 
 def test_swizzled_cache_rows():
