@@ -264,10 +264,11 @@ def main(argv=None) -> int:
         if args.only == "prefill":
             from paged_llm_rs_b200.engine.step import StepEntry
             prompt = np.random.default_rng(0).integers(0, V, PREFILL_TOKENS).tolist()
+            one_zero = np.zeros(1, dtype=np.float32)
             for _ in range(warmup + steps):
                 runner.cache.open("prefill")
                 runner.cache.reserve("prefill", PREFILL_TOKENS)
-                runner.step([StepEntry("prefill", prompt, [PREFILL_TOKENS - 1])], check=False)
+                runner.step_and_sample([StepEntry("prefill", prompt, [PREFILL_TOKENS - 1])], one_zero, one_zero)
                 runner.cache.close("prefill")
             torch.cuda.synchronize()
             print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "steps": steps}))
@@ -295,10 +296,13 @@ def main(argv=None) -> int:
         from paged_llm_rs_b200.engine.step import StepEntry
         prompt = np.random.default_rng(0).integers(0, V, PREFILL_TOKENS).tolist()
 
+        one_zero = np.zeros(1, dtype=np.float32)
+
         def prefill():
             runner.cache.open("prefill")
             runner.cache.reserve("prefill", PREFILL_TOKENS)
-            runner.step([StepEntry("prefill", prompt, [PREFILL_TOKENS - 1])], check=False)
+            # as the engine runs a prompt's portion: the step and its greedy sample, captured and replayed
+            runner.step_and_sample([StepEntry("prefill", prompt, [PREFILL_TOKENS - 1])], one_zero, one_zero)
             runner.cache.close("prefill")
 
         pms, span = time_on_device(prefill, 5, 3)

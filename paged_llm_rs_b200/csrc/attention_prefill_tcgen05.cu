@@ -40,6 +40,12 @@ constexpr int P_ROWS = 128, P_BK = 64, P_STAGES = 5, P_THREADS = 192;
 constexpr int P_PLANE = P_BK * 128;            // 64 keys x 128 bytes
 constexpr float P_RESCALE = 8.0f;              // log2 units the running maximum may lag behind
 
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
 }  // namespace
 
 template <int HD>
@@ -190,31 +196,50 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
         const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
         float m_used = -CUDART_INF_F, l_run = 0.f;
         bool ok = true;
+#ifdef PLLM_ATTN_DEBUG
+        const bool dbg = blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0;
+        unsigned long long* stamps = reinterpret_cast<unsigned long long*>(part_o);
+#define STAMP(k) if (dbg && t < 40) { unsigned long long ts; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ts)); stamps[t * 8 + (k)] = ts; }
+#else
+#define STAMP(k)
+#endif
         for (int t = 0; t < n_tiles; t++) {
             const int kv0 = w.kv_begin + t * P_BK;
+            STAMP(0)
             if (!mbar_wait(s_full + 8 * (t & 1), (t >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
+            STAMP(1)
             uint32_t v0[32], v1[32];
             tmem_ld32(lane_base + S_COL + (t & 1) * P_BK, v0);
             tmem_ld32(lane_base + S_COL + (t & 1) * P_BK + 32, v1);
             tmem_wait_ld();
-            float sc[64];
-            float mx = -CUDART_INF_F;
-            const int vis = hi - kv0;            // keys of this tile below it are visible
+            // keys of this tile at or past vis are hidden from this row (only tiles on the diagonal have any)
+            const int vis = hi - kv0;
+            if (vis < P_BK) {
 #pragma unroll
-            for (int i = 0; i < 64; i++) {
-                const float x = __uint_as_float(i < 32 ? v0[i] : v1[i - 32]) * scale_log2;
-                sc[i] = i < vis ? x : -CUDART_INF_F;
-                mx = fmaxf(mx, sc[i]);
+                for (int i = 0; i < 32; i++) {
+                    if (i >= vis) v0[i] = 0xff800000u;          // -inf
+                    if (i + 32 >= vis) v1[i] = 0xff800000u;
+                }
             }
+            // the row's maximum, four chains side by side (one warp to a scheduler: the chain's latency is the time)
+            float m4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+#pragma unroll
+                for (int k = 0; k < 4; k++) m4[k] = fmaxf(m4[k], fmaxf(__uint_as_float(v0[i + k]), __uint_as_float(v1[i + k])));
+            }
+            const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scale_log2;   // the scale is positive
             // move the maximum only when it grew by more than 2^8 (or is not set yet)
             const bool grow = mx > m_used + P_RESCALE || (m_used == -CUDART_INF_F && mx > -CUDART_INF_F);
             // P of the tile before this one must be read out of shared memory before it is overwritten,
             // and its O += P V done before O may be touched
+            STAMP(2)
             if (t > 0 && !mbar_wait(p_empty, (t - 1) & 1, abort_flag)) { ok = false; break; }
+            STAMP(3)
             if (t > 0 && __any_sync(0xffffffffu, grow)) {
                 tc_fence_after();
-                const float alpha = (grow && m_used > -CUDART_INF_F) ? exp2f(m_used - mx) : (grow ? 0.f : 1.f);
+                const float alpha = (grow && m_used > -CUDART_INF_F) ? ex2(m_used - mx) : (grow ? 0.f : 1.f);
                 l_run *= alpha;
 #pragma unroll
                 for (int c = 0; c < HD / 32; c++) {
@@ -228,27 +253,32 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 tmem_wait_st();
             }
             if (grow) m_used = mx;
+            // weights 2^(s * scale - m): one multiply-add and one exponential each; a hidden key's -inf gives 0
+            const float neg_m = m_used > -CUDART_INF_F ? -m_used : 0.f;
             uint32_t pw[32];
-            float sum = 0.f;
+            float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < 32; i++) {
-                const float p0 = m_used > -CUDART_INF_F ? exp2f(sc[2 * i] - m_used) : 0.f;
-                const float p1 = m_used > -CUDART_INF_F ? exp2f(sc[2 * i + 1] - m_used) : 0.f;
-                // the sum is taken of the rounded weights, the ones the values are multiplied by
+                const uint32_t a = i < 16 ? v0[2 * i] : v1[2 * i - 32], b2 = i < 16 ? v0[2 * i + 1] : v1[2 * i - 31];
+                const float p0 = ex2(fmaf(__uint_as_float(a), scale_log2, neg_m));
+                const float p1 = ex2(fmaf(__uint_as_float(b2), scale_log2, neg_m));
                 __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                 pw[i] = *reinterpret_cast<uint32_t*>(&h);
-                sum += __low2float(h) + __high2float(h);
+                s4[i & 3] += p0 + p1;
             }
+            const float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
             l_run += sum;
             // the row's 128 bytes, chunk c at c ^ (row & 7)
             unsigned char* prow = smem + Q_BYTES + P_STAGES * STAGE + row * 128;
 #pragma unroll
             for (int c = 0; c < 8; c++)
                 *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pw[4 * c], pw[4 * c + 1], pw[4 * c + 2], pw[4 * c + 3]);
+            STAMP(4)
             fence_async_smem();          // the tensor cores read shared memory through the async proxy
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
+            STAMP(5)
         }
         if (ok && mbar_wait(o_full, 0, abort_flag)) {
             tc_fence_after();

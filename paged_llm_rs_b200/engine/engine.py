@@ -35,6 +35,7 @@ class Engine:
                                   cache_bytes=None if blocks is not None else cache_mib << 20,
                                   max_requests=max_requests or max(256, 2 * max_batch), device=device,
                                   prefix_cache=prefix_cache)
+        self.runner.graph_step_tokens = chunk if (chunk is not None and chunk <= 8192) else None
         self.scheduler = Scheduler(self.runner.cache, max_batch=max_batch, chunk=chunk,
                                    max_positions=self.runner.spec.max_positions, max_prefill_seqs=max_prefill_seqs)
         self._next_id = 0

@@ -45,24 +45,29 @@ def parse_dtype(name) -> torch.dtype:
 
 
 class _DecodeGraph:
-    """One captured decode step for up to ``B`` requests whose block tables are at
-    most ``W`` pages wide.  Every launch argument is fixed: the step's data (token
-    ids, positions, slots, tables, work items, sampling numbers) lives in one
-    device buffer that each replay overwrites; what does not fill the capacities
-    is padding that writes nothing (slot -1) and attends to nothing (no work item)."""
+    """One captured step.  The decode form: up to ``B`` requests, one token each, block
+    tables at most ``W`` pages wide.  The general form (``segments`` given): up to ``B``
+    tokens in up to ``segments`` requests, portions of prompts beside decoded tokens.
+    Every launch argument is fixed: the step's data (token ids, positions, slots,
+    tables, work items, sampling numbers) lives in one device buffer that each replay
+    overwrites; what does not fill the capacities is padding that writes nothing
+    (slot -1) and attends to nothing (no work item)."""
 
-    def __init__(self, runner: "ModelRunner", B: int, W: int):
+    def __init__(self, runner: "ModelRunner", B: int, W: int, segments: Optional[int] = None):
         self.runner, self.B, self.W = runner, B, W
         pk = runner.packer
-        self.caps = StepCaps(tokens=B, wanted=B, segments=B, table_width=W)
-        self.work_caps = [attention_plan.plan_limits(B, p.tile_tokens, pk.target_ctas, p.ctas_per_item) for p in pk.plans]
+        self.decode = segments is None
+        n_seg = B if self.decode else segments
+        self.caps = StepCaps(tokens=B, wanted=n_seg, segments=n_seg, table_width=W, kinds=1 if self.decode else 3)
+        self.work_caps = [attention_plan.plan_limits(B, p.tile_tokens, pk.target_ctas, p.ctas_per_item, n_seg)
+                          for p in pk.plans]
         host, self.layout, self.sizes = pk.pack([], runner._heads, self.caps, self.work_caps)
         self.pinned = torch.from_numpy(host.copy()).pin_memory()
-        self.native = NativeDecodePacker(pk, self.caps, self.work_caps, self.layout, self.pinned.numpy())
+        self.native = NativeDecodePacker(pk, self.caps, self.work_caps, self.layout, self.pinned.numpy()) if self.decode else None
         self.dev = self.pinned.to(runner.device)
         self.nbytes = host.nbytes
         self.state = pk.to_state(self.dev, self.layout, self.sizes, runner._heads, full=True)
-        self.tokens = torch.zeros(1 + B, dtype=torch.int32, device=runner.device)
+        self.tokens = torch.zeros(1 + n_seg, dtype=torch.int32, device=runner.device)
         # Warm up on a side stream (library handles, workspaces), then capture.
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -95,12 +100,16 @@ class _DecodeGraph:
 
     def run(self, entries, temperature, uniform):
         r = self.runner
-        self.native.pack(entries, temperature, uniform)     # straight into the pinned buffer
+        if self.native is not None:
+            self.native.pack(entries, temperature, uniform)     # straight into the pinned buffer
+        else:
+            host, _, _ = r.packer.pack(entries, r._heads, self.caps, self.work_caps, temperature, uniform)
+            self.pinned.numpy()[:] = host
         self.dev.copy_(self.pinned, non_blocking=True)
         self.graph.replay()
         r.bytes_h2d = self.nbytes
         r.last_launches = self.launches
-        n = len(entries)
+        n = sum(len(e.want) for e in entries)
         return self.logits[:n], self.tokens[:1 + n]
 
 
@@ -157,6 +166,9 @@ class ModelRunner:
         self.use_graphs = use_graphs and all(getattr(b.mixer, "graph_safe", False) for b in self.model.blocks)
         self.max_graph_batch = max_graph_batch
         self._graphs = {}
+        # the engine's token budget a step: steps of prompt portions that fill more than half of it are
+        # captured once and replayed (None: such steps are launched kernel by kernel)
+        self.graph_step_tokens: Optional[int] = None
         self.bytes_h2d = 0        # bytes the last step copied to the device
         self.last_launches = 0    # kernels of this library the last step launched
 
@@ -177,8 +189,11 @@ class ModelRunner:
         if not entries:
             return torch.zeros((0, self.vocab_size), dtype=torch.float32, device=self.device), None
         self.bytes_h2d = 0
-        if self.use_graphs and temperature is not None and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            g = self._decode_graph(entries)
+        if self.use_graphs and temperature is not None:
+            if all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+                g = self._decode_graph(entries)
+            else:
+                g = self._portion_graph(entries)
             if g is not None:
                 return g.run(entries, temperature, uniform)
         host, layout, sizes = self.packer.pack(entries, self._heads, temperature=temperature, uniform=uniform)
@@ -216,6 +231,30 @@ class ModelRunner:
         g = self._graphs.get(key)
         if g is None:
             g = _DecodeGraph(self, B, W)
+            self._graphs[key] = g
+        return g
+
+    def _portion_graph(self, entries):
+        """The captured step for portions of prompts (beside decoded tokens), when the engine
+        runs under a token budget: one capture per (budget, requests, table width), replayed for
+        every step that fills more than half of it.  Smaller steps are launched one by one, so
+        that no step computes mostly padding."""
+        cap = self.graph_step_tokens
+        total = sum(len(e.tokens) for e in entries)
+        if not cap or total > cap or 2 * total <= cap or len(entries) > self.max_graph_batch:
+            return None
+        S = 1
+        while S < len(entries):
+            S *= 2
+        width = max((len(self.cache.get(e.request_id).tables[gi].blocks) for e in entries
+                     for gi in range(len(self.cache.groups))), default=1)
+        W = 64
+        while W < width:
+            W *= 2
+        key = (cap, W, S)
+        g = self._graphs.get(key)
+        if g is None:
+            g = _DecodeGraph(self, cap, W, segments=S)
             self._graphs[key] = g
         return g
 

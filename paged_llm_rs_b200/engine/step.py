@@ -52,6 +52,7 @@ class StepCaps:
     wanted: int
     segments: int
     table_width: int
+    kinds: int = 1        # what the captured step's attention items may be (1: single tokens only, 3: anything)
 
 
 class StepPacker:
@@ -210,7 +211,7 @@ class StepPacker:
             counts = p[2][:, 2] if len(p[2]) else np.zeros(0, np.int32)
             kinds |= (1 if (counts == 1).any() else 0) | (2 if (counts > 1).any() else 0)
         if caps is not None:
-            kinds = 1
+            kinds = caps.kinds      # a captured step launches the same kernels whatever it holds
         sizes = dict(tokens=T, wanted=n_want, segments=n_seg, tokens_cap=Tc, wanted_cap=nc, segments_cap=sc, kinds=kinds,
                      groups=[dict(parts=p[4], max_work=p[5], max_red=p[6], table_width=p[7]) for p in group_parts],
                      host_segments=segs)

@@ -95,15 +95,22 @@ def plan_attention(segments: Sequence[Tuple[int, int, int]], tile_tokens: int, w
     return work.astype(np.int32), red.astype(np.int32).reshape(-1, 4), int(rows_of.sum())
 
 
-def plan_limits(max_step_tokens: int, tile_tokens: int, target_ctas: int, ctas_per_item: int = 1) -> Tuple[int, int, int]:
+def plan_limits(max_step_tokens: int, tile_tokens: int, target_ctas: int, ctas_per_item: int = 1,
+                max_segments: Optional[int] = None) -> Tuple[int, int, int]:
     """Upper bounds (work items, reductions, partial rows) for any step of at most
-    ``max_step_tokens`` tokens, so that buffers and launch grids can be sized once.
-    Tight, because a captured step launches the bound and the idle CTAs cost time."""
-    # Unsplit: one item per tile, at most one tile per token.  Split: tiles * ctas_per_item
-    # is below the target and each tile is cut into max(2, target // (tiles * ctas_per_item))
-    # parts, which is at most 2 * target / ctas_per_item items in all.
+    ``max_step_tokens`` tokens (in at most ``max_segments`` segments, when given), so that
+    buffers and launch grids can be sized once.  Tight, because a captured step launches the
+    bound and the idle CTAs cost time (a CTA of the tcgen05 kernel holds an SM's whole shared
+    memory even to find that it has nothing to do)."""
+    # Unsplit: one item per tile; a segment of n tokens has at most n / tile + 1 tiles, and there
+    # is at most one tile per token.  Split: tiles * ctas_per_item is below the target and each
+    # tile is cut into max(2, target // (tiles * ctas_per_item)) parts, which is at most
+    # 2 * target / ctas_per_item items in all.
     split_items = -(-2 * target_ctas // max(1, ctas_per_item))
-    max_work = max(max_step_tokens, split_items)
+    tiles = max_step_tokens
+    if max_segments is not None:
+        tiles = min(tiles, max_segments + max_step_tokens // max(1, tile_tokens))
+    max_work = max(tiles, split_items)
     max_red = max_step_tokens
     max_parts = split_items * tile_tokens
     return max_work, max_red, max_parts
