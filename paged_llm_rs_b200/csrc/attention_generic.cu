@@ -174,31 +174,35 @@ __global__ void attention_reduce_kernel(const float* part_o, const float* part_m
     __shared__ float inv_s;
     pdl_launch_dependents();
     pdl_wait(KID_ATT_REDUCE);
-    const int t = blockIdx.x, head = blockIdx.y;
-    if (t >= *n_red_ptr) return;
-    const int token = red[t * 4], first = red[t * 4 + 1], count = min(red[t * 4 + 2], RED_MAX_SPLITS), stride = red[t * 4 + 3];
-    if (count <= 0) return;
-    if (threadIdx.x < 32) {
-        float M = -CUDART_INF_F;
-        for (int s = threadIdx.x; s < count; s += 32) M = fmaxf(M, part_ml[((size_t)(first + s * stride) * nh + head) * 2]);
-        M = warp_max(M);
-        float L = 0.f;
-        for (int s = threadIdx.x; s < count; s += 32) {
-            const size_t pr = (size_t)(first + s * stride) * nh + head;
-            const float ms = part_ml[pr * 2];
-            const float f = ms == -CUDART_INF_F ? 0.f : expf(ms - M);
-            wgt[s] = f;
-            L += part_ml[pr * 2 + 1] * f;
+    const int head = blockIdx.y, n_red = *n_red_ptr;
+    // a CTA takes entries blockIdx.x, blockIdx.x + gridDim.x, ...: a captured step launches a grid for
+    // the most entries a step could have, and CTAs with nothing to do must be few
+    for (int t = blockIdx.x; t < n_red; t += gridDim.x) {
+        const int token = red[t * 4], first = red[t * 4 + 1], count = min(red[t * 4 + 2], RED_MAX_SPLITS), stride = red[t * 4 + 3];
+        if (count <= 0) continue;
+        __syncthreads();       // the weights of the entry before are no longer read
+        if (threadIdx.x < 32) {
+            float M = -CUDART_INF_F;
+            for (int s = threadIdx.x; s < count; s += 32) M = fmaxf(M, part_ml[((size_t)(first + s * stride) * nh + head) * 2]);
+            M = warp_max(M);
+            float L = 0.f;
+            for (int s = threadIdx.x; s < count; s += 32) {
+                const size_t pr = (size_t)(first + s * stride) * nh + head;
+                const float ms = part_ml[pr * 2];
+                const float f = ms == -CUDART_INF_F ? 0.f : expf(ms - M);
+                wgt[s] = f;
+                L += part_ml[pr * 2 + 1] * f;
+            }
+            L = warp_sum(L);
+            if (threadIdx.x == 0) inv_s = L > 0.f ? 1.0f / L : 0.f;
         }
-        L = warp_sum(L);
-        if (threadIdx.x == 0) inv_s = L > 0.f ? 1.0f / L : 0.f;
-    }
-    __syncthreads();
-    const float inv = inv_s;
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float o = 0.f;
-        for (int s = 0; s < count; s++) o = fmaf(part_o[((size_t)(first + s * stride) * nh + head) * hd + d], wgt[s], o);
-        out[((size_t)token * nh + head) * hd + d] = from_f32<T>(o * inv);
+        __syncthreads();
+        const float inv = inv_s;
+        for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+            float o = 0.f;
+            for (int s = 0; s < count; s++) o = fmaf(part_o[((size_t)(first + s * stride) * nh + head) * hd + d], wgt[s], o);
+            out[((size_t)token * nh + head) * hd + d] = from_f32<T>(o * inv);
+        }
     }
 }
 
@@ -238,7 +242,7 @@ PLLM_EXPORT int pllm_attention_reduce(int dtype, const float* part_o, const floa
                                       cudaStream_t stream) {
     if (max_red <= 0) return PLLM_OK;
     PLLM_DISPATCH_DTYPE(dtype, {
-        dim3 grid(max_red, nh);
+        dim3 grid(max_red < 64 ? max_red : 64, nh);
         launch_chained(attention_reduce_kernel<T>, grid, dim3(hd >= 128 ? 128 : 64), 0, stream, part_o, part_ml, red,
                        n_red_ptr, (T*)out, nh, hd);
     });
