@@ -12,11 +12,16 @@
 //                 P rounded to bfloat16 into shared memory in the tensor cores' layout
 //   O += P V      tcgen05.mma, 128 x head_dim, O stays in tensor memory for the whole item
 //
-// Six warps: 0-3 softmax and epilogue, 4 the producer (TMA), 5 allocates tensor memory and
-// one of its lanes issues every tcgen05.mma.  S has two buffers, so the tensor cores form
-// the next tile's scores while the warps work on this one's; the rows' running maximum is
-// only moved when it grew by more than 2^8 (then O is rescaled in tensor memory), which is
-// exact after the final division and keeps the tensor memory traffic off the common path.
+// Twelve warps: 0-3 and 4-7 are two softmax groups that take the key tiles in turn (even tiles
+// the first, odd the second: a group's warp w owns rows 32 w .. 32 w + 31 like its twin in
+// the other group), 8 and 10 are the producers (TMA: queries and key tiles; value tiles), one lane
+// of warp 9 issues the tcgen05.mma of the scores, one of warp 11's those of the sums; warp 9 also
+// allocates the tensor memory.  S and P have two buffers each, one a group, so the tensor cores
+// form the next tiles' scores and sums while the groups work on theirs, and two warps share
+// each scheduler (the exponentials of one hide the waits of the other).  A row's running
+// maximum is only moved when it grew by more than 2^8 (then O is rescaled in tensor memory),
+// which is exact after the final division; the groups hand it to one another through shared
+// memory, tile by tile, each keeping its own part of the row's sum.
 //
 // Shared-memory layouts.  A tile for the tensor cores has rows of 128 bytes (64 values) with
 // the 128-byte swizzle (tcgen05.cuh).  The cache stores a key's or value's row (head_dim
@@ -36,7 +41,7 @@ struct AttnWork { int seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slo
 
 namespace {
 
-constexpr int P_ROWS = 128, P_BK = 64, P_STAGES = 5, P_THREADS = 192;
+constexpr int P_ROWS = 128, P_BK = 64, P_STAGES = 4, P_THREADS = 384;   // P_STAGES: key tiles, and as many value tiles, in flight
 constexpr int P_PLANE = P_BK * 128;            // 64 keys x 128 bytes
 constexpr float P_RESCALE = 8.0f;              // log2 units the running maximum may lag behind
 
@@ -56,7 +61,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     int nh, int nkv, int page_size, int page_shift, int n_pages, int table_width, float scale_log2, int heads_per_cta,
     int tile_tokens, int* status) {
     constexpr int NHALF = HD / 64;
-    constexpr int Q_BYTES = NHALF * P_ROWS * 128, STAGE = 2 * NHALF * P_PLANE, P_BYTES = P_ROWS * 128;
+    constexpr int Q_BYTES = NHALF * P_ROWS * 128, STAGE = NHALF * P_PLANE, P_BYTES = P_ROWS * 128;   // STAGE: a key (or value) tile
     constexpr uint32_t TMEM_COLS = 256, S_COL = 0, O_COL = 128;
     if ((int)blockIdx.y >= *n_work_ptr) return;
     const AttnWork w = work[blockIdx.y];
@@ -76,27 +81,40 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t q_s = smem_u32(smem);
-    const uint32_t kv_s = q_s + Q_BYTES;
-    const uint32_t p_s = kv_s + P_STAGES * STAGE;
-    unsigned char* ctl = smem + Q_BYTES + P_STAGES * STAGE + P_BYTES;
+    const uint32_t k_ring = q_s + Q_BYTES, v_ring = k_ring + P_STAGES * STAGE;
+    const uint32_t p_s = v_ring + P_STAGES * STAGE;            // two P buffers
+    constexpr int RINGS = 2 * P_STAGES * STAGE;
+    float* mstate = reinterpret_cast<float*>(smem + Q_BYTES + RINGS + 2 * P_BYTES);   // [128] a row's maximum in use
+    float* lpart = mstate + P_ROWS;                                                               // [2][128] the groups' sums
+    unsigned char* ctl = smem + Q_BYTES + RINGS + 2 * P_BYTES + 3 * P_ROWS * 4;
     const uint32_t bars = smem_u32(ctl);
-    const uint32_t q_full = bars, kv_full = bars + 8, kv_empty = kv_full + 8 * P_STAGES, s_full = kv_empty + 8 * P_STAGES,
-                   p_full = s_full + 16, p_empty = p_full + 8, o_full = p_empty + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctl + 8 * (2 * P_STAGES + 6));
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(ctl + 8 * (2 * P_STAGES + 6) + 8);
+    const uint32_t q_full = bars, k_full = bars + 8, k_empty = k_full + 8 * P_STAGES, v_full = k_empty + 8 * P_STAGES,
+                   v_empty = v_full + 8 * P_STAGES, s_full = v_empty + 8 * P_STAGES,
+                   p_full = s_full + 16, p_empty = p_full + 16, o_full = p_empty + 16, m_ready = o_full + 8,   // m_ready[2][4]
+                   s_free = m_ready + 64;
+    constexpr int N_BARS = 4 * P_STAGES + 1 + 2 + 2 + 2 + 1 + 8 + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctl + 8 * N_BARS);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(ctl + 8 * N_BARS + 8);
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < P_STAGES; s++) { mbar_init(kv_full + 8 * s, 1); mbar_init(kv_empty + 8 * s, 1); }
-        mbar_init(s_full, 1); mbar_init(s_full + 8, 1);
-        mbar_init(p_full, 4);        // one arrival from each softmax warp
-        mbar_init(p_empty, 1);
+        for (int s = 0; s < P_STAGES; s++) {
+            mbar_init(k_full + 8 * s, 1); mbar_init(k_empty + 8 * s, 1);
+            mbar_init(v_full + 8 * s, 1); mbar_init(v_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(s_full + 8 * b, 1);
+            mbar_init(p_full + 8 * b, 4);        // one arrival from each warp of the group
+            mbar_init(p_empty + 8 * b, 1);
+            mbar_init(s_free + 8 * b, 4);        // the group has its scores in registers
+            for (int wq = 0; wq < 4; wq++) mbar_init(m_ready + 8 * (4 * b + wq), 1);
+        }
         mbar_init(o_full, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
         fence_async_smem();
     }
-    if (warp == 5) {
+    if (warp == 9) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
@@ -105,114 +123,132 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 4) {
-        // ---- producer: the queries once, then key and value planes tile by tile --------------------
+    if (warp == 8 || warp == 10) {
+        // ---- producers: warp 8 the queries and the key tiles, warp 10 the value tiles, each with a ring
+        // of its own (a key tile's place comes free when its scores are formed, two tiles before its
+        // values' does; with one ring for both the keys would be fetched only two tiles ahead) --------
+        const bool keys = warp == 8;
         pdl_wait();           // the queries and this step's cache rows come from the kernel before
-        if (lane == 0) {
+        if (keys && lane == 0) {
             mbar_expect_tx(q_full, (uint32_t)(NHALF * 128 * heads_per_cta * tile_tokens));
             for (int h = 0; h < NHALF; h++) tma_load_3d(q_s + h * P_ROWS * 128, &map_q, h * 64, head0, w.q_token0, q_full);
         }
+        const CUtensorMap* map = keys ? &map_k : &map_v;
+        const uint32_t ring = keys ? k_ring : v_ring, full = keys ? k_full : v_full, empty = keys ? k_empty : v_empty;
+        unsigned char* ring_ptr = smem + Q_BYTES + (keys ? 0 : P_STAGES * STAGE);
         const int slab_rows = page_size < P_BK ? page_size : P_BK;
         const int slabs = P_BK / slab_rows;                  // at most 8
         const uint32_t slab_bytes = (uint32_t)slab_rows * 128;
         const int* table = block_tables + (size_t)w.seg * table_width;
+        // the table entries of the key range, 32 at a time, one in each lane, fetched ahead
+        int win0 = w.kv_begin >> page_shift;
+        int tbl = (win0 + lane < table_width) ? table[win0 + lane] : -1;
         for (int t = 0; t < n_tiles; t++) {
             const int s = t % P_STAGES;
             const int kv0 = w.kv_begin + t * P_BK;
-            if (t >= P_STAGES && !mbar_wait(kv_empty + 8 * s, ((t / P_STAGES) - 1) & 1, abort_flag)) break;
-            // lane i looks up slab i's page
-            int page = -1;
-            if (lane < slabs) {
-                const int j = kv0 + lane * slab_rows;
-                if (j < w.kv_end && (j >> page_shift) < table_width) page = table[j >> page_shift];
-                if (page >= n_pages) { atomicOr(status, 8); page = -1; }
+            if (((kv0 + P_BK - 1) >> page_shift) >= win0 + 32) {
+                win0 = kv0 >> page_shift;
+                tbl = (win0 + lane < table_width) ? table[win0 + lane] : -1;
             }
+            // lane i takes slab i: its page out of the window
+            const int jl = kv0 + (lane < slabs ? lane : 0) * slab_rows;
+            int page = __shfl_sync(0xffffffffu, tbl, ((jl >> page_shift) - win0) & 31);
+            if (lane >= slabs || jl >= w.kv_end) page = -1;
+            if (page >= n_pages) { atomicOr(status, 8); page = -1; }
+            if (t >= P_STAGES && !mbar_wait(empty + 8 * s, ((t / P_STAGES) - 1) & 1, abort_flag)) break;
             const uint32_t have = __ballot_sync(0xffffffffu, page >= 0) & ((1u << slabs) - 1);
-            const uint32_t st_base = kv_s + s * STAGE;
-            unsigned char* st_ptr = smem + Q_BYTES + s * STAGE;
+            const uint32_t st_base = ring + s * STAGE;
+            unsigned char* st_ptr = ring_ptr + s * STAGE;
             if (have != (1u << slabs) - 1) {
                 // slabs with no page behind them are zeroed by hand: nothing stale is multiplied
                 for (int i = 0; i < slabs; i++) {
                     if (have & (1u << i)) continue;
-                    for (int pl = 0; pl < 2 * NHALF; pl++)
+                    for (int pl = 0; pl < NHALF; pl++)
                         for (int o = lane * 16; o < (int)slab_bytes; o += 32 * 16)
                             *reinterpret_cast<uint4*>(st_ptr + pl * P_PLANE + i * slab_bytes + o) = make_uint4(0, 0, 0, 0);
                 }
                 fence_async_smem();
                 __syncwarp();
             }
-            if (lane == 0) mbar_expect_tx(kv_full + 8 * s, 2 * NHALF * slab_bytes * __popc(have));
+            if (lane == 0) mbar_expect_tx(full + 8 * s, NHALF * slab_bytes * __popc(have));
             __syncwarp();
             if (lane < slabs && page >= 0) {
-                const int j = kv0 + lane * slab_rows;
-                const int row = (page * nkv + kh) * page_size + (j & (page_size - 1));
-                for (int h = 0; h < NHALF; h++) {
-                    tma_load_2d(st_base + h * P_PLANE + lane * slab_bytes, &map_k, h * 64, row, kv_full + 8 * s);
-                    tma_load_2d(st_base + (NHALF + h) * P_PLANE + lane * slab_bytes, &map_v, h * 64, row, kv_full + 8 * s);
-                }
+                const int row = (page * nkv + kh) * page_size + (jl & (page_size - 1));
+                for (int h = 0; h < NHALF; h++) tma_load_2d(st_base + h * P_PLANE + lane * slab_bytes, map, h * 64, row, full + 8 * s);
             }
         }
-    } else if (warp == 5) {
-        // ---- tensor-core issue ----------------------------------------------------------------------
+    } else if (warp == 9) {
+        // ---- tensor-core issue, the scores: S[t & 1] = Q K_t^T.  (Two issuing threads, this one and
+        // warp 11's for O += P V: each tile costs an issuing thread a handful of waits, instructions
+        // and commits one after the other, and that, not the tensor cores' time, bounds the kernel.)
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = instr_desc(P_ROWS, P_BK), idesc_pv = instr_desc(P_ROWS, HD, 1);
+            constexpr uint32_t idesc_qk = instr_desc(P_ROWS, P_BK);
+            // descriptors differ only in their address field (bits 0-13, units of 16 bytes): the rest is
+            // made once, and an address offset is one addition
+            const uint64_t q_desc = smem_desc(q_s), k_desc = smem_desc(k_ring);
             bool ok = mbar_wait(q_full, 0, abort_flag);
-            auto scores = [&](int t) {       // S[t & 1] = Q K_t^T
+            for (int t = 0; t < n_tiles && ok; t++) {
                 const int s = t % P_STAGES;
-                if (!mbar_wait(kv_full + 8 * s, (t / P_STAGES) & 1, abort_flag)) return false;
+                // the group must have read the scores of two tiles ago out of this buffer
+                if (t >= 2 && !mbar_wait(s_free + 8 * (t & 1), ((t - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(k_full + 8 * s, (t / P_STAGES) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t k_base = kv_s + s * STAGE;
+                const uint64_t kd = k_desc + (uint64_t)((s * STAGE) >> 4);
+                const uint32_t d = tmem + S_COL + (t & 1) * P_BK;
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++)
-                    mma_ss(tmem + S_COL + (t & 1) * P_BK, smem_desc(q_s + (ks / 4) * P_ROWS * 128 + (ks % 4) * 32),
-                           smem_desc(k_base + (ks / 4) * P_PLANE + (ks % 4) * 32), idesc_qk, ks ? 1u : 0u);
+                    mma_ss(d, q_desc + (uint64_t)(((ks / 4) * P_ROWS * 128 + (ks % 4) * 32) >> 4),
+                           kd + (uint64_t)(((ks / 4) * P_PLANE + (ks % 4) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
+                mma_commit(k_empty + 8 * s);         // the key tile's place is free once these have read it
                 mma_commit(s_full + 8 * (t & 1));
-                return true;
-            };
-            for (int t = 0; t < 2 && t < n_tiles && ok; t++) ok = scores(t);
+            }
+        }
+    } else if (warp == 11) {
+        // ---- tensor-core issue, the sums: O += P_t V_t --------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_pv = instr_desc(P_ROWS, HD, 1);
+            const uint64_t p_desc = smem_desc(p_s), v_desc = smem_desc(v_ring, P_PLANE);
+            bool ok = true;
             for (int t = 0; t < n_tiles && ok; t++) {
-                if (!mbar_wait(p_full, t & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(p_full + 8 * (t & 1), (t >> 1) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(v_full + 8 * (t % P_STAGES), (t / P_STAGES) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t v_base = kv_s + (t % P_STAGES) * STAGE + NHALF * P_PLANE;
+                const uint64_t vd = v_desc + (uint64_t)(((t % P_STAGES) * STAGE) >> 4);
+                const uint64_t pd = p_desc + (uint64_t)(((t & 1) * P_BYTES) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < P_BK / 16; ks++)     // 16 keys = 2048 bytes down the value planes
-                    mma_ss(tmem + O_COL, smem_desc(p_s + ks * 32), smem_desc(v_base + ks * 2048, P_PLANE), idesc_pv,
+                    mma_ss(tmem + O_COL, pd + (uint64_t)((ks * 32) >> 4), vd + (uint64_t)((ks * 2048) >> 4), idesc_pv,
                            (t | ks) ? 1u : 0u);
-                mma_commit(kv_empty + 8 * (t % P_STAGES));   // keys and values of this tile are read
-                mma_commit(p_empty);                         // and so is P
-                if (t + 2 < n_tiles) ok = scores(t + 2);
+                mma_commit(v_empty + 8 * (t % P_STAGES));    // the values of this tile are read
+                mma_commit(p_empty + 8 * (t & 1));           // and so is this group's P (and O holds the tile)
             }
             if (ok) mma_commit(o_full);
         }
     } else {
-        // ---- softmax, one row a thread; then the epilogue -------------------------------------------
+        // ---- softmax, one row a thread, the two groups taking the tiles in turn; then the epilogue ----
         pdl_launch_dependents();
-        const int row = warp * 32 + lane;
+        const int grp = warp >> 2, wq = warp & 3;
+        const int row = wq * 32 + lane;
         const int tq = row / heads_per_cta, hh = row % heads_per_cta;
         const bool live = tq < w.q_count && hh < n_heads && tq < tile_tokens;
         // keys below hi are visible to this row; rows that are no query's see everything (their
         // results are never stored, and a row of nothing but masked keys would make NaN)
         const int hi = live ? min(w.kv_end, w.q_pos0 + tq + 1) : w.kv_end;
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-        float m_used = -CUDART_INF_F, l_run = 0.f;
+        const uint32_t lane_base = tmem + ((uint32_t)(wq * 32) << 16);
+        // this group's part of the row's sum, in units of 2^m_ref
+        float m_ref = -CUDART_INF_F, l_run = 0.f;
         bool ok = true;
-#ifdef PLLM_ATTN_DEBUG
-        const bool dbg = blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0;
-        unsigned long long* stamps = reinterpret_cast<unsigned long long*>(part_o);
-#define STAMP(k) if (dbg && t < 40) { unsigned long long ts; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ts)); stamps[t * 8 + (k)] = ts; }
-#else
-#define STAMP(k)
-#endif
-        for (int t = 0; t < n_tiles; t++) {
+        for (int t = grp; t < n_tiles; t += 2) {
             const int kv0 = w.kv_begin + t * P_BK;
-            STAMP(0)
-            if (!mbar_wait(s_full + 8 * (t & 1), (t >> 1) & 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(s_full + 8 * grp, (t >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            STAMP(1)
             uint32_t v0[32], v1[32];
-            tmem_ld32(lane_base + S_COL + (t & 1) * P_BK, v0);
-            tmem_ld32(lane_base + S_COL + (t & 1) * P_BK + 32, v1);
+            tmem_ld32(lane_base + S_COL + grp * P_BK, v0);
+            tmem_ld32(lane_base + S_COL + grp * P_BK + 32, v1);
             tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free + 8 * grp);        // the buffer may take the scores of two tiles on
             // keys of this tile at or past vis are hidden from this row (only tiles on the diagonal have any)
             const int vis = hi - kv0;
             if (vis < P_BK) {
@@ -222,7 +258,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                     if (i + 32 >= vis) v1[i] = 0xff800000u;
                 }
             }
-            // the row's maximum, four chains side by side (one warp to a scheduler: the chain's latency is the time)
+            // the row's maximum, four chains side by side
             float m4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
@@ -230,17 +266,24 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 for (int k = 0; k < 4; k++) m4[k] = fmaxf(m4[k], fmaxf(__uint_as_float(v0[i + k]), __uint_as_float(v1[i + k])));
             }
             const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scale_log2;   // the scale is positive
-            // move the maximum only when it grew by more than 2^8 (or is not set yet)
-            const bool grow = mx > m_used + P_RESCALE || (m_used == -CUDART_INF_F && mx > -CUDART_INF_F);
-            // P of the tile before this one must be read out of shared memory before it is overwritten,
-            // and its O += P V done before O may be touched
-            STAMP(2)
-            if (t > 0 && !mbar_wait(p_empty, (t - 1) & 1, abort_flag)) { ok = false; break; }
-            STAMP(3)
+            // the maximum in use after the tile before this one, which the other group decided
+            float m_prev = -CUDART_INF_F;
+            if (t > 0) {
+                if (!mbar_wait(m_ready + 8 * (4 * (grp ^ 1) + wq), ((t - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                m_prev = mstate[row];
+            }
+            // it moves only when it grew by more than 2^8 (or is not set yet)
+            const bool grow = mx > m_prev + P_RESCALE || (m_prev == -CUDART_INF_F && mx > -CUDART_INF_F);
+            const float m_used = grow ? mx : m_prev;
+            mstate[row] = m_used;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(m_ready + 8 * (4 * grp + wq));      // the other group may go on with its tile
             if (t > 0 && __any_sync(0xffffffffu, grow)) {
+                // O is rescaled once the tile before this one is in it (this tile's is not issued before
+                // this group says so, nor the next one's before this tile's)
+                if (!mbar_wait(p_empty + 8 * (grp ^ 1), ((t - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const float alpha = (grow && m_used > -CUDART_INF_F) ? ex2(m_used - mx) : (grow ? 0.f : 1.f);
-                l_run *= alpha;
+                const float alpha = (grow && m_prev > -CUDART_INF_F) ? ex2(m_prev - m_used) : (grow ? 0.f : 1.f);
 #pragma unroll
                 for (int c = 0; c < HD / 32; c++) {
                     uint32_t o[32];
@@ -252,7 +295,11 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 }
                 tmem_wait_st();
             }
-            if (grow) m_used = mx;
+            // this group's sum so far, brought to the maximum now in use
+            if (m_ref != m_used) {
+                l_run = m_ref > -CUDART_INF_F ? l_run * ex2(m_ref - m_used) : 0.f;
+                m_ref = m_used;
+            }
             // weights 2^(s * scale - m): one multiply-add and one exponential each; a hidden key's -inf gives 0
             const float neg_m = m_used > -CUDART_INF_F ? -m_used : 0.f;
             uint32_t pw[32];
@@ -266,25 +313,33 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 pw[i] = *reinterpret_cast<uint32_t*>(&h);
                 s4[i & 3] += p0 + p1;
             }
-            const float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
-            l_run += sum;
+            l_run += (s4[0] + s4[1]) + (s4[2] + s4[3]);
+            // this group's P of two tiles ago must be read out of shared memory before it is overwritten
+            if (t >= 2 && !mbar_wait(p_empty + 8 * grp, ((t - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
             // the row's 128 bytes, chunk c at c ^ (row & 7)
-            unsigned char* prow = smem + Q_BYTES + P_STAGES * STAGE + row * 128;
+            unsigned char* prow = smem + Q_BYTES + RINGS + grp * P_BYTES + row * 128;
 #pragma unroll
             for (int c = 0; c < 8; c++)
                 *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pw[4 * c], pw[4 * c + 1], pw[4 * c + 2], pw[4 * c + 3]);
-            STAMP(4)
             fence_async_smem();          // the tensor cores read shared memory through the async proxy
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
-            STAMP(5)
+            if (lane == 0) mbar_arrive(p_full + 8 * grp);
         }
-        if (ok && mbar_wait(o_full, 0, abort_flag)) {
+        // ---- the groups' sums meet; each group stores half of the columns -------------------------------
+        if (!ok || *abort_flag) *abort_flag = 1;
+        asm volatile("bar.sync 1, 256;\n" ::: "memory");          // (the eight softmax warps; the others are elsewhere)
+        const float m_fin = mstate[row];                           // after the last tile (every row has one)
+        lpart[grp * P_ROWS + row] = (m_ref > -CUDART_INF_F && m_fin > -CUDART_INF_F) ? l_run * ex2(m_ref - m_fin) : 0.f;
+        asm volatile("bar.sync 1, 256;\n" ::: "memory");
+        const float l_tot = lpart[row] + lpart[P_ROWS + row];
+        if (!*abort_flag && mbar_wait(o_full, 0, abort_flag)) {
             tc_fence_after();
-            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            const float inv = l_tot > 0.f ? 1.0f / l_tot : 0.f;
+            constexpr int HALF_CHUNKS = HD / 64;                   // chunks of 32 columns a group
 #pragma unroll
-            for (int c = 0; c < HD / 32; c++) {
+            for (int cc = 0; cc < HALF_CHUNKS; cc++) {
+                const int c = grp * HALF_CHUNKS + cc;
                 uint32_t o[32];
                 tmem_ld32(lane_base + O_COL + c * 32, o);
                 tmem_wait_ld();
@@ -310,7 +365,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                     for (int i = 0; i < 8; i++)
                         *reinterpret_cast<float4*>(dst + 4 * i) = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]),
                                                                               __uint_as_float(o[4 * i + 2]), __uint_as_float(o[4 * i + 3]));
-                    if (c == 0) { part_ml[pr * 2] = m_used * 0.6931471805599453f; part_ml[pr * 2 + 1] = l_run; }   // natural-log units
+                    if (c == 0) { part_ml[pr * 2] = m_fin * 0.6931471805599453f; part_ml[pr * 2 + 1] = l_tot; }   // natural-log units
                 }
             }
         }
@@ -318,7 +373,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     // ---- everyone meets; the allocating warp gives the tensor memory back ---------------------------
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS));
     }
@@ -361,8 +416,8 @@ static int launch_prefill(const void* q, const void* k_pool, const void* v_pool,
         if (tensor_map(v_pool, 2, dp, sp, bp, false, &map_v) != 0) return PLLM_ERR_SIZE;
     }
     constexpr int NHALF = HD / 64;
-    const size_t smem = (size_t)NHALF * P_ROWS * 128 + (size_t)P_STAGES * 2 * NHALF * P_PLANE + P_ROWS * 128 +
-                        8 * (2 * P_STAGES + 6) + 16 + 1024;
+    const size_t smem = (size_t)NHALF * P_ROWS * 128 + (size_t)P_STAGES * 2 * NHALF * P_PLANE + 2 * P_ROWS * 128 +
+                        3 * P_ROWS * 4 + 8 * (4 * P_STAGES + 18) + 16 + 1024;
     cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_chained(attention_prefill_tcgen05_kernel<HD>, dim3(nkv * gparts, max_work), dim3(P_THREADS), smem, stream, map_q,
                    map_k, map_v, block_tables, (const AttnWork*)work, n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv,
