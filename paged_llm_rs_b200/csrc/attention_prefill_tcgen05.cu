@@ -59,13 +59,15 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_tables, const AttnWork* __restrict__ work,
     const int* __restrict__ n_work_ptr, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     int nh, int nkv, int page_size, int page_shift, int n_pages, int table_width, float scale_log2, int heads_per_cta,
-    int tile_tokens, int* status) {
+    int tile_tokens, int take_single, int* status) {
     constexpr int NHALF = HD / 64;
     constexpr int Q_BYTES = NHALF * P_ROWS * 128, STAGE = NHALF * P_PLANE, P_BYTES = P_ROWS * 128;   // STAGE: a key (or value) tile
     constexpr uint32_t TMEM_COLS = 256, S_COL = 0, O_COL = 128;
     if ((int)blockIdx.y >= *n_work_ptr) return;
     const AttnWork w = work[blockIdx.y];
-    if (w.q_count <= 1) return;                       // single decoded tokens are another kernel's
+    // single decoded tokens are another kernel's, unless this one is told to take them too (a step of
+    // portions beside a few decoded tokens: one launch instead of two; their rows are few, their keys the same)
+    if (w.q_count <= 1 && !take_single) return;
     if (w.kv_begin & (P_BK - 1)) {
         if (threadIdx.x == 0) atomicOr(status, 32);
         return;
@@ -396,8 +398,8 @@ PLLM_EXPORT int pllm_attention_prefill_tcgen05_supports(int dtype, int nh, int n
 template <int HD>
 static int launch_prefill(const void* q, const void* k_pool, const void* v_pool, const int* block_tables, const int* work,
                           const int* n_work_ptr, int max_work, void* out, float* part_o, float* part_ml, int n_tokens,
-                          int nh, int nkv, int page_size, int n_pages, int table_width, float scale, int* status,
-                          cudaStream_t stream) {
+                          int nh, int nkv, int page_size, int n_pages, int table_width, float scale, int take_single,
+                          int* status, cudaStream_t stream) {
     const int group = nh / nkv;
     const int heads_per_cta = group < 16 ? group : 16;
     const int gparts = (group + heads_per_cta - 1) / heads_per_cta;
@@ -421,7 +423,8 @@ static int launch_prefill(const void* q, const void* k_pool, const void* v_pool,
     cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_chained(attention_prefill_tcgen05_kernel<HD>, dim3(nkv * gparts, max_work), dim3(P_THREADS), smem, stream, map_q,
                    map_k, map_v, block_tables, (const AttnWork*)work, n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv,
-                   page_size, page_shift, n_pages, table_width, scale * 1.4426950408889634f, heads_per_cta, tile_tokens, status);
+                   page_size, page_shift, n_pages, table_width, scale * 1.4426950408889634f, heads_per_cta, tile_tokens, take_single,
+                   status);
     return launch_status();
 }
 
@@ -429,14 +432,14 @@ static int launch_prefill(const void* q, const void* k_pool, const void* v_pool,
 PLLM_EXPORT int pllm_attention_prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool, const int* block_tables,
                                                const int* work, const int* n_work_ptr, int max_work, void* out,
                                                float* part_o, float* part_ml, int n_tokens, int nh, int nkv, int hd,
-                                               int page_size, int n_pages, int table_width, float scale, int* status,
-                                               cudaStream_t stream) {
+                                               int page_size, int n_pages, int table_width, float scale, int take_single,
+                                               int* status, cudaStream_t stream) {
     if (max_work <= 0 || n_tokens <= 0) return PLLM_OK;
     if (!pllm_attention_prefill_tcgen05_supports(PLLM_BF16, nh, nkv, hd, page_size, 0)) return PLLM_ERR_SIZE;
     if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) return PLLM_ERR_ALIGN;
     if (hd == 128)
         return launch_prefill<128>(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, n_tokens,
-                                   nh, nkv, page_size, n_pages, table_width, scale, status, stream);
+                                   nh, nkv, page_size, n_pages, table_width, scale, take_single, status, stream);
     return launch_prefill<64>(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, n_tokens, nh,
-                              nkv, page_size, n_pages, table_width, scale, status, stream);
+                              nkv, page_size, n_pages, table_width, scale, take_single, status, stream);
 }

@@ -62,7 +62,7 @@ def lib():
         sig["pllm_set_pdl"] = [c_int]
         sig["pllm_attention_prefill_tcgen05_tile_tokens"] = [c_int, c_int]
         sig["pllm_attention_prefill_tcgen05_supports"] = [c_int] * 6
-        sig["pllm_attention_prefill_tcgen05"] = [P] * 10 + [c_int] * 7 + [c_float, P, P]
+        sig["pllm_attention_prefill_tcgen05"] = [P] * 10 + [c_int] * 7 + [c_float, c_int, P, P]
         sig["pllm_gemm_tcgen05_supports"] = [c_int, c_int, c_int, c_int]
         sig["pllm_gemm_tcgen05"] = [P, P, P, c_int, c_int, c_int, c_int, P, P]
         sig["pllm_pack_decode_step"] = [P, c_int, c_int, P, P, P, P, P] + [c_int] * 16 + [P, P]
@@ -313,9 +313,11 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
             _check(L.pllm_attention_prefill_tcgen05(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
                                                     _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml),
                                                     q.shape[0], num_heads, num_kv_heads, head_dim, page_size, n_pages,
-                                                    block_tables.shape[-1], float(scale), _ptr(status), _stream()),
+                                                    block_tables.shape[-1], float(scale), 1 if kinds == 3 else 0,
+                                                    _ptr(status), _stream()),
                    "paged_attention (tcgen05)")
-            kinds &= ~2
+            # beside portions it takes the single decoded tokens too: one launch a layer, not two
+            kinds = 0 if kinds == 3 else kinds & ~2
         take = (kinds & TMA_KINDS) if tma_ok else 0
         rest = kinds & ~take
         group = num_heads // num_kv_heads
