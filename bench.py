@@ -136,13 +136,13 @@ def decode_point(runner, batch, context, steps, warmup, clocks):
     return ms, launches
 
 
-TRACE_KERNELS = {1: "embed", 2: "rmsnorm", 3: "swiglu", 4: "qk_norm_rope_kv", 5: "attention_generic", 6: "attention_reduce",
-                 7: "attention_mma", 8: "attention_tma", 9: "skinny_gemm", 10: "sample_partial", 11: "sample_final"}
+TRACE_KERNELS = {0: "(tcgen05 kernel)", 1: "embed", 2: "rmsnorm", 3: "swiglu", 4: "qk_norm_rope_kv", 5: "attention_generic", 6: "attention_reduce",
+                 7: "attention_mma", 8: "attention_tma", 9: "skinny_gemm", 10: "sample_partial", 11: "sample_final", 12: "gemm_tcgen05", 13: "attention_tcgen05"}
 TRACE_FILES = ["elementwise", "qk_norm_rope_kv", "attention_generic", "attention_mma", "attention_decode_tma", "sampling",
-               "skinny_gemm"]
+               "skinny_gemm", "gemm_tcgen05", "attention_prefill_tcgen05"]
 
 
-def timeline(runner, batch, context, layers) -> int:
+def timeline(runner, batch, context, layers, prefill_tokens=0, vocab=1000) -> int:
     """One replay of the captured decode step, clocked by the kernels themselves (thread 0 of
     each kernel's first CTA reads the global timer before and after its wait for the kernel
     before it).  "to next" is the time from a kernel's wait ending to the next kernel's wait
@@ -168,15 +168,25 @@ def timeline(runner, batch, context, layers) -> int:
         return sorted(recs)
 
     cache = runner.cache
-    ids = [f"t{b}" for b in range(batch)]
-    for r in ids:
-        cache.open(r)
-        assert cache.reserve(r, context)
-        cache.commit(r, context - 1)
-    entries = [StepEntry(r, [1 + i], [0]) for i, r in enumerate(ids)]
-    zeros = np.zeros(batch, dtype=np.float32)
-    runner.step_and_sample(entries, zeros, zeros)
-    graph = runner._decode_graph(entries)
+    if prefill_tokens:
+        prompt = np.random.default_rng(0).integers(0, vocab, prefill_tokens).tolist()
+        cache.open("tp")
+        assert cache.reserve("tp", prefill_tokens)
+        entries = [StepEntry("tp", prompt, [prefill_tokens - 1])]
+        zeros = np.zeros(1, dtype=np.float32)
+        runner.step_and_sample(entries, zeros, zeros)
+        graph = runner._portion_graph(entries)
+        assert graph is not None, "the portion does not run as a captured step"
+    else:
+        ids = [f"t{b}" for b in range(batch)]
+        for r in ids:
+            cache.open(r)
+            assert cache.reserve(r, context)
+            cache.commit(r, context - 1)
+        entries = [StepEntry(r, [1 + i], [0]) for i, r in enumerate(ids)]
+        zeros = np.zeros(batch, dtype=np.float32)
+        runner.step_and_sample(entries, zeros, zeros)
+        graph = runner._decode_graph(entries)
     for _ in range(5):
         graph.graph.replay()
     torch.cuda.synchronize()
@@ -190,7 +200,8 @@ def timeline(runner, batch, context, layers) -> int:
         rows.append((TRACE_KERNELS.get(kid, str(kid)), (after - recs[0][0]) / 1e3, (nxt - after) / 1e3, (after - before) / 1e3))
     per_layer = max(1, (len(rows) - 4) // max(1, layers))
     start = min(len(rows), 2 + per_layer * (layers // 2))
-    print(f"decode step, batch {batch}, context {context}, {layers} layers: {len(rows)} kernels stamped, "
+    what = f"prefill step, {prefill_tokens} tokens" if prefill_tokens else f"decode step, batch {batch}, context {context}"
+    print(f"{what}, {layers} layers: {len(rows)} kernels stamped, "
           f"{(recs[-1][0] - recs[0][0]) / 1e3:.1f} us from first to last")
     print(f"one layer from the middle:\n{'kernel':18s} {'at us':>9s} {'to next':>8s} {'in place':>8s}")
     for name, t, d, w in rows[start:start + per_layer]:
@@ -215,6 +226,8 @@ def main(argv=None) -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the shape has (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--timeline-prefill", action="store_true",
+                    help="with --only timeline: the captured step of a 2048-token prompt portion instead of the decode step")
     ap.add_argument("--only", choices=["decode", "prefill", "timeline"], default=None,
                     help="run one part alone and print a short line (for profiling; not a bench record); "
                          "timeline: one captured decode step as the kernels themselves clocked it")
@@ -275,7 +288,7 @@ def main(argv=None) -> int:
             return 0
 
         if args.only == "timeline":
-            return timeline(runner, B, ctx, L)
+            return timeline(runner, B, ctx, L, PREFILL_TOKENS if args.timeline_prefill else 0, V)
 
         # -- decode, on the device -------------------------------------------------------
         ms, launches = decode_point(runner, B, ctx, steps, warmup, clocks)

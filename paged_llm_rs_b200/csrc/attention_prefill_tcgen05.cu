@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
         // of its own (a key tile's place comes free when its scores are formed, two tiles before its
         // values' does; with one ring for both the keys would be fetched only two tiles ahead) --------
         const bool keys = warp == 8;
-        pdl_wait();           // the queries and this step's cache rows come from the kernel before
+        pdl_wait(KID_ATT_TC, keys && lane == 0);           // the queries and this step's cache rows come from the kernel before
         if (keys && lane == 0) {
             mbar_expect_tx(q_full, (uint32_t)(NHALF * 128 * heads_per_cta * tile_tokens));
             for (int h = 0; h < NHALF; h++) tma_load_3d(q_s + h * P_ROWS * 128, &map_q, h * 64, head0, w.q_token0, q_full);
@@ -443,3 +443,5 @@ PLLM_EXPORT int pllm_attention_prefill_tcgen05(const void* q, const void* k_pool
     return launch_prefill<64>(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, n_tokens, nh,
                               nkv, page_size, n_pages, table_width, scale, take_single, status, stream);
 }
+
+PLLM_TRACE_EXPORT(attention_prefill_tcgen05)

@@ -114,7 +114,7 @@ static inline int launch_status() {
 // at once.  Weights, tables and the host's step buffer may use the read-only path.
 // Without the attribute both calls do nothing.
 #ifndef PLLM_TRACE
-__device__ __forceinline__ void pdl_wait(int kernel_id = 0) { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait(int kernel_id = 0, bool this_thread = false) { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 #define PLLM_TRACE_EXPORT(file)
 #else
 // A build for timelines (-DPLLM_TRACE=1): thread 0 of block (0, 0) of every kernel stamps the
@@ -129,8 +129,11 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ void pdl_wait(int kernel_id = 0) {
-    const bool me = (threadIdx.x | threadIdx.y | blockIdx.x | blockIdx.y | blockIdx.z) == 0;
+// (this_thread: the caller is the one thread of the kernel's first CTA that is to stamp, in kernels
+// whose thread 0 does not wait)
+__device__ __forceinline__ void pdl_wait(int kernel_id = 0, bool this_thread = false) {
+    const bool me = this_thread ? (blockIdx.x | blockIdx.y | blockIdx.z) == 0
+                                : (threadIdx.x | threadIdx.y | blockIdx.x | blockIdx.y | blockIdx.z) == 0;
     const unsigned long long t0 = me ? global_ns() : 0;
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
     if (me) {
@@ -153,7 +156,7 @@ __device__ __forceinline__ void pdl_wait(int kernel_id = 0) {
 #endif
 // Kernel ids of the timeline.
 enum : int { KID_EMBED = 1, KID_RMSNORM, KID_SWIGLU, KID_QK, KID_ATT_GENERIC, KID_ATT_REDUCE, KID_ATT_MMA, KID_ATT_TMA,
-             KID_GEMM, KID_SAMPLE_PART, KID_SAMPLE_FINAL };
+             KID_GEMM, KID_SAMPLE_PART, KID_SAMPLE_FINAL, KID_GEMM_TC, KID_ATT_TC };
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 
 extern int pllm_pdl_enabled;  // defined in elementwise.cu; set through pllm_set_pdl

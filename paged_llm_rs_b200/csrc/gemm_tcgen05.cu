@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tcgen05_kernel(const __grid
     if (warp == 4) {
         // ---- producer ---------------------------------------------------------------------------
         if (lane == 0) {
-            pdl_wait();      // x comes from the kernel before this one
+            pdl_wait(KID_GEMM_TC, true);      // x comes from the kernel before this one
             int it = 0;      // k blocks loaded so far, over all of this CTA's tiles
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
@@ -239,3 +239,5 @@ PLLM_EXPORT int pllm_gemm_tcgen05(const void* x, const void* w, void* y, int M, 
     if (glu) return wide ? launch_gemm<1, 256>(x, w, y, M, n_out, K, status, stream) : launch_gemm<1, 128>(x, w, y, M, n_out, K, status, stream);
     return wide ? launch_gemm<0, 256>(x, w, y, M, n_out, K, status, stream) : launch_gemm<0, 128>(x, w, y, M, n_out, K, status, stream);
 }
+
+PLLM_TRACE_EXPORT(gemm_tcgen05)
