@@ -97,13 +97,54 @@ template <int HD> __device__ __forceinline__ uint32_t toff(int row, int chunk) {
 
 }  // namespace
 
+// What the kernel needs to do the work of the q/k norm + rotation + cache-write kernel itself, for
+// steps of single decoded tokens (qkv null: not asked to).  The reference does these as separate
+// tensor operations before its attention (crates/pagedllm/src/model/attention.rs:148-158); in a
+// decode step each is a launch of a few microseconds for a few kilobytes.
+struct FusedQK {
+    const bf16* qkv;                 // [tokens, (nh + 2 nkv) * hd], the projection's output
+    const float *q_gain, *k_gain;    // [hd] or null: no norm
+    const float *cos_t, *sin_t;      // [max_pos, hd / 2] or null: no rotation
+    bf16 *k_pool, *v_pool;           // the pools again, to write the token's own row
+    float eps;
+    int max_pos;
+};
+
+// One head's row, hd / 32 values a lane (lane l: dims l * VPL ..): the norm over the row, then the
+// rotation of dim d with d +- hd / 2 (16 lanes away), in float; the arithmetic of qk_norm_rope_kv.cu.
+template <int HD>
+__device__ __forceinline__ void norm_rope_row(const bf16* src, const float* gain, const float* cs, const float* sn, float eps,
+                                              int lane, float (&f)[HD / 32]) {
+    constexpr int VPL = HD / 32;
+#pragma unroll
+    for (int k = 0; k < VPL; k++) f[k] = __bfloat162float(src[lane * VPL + k]);
+    if (gain) {
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPL; k++) ss += f[k] * f[k];
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+        for (int k = 0; k < VPL; k++) f[k] = f[k] * inv * gain[lane * VPL + k];
+    }
+    if (cs) {
+        const bool upper = lane >= 16;
+#pragma unroll
+        for (int k = 0; k < VPL; k++) {
+            const float other = __shfl_xor_sync(0xffffffffu, f[k], 16);
+            const int i = (lane & 15) * VPL + k;
+            f[k] = upper ? f[k] * cs[i] + other * sn[i] : f[k] * cs[i] - other * sn[i];
+        }
+    }
+}
+
 template <int HD>
 __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_tma_kernel(
     const bf16* q, const bf16* k_pool, const bf16* v_pool,   // written by the kernels before this one: no __restrict__
     const int* __restrict__ block_tables, const AttnWork* __restrict__ work, const int* __restrict__ n_work_ptr,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     int nh, int nkv, int page_size, int page_shift, int n_pages, int table_width, float scale_log2,
-    int heads_per_cta, int kinds_mask, int* counters, int* status) {
+    int heads_per_cta, int kinds_mask, int* counters, FusedQK fq, int* status) {
     // The work items and block tables came from the host before the step, and the cache below
     // the step's own positions was written by earlier steps: neither depends on the kernels
     // just before this one.  So nobody waits for those kernels yet: the producer starts the
@@ -211,13 +252,67 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
     }
 
     // the query rows, zero beyond them (the first tiles are on their way meanwhile)
-    pdl_wait(KID_ATT_TMA);
-    for (int idx = threadIdx.x; idx < (decode ? 16 : TD_QROWS) * CH; idx += TD_CONSUMERS * 32) {
-        const int row = idx / CH, chunk = idx % CH;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < rows)
-            v = *reinterpret_cast<const uint4*>(q + ((size_t)(w.q_token0 + row / n_heads) * nh + head0 + row % n_heads) * HD + chunk * 8);
-        *reinterpret_cast<uint4*>(smem + TD_STAGES * STAGE_BYTES + toff<HD>(row, chunk)) = v;
+    const bool fused = fq.qkv != nullptr && decode;
+    // fused: this CTA's range ends with the token's own key, which it makes itself (norm, rotation),
+    // stores to the cache for later steps and puts into the last tile in shared memory
+    const bool owns_new = fused && w.kv_end == w.q_pos0 + 1;
+    constexpr int VPL = HD / 32;
+    uint32_t new_k[VPL / 2], new_v[VPL / 2];       // the row's values of this lane, packed (warps 2 and 3)
+    if (fused) {
+        int pos = w.q_pos0;
+        if (fq.cos_t && (pos < 0 || pos >= fq.max_pos)) { if (threadIdx.x == 0) atomicOr(status, 4); pos = 0; }
+        const float* cs = fq.cos_t ? fq.cos_t + (size_t)pos * (HD / 2) : nullptr;
+        const float* sn = fq.sin_t ? fq.sin_t + (size_t)pos * (HD / 2) : nullptr;
+        const int heads_total = nh + 2 * nkv;
+        pdl_wait(KID_ATT_TMA);
+        const bf16* tok = fq.qkv + (size_t)w.q_token0 * heads_total * HD;
+        for (int row = warp; row < 16; row += TD_CONSUMERS) {
+            uint32_t pk[VPL / 2];
+#pragma unroll
+            for (int k = 0; k < VPL / 2; k++) pk[k] = 0;
+            if (row < n_heads) {
+                float f[VPL];
+                norm_rope_row<HD>(tok + (size_t)(head0 + row) * HD, fq.q_gain, cs, sn, fq.eps, lane, f);
+#pragma unroll
+                for (int k = 0; k < VPL / 2; k++) pk[k] = pack2(f[2 * k], f[2 * k + 1]);
+            }
+            // lane l's values are dims l * VPL ..: chunk (l * VPL) / 8 of the row, (l * VPL) % 8 values in
+            unsigned char* dst = smem + TD_STAGES * STAGE_BYTES + toff<HD>(row, lane * VPL / 8) + (lane * VPL % 8) * 2;
+#pragma unroll
+            for (int k = 0; k < VPL / 2; k++) reinterpret_cast<uint32_t*>(dst)[k] = pk[k];
+        }
+        if (owns_new && warp >= TD_CONSUMERS - 2) {
+            const bool is_k = warp == TD_CONSUMERS - 2;
+            float f[VPL];
+            norm_rope_row<HD>(tok + (size_t)(nh + (is_k ? 0 : nkv) + kh) * HD, is_k ? fq.k_gain : nullptr, is_k ? cs : nullptr,
+                              is_k ? sn : nullptr, fq.eps, lane, f);
+            uint32_t pk[VPL / 2];
+#pragma unroll
+            for (int k = 0; k < VPL / 2; k++) pk[k] = pack2(f[2 * k], f[2 * k + 1]);
+            // into the cache, chunk c at c ^ (offset in page & 7), for the steps to come
+            const int page = block_tables[(size_t)w.seg * table_width + (w.q_pos0 >> page_shift)];
+            const int off = w.q_pos0 & (page_size - 1);
+            if (page >= 0 && page < n_pages) {
+                bf16* row_w = (is_k ? fq.k_pool : fq.v_pool) + (((size_t)page * nkv + kh) * page_size + off) * HD;
+                uint32_t* dst = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(row_w) +
+                                                            (((lane * VPL / 8) ^ (off & 7)) << 4) + (lane * VPL % 8) * 2);
+#pragma unroll
+                for (int k = 0; k < VPL / 2; k++) dst[k] = pk[k];
+            } else if (lane == 0) {
+                atomicOr(status, 2);
+            }
+#pragma unroll
+            for (int k = 0; k < VPL / 2; k++) { if (is_k) new_k[k] = pk[k]; else new_v[k] = pk[k]; }
+        }
+    } else {
+        pdl_wait(KID_ATT_TMA);
+        for (int idx = threadIdx.x; idx < (decode ? 16 : TD_QROWS) * CH; idx += TD_CONSUMERS * 32) {
+            const int row = idx / CH, chunk = idx % CH;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row < rows)
+                v = *reinterpret_cast<const uint4*>(q + ((size_t)(w.q_token0 + row / n_heads) * nh + head0 + row % n_heads) * HD + chunk * 8);
+            *reinterpret_cast<uint4*>(smem + TD_STAGES * STAGE_BYTES + toff<HD>(row, chunk)) = v;
+        }
     }
     asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
 
@@ -257,6 +352,18 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
         if (!mbar_wait(bars + 8 * s, (t / TD_STAGES) & 1, abort_flag)) { alive = false; break; }
         const int kv0 = w.kv_begin + t * TD_BK + key_base;
         const uint32_t k_s = base + s * STAGE_BYTES, v_s = k_s + TILE_BYTES;
+        if (owns_new && t == n_tiles - 1) {
+            // the token's own key and value over what the copy brought for that row (whatever the page held)
+            if (warp >= TD_CONSUMERS - 2) {
+                const int r = w.q_pos0 - (w.kv_begin + t * TD_BK);
+                unsigned char* dst = smem + s * STAGE_BYTES + (warp == TD_CONSUMERS - 2 ? 0 : TILE_BYTES) +
+                                     toff<HD>(r, lane * VPL / 8) + (lane * VPL % 8) * 2;
+#pragma unroll
+                for (int k = 0; k < VPL / 2; k++)
+                    reinterpret_cast<uint32_t*>(dst)[k] = warp == TD_CONSUMERS - 2 ? new_k[k] : new_v[k];
+            }
+            asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
+        }
         if (kv0 < warp_hi) {   // some key of this warp's share is visible to one of its rows
             float s_acc[8][4];
 #pragma unroll
@@ -495,8 +602,8 @@ PLLM_EXPORT int pllm_attention_decode_tma_supports(int dtype, int nh, int nkv, i
 template <int HD>
 static int launch_tma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables, const int* work,
                       const int* n_work_ptr, int max_work, void* out, float* part_o, float* part_ml, int nh, int nkv,
-                      int page_size, int n_pages, int table_width, float scale, int kinds_mask, int* counters, int* status,
-                      cudaStream_t stream) {
+                      int page_size, int n_pages, int table_width, float scale, int kinds_mask, int* counters, FusedQK fq,
+                      int* status, cudaStream_t stream) {
     const int group = nh / nkv;
     const int heads_per_cta = group < 16 ? group : 16;
     const int gparts = (group + heads_per_cta - 1) / heads_per_cta;
@@ -507,8 +614,21 @@ static int launch_tma(const void* q, const void* k_pool, const void* v_pool, con
     launch_chained(attention_decode_tma_kernel<HD>, dim3(nkv * gparts, max_work), dim3((TD_CONSUMERS + 1) * 32), smem, stream,
                    (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
                    n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
-                   scale * 1.4426950408889634f, heads_per_cta, kinds_mask, counters, status);
+                   scale * 1.4426950408889634f, heads_per_cta, kinds_mask, counters, fq, status);
     return launch_status();
+}
+
+static int dispatch_tma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables, const int* work,
+                        const int* n_work_ptr, int max_work, void* out, float* part_o, float* part_ml, int nh, int nkv,
+                        int hd, int page_size, int n_pages, int table_width, float scale, int kinds_mask, int* counters,
+                        FusedQK fq, int* status, cudaStream_t stream) {
+    if (max_work <= 0) return PLLM_OK;
+    if (!pllm_attention_decode_tma_supports(PLLM_BF16, nh, nkv, hd, page_size, 0)) return PLLM_ERR_SIZE;
+    if (hd == 128)
+        return launch_tma<128>(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv,
+                               page_size, n_pages, table_width, scale, kinds_mask, counters, fq, status, stream);
+    return launch_tma<64>(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv,
+                          page_size, n_pages, table_width, scale, kinds_mask, counters, fq, status, stream);
 }
 
 PLLM_EXPORT int pllm_attention_decode_tma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables,
@@ -516,13 +636,24 @@ PLLM_EXPORT int pllm_attention_decode_tma(const void* q, const void* k_pool, con
                                           float* part_o, float* part_ml, int nh, int nkv, int hd, int page_size,
                                           int n_pages, int table_width, float scale, int kinds_mask, int* counters,
                                           int* status, cudaStream_t stream) {
-    if (max_work <= 0) return PLLM_OK;
-    if (!pllm_attention_decode_tma_supports(PLLM_BF16, nh, nkv, hd, page_size, 0)) return PLLM_ERR_SIZE;
-    if (hd == 128)
-        return launch_tma<128>(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv,
-                               page_size, n_pages, table_width, scale, kinds_mask, counters, status, stream);
-    return launch_tma<64>(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv,
-                          page_size, n_pages, table_width, scale, kinds_mask, counters, status, stream);
+    FusedQK none = {};
+    return dispatch_tma(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv, hd,
+                        page_size, n_pages, table_width, scale, kinds_mask, counters, none, status, stream);
+}
+
+// The same for a step of single decoded tokens, straight from the projection's output: the kernel
+// norms and rotates the queries and each token's new key itself and writes key and value to the
+// cache (rotation over the whole head or none; gains and tables may be null).
+PLLM_EXPORT int pllm_attention_decode_tma_fused(const void* qkv, const float* q_gain, const float* k_gain, float eps,
+                                                const float* cos_t, const float* sin_t, int max_pos, void* k_pool,
+                                                void* v_pool, const int* block_tables, const int* work,
+                                                const int* n_work_ptr, int max_work, void* out, float* part_o,
+                                                float* part_ml, int nh, int nkv, int hd, int page_size, int n_pages,
+                                                int table_width, float scale, int* status, cudaStream_t stream) {
+    if (qkv == nullptr || ((uintptr_t)qkv & 15)) return PLLM_ERR_ALIGN;
+    FusedQK fq = {(const bf16*)qkv, q_gain, k_gain, cos_t, sin_t, (bf16*)k_pool, (bf16*)v_pool, eps, max_pos};
+    return dispatch_tma(nullptr, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv, hd,
+                        page_size, n_pages, table_width, scale, 1, nullptr, fq, status, stream);
 }
 
 PLLM_TRACE_EXPORT(attention_decode_tma)

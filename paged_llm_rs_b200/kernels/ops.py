@@ -60,6 +60,7 @@ def lib():
                                           c_float, c_int, P, P, P],
         }
         sig["pllm_set_pdl"] = [c_int]
+        sig["pllm_attention_decode_tma_fused"] = [P, P, P, c_float, P, P, c_int, P, P, P, P, P, c_int, P, P, P] + [c_int] * 6 + [c_float, P, P]
         sig["pllm_attention_prefill_tcgen05_tile_tokens"] = [c_int, c_int]
         sig["pllm_attention_prefill_tcgen05_supports"] = [c_int] * 6
         sig["pllm_attention_prefill_tcgen05"] = [P] * 10 + [c_int] * 7 + [c_float, c_int, P, P]
@@ -351,6 +352,56 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                                         block_tables.shape[-1], int(window), float(scale), _ptr(status), _stream()),
                "paged_attention")
     _check(L.pllm_attention_reduce(_code(q), _ptr(part_o), _ptr(part_ml), _ptr(red), _ptr(n_red), max_red,
+                                   _ptr(out), num_heads, head_dim, _stream()), "attention_reduce")
+    return out
+
+
+# A step of single decoded tokens: the q/k norm, the rotation and the cache write are done by the
+# attention kernel itself (PAGED_LLM_FUSE_QK=0: by their own kernel before it, as for prompt portions).
+FUSE_QK = os.environ.get("PAGED_LLM_FUSE_QK", "1") != "0"
+
+
+def decode_attention_fuses(dtype, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
+                           rotary_dim: int, swizzled: bool) -> bool:
+    """Whether ``decode_attention_fused`` takes a step of single tokens of this shape: the bulk-copy
+    kernel's conditions, and a rotation over the whole head or none."""
+    if not FUSE_QK or not swizzled or not (TMA_KINDS & 1) or rotary_dim not in (0, head_dim):
+        return False
+    if not attention_uses_tensor_cores(dtype, num_heads, num_kv_heads, head_dim):
+        return False
+    return bool(lib().pllm_attention_decode_tma_supports(_BF16, num_heads, num_kv_heads, head_dim, int(page_size),
+                                                         int(window or 0)))
+
+
+def decode_attention_fused(qkv: torch.Tensor, q_gain, k_gain, eps: float, cos, sin, k_pool: torch.Tensor,
+                           v_pool: torch.Tensor, block_tables: torch.Tensor, work: torch.Tensor, n_work: torch.Tensor,
+                           max_work: int, out: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
+                           red: torch.Tensor, n_red: torch.Tensor, max_red: int, num_heads: int, num_kv_heads: int,
+                           head_dim: int, scale: float, status: torch.Tensor) -> torch.Tensor:
+    """Attention of a step of single decoded tokens straight from the projection's output
+    ``qkv`` [tokens, (heads + 2 kv heads) * head_dim]: per-head norm of q and k, rotation at each
+    token's position (the work item's), the token's key and value written to its cache slot
+    (found through the block table), attention over the cache, reduction of split items."""
+    _dev(qkv, k_pool, v_pool, block_tables, work, n_work, out, part_o, part_ml, red, n_red, status, q_gain, k_gain, cos, sin)
+    _f32(q_gain, "q_gain"); _f32(k_gain, "k_gain"); _f32(cos, "cos"); _f32(sin, "sin")
+    _f32(part_o, "part_o"); _f32(part_ml, "part_ml")
+    for t, n in ((block_tables, "block_tables"), (work, "work"), (n_work, "n_work"), (red, "red"), (n_red, "n_red")):
+        _i32(t, n)
+    if qkv.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("decode_attention_fused: bfloat16 only")
+    if qkv.shape[-1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise KernelError("decode_attention_fused: qkv's width is not (heads + 2 kv heads) * head_dim")
+    if (cos is None) != (sin is None) or (cos is not None and cos.shape[-1] * 2 != head_dim):
+        raise KernelError("decode_attention_fused: the rotation must span the whole head (or be absent)")
+    n_pages, page_size = k_pool.shape[0], k_pool.shape[2]
+    L = lib()
+    _check(L.pllm_attention_decode_tma_fused(_ptr(qkv), _ptr(q_gain), _ptr(k_gain), float(eps), _ptr(cos), _ptr(sin),
+                                             cos.shape[0] if cos is not None else 0, _ptr(k_pool), _ptr(v_pool),
+                                             _ptr(block_tables), _ptr(work), _ptr(n_work), max_work, _ptr(out),
+                                             _ptr(part_o), _ptr(part_ml), num_heads, num_kv_heads, head_dim, page_size,
+                                             n_pages, block_tables.shape[-1], float(scale), _ptr(status), _stream()),
+           "decode_attention_fused")
+    _check(L.pllm_attention_reduce(_code(out), _ptr(part_o), _ptr(part_ml), _ptr(red), _ptr(n_red), max_red,
                                    _ptr(out), num_heads, head_dim, _stream()), "attention_reduce")
     return out
 

@@ -311,6 +311,67 @@ def test_prompt_portions_take_the_tcgen05_kernel(nh, nkv, hd, page):
     torch.testing.assert_close(got, want, **tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("nh,nkv,hd,page,norm,rope", [(16, 8, 128, 16, True, True), (8, 1, 64, 8, True, True),
+                                                        (40, 2, 64, 16, False, True), (4, 4, 128, 64, True, False),
+                                                        (6, 3, 64, 32, False, False)])
+def test_decode_attention_does_the_norm_the_rotation_and_the_cache_write_itself(nh, nkv, hd, page, norm, rope):
+    # the same decode step two ways: the q/k kernel then the attention kernels, and the attention
+    # kernel alone from the projection's output.  Outputs and both pools must be equal bit for bit.
+    from paged_llm_rs_b200.parts.base import Runtime
+    from paged_llm_rs_b200.parts.position import RotaryEncoding
+    from paged_llm_rs_b200.parts.spec import PartSpec
+    assert ops.decode_attention_fuses(torch.bfloat16, nh, nkv, hd, page, 0, hd if rope else 0, True)
+    g = torch.Generator(device=DEV).manual_seed(nh + hd)
+    ctxs = [0, 1, 63, 64, 127, 700, 1023, 15, page * 3, 331, 2000]         # tokens in the cache before the step
+    B = len(ctxs)
+    width = max(-(-(c + 1) // page) for c in ctxs)
+    n_pages = sum(-(-(c + 1) // page) for c in ctxs) + 2
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(1)).tolist()
+    tables = torch.full((B, width), -1, dtype=torch.int32)
+    for r, c in enumerate(ctxs):
+        for b in range(-(-(c + 1) // page)):
+            tables[r, b] = perm.pop()
+    tables = tables.to(DEV)
+    kp = torch.randn(n_pages, nkv, page, hd, device=DEV, generator=g).bfloat16()
+    vp = torch.randn(n_pages, nkv, page, hd, device=DEV, generator=g).bfloat16()
+    qkv = torch.randn(B, (nh + 2 * nkv) * hd, device=DEV, generator=g).bfloat16()
+    qg = 1 + 0.1 * torch.randn(hd, device=DEV, generator=g) if norm else None
+    kg = 1 + 0.1 * torch.randn(hd, device=DEV, generator=g) if norm else None
+    cos = sin = None
+    if rope:
+        enc = RotaryEncoding(PartSpec("rope", dict(head_dim=hd, rotary_dim=hd, theta=1e6, max_positions=4096)),
+                             Runtime(torch.device(DEV), torch.bfloat16))
+        cos, sin, _ = enc.rotary()
+    pos = torch.tensor(ctxs, dtype=torch.int32, device=DEV)
+    slots = torch.tensor([int(tables[r, c // page]) * page + c % page for r, c in enumerate(ctxs)], dtype=torch.int32, device=DEV)
+    for target in (1, 10 ** 6):
+        work, red, parts = attention_plan.plan_attention([(r, 1, c) for r, c in enumerate(ctxs)], 1, None, nkv * (-(-(nh // nkv) // 16)),
+                                                         target, min_split_keys=128)
+        workd = torch.from_numpy(np.ascontiguousarray(work)).reshape(-1, 8).to(DEV)
+        redd = torch.from_numpy(np.ascontiguousarray(red)).reshape(-1, 4).to(DEV) if len(red) else torch.zeros(1, 4, dtype=torch.int32, device=DEV)
+        nw = torch.tensor([len(work)], dtype=torch.int32, device=DEV)
+        nr = torch.tensor([len(red)], dtype=torch.int32, device=DEV)
+        part_o = torch.zeros(max(parts, 1), nh, hd, device=DEV)
+        part_ml = torch.zeros(max(parts, 1), nh, 2, device=DEV)
+        st = status()
+        # the two kernels
+        k1, v1 = kp.clone(), vp.clone()
+        q = torch.empty(B, nh * hd, device=DEV, dtype=torch.bfloat16)
+        ops.qk_norm_rope_kv(qkv, q, qg, kg, 1e-6, cos, sin, hd if rope else 0, pos, slots, k1, v1, nh, nkv, hd, st, swizzled=True)
+        o1 = torch.zeros_like(q)
+        ops.paged_attention(q, k1, v1, tables, workd, nw, len(work), o1, part_o, part_ml, redd, nr, len(red), nh, nkv, hd, 0,
+                            hd ** -0.5, st, swizzled=True, kinds=1)
+        # the one
+        k2, v2 = kp.clone(), vp.clone()
+        o2 = torch.zeros_like(q)
+        ops.decode_attention_fused(qkv, qg, kg, 1e-6, cos, sin, k2, v2, tables, workd, nw, len(work), o2, part_o, part_ml,
+                                   redd, nr, len(red), nh, nkv, hd, hd ** -0.5, st)
+        assert st.item() == 0
+        assert torch.equal(k1, k2) and torch.equal(v1, v2)
+        assert not torch.equal(k1, kp)                   # (the step did write)
+        assert torch.equal(o1, o2)
+
+
 def test_swizzled_cache_rows():
     from paged_llm_rs_b200.parts.base import Runtime
     g = torch.Generator(device=DEV).manual_seed(4)
