@@ -85,7 +85,9 @@ class _DecodeGraph:
         collecting = gc.isenabled()
         gc.disable()
         try:
-            with torch.cuda.graph(self.graph), torch.no_grad():
+            # one memory pool for all of this runner's captured steps: they never run at the same time, so
+            # the activations of one may lie where another's did (a 2048-token step holds some 150 MB)
+            with torch.cuda.graph(self.graph, pool=runner.graph_pool), torch.no_grad():
                 self._body()
         finally:
             if collecting:
@@ -166,6 +168,7 @@ class ModelRunner:
         self.use_graphs = use_graphs and all(getattr(b.mixer, "graph_safe", False) for b in self.model.blocks)
         self.max_graph_batch = max_graph_batch
         self._graphs = {}
+        self.graph_pool = torch.cuda.graph_pool_handle()
         # the engine's token budget a step: steps of prompt portions that fill more than half of it are
         # captured once and replayed (None: such steps are launched kernel by kernel)
         self.graph_step_tokens: Optional[int] = None
