@@ -44,7 +44,7 @@ def lib():
             "pllm_attention_generic": [c_int, P, P, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int,
                                        c_int, c_int, c_int, c_float, P, P],
             "pllm_attention_generic_tile_tokens": [c_int, c_int],
-            "pllm_attention_reduce": [c_int, P, P, P, P, c_int, P, c_int, c_int, P],
+            "pllm_attention_reduce": [c_int, P, P, P, P, c_int, P, c_int, c_int, c_int, P],
             "pllm_sample": [P, c_int, c_int, c_ll, P, P, P, P, P],
             "pllm_sample_scratch_floats": [c_int, c_int],
             "pllm_skinny_gemm_supports": [c_int, c_int, c_int],
@@ -270,6 +270,14 @@ def attention_tile_tokens(num_heads: int, num_kv_heads: int, dtype: torch.dtype 
     return lib().pllm_attention_generic_tile_tokens(num_heads, num_kv_heads)
 
 
+def _many_splits(tokens: int, num_heads: int, num_kv_heads: int) -> int:
+    """Whether a step of this many tokens is cut into eight splits or more a tile (the planner's
+    arithmetic for single tokens: target CTAs over tiles x CTAs an item)."""
+    group = num_heads // num_kv_heads
+    ctas_per_item = num_kv_heads * -(-group // min(group, 16))
+    return 1 if 2 * 148 // max(1, tokens * ctas_per_item) >= 8 else 0
+
+
 def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
                     work: torch.Tensor, n_work: torch.Tensor, max_work: int, out: torch.Tensor,
                     part_o: torch.Tensor, part_ml: torch.Tensor, red: torch.Tensor, n_red: torch.Tensor,
@@ -352,7 +360,8 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                                         block_tables.shape[-1], int(window), float(scale), _ptr(status), _stream()),
                "paged_attention")
     _check(L.pllm_attention_reduce(_code(q), _ptr(part_o), _ptr(part_ml), _ptr(red), _ptr(n_red), max_red,
-                                   _ptr(out), num_heads, head_dim, _stream()), "attention_reduce")
+                                   _ptr(out), num_heads, head_dim, _many_splits(q.shape[0], num_heads, num_kv_heads),
+                                   _stream()), "attention_reduce")
     return out
 
 
@@ -402,7 +411,8 @@ def decode_attention_fused(qkv: torch.Tensor, q_gain, k_gain, eps: float, cos, s
                                              n_pages, block_tables.shape[-1], float(scale), _ptr(status), _stream()),
            "decode_attention_fused")
     _check(L.pllm_attention_reduce(_code(out), _ptr(part_o), _ptr(part_ml), _ptr(red), _ptr(n_red), max_red,
-                                   _ptr(out), num_heads, head_dim, _stream()), "attention_reduce")
+                                   _ptr(out), num_heads, head_dim, _many_splits(qkv.shape[0], num_heads, num_kv_heads),
+                                   _stream()), "attention_reduce")
     return out
 
 

@@ -258,8 +258,8 @@ def test_decode_only_steps_take_the_bulk_copy_kernel(nh, nkv, hd, page):
 
 @pytest.mark.parametrize("nh,nkv,hd,page", [(16, 8, 128, 16), (8, 1, 64, 8), (40, 2, 64, 16), (6, 3, 64, 32)])
 def test_bulk_copy_kernel_combines_its_splits_itself(nh, nkv, hd, page):
-    # the same steps with the reduction kernel and with the last CTA of each tile combining: equal
-    # bit for bit (same arithmetic, same order), twice in a row (the counters are left at zero)
+    # the same steps with the reduction kernel and with the last CTA of each tile combining: equal to
+    # rounding, twice in a row (the counters are left at zero)
     decode = [(63, 1), (700, 1), (1023, 1), (15, 1), (331, 1), (2000, 1)]
     mixed = [(100, 1), (400, 9), (513, 1), (0, 70), (900, 33)]
     counters = torch.zeros(1 << 16, dtype=torch.int32, device=DEV)
@@ -281,7 +281,8 @@ def _check_fused_combine(cases, bases, counters, nh, nkv, hd, page):
         for _ in range(2):
             got, _ = run_attention(torch.bfloat16, reqs, nh, nkv, hd, page, None, 10 ** 6, kinds=kinds, counters=counters,
                                    raw=True)
-            assert torch.equal(got, base)
+            # (the same partial results, summed in another order: a last place of bfloat16 at most)
+            torch.testing.assert_close(got.float(), base.float(), atol=2e-3, rtol=8e-3)
             assert int(counters.abs().sum()) == 0
         assert ops.LAUNCHES - launches == 2          # one kernel a step: no reduction kernel
 
