@@ -87,6 +87,12 @@ __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint3
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// An 8x8 block of 16-bit values held one row in four lanes, transposed across the warp.
+__device__ __forceinline__ uint32_t movmatrix_t(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
@@ -138,7 +144,7 @@ __device__ __forceinline__ void norm_rope_row(const bf16* src, const float* gain
     }
 }
 
-template <int HD>
+template <int HD, bool KEYS_AS_ROWS>
 __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_tma_kernel(
     const bf16* q, const bf16* k_pool, const bf16* v_pool,   // written by the kernels before this one: no __restrict__
     const int* __restrict__ block_tables, const AttnWork* __restrict__ work, const int* __restrict__ n_work_ptr,
@@ -153,6 +159,7 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
     if ((int)blockIdx.y >= *n_work_ptr) return;
     const AttnWork w = work[blockIdx.y];
     if (!(kinds_mask & (w.q_count == 1 ? 1 : 2))) return;   // another kernel's item
+    if (KEYS_AS_ROWS && w.q_count != 1) return;             // (this variant is for single tokens only)
     if (w.kv_begin & (TD_BK - 1)) {  // slabs and the swizzle need the range to start on a tile boundary
         if (threadIdx.x == 0) atomicOr(status, 32);
         return;
@@ -316,6 +323,133 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
     }
     asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
 
+    float* o_s = reinterpret_cast<float*>(smem);          // [4][16][HD], once the ring is no longer read
+    float* ml_s = o_s + TD_CONSUMERS * 16 * HD;           // [4][16][2]
+    if constexpr (KEYS_AS_ROWS) {
+    // ---- consumers, one query token of at most 8 heads: the KEYS are the 16 rows of the score block --------
+    // and the heads its 8 columns, S^T = K q^T and O^T = V^T P^T.  A block of 16 keys costs 8 + HD / 16
+    // mma instead of twice that with the (two, four, eight) heads padded to 16 rows, the output is
+    // HD / 16 x 4 registers instead of HD / 8 x 4, and the queries are 2 registers a k-step instead of 4.
+    uint32_t qb[KSTEPS][2];
+    {
+#pragma unroll
+        for (int kp = 0; kp < KSTEPS / 2; kp++) {
+            uint32_t r[4];
+            ldsm4(r, q_s + toff<HD>(lane & 7, kp * 4 + (lane >> 3)));
+            qb[2 * kp][0] = r[0]; qb[2 * kp][1] = r[1]; qb[2 * kp + 1][0] = r[2]; qb[2 * kp + 1][1] = r[3];
+        }
+    }
+    const int hi0 = min(w.kv_end, w.q_pos0 + 1);     // keys the token may see, the same for all its heads
+    // this thread: keys lane / 4 and + 8 of the warp's 16, heads 2 * (lane % 4) and + 1
+    float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_run[2] = {0.f, 0.f};
+    constexpr int MT = HD / 16;
+    float o_acc[MT][4];
+#pragma unroll
+    for (int d = 0; d < MT; d++) { o_acc[d][0] = o_acc[d][1] = o_acc[d][2] = o_acc[d][3] = 0.f; }
+    const int key_base = warp * 16;
+    const int mat = lane >> 3;
+    for (int t = 0; t < n_tiles; t++) {
+        const int s = t % TD_STAGES;
+        if (!mbar_wait(bars + 8 * s, (t / TD_STAGES) & 1, abort_flag)) break;
+        const int kv0 = w.kv_begin + t * TD_BK + key_base;
+        const uint32_t k_s = base + s * STAGE_BYTES, v_s = k_s + TILE_BYTES;
+        if (owns_new && t == n_tiles - 1) {
+            // the token's own key and value over what the copy brought for that row (whatever the page held)
+            if (warp >= TD_CONSUMERS - 2) {
+                const int r = w.q_pos0 - (w.kv_begin + t * TD_BK);
+                unsigned char* dst = smem + s * STAGE_BYTES + (warp == TD_CONSUMERS - 2 ? 0 : TILE_BYTES) +
+                                     toff<HD>(r, lane * VPL / 8) + (lane * VPL % 8) * 2;
+#pragma unroll
+                for (int k = 0; k < VPL / 2; k++)
+                    reinterpret_cast<uint32_t*>(dst)[k] = warp == TD_CONSUMERS - 2 ? new_k[k] : new_v[k];
+            }
+            asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
+        }
+        if (kv0 < hi0) {
+            // two chains of mma over the k-steps, added at the end
+            float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+            const int krow = key_base + (lane & 7) + (mat & 1) * 8;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ks += 2) {
+                uint32_t ka[4], kb[4];
+                ldsm4(ka, k_s + toff<HD>(krow, ks * 2 + (mat >> 1)));
+                ldsm4(kb, k_s + toff<HD>(krow, ks * 2 + 2 + (mat >> 1)));
+                mma(sa, ka, qb[ks][0], qb[ks][1]);
+                mma(sb, kb, qb[ks + 1][0], qb[ks + 1][1]);
+            }
+            const int j0 = kv0 + (lane >> 2);
+            const bool see0 = j0 < hi0, see1 = j0 + 8 < hi0;
+            float sc[4];
+            sc[0] = see0 ? (sa[0] + sb[0]) * scale_log2 : -CUDART_INF_F;
+            sc[1] = see0 ? (sa[1] + sb[1]) * scale_log2 : -CUDART_INF_F;
+            sc[2] = see1 ? (sa[2] + sb[2]) * scale_log2 : -CUDART_INF_F;
+            sc[3] = see1 ? (sa[3] + sb[3]) * scale_log2 : -CUDART_INF_F;
+            float mx[2] = {fmaxf(sc[0], sc[2]), fmaxf(sc[1], sc[3])};
+            float corr[2], m_use[2];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 4));
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 8));
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 16));
+                const float m_new = fmaxf(m_run[i], mx[i]);
+                m_use[i] = m_new == -CUDART_INF_F ? 0.f : m_new;
+                corr[i] = exp2f(m_run[i] - m_use[i]);
+                m_run[i] = m_new;
+                l_run[i] *= corr[i];
+            }
+            const float p0 = exp2f(sc[0] - m_use[0]), p1 = exp2f(sc[1] - m_use[1]);
+            const float p2 = exp2f(sc[2] - m_use[0]), p3 = exp2f(sc[3] - m_use[1]);
+            l_run[0] += p0 + p2;
+            l_run[1] += p1 + p3;
+            // P^T as the second operand: (key, head pair) in this thread becomes (head, key pair)
+            const uint32_t pb0 = movmatrix_t(pack2(p0, p1)), pb1 = movmatrix_t(pack2(p2, p3));
+            if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
+#pragma unroll
+                for (int d = 0; d < MT; d++) {
+                    o_acc[d][0] *= corr[0]; o_acc[d][1] *= corr[1];
+                    o_acc[d][2] *= corr[0]; o_acc[d][3] *= corr[1];
+                }
+            }
+            const int vkey = key_base + (lane & 7) + (mat >> 1) * 8;
+#pragma unroll
+            for (int d4 = 0; d4 < MT; d4 += 4) {
+                uint32_t vf[4][4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) ldsm4_t(vf[i], v_s + toff<HD>(vkey, (d4 + i) * 2 + (mat & 1)));
+#pragma unroll
+                for (int i = 0; i < 4; i++) mma(o_acc[d4 + i], vf[i], pb0, pb1);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + 8 * (TD_STAGES + s));   // this warp is done with the stage
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 4);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 8);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 16);
+    }
+    pdl_launch_dependents();   // the key tiles are done: the next kernel's CTAs may take their places
+    asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicOr(status, 16);
+        return;
+    }
+    // the four warps' results meet, head by head
+    {
+        const int qh = (lane & 3) * 2;
+#pragma unroll
+        for (int d = 0; d < MT; d++) {
+            float* a = o_s + ((size_t)(warp * 16 + qh) * HD + d * 16 + (lane >> 2));
+            a[0] = o_acc[d][0]; a[HD] = o_acc[d][1];
+            a[8] = o_acc[d][2]; a[HD + 8] = o_acc[d][3];
+        }
+        if (lane < 4) {
+            ml_s[(warp * 16 + qh) * 2] = m_run[0]; ml_s[(warp * 16 + qh) * 2 + 1] = l_run[0];
+            ml_s[(warp * 16 + qh + 1) * 2] = m_run[1]; ml_s[(warp * 16 + qh + 1) * 2 + 1] = l_run[1];
+        }
+    }
+    } else {
     // ---- consumers ------------------------------------------------------------------------------
     // One query token: the group's heads are ONE 16-row block and the warps share each tile's
     // keys (16 each).  Several query tokens: the rows (token, head) are spread over the warps,
@@ -488,8 +622,6 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
         }
     } else {
     // ---- one query token: the four warps' results meet ---------------------------------------
-    float* o_s = reinterpret_cast<float*>(smem);          // [4][16][HD]; the ring is no longer read
-    float* ml_s = o_s + TD_CONSUMERS * 16 * HD;           // [4][16][2]
 #pragma unroll
     for (int d = 0; d < DTILES; d++) {
         const int c = d * 8 + (lane & 3) * 2;
@@ -501,6 +633,9 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
         ml_s[(warp * 16 + (lane >> 2)) * 2] = m_run[0]; ml_s[(warp * 16 + (lane >> 2)) * 2 + 1] = l_run[0];
         ml_s[(warp * 16 + (lane >> 2) + 8) * 2] = m_run[1]; ml_s[(warp * 16 + (lane >> 2) + 8) * 2 + 1] = l_run[1];
     }
+    }
+    }
+    if (decode) {
     asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
     for (int idx = threadIdx.x; idx < rows * HD; idx += TD_CONSUMERS * 32) {
         const int r = idx / HD, c = idx % HD;
@@ -610,11 +745,25 @@ static int launch_tma(const void* q, const void* k_pool, const void* v_pool, con
     int page_shift = 0;
     while ((1 << page_shift) < page_size) page_shift++;
     const size_t smem = (size_t)TD_STAGES * 2 * TD_BK * HD * 2 + TD_QROWS * HD * 2 + 16 * TD_STAGES + 16;
-    cudaFuncSetAttribute(attention_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_chained(attention_decode_tma_kernel<HD>, dim3(nkv * gparts, max_work), dim3((TD_CONSUMERS + 1) * 32), smem, stream,
-                   (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
-                   n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
-                   scale * 1.4426950408889634f, heads_per_cta, kinds_mask, counters, fq, status);
+    const float scale_log2 = scale * 1.4426950408889634f;
+    // single tokens of groups of at most 8 heads go to the variant with the keys as rows; what else the
+    // caller asked for (several query tokens) to the other, as a launch of its own
+    int rest = kinds_mask;
+    if (group <= 8 && (kinds_mask & 1)) {
+        cudaFuncSetAttribute(attention_decode_tma_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_chained(attention_decode_tma_kernel<HD, true>, dim3(nkv * gparts, max_work), dim3((TD_CONSUMERS + 1) * 32), smem,
+                       stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
+                       n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
+                       scale_log2, heads_per_cta, 1, counters, fq, status);
+        rest &= ~1;
+    }
+    if (rest) {
+        cudaFuncSetAttribute(attention_decode_tma_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_chained(attention_decode_tma_kernel<HD, false>, dim3(nkv * gparts, max_work), dim3((TD_CONSUMERS + 1) * 32), smem,
+                       stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
+                       n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
+                       scale_log2, heads_per_cta, rest, counters, fq, status);
+    }
     return launch_status();
 }
 
