@@ -177,6 +177,28 @@ static inline void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
     cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// The same with the CTAs of `cluster_y` consecutive blockIdx.y in one thread-block cluster (they
+// run at the same time on neighbouring SMs and may read one another's shared memory).
+template <typename... KArgs, typename... Args>
+static inline void launch_chained_cluster_y(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                            int cluster_y, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = (unsigned)cluster_y;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pllm_pdl_enabled ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 #define PLLM_DISPATCH_DTYPE(dtype, ...)                         \
     do {                                                        \
         if ((dtype) == PLLM_F32) { typedef float T; __VA_ARGS__; } \

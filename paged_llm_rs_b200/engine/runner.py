@@ -157,7 +157,9 @@ class ModelRunner:
             nh = nkv * g.max_group_size
             tile = ops.attention_tile_tokens(nh, nkv, self.dtype, g.need.head_dim, page_size, g.window or 0)
             gparts = -(-g.max_group_size // 16)
-            plans.append(GroupPlanConfig(tile, nkv * gparts, g.window))
+            limit = min((self.model.blocks[self.model.schedule[i].layer].mixer.cluster_limit(page_size) for i in g.entries),
+                        default=0)
+            plans.append(GroupPlanConfig(tile, nkv * gparts, g.window, limit))
             nh_max = max(getattr(self.model.blocks[self.model.schedule[i].layer].mixer, "nh", nh) for i in g.entries)
             self._heads.append((nh_max, g.need.head_dim))
         self.packer = StepPacker(self.cache, plans, SM_COUNT_TARGET, self.spec.vocab_size, self.spec.max_positions,

@@ -41,6 +41,7 @@ class GroupPlanConfig:
     tile_tokens: int      # query tokens per attention work item
     ctas_per_item: int    # CTAs the kernel launches per item (kv heads x group parts)
     window: Optional[int]
+    max_cluster: int = 0  # items of one single token the kernel can combine in a thread-block cluster (0: none)
 
 
 @dataclass
@@ -53,6 +54,8 @@ class StepCaps:
     segments: int
     table_width: int
     kinds: int = 1        # what the captured step's attention items may be (1: single tokens only, 3: anything)
+    # (a captured step of single tokens cuts its attention for ``tokens`` requests however many it holds: the
+    # cluster size is part of the launch)
 
 
 class StepPacker:
@@ -75,6 +78,12 @@ class StepPacker:
                    torch.empty((rows, nh, 2), dtype=torch.float32, device=self.device))
             self._scratch[gi] = cur
         return cur
+
+    def cluster_for(self, gi: int, n_tokens: int) -> int:
+        """Items every token of a step of ``n_tokens`` single tokens gets in group gi, when the
+        group's kernel combines them in a cluster (0: the step is planned for the reduction kernel)."""
+        plan = self.plans[gi]
+        return attention_plan.decode_cluster(n_tokens, plan.ctas_per_item, self.target_ctas, plan.max_cluster)
 
     def counters(self, gi: int, max_work: int) -> torch.Tensor:
         """Zeros for the kernel that combines split items itself (one per work item and CTA of
@@ -160,17 +169,24 @@ class StepPacker:
                         raise CacheError(f"request {rc.request_id!r} writes into a page it gave back")
                     slots[t0:t0 + n] = page * ps + pp % ps
             plan = self.plans[gi]
+            # a step of single tokens whose splits the kernel combines in clusters: of the captured step's
+            # size when it is one (the cluster is part of its launches), else of this step's
+            cluster = 0
+            if caps is not None and caps.kinds == 1:
+                cluster = self.cluster_for(gi, caps.tokens)
+            elif caps is None and segs and all(n == 1 for (_, n, _, _) in segs):
+                cluster = self.cluster_for(gi, n_seg)
             # groups that cut their work alike (same tile, window, CTAs an item) share one plan
-            key = (plan.tile_tokens, plan.window, plan.ctas_per_item)
+            key = (plan.tile_tokens, plan.window, plan.ctas_per_item, cluster)
             if key not in planned:
                 planned[key] = attention_plan.plan_attention(
                     [(t0, n, p0) for (t0, n, p0, _) in segs], plan.tile_tokens, plan.window, plan.ctas_per_item,
-                    self.target_ctas)
+                    self.target_ctas, cluster=cluster if segs else 0)
             work, red, parts = planned[key]
             mw, mr, mp = (work_caps[gi] if work_caps else (len(work), len(red), parts))
             if len(work) > mw or len(red) > mr or parts > mp:
                 raise ConfigError("the step's attention work does not fit the capacities it was given")
-            group_parts.append((slots, tables, work, red, mp, mw, mr, W))
+            group_parts.append((slots, tables, work, red, mp, mw, mr, W, cluster))
 
         # layout: offsets in int32 units
         off = 0
@@ -183,7 +199,7 @@ class StepPacker:
 
         take("tokens", Tc); take("positions", Tc); take("logit_rows", max(nc, 1)); take("segments", max(sc, 1) * 4)
         take("temperature", max(nc, 1)); take("uniform", max(nc, 1))
-        for gi, (slots, tables, work, red, parts, mw, mr, W) in enumerate(group_parts):
+        for gi, (slots, tables, work, red, parts, mw, mr, W, _) in enumerate(group_parts):
             take(f"g{gi}.slots", Tc); take(f"g{gi}.tables", sc * W)
             take(f"g{gi}.n_work", 1); take(f"g{gi}.n_red", 1)
             take(f"g{gi}.work", max(mw, 1) * 8); take(f"g{gi}.red", max(mr, 1) * 4)
@@ -199,7 +215,7 @@ class StepPacker:
             put("temperature", np.asarray(temperature, dtype=np.float32).view(np.int32))
             put("uniform", np.asarray(uniform, dtype=np.float32).view(np.int32))
         put("segments", np.asarray(segs, dtype=np.int32).reshape(-1) if segs else [])
-        for gi, (slots, tables, work, red, parts, mw, mr, W) in enumerate(group_parts):
+        for gi, (slots, tables, work, red, parts, mw, mr, W, _) in enumerate(group_parts):
             put(f"g{gi}.slots", slots); put(f"g{gi}.tables", tables)
             put(f"g{gi}.n_work", [len(work)]); put(f"g{gi}.n_red", [len(red)])
             put(f"g{gi}.work", work); put(f"g{gi}.red", red)
@@ -213,7 +229,7 @@ class StepPacker:
         if caps is not None:
             kinds = caps.kinds      # a captured step launches the same kernels whatever it holds
         sizes = dict(tokens=T, wanted=n_want, segments=n_seg, tokens_cap=Tc, wanted_cap=nc, segments_cap=sc, kinds=kinds,
-                     groups=[dict(parts=p[4], max_work=p[5], max_red=p[6], table_width=p[7]) for p in group_parts],
+                     groups=[dict(parts=p[4], max_work=p[5], max_red=p[6], table_width=p[7], cluster=p[8]) for p in group_parts],
                      host_segments=segs)
         return host, layout, sizes
 
@@ -236,7 +252,8 @@ class StepPacker:
                 slots=view(f"g{gi}.slots", T),
                 work=view(f"g{gi}.work").view(-1, 8), n_work=view(f"g{gi}.n_work"), max_work=gs["max_work"],
                 red=view(f"g{gi}.red").view(-1, 4), n_red=view(f"g{gi}.n_red"), max_red=gs["max_red"],
-                part_o=part_o, part_ml=part_ml, kinds=sizes["kinds"], counters=self.counters(gi, gs["max_work"])))
+                part_o=part_o, part_ml=part_ml, kinds=sizes["kinds"], counters=self.counters(gi, gs["max_work"]),
+                cluster=gs.get("cluster", 0)))
         state = StepState(n_tokens=T, tokens=view("tokens", T), positions=view("positions", T), groups=groups,
                           logit_rows=view("logit_rows", nw), n_wanted=nw,
                           segments=view("segments").view(-1, 4), host_segments=list(sizes["host_segments"]))
@@ -250,6 +267,7 @@ class _GroupPack(ctypes.Structure):
     _fields_ = [("tables", ctypes.POINTER(ctypes.c_void_p)), ("table_len", ctypes.POINTER(ctypes.c_int)),
                 ("window", ctypes.c_int), ("ctas_per_item", ctypes.c_int),
                 ("max_work", ctypes.c_int), ("max_red", ctypes.c_int), ("max_parts", ctypes.c_int),
+                ("cluster", ctypes.c_int),
                 ("off_slots", ctypes.c_int), ("off_tables", ctypes.c_int), ("off_n_work", ctypes.c_int),
                 ("off_n_red", ctypes.c_int), ("off_work", ctypes.c_int), ("off_red", ctypes.c_int)]
 
@@ -292,6 +310,7 @@ class NativeDecodePacker:
             g.table_len = ctypes.cast(lens, ctypes.POINTER(ctypes.c_int))
             g.window, g.ctas_per_item = int(plan.window or 0), plan.ctas_per_item
             g.max_work, g.max_red, g.max_parts = work_caps[gi]
+            g.cluster = packer.cluster_for(gi, caps.tokens)
             for name in ("slots", "tables", "n_work", "n_red", "work", "red"):
                 setattr(g, f"off_{name}", layout[f"g{gi}.{name}"][0])
         self.n_groups = n_groups

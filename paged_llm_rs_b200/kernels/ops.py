@@ -57,10 +57,11 @@ def lib():
                                    c_int, c_float, c_int, c_int, P, P],
             "pllm_attention_decode_tma_supports": [c_int, c_int, c_int, c_int, c_int, c_int],
             "pllm_attention_decode_tma": [P, P, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
-                                          c_float, c_int, P, P, P],
+                                          c_float, c_int, P, c_int, P, P],
+            "pllm_attention_decode_tma_max_cluster": [c_int, c_int, c_int, c_int, c_int, c_int],
         }
         sig["pllm_set_pdl"] = [c_int]
-        sig["pllm_attention_decode_tma_fused"] = [P, P, P, c_float, P, P, c_int, P, P, P, P, P, c_int, P, P, P] + [c_int] * 6 + [c_float, P, P]
+        sig["pllm_attention_decode_tma_fused"] = [P, P, P, c_float, P, P, c_int, P, P, P, P, P, c_int, P, P, P] + [c_int] * 6 + [c_float, c_int, P, P]
         sig["pllm_attention_prefill_tcgen05_tile_tokens"] = [c_int, c_int]
         sig["pllm_attention_prefill_tcgen05_supports"] = [c_int] * 6
         sig["pllm_attention_prefill_tcgen05"] = [P] * 10 + [c_int] * 7 + [c_float, c_int, P, P]
@@ -283,7 +284,7 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     part_o: torch.Tensor, part_ml: torch.Tensor, red: torch.Tensor, n_red: torch.Tensor,
                     max_red: int, num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
                     status: torch.Tensor, swizzled: bool = False, kinds: int = 3,
-                    counters: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    counters: Optional[torch.Tensor] = None, cluster: int = 0) -> torch.Tensor:
     """Attention of the step's tokens over the paged cache, then the reduction of
     split items.  ``work`` is int32 [>=max_work, 8], ``red`` int32 [>=max_red, 4];
     n_work / n_red are int32 scalars on the device saying how many are live.
@@ -292,7 +293,9 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     several tokens only, 3 both, so that only the kernels with work are launched.
     ``counters`` (int32 zeros, max_work x CTAs an item, left zero): with them the
     bulk-copy kernel, where it takes all the work, combines the splits itself and
-    the reduction kernel is not launched."""
+    the reduction kernel is not launched.  ``cluster`` > 1: the list was planned with
+    that many items for every (single) token, which the bulk-copy kernel combines
+    inside a thread-block cluster; nothing else takes such a list."""
     _dev(q, k_pool, v_pool, block_tables, work, n_work, out, part_o, part_ml, red, n_red, status)
     for t, n in ((block_tables, "block_tables"), (work, "work"), (n_work, "n_work"), (red, "red"), (n_red, "n_red")):
         _i32(t, n)
@@ -329,6 +332,17 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
             kinds = 0 if kinds == 3 else kinds & ~2
         take = (kinds & TMA_KINDS) if tma_ok else 0
         rest = kinds & ~take
+        if cluster > 1:
+            if take != 1 or rest or multi_tc or cluster > attention_max_cluster(q.dtype, num_heads, num_kv_heads, head_dim,
+                                                                                page_size, int(window), swizzled):
+                raise KernelError("paged_attention: a list planned for clusters, and no kernel here that combines in clusters")
+            _check(L.pllm_attention_decode_tma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
+                                               _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml),
+                                               num_heads, num_kv_heads, head_dim, page_size, n_pages,
+                                               block_tables.shape[-1], float(scale), 1, None, int(cluster),
+                                               _ptr(status), _stream()),
+                   "paged_attention (bulk copy, clusters)")
+            return out
         group = num_heads // num_kv_heads
         ctas_per_item = num_kv_heads * -(-group // min(group, 16))
         fused = bool(FUSE_REDUCE and take and not rest and not multi_tc and counters is not None
@@ -341,7 +355,7 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                                                _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml),
                                                num_heads, num_kv_heads, head_dim, page_size, n_pages,
                                                block_tables.shape[-1], float(scale), take,
-                                               _ptr(counters) if fused else None, _ptr(status), _stream()),
+                                               _ptr(counters) if fused else None, 0, _ptr(status), _stream()),
                    "paged_attention (bulk copy)")
         if rest:
             _check(L.pllm_attention_mma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
@@ -352,6 +366,8 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         if fused:
             return out
     else:
+        if cluster > 1:
+            raise KernelError("paged_attention: a list planned for clusters, and no kernel here that combines in clusters")
         if swizzled:
             raise KernelError("paged_attention: the generic kernel reads plain pools, not swizzled ones")
         _check(L.pllm_attention_generic(_code(q), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables),
@@ -363,6 +379,28 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                                    _ptr(out), num_heads, head_dim, _many_splits(q.shape[0], num_heads, num_kv_heads),
                                    _stream()), "attention_reduce")
     return out
+
+
+# PAGED_LLM_CLUSTER=1: steps of single tokens whose splits fit a thread-block cluster are combined inside the
+# attention kernel, through the cluster's shared memory, instead of through global memory and the reduction
+# kernel.  Off by default: it measured no faster (0.6B shape, context 4096, a captured step: batch 8 1.386 ms
+# against 1.390, batch 16 2.041 against 2.037, batch 4 with clusters of 8 1.29 against 1.07).  The reduction
+# kernel's 3.7 us a layer go, but a cluster starts only when all its CTAs find room in one GPC at once, so the
+# attention's CTAs no longer trickle in behind the product before them, and the two cluster barriers and the
+# remote reads add 2 us to the attention itself.
+CLUSTER_COMBINE = os.environ.get("PAGED_LLM_CLUSTER", "0") == "1"
+
+
+def attention_max_cluster(dtype, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
+                          swizzled: bool = True) -> int:
+    """The most items of one single token that ``paged_attention`` / ``decode_attention_fused`` can combine
+    inside a cluster for this shape (0: none; the planner then cuts as for the reduction kernel)."""
+    if not CLUSTER_COMBINE or not swizzled or not (TMA_KINDS & 1) or dtype != torch.bfloat16:
+        return 0
+    if not attention_uses_tensor_cores(dtype, num_heads, num_kv_heads, head_dim):
+        return 0
+    return int(lib().pllm_attention_decode_tma_max_cluster(_BF16, num_heads, num_kv_heads, head_dim, int(page_size),
+                                                           int(window or 0)))
 
 
 # A step of single decoded tokens: the q/k norm, the rotation and the cache write are done by the
@@ -386,11 +424,12 @@ def decode_attention_fused(qkv: torch.Tensor, q_gain, k_gain, eps: float, cos, s
                            v_pool: torch.Tensor, block_tables: torch.Tensor, work: torch.Tensor, n_work: torch.Tensor,
                            max_work: int, out: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
                            red: torch.Tensor, n_red: torch.Tensor, max_red: int, num_heads: int, num_kv_heads: int,
-                           head_dim: int, scale: float, status: torch.Tensor) -> torch.Tensor:
+                           head_dim: int, scale: float, status: torch.Tensor, cluster: int = 0) -> torch.Tensor:
     """Attention of a step of single decoded tokens straight from the projection's output
     ``qkv`` [tokens, (heads + 2 kv heads) * head_dim]: per-head norm of q and k, rotation at each
     token's position (the work item's), the token's key and value written to its cache slot
-    (found through the block table), attention over the cache, reduction of split items."""
+    (found through the block table), attention over the cache, reduction of split items
+    (``cluster`` > 1: the list holds that many items a token, combined inside the kernel)."""
     _dev(qkv, k_pool, v_pool, block_tables, work, n_work, out, part_o, part_ml, red, n_red, status, q_gain, k_gain, cos, sin)
     _f32(q_gain, "q_gain"); _f32(k_gain, "k_gain"); _f32(cos, "cos"); _f32(sin, "sin")
     _f32(part_o, "part_o"); _f32(part_ml, "part_ml")
@@ -408,8 +447,11 @@ def decode_attention_fused(qkv: torch.Tensor, q_gain, k_gain, eps: float, cos, s
                                              cos.shape[0] if cos is not None else 0, _ptr(k_pool), _ptr(v_pool),
                                              _ptr(block_tables), _ptr(work), _ptr(n_work), max_work, _ptr(out),
                                              _ptr(part_o), _ptr(part_ml), num_heads, num_kv_heads, head_dim, page_size,
-                                             n_pages, block_tables.shape[-1], float(scale), _ptr(status), _stream()),
+                                             n_pages, block_tables.shape[-1], float(scale), int(cluster), _ptr(status),
+                                             _stream()),
            "decode_attention_fused")
+    if cluster > 1:
+        return out
     _check(L.pllm_attention_reduce(_code(out), _ptr(part_o), _ptr(part_ml), _ptr(red), _ptr(n_red), max_red,
                                    _ptr(out), num_heads, head_dim, _many_splits(qkv.shape[0], num_heads, num_kv_heads),
                                    _stream()), "attention_reduce")

@@ -61,6 +61,12 @@ class GQAttention(Mixer):
 
     takes_normed_input = True
 
+    def cluster_limit(self, page_size: int) -> int:
+        if self.rt.device.type != "cuda":
+            return 0
+        return ops.attention_max_cluster(self.rt.dtype, self.nh, self.nkv, self.hd, page_size, self.window or 0,
+                                         self.cache_need().swizzled)
+
     def forward(self, x, step, cache, writes_cache=True):
         k_pool, v_pool, gi = cache
         g = step.groups[gi]
@@ -76,7 +82,8 @@ class GQAttention(Mixer):
             o = torch.empty((T, self.nh * self.hd), dtype=x.dtype, device=x.device)
             ops.decode_attention_fused(qkv, self.q_gain, self.k_gain, self.qk_norm_eps or 0.0, cos, sin, k_pool, v_pool,
                                        g.block_tables, g.work, g.n_work, g.max_work, o, g.part_o, g.part_ml, g.red,
-                                       g.n_red, g.max_red, self.nh, self.nkv, self.hd, self.scale, self.rt.status)
+                                       g.n_red, g.max_red, self.nh, self.nkv, self.hd, self.scale, self.rt.status,
+                                       cluster=g.cluster)
             return ops.linear(o, self.w_o, status=self.rt.status)
         q = torch.empty((T, self.nh * self.hd), dtype=x.dtype, device=x.device)
         ops.qk_norm_rope_kv(qkv, q, self.q_gain, self.k_gain, self.qk_norm_eps or 0.0, cos, sin, rdim,
@@ -86,7 +93,7 @@ class GQAttention(Mixer):
         o = torch.empty_like(q)
         ops.paged_attention(q, k_pool, v_pool, g.block_tables, g.work, g.n_work, g.max_work, o, g.part_o, g.part_ml,
                             g.red, g.n_red, g.max_red, self.nh, self.nkv, self.hd, self.window or 0, self.scale,
-                            self.rt.status, swizzled=swizzled, kinds=g.kinds, counters=g.counters)
+                            self.rt.status, swizzled=swizzled, kinds=g.kinds, counters=g.counters, cluster=g.cluster)
         return ops.linear(o, self.w_o, status=self.rt.status)
 
 

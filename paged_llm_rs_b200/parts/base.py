@@ -87,6 +87,8 @@ class GroupStep:
     kinds: int = 3              # what the work items are: 1 single tokens only, 2 portions only, 3 both
     counters: Optional[torch.Tensor] = None   # int32 zeros [max_work * CTAs an item]: a kernel that combines
                                               # the splits itself counts them off here and leaves zeros
+    cluster: int = 0            # > 1: the list holds that many items for every (single) token, which the
+                                # attention kernel combines inside a thread-block cluster; red is empty
 
 
 @dataclass
@@ -171,6 +173,12 @@ class Mixer(Part):
     def cache_need(self):
         """KVNeed, StateNeed or None."""
         return None
+
+    def cluster_limit(self, page_size: int) -> int:
+        """For a mixer that reads its group's attention work items: the most items of one single
+        token it can take as a cluster (GroupStep.cluster), 0 when it wants split items with
+        partial rows and reductions.  The packer plans a group for the least of its mixers."""
+        return 0
 
     def forward(self, x: torch.Tensor, step: StepState, cache, writes_cache: bool = True) -> torch.Tensor:
         """x [tokens, hidden] -> [tokens, hidden].  ``cache`` is what the cache

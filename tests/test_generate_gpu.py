@@ -90,6 +90,32 @@ def test_greedy_tiny_d_tensor_core_kernels(tmp_path, dtype):
     assert plain.generate(prompts, max_tokens=24) == outs          # captured and plain launches agree
 
 
+def test_greedy_with_splits_combined_in_clusters(tmp_path):
+    # the option that combines a decoded token's splits inside a thread-block cluster, through the engine:
+    # the packer cuts every token into whole clusters, the captured step launches them, no reduction runs
+    from paged_llm_rs_b200 import Engine
+    from paged_llm_rs_b200.kernels import ops
+    cfg, seed = CONFIGS["D"]
+    model = write_model(tmp_path, "D")
+    prompts = prompts_for(cfg["vocab_size"], [90, 3, 130, 64], 21)
+    was, ops.CLUSTER_COMBINE = ops.CLUSTER_COMBINE, True
+    try:
+        for graphs in (True, False):
+            eng = Engine(model, dtype="bfloat16", block_size=16, blocks=64, chunk=48)
+            eng.runner.use_graphs = graphs
+            pk = eng.runner.packer
+            assert pk.plans[0].max_cluster == 8
+            pk.target_ctas = 4 * 4 * pk.plans[0].ctas_per_item          # four requests: clusters of four
+            assert pk.cluster_for(0, 4) == 4
+            outs = eng.generate(prompts, max_tokens=24)
+            check_greedy(model, prompts, outs, 24, "bfloat16")
+            if graphs:
+                g = eng.runner._graphs[(4, 64)]
+                assert g.state.groups[0].cluster == 4
+    finally:
+        ops.CLUSTER_COMBINE = was
+
+
 def vocab_order_choice(logits64, temperature, u):
     """The engine's device draw: ids upward, the first id whose running sum reaches u * total."""
     p = torch.softmax(logits64 / temperature, -1)

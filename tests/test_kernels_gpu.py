@@ -12,6 +12,7 @@ import numpy as np
 import pytest
 import torch
 
+from paged_llm_rs_b200.errors import KernelError
 from paged_llm_rs_b200.kernels import attention_plan, ops
 
 pytestmark = pytest.mark.gpu
@@ -159,7 +160,7 @@ def attention_ref(q, k, v, scale, window):
 
 
 def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, craft=None, kinds=3, counters=None,
-                  raw=False):
+                  raw=False, cluster=0, idle_items=0):
     """reqs: list of (context before the step, query tokens).  Builds a paged cache
     with shuffled pages, runs the kernel, returns (got, want) per request."""
     g = torch.Generator().manual_seed(seed)
@@ -197,9 +198,11 @@ def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, c
     tile = ops.attention_tile_tokens(nh, nkv, dtype, hd, page, window or 0)
     # (splits from 128 keys on, shorter than the engine cuts them, so that the short contexts here have some)
     work, red, parts = attention_plan.plan_attention(segs, tile, window, nkv * (-(-(nh // nkv) // 16)), target_ctas,
-                                                     min_split_keys=128)
+                                                     min_split_keys=128, cluster=cluster)
     dev = lambda t: t.to(DEV)
     workd = dev(torch.from_numpy(np.ascontiguousarray(work)).reshape(-1, 8)) if len(work) else torch.zeros(1, 8, dtype=torch.int32, device=DEV)
+    if idle_items:   # a list with room to spare, as a captured step's is
+        workd = torch.cat([workd, torch.zeros(idle_items, 8, dtype=torch.int32, device=DEV)])
     redd = dev(torch.from_numpy(np.ascontiguousarray(red)).reshape(-1, 4)) if len(red) else torch.zeros(1, 4, dtype=torch.int32, device=DEV)
     qd = dev(torch.cat(qs).reshape(t0, nh * hd).contiguous())
     out = torch.zeros_like(qd)
@@ -212,8 +215,9 @@ def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, c
     if swz:
         ops.swizzle_pool_(kpd); ops.swizzle_pool_(vpd)
     ops.paged_attention(qd, kpd, vpd, dev(tables), workd, dev(torch.tensor([len(work)], dtype=torch.int32)),
-                        len(work), out, part_o, part_ml, redd, dev(torch.tensor([len(red)], dtype=torch.int32)),
-                        len(red), nh, nkv, hd, window or 0, scale, st, swizzled=swz, kinds=kinds, counters=counters)
+                        len(work) + idle_items, out, part_o, part_ml, redd, dev(torch.tensor([len(red)], dtype=torch.int32)),
+                        len(red), nh, nkv, hd, window or 0, scale, st, swizzled=swz, kinds=kinds, counters=counters,
+                        cluster=cluster)
     assert st.item() == 0
     if raw:
         return out, len(red)
@@ -254,6 +258,51 @@ def test_decode_only_steps_take_the_bulk_copy_kernel(nh, nkv, hd, page):
     res, _ = run_attention(torch.bfloat16, [(100, 1), (40, 9), (513, 1), (0, 70)], nh, nkv, hd, page, None, 10 ** 6, kinds=3)
     for got, want in res:
         torch.testing.assert_close(got, want, **tol(torch.bfloat16))
+
+
+@pytest.fixture
+def cluster_combine():
+    # (an option that is off by default: see ops.CLUSTER_COMBINE)
+    was, ops.CLUSTER_COMBINE = ops.CLUSTER_COMBINE, True
+    yield
+    ops.CLUSTER_COMBINE = was
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page", [(16, 8, 128, 16), (8, 1, 64, 8), (32, 8, 128, 64), (4, 4, 128, 128), (6, 3, 64, 32),
+                                            (7, 1, 128, 16)])
+@pytest.mark.parametrize("cluster", [2, 3, 4, 8])
+def test_single_tokens_are_combined_inside_a_cluster(cluster_combine, nh, nkv, hd, page, cluster):
+    # every token's key range in `cluster` items (some of them empty), combined through the cluster's
+    # shared memory: one kernel, no reduction, no partial rows; contexts that end on and off tile and
+    # page edges, shorter than one split and longer than all; and a list with idle clusters behind it
+    reqs = [(0, 1), (63, 1), (64, 1), (127, 1), (128, 1), (700, 1), (1023, 1), (15, 1), (page * 3, 1), (331, 1), (2500, 1)]
+    assert ops.attention_max_cluster(torch.bfloat16, nh, nkv, hd, page, 0) >= cluster
+    for idle in (0, 2 * cluster + 1):
+        launches = ops.LAUNCHES
+        res, n_red = run_attention(torch.bfloat16, reqs, nh, nkv, hd, page, None, 10 ** 6, kinds=1, cluster=cluster,
+                                   idle_items=idle)
+        assert n_red == 0 and ops.LAUNCHES - launches == 1
+        for got, want in res:
+            torch.testing.assert_close(got, want, **tol(torch.bfloat16))
+    # one key far back decides: it lies in another split than the token itself
+    def craft(r, q, k, v):
+        q[0] *= 0; q[0, :, 3] = 16.0
+        k[:, :, 3] = -1.0; k[41, :, 3] = 16.0
+        v[41] = 5.0
+    res, _ = run_attention(torch.bfloat16, [(1500, 1)], nh, nkv, hd, page, None, 10 ** 6, kinds=1, cluster=cluster, craft=craft)
+    got, want = res[0]
+    assert (got[0] - 5.0).abs().max() < 0.1
+    torch.testing.assert_close(got, want, **tol(torch.bfloat16))
+
+
+def test_cluster_lists_are_refused_where_no_kernel_combines_them(cluster_combine):
+    assert ops.attention_max_cluster(torch.bfloat16, 32, 2, 128, 16, 0) == 0       # groups of 16 heads
+    assert ops.attention_max_cluster(torch.float32, 16, 8, 128, 16, 0) == 0
+    assert ops.attention_max_cluster(torch.bfloat16, 16, 8, 128, 16, 100) == 0      # a window
+    with pytest.raises(KernelError):
+        run_attention(torch.bfloat16, [(300, 1)], 32, 2, 128, 16, None, 10 ** 6, kinds=1, cluster=4)
+    with pytest.raises(KernelError):
+        run_attention(torch.float32, [(300, 1)], 16, 8, 128, 16, None, 10 ** 6, kinds=1, cluster=4)
 
 
 @pytest.mark.parametrize("nh,nkv,hd,page", [(16, 8, 128, 16), (8, 1, 64, 8), (40, 2, 64, 16), (6, 3, 64, 32)])
@@ -315,7 +364,7 @@ def test_prompt_portions_take_the_tcgen05_kernel(nh, nkv, hd, page):
 @pytest.mark.parametrize("nh,nkv,hd,page,norm,rope", [(16, 8, 128, 16, True, True), (8, 1, 64, 8, True, True),
                                                         (40, 2, 64, 16, False, True), (4, 4, 128, 64, True, False),
                                                         (6, 3, 64, 32, False, False)])
-def test_decode_attention_does_the_norm_the_rotation_and_the_cache_write_itself(nh, nkv, hd, page, norm, rope):
+def test_decode_attention_does_the_norm_the_rotation_and_the_cache_write_itself(cluster_combine, nh, nkv, hd, page, norm, rope):
     # the same decode step two ways: the q/k kernel then the attention kernels, and the attention
     # kernel alone from the projection's output.  Outputs and both pools must be equal bit for bit.
     from paged_llm_rs_b200.parts.base import Runtime
@@ -345,9 +394,10 @@ def test_decode_attention_does_the_norm_the_rotation_and_the_cache_write_itself(
         cos, sin, _ = enc.rotary()
     pos = torch.tensor(ctxs, dtype=torch.int32, device=DEV)
     slots = torch.tensor([int(tables[r, c // page]) * page + c % page for r, c in enumerate(ctxs)], dtype=torch.int32, device=DEV)
-    for target in (1, 10 ** 6):
+    clusters = (0, 0, 2, 8) if ops.attention_max_cluster(torch.bfloat16, nh, nkv, hd, page, 0) else (0, 0)
+    for target, cluster in zip((1, 10 ** 6, 10 ** 6, 10 ** 6), clusters):     # whole; split; split and combined in clusters
         work, red, parts = attention_plan.plan_attention([(r, 1, c) for r, c in enumerate(ctxs)], 1, None, nkv * (-(-(nh // nkv) // 16)),
-                                                         target, min_split_keys=128)
+                                                         target, min_split_keys=128, cluster=cluster)
         workd = torch.from_numpy(np.ascontiguousarray(work)).reshape(-1, 8).to(DEV)
         redd = torch.from_numpy(np.ascontiguousarray(red)).reshape(-1, 4).to(DEV) if len(red) else torch.zeros(1, 4, dtype=torch.int32, device=DEV)
         nw = torch.tensor([len(work)], dtype=torch.int32, device=DEV)
@@ -361,12 +411,12 @@ def test_decode_attention_does_the_norm_the_rotation_and_the_cache_write_itself(
         ops.qk_norm_rope_kv(qkv, q, qg, kg, 1e-6, cos, sin, hd if rope else 0, pos, slots, k1, v1, nh, nkv, hd, st, swizzled=True)
         o1 = torch.zeros_like(q)
         ops.paged_attention(q, k1, v1, tables, workd, nw, len(work), o1, part_o, part_ml, redd, nr, len(red), nh, nkv, hd, 0,
-                            hd ** -0.5, st, swizzled=True, kinds=1)
+                            hd ** -0.5, st, swizzled=True, kinds=1, cluster=cluster)
         # the one
         k2, v2 = kp.clone(), vp.clone()
         o2 = torch.zeros_like(q)
         ops.decode_attention_fused(qkv, qg, kg, 1e-6, cos, sin, k2, v2, tables, workd, nw, len(work), o2, part_o, part_ml,
-                                   redd, nr, len(red), nh, nkv, hd, hd ** -0.5, st)
+                                   redd, nr, len(red), nh, nkv, hd, hd ** -0.5, st, cluster=cluster)
         assert st.item() == 0
         assert torch.equal(k1, k2) and torch.equal(v1, v2)
         assert not torch.equal(k1, kp)                   # (the step did write)

@@ -30,6 +30,8 @@ def setup(needs, plans, pages, page_size, B, W, target):
 @pytest.mark.parametrize("needs,plans", [
     ([FULL], [GroupPlanConfig(8, 2, None)]),
     ([FULL, WIN], [GroupPlanConfig(8, 2, None), GroupPlanConfig(16, 1, 300)]),
+    ([FULL], [GroupPlanConfig(8, 2, None, 8)]),        # the kernel combines up to 8 items a token in a cluster
+    ([FULL, WIN], [GroupPlanConfig(8, 4, None, 4), GroupPlanConfig(16, 1, 300)]),
 ])
 def test_native_decode_packer_writes_what_the_python_packer_writes(needs, plans, target):
     rng = np.random.default_rng(target)
@@ -71,3 +73,33 @@ def test_native_decode_packer_refuses_like_the_python_packer():
         with pytest.raises(ConfigError):
             pack([StepEntry("a", [1], [0])] * 5)       # more requests than the step holds
         pack([StepEntry("a", [999], [0])])
+
+
+@pytest.mark.parametrize("n,cpi,target,limit,expect", [
+    (8, 8, 296, 8, 4), (4, 8, 296, 8, 8), (2, 8, 296, 8, 0), (16, 8, 296, 8, 2), (32, 8, 296, 8, 2), (64, 8, 296, 8, 0),
+    (8, 8, 296, 0, 0), (8, 8, 296, 2, 2), (8, 8, 296, 1, 0), (1, 1, 296, 8, 0),
+])
+def test_cluster_size_of_a_decode_step(n, cpi, target, limit, expect):
+    assert attention_plan.decode_cluster(n, cpi, target, limit) == expect
+
+
+def test_cluster_plan_gives_every_token_whole_clusters_that_cover_its_keys():
+    rng = np.random.default_rng(5)
+    for C in (2, 3, 4, 8):
+        pos = [int(p) for p in rng.choice([0, 1, 62, 63, 64, 65, 255, 256, 511, 512, 1000, 4095, 4096, 20000], size=9)]
+        segs = [(i, 1, p) for i, p in enumerate(pos)]
+        work, red, parts = attention_plan.plan_attention(segs, 8, None, 8, 296, cluster=C)
+        assert len(red) == 0 and parts == 0 and len(work) == C * len(segs)
+        for i, p in enumerate(pos):
+            items = work[C * i:C * i + C]
+            assert (items[:, 0] == i).all() and (items[:, 1] == i).all() and (items[:, 2] == 1).all() and (items[:, 3] == p).all()
+            assert (items[:, 6] == -1).all() and list(items[:, 7]) == [(C << 16) | k for k in range(C)]
+            assert (items[:, 4] % 64 == 0).all()                # every range starts on a key tile, the empty ones too
+            live = items[items[:, 5] > items[:, 4]]
+            assert live[0, 4] == 0 and live[-1, 5] == p + 1     # the keys 0 .. p, each once, in order
+            assert (live[1:, 4] == live[:-1, 5]).all()
+            assert len(live) == max(1, min(C, (p + 1) // attention_plan.MIN_SPLIT_KEYS)) or len(live) < C
+            empty = items[items[:, 5] == items[:, 4]]
+            assert len(live) + len(empty) == C and (items[:len(live)] == live).all()   # the live ones come first
+    with pytest.raises(ValueError):
+        attention_plan.plan_attention([(0, 2, 10)], 8, None, 8, 296, cluster=4)
