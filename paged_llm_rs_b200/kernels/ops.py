@@ -67,6 +67,8 @@ def lib():
         sig["pllm_attention_prefill_tcgen05"] = [P] * 10 + [c_int] * 7 + [c_float, c_int, P, P]
         sig["pllm_gemm_tcgen05_supports"] = [c_int, c_int, c_int, c_int]
         sig["pllm_gemm_tcgen05"] = [P, P, P, c_int, c_int, c_int, c_int, P, P]
+        sig["pllm_gemm_tcgen05_qkv_supports"] = [c_int] * 6
+        sig["pllm_gemm_tcgen05_qkv"] = [P, P, P, P, P, c_float, P, P, c_int, P, P, P, P] + [c_int] * 8 + [P, P]
         sig["pllm_pack_decode_step"] = [P, c_int, c_int, P, P, P, P, P] + [c_int] * 16 + [P, P]
         for name, args in sig.items():
             fn = getattr(L, name)
@@ -546,6 +548,62 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, glu: bool = False, statu
     _check(lib().pllm_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), M, n_out, K, 1 if glu else 0, _ptr(st), _stream()),
            "gemm_tcgen05")
     return out
+
+
+# PAGED_LLM_FUSE_QKV_GEMM=1: the attention's input projection for the many rows of a prompt portion with the
+# per-head norm, the rotation and the cache write in the product's epilogue, instead of the library product
+# and then the q/k kernel over its output.  Off by default: it measured slower (2048 tokens of the 0.6B
+# shape: 43 us alone with cold caches against 21 + 19, and 36 us against 17 + 11 inside the step, 3.64 ms
+# against 3.41 for the prompt).  The product itself is 25 us here against the library's 21, and the epilogue
+# of four warps takes 17 us for a tile of 256 columns with the norm and the rotation (4 us plain), of which
+# only the first of a CTA's two tiles hides behind the tensor cores.
+FUSE_QKV_GEMM = os.environ.get("PAGED_LLM_FUSE_QKV_GEMM", "0") == "1"
+
+
+def qkv_projection_fuses(x, weight: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                         rotary_dim: int) -> bool:
+    """Whether ``qkv_projection_fused`` takes this step: bfloat16, enough rows for the tensor-core tiles,
+    heads of 64 or 128 values rotated over their whole width or not at all."""
+    if not FUSE_QKV_GEMM or not TCGEN05_GEMM or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        return False
+    if x.shape[0] < TCGEN05_MIN_M or not weight.is_contiguous() or weight.shape[0] != (num_heads + 2 * num_kv_heads) * head_dim:
+        return False
+    return bool(lib().pllm_gemm_tcgen05_qkv_supports(x.shape[0], weight.shape[1], num_heads, num_kv_heads, head_dim,
+                                                     int(rotary_dim)))
+
+
+def qkv_projection_fused(x, weight: torch.Tensor, q_out: torch.Tensor, q_gain, k_gain, eps: float, cos, sin,
+                         positions: torch.Tensor, slots: Optional[torch.Tensor], k_pool: Optional[torch.Tensor],
+                         v_pool: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int,
+                         status: torch.Tensor, swizzled: bool = False) -> torch.Tensor:
+    """q_out = rope(norm(x Wq^T)), and with pools: rope(norm(x Wk^T)) and x Wv^T into the cache rows that
+    ``slots`` names (-1: none), all from one product on the tcgen05 tensor cores whose epilogue threads
+    each hold one token's heads.  ``weight`` is [q rows; k rows; v rows]; without pools only q is made."""
+    x = as_tensor(x)
+    if not qkv_projection_fuses(x, weight, num_heads, num_kv_heads, head_dim, head_dim if cos is not None else 0):
+        raise KernelError(f"qkv_projection_fused: does not take x {tuple(x.shape)} {x.dtype}, W {tuple(weight.shape)}")
+    _dev(x, weight, q_out, q_gain, k_gain, cos, sin, positions, slots, k_pool, v_pool, status)
+    _f32(q_gain, "q_gain"); _f32(k_gain, "k_gain"); _f32(cos, "cos"); _f32(sin, "sin")
+    _i32(positions, "positions")
+    if slots is not None:
+        _i32(slots, "slots")
+    M, K = x.shape
+    if not x.is_contiguous() or weight.shape[1] != K or q_out.shape != (M, num_heads * head_dim) or q_out.dtype != torch.bfloat16 \
+            or not q_out.is_contiguous() or positions.numel() < M or (slots is not None and slots.numel() < M):
+        raise KernelError("qkv_projection_fused: shapes do not fit")
+    if (cos is None) != (sin is None) or (cos is not None and cos.shape[-1] * 2 != head_dim):
+        raise KernelError("qkv_projection_fused: the rotation must span the whole head (or be absent)")
+    keep = k_pool is not None
+    if keep and (v_pool is None or slots is None or k_pool.shape != v_pool.shape or k_pool.dtype != torch.bfloat16
+                 or k_pool.dim() != 4 or k_pool.shape[1] != num_kv_heads or k_pool.shape[3] != head_dim):
+        raise KernelError(f"qkv_projection_fused: pools must be bfloat16 [pages, {num_kv_heads}, page_size, {head_dim}]")
+    _check(lib().pllm_gemm_tcgen05_qkv(_ptr(x), _ptr(weight), _ptr(q_out), _ptr(q_gain), _ptr(k_gain), float(eps),
+                                       _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0, _ptr(positions),
+                                       _ptr(slots) if keep else None, _ptr(k_pool) if keep else None,
+                                       _ptr(v_pool) if keep else None, M, K, num_heads, num_kv_heads, head_dim,
+                                       k_pool.shape[2] if keep else 1, k_pool.shape[0] if keep else 0,
+                                       1 if swizzled else 0, _ptr(status), _stream()), "qkv_projection_fused")
+    return q_out
 
 
 class NormedInput:

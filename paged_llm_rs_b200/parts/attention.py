@@ -71,10 +71,23 @@ class GQAttention(Mixer):
         k_pool, v_pool, gi = cache
         g = step.groups[gi]
         T = x.shape[0]
-        qkv = ops.linear(x, self.w_qkv, status=self.rt.status)
         rot = self.position.rotary() if self.position is not None else None
         cos, sin, rdim = rot if rot is not None else (None, None, 0)
         swizzled = self.cache_need().swizzled
+        if ops.qkv_projection_fuses(x, self.w_qkv, self.nh, self.nkv, self.hd, rdim):
+            # many rows (a prompt portion): the product's epilogue norms and rotates q and k and writes
+            # the cache rows; the [tokens, q + k + v] intermediate is never stored
+            q = torch.empty((T, self.nh * self.hd), dtype=x.dtype, device=x.device)
+            ops.qkv_projection_fused(x, self.w_qkv, q, self.q_gain, self.k_gain, self.qk_norm_eps or 0.0, cos, sin,
+                                     step.positions, g.slots, k_pool if writes_cache else None,
+                                     v_pool if writes_cache else None, self.nh, self.nkv, self.hd, self.rt.status,
+                                     swizzled=swizzled)
+            o = torch.empty_like(q)
+            ops.paged_attention(q, k_pool, v_pool, g.block_tables, g.work, g.n_work, g.max_work, o, g.part_o, g.part_ml,
+                                g.red, g.n_red, g.max_red, self.nh, self.nkv, self.hd, self.window or 0, self.scale,
+                                self.rt.status, swizzled=swizzled, kinds=g.kinds, counters=g.counters, cluster=g.cluster)
+            return ops.linear(o, self.w_o, status=self.rt.status)
+        qkv = ops.linear(x, self.w_qkv, status=self.rt.status)
         if writes_cache and g.kinds == 1 and ops.decode_attention_fuses(x.dtype, self.nh, self.nkv, self.hd, k_pool.shape[2],
                                                                           self.window or 0, rdim, swizzled):
             # a step of single decoded tokens: the attention kernel norms and rotates q and k and

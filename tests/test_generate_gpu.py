@@ -116,6 +116,23 @@ def test_greedy_with_splits_combined_in_clusters(tmp_path):
         ops.CLUSTER_COMBINE = was
 
 
+def test_greedy_with_the_input_projection_that_norms_rotates_and_writes_the_cache(tmp_path, monkeypatch):
+    # the option that folds the q/k norm, the rotation and the cache write into the product's epilogue,
+    # through the engine: prompts long enough for the tensor-core tiles, then decoding from what it wrote
+    from paged_llm_rs_b200 import Engine
+    from paged_llm_rs_b200.kernels import ops
+    cfg, seed = CONFIGS["D"]
+    model = write_model(tmp_path, "D")
+    prompts = prompts_for(cfg["vocab_size"], [90, 130, 64], 22)
+    monkeypatch.setattr(ops, "FUSE_QKV_GEMM", True)
+    eng = Engine(model, dtype="bfloat16", block_size=16, blocks=64, chunk=None)
+    m = eng.runner.model.blocks[0].mixer
+    x = torch.zeros(90, m.w_qkv.shape[1], dtype=torch.bfloat16, device="cuda:0")
+    assert ops.qkv_projection_fuses(x, m.w_qkv, m.nh, m.nkv, m.hd, m.hd)
+    outs = eng.generate(prompts, max_tokens=12)
+    check_greedy(model, prompts, outs, 12, "bfloat16")
+
+
 def vocab_order_choice(logits64, temperature, u):
     """The engine's device draw: ids upward, the first id whose running sum reaches u * total."""
     p = torch.softmax(logits64 / temperature, -1)

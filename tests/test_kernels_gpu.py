@@ -138,6 +138,65 @@ def test_qk_norm_rope_kv_write(dtype, nh, nkv, hd, rot, page, T):
     assert (flat[~written] == 0).all()          # nothing else was touched
 
 
+@pytest.mark.parametrize("nh,nkv,hd,K", [(16, 8, 128, 1024), (4, 2, 64, 192), (6, 1, 128, 72), (2, 2, 64, 320), (32, 8, 128, 256)])
+@pytest.mark.parametrize("T", [64, 301, 2048])
+@pytest.mark.parametrize("norm,rope,swizzled", [(True, True, True), (False, True, False), (True, False, True)])
+def test_input_projection_with_norm_rotation_and_cache_write_in_its_epilogue(monkeypatch, nh, nkv, hd, K, T, norm, rope, swizzled):
+    # the tcgen05 product whose epilogue threads hold one token's heads, against x W^T rounded to
+    # bfloat16, then the norm per head, the rotation and the scatter in float; rows beyond the last
+    # tile's tokens, a token without a slot, positions all over the table
+    from paged_llm_rs_b200.parts.base import Runtime
+    from paged_llm_rs_b200.parts.position import RotaryEncoding
+    from paged_llm_rs_b200.parts.spec import PartSpec
+    if T == 2048 and K != 1024:
+        pytest.skip("the large step once")
+    monkeypatch.setattr(ops, "FUSE_QKV_GEMM", True)       # (an option that is off by default)
+    g = torch.Generator(device=DEV).manual_seed(nh * hd + T)
+    page, eps, theta = 16, 1e-6, 1e6
+    pages = -(-T // page) + 5
+    x = torch.randn(T, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn((nh + 2 * nkv) * hd, K, device=DEV, generator=g) * K ** -0.5).bfloat16()
+    qg = 1 + 0.1 * torch.randn(hd, device=DEV, generator=g) if norm else None
+    kg = 1 + 0.1 * torch.randn(hd, device=DEV, generator=g) if norm else None
+    pos = torch.randint(0, 3000, (T,), device=DEV, generator=g, dtype=torch.int32)
+    slots = torch.randperm(pages * page, device=DEV, generator=g)[:T].to(torch.int32)
+    slots[5] = -1
+    cos = sin = None
+    if rope:
+        enc = RotaryEncoding(PartSpec("rope", dict(head_dim=hd, rotary_dim=hd, theta=theta, max_positions=3000)),
+                             Runtime(torch.device(DEV), torch.bfloat16))
+        cos, sin, _ = enc.rotary()
+    assert ops.qkv_projection_fuses(x, w, nh, nkv, hd, hd if rope else 0)
+    kp = torch.zeros(pages, nkv, page, hd, device=DEV, dtype=torch.bfloat16)
+    vp = torch.zeros_like(kp)
+    q = torch.zeros(T, nh * hd, device=DEV, dtype=torch.bfloat16)
+    st = status()
+    launches = ops.LAUNCHES
+    ops.qkv_projection_fused(x, w, q, qg, kg, eps, cos, sin, pos, slots, kp, vp, nh, nkv, hd, st, swizzled=swizzled)
+    assert st.item() == 0 and ops.LAUNCHES - launches == 1
+    if swizzled:      # back to plain rows for the comparison
+        ops.swizzle_pool_(kp); ops.swizzle_pool_(vp)       # (its own inverse)
+
+    y = (x.float() @ w.float().T).bfloat16().float().view(T, nh + 2 * nkv, hd)
+    nrm = (lambda v, gain: v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * gain) if norm else (lambda v, gain: v)
+    rot = (lambda v: rope_ref(v, pos.cpu(), theta, hd)) if rope else (lambda v: v)
+    q_ref, k_ref, v_ref = rot(nrm(y[:, :nh], qg)), rot(nrm(y[:, nh:nh + nkv], kg)), y[:, nh + nkv:]
+    torch.testing.assert_close(q.float().view(T, nh, hd), q_ref, **tol(torch.bfloat16))
+    ok = slots >= 0
+    sl = slots[ok].long()
+    torch.testing.assert_close(kp[sl // page, :, sl % page].float(), k_ref[ok], **tol(torch.bfloat16))
+    torch.testing.assert_close(vp[sl // page, :, sl % page].float(), v_ref[ok], **tol(torch.bfloat16))
+    written = torch.zeros(pages * page, dtype=torch.bool, device=DEV)
+    written[sl] = True
+    flat = kp.float().permute(0, 2, 1, 3).reshape(pages * page, -1).abs().sum(-1)
+    assert (flat[~written] == 0).all()          # nothing else was touched
+
+    # q alone (a layer that reads another layer's cache): the same q, no pool needed
+    q2 = torch.zeros_like(q)
+    ops.qkv_projection_fused(x, w, q2, qg, kg, eps, cos, sin, pos, None, None, None, nh, nkv, hd, st, swizzled=swizzled)
+    assert st.item() == 0 and torch.equal(q2, q)
+
+
 # --- attention -------------------------------------------------------------------------
 
 def attention_ref(q, k, v, scale, window):
