@@ -98,7 +98,11 @@ class Engine:
         if tokens_dev is None:
             self.bytes_d2h = 0
             return []
-        back = tokens_dev.cpu()
+        back = self.runner.tokens_host
+        if back is not None:     # a captured step copies them to pinned memory itself
+            torch.cuda.current_stream().synchronize()
+        else:
+            back = tokens_dev.cpu()
         self.bytes_d2h = back.numel() * 4
         if int(back[0]):
             self.runner.check_status()

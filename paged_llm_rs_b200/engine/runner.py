@@ -68,6 +68,8 @@ class _DecodeGraph:
         self.nbytes = host.nbytes
         self.state = pk.to_state(self.dev, self.layout, self.sizes, runner._heads, full=True)
         self.tokens = torch.zeros(1 + n_seg, dtype=torch.int32, device=runner.device)
+        # the status word and the chosen tokens come back by a copy that is part of the captured step
+        self.tokens_host = torch.zeros(1 + n_seg, dtype=torch.int32).pin_memory()
         # Warm up on a side stream (library handles, workspaces), then capture.
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -96,9 +98,11 @@ class _DecodeGraph:
 
     def _body(self):
         r = self.runner
+        self.dev.copy_(self.pinned, non_blocking=True)      # the step's packed buffer: the graph's first node
         self.logits = r.model.forward(self.state, r.caches)
         ops.sample(self.logits, self.state.temperature, self.state.uniform, self.tokens[1:])
         self.tokens[:1].copy_(r.rt.status)
+        self.tokens_host.copy_(self.tokens, non_blocking=True)
 
     def run(self, entries, temperature, uniform):
         r = self.runner
@@ -107,11 +111,11 @@ class _DecodeGraph:
         else:
             host, _, _ = r.packer.pack(entries, r._heads, self.caps, self.work_caps, temperature, uniform)
             self.pinned.numpy()[:] = host
-        self.dev.copy_(self.pinned, non_blocking=True)
         self.graph.replay()
         r.bytes_h2d = self.nbytes
         r.last_launches = self.launches
         n = sum(len(e.want) for e in entries)
+        r.tokens_host = self.tokens_host[:1 + n]
         return self.logits[:n], self.tokens[:1 + n]
 
 
@@ -175,6 +179,8 @@ class ModelRunner:
         # captured once and replayed (None: such steps are launched kernel by kernel)
         self.graph_step_tokens: Optional[int] = None
         self.bytes_h2d = 0        # bytes the last step copied to the device
+        self.tokens_host: Optional[torch.Tensor] = None   # pinned copy of the last step's (status, tokens), valid
+                                                          # once the stream is synchronized; None: not made
         self.last_launches = 0    # kernels of this library the last step launched
 
     # -- the step ----------------------------------------------------------------------
@@ -194,6 +200,7 @@ class ModelRunner:
         if not entries:
             return torch.zeros((0, self.vocab_size), dtype=torch.float32, device=self.device), None
         self.bytes_h2d = 0
+        self.tokens_host = None
         if self.use_graphs and temperature is not None:
             if all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
                 g = self._decode_graph(entries)

@@ -159,6 +159,8 @@ class Scheduler:
         return None
 
     def _mixed(self) -> Optional[Plan]:
+        if not self.waiting and self._prompt_in_flight() is None:
+            return None         # no prompt to feed: a plain decode step, planned once (by _decode)
         budget = self.chunk
         ids, advanced, entries = [], [], []
         cap = min(self.max_batch, budget)
