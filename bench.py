@@ -43,6 +43,12 @@ SHAPE_0_6B = dict(
     head_dim=128, rms_norm_eps=1e-6, vocab_size=151936, max_position_embeddings=40960, tie_word_embeddings=True,
     rope_theta=1000000.0, sliding_window=None, use_sliding_window=False,
 )
+# the other two shapes the baseline names, for --shape: the default run and its JSON contract stay the 0.6B one
+SHAPE_8B = dict(SHAPE_0_6B, hidden_size=4096, intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32,
+                num_key_value_heads=8, tie_word_embeddings=False)
+SHAPE_32B = dict(SHAPE_0_6B, hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64,
+                 num_key_value_heads=8, tie_word_embeddings=False)
+SHAPES = {"0.6b": ("Qwen3-0.6B", SHAPE_0_6B), "8b": ("Qwen3-8B", SHAPE_8B), "32b": ("Qwen3-32B", SHAPE_32B)}
 PAGE = 16
 PREFILL_TOKENS = 2048
 
@@ -224,6 +230,7 @@ def main(argv=None) -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="0.6b", help="layer sizes: the baseline's 0.6B (default), 8B or 32B shape")
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the shape has (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--timeline-prefill", action="store_true",
@@ -251,7 +258,7 @@ def main(argv=None) -> int:
     from paged_llm_rs_b200 import Engine, write_random_model
 
     pk = peaks()
-    shape = dict(SHAPE_0_6B)
+    shape_name, shape = SHAPES[args.shape][0], dict(SHAPES[args.shape][1])
     layers_full = shape["num_hidden_layers"]
     if args.layers:
         shape["num_hidden_layers"] = args.layers
@@ -351,13 +358,13 @@ def main(argv=None) -> int:
         shutil.rmtree(tmp, ignore_errors=True)
 
     line = {
-        "metric": "decode tokens/s (Qwen3-0.6B shape, batch 8, context 4096)", "value": round(value, 1),
+        "metric": f"decode tokens/s ({shape_name} shape, batch {B}, context {ctx})", "value": round(value, 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {
-            "model": "Qwen3-0.6B shape, random weights N(0,0.02) seed 0", "layers": L, "layers_of_shape": layers_full,
+            "model": f"{shape_name} shape, random weights N(0,0.02) seed 0", "layers": L, "layers_of_shape": layers_full,
             "hidden": H, "heads": nh, "kv_heads": nkv, "head_dim": hd, "intermediate": I, "vocab": V,
-            "tie_word_embeddings": True, "global_batch": B, "seq_len": ctx, "page_size": PAGE,
+            "tie_word_embeddings": bool(shape["tie_word_embeddings"]), "global_batch": B, "seq_len": ctx, "page_size": PAGE,
             "prefill_tokens": PREFILL_TOKENS, "parallelism": "one GPU",
             "l2": f"inputs larger than L2: a step reads {step_bytes / 1e6:.0f} MB",
             "peaks": pk["source"], "hbm_gbs_peak": pk["hbm_gbs"], "bf16_tflops_peak": pk["bf16_tflops"],

@@ -273,11 +273,17 @@ __global__ void __launch_bounds__(WMAX * 32, WMAX == 8 ? 3 : 1) skinny_gemm_kern
     }
 }
 
-// For tuning runs: a number of warps a CTA to use instead of the heuristic's (0: the heuristic).
-static int g_skinny_warps_override = 0;
+// For tuning runs: a number of warps a CTA to use instead of the heuristic's (0: the heuristic), and
+// likewise the number of 8-row tiles of W a CTA takes (1, 2 or 4).
+static int g_skinny_warps_override = 0, g_skinny_nt_override = 0;
 PLLM_EXPORT int pllm_skinny_gemm_set_warps(int warps) {
     const int was = g_skinny_warps_override;
     g_skinny_warps_override = warps;
+    return was;
+}
+PLLM_EXPORT int pllm_skinny_gemm_set_tiles(int nt) {
+    const int was = g_skinny_nt_override;
+    g_skinny_nt_override = nt;
     return was;
 }
 
@@ -334,8 +340,15 @@ PLLM_EXPORT int pllm_skinny_gemm(const void* x, const void* w, void* y, int M, i
     if (!pllm_skinny_gemm_supports(M, N, K)) return PLLM_ERR_SIZE;
     if (((uintptr_t)x | (uintptr_t)w) & 15) return PLLM_ERR_ALIGN;
     // Tiles of 16 rows of W while that still gives every SM several CTAs, else of 8.
-    const int nt = (N / 16 >= 2 * 148) ? 2 : 1;
+    // (With long rows, K >= 4096, a CTA has work enough for one tile of 16 to an SM to do, and every CTA reads
+    // all of x from L2, as many bytes as 8 rows of W: measured at 8 rows, 4096 x 12288, 34.8 us with tiles of 8
+    // and 26.6 with tiles of 16; 4096 x 4096, 19.5 and 16.4.)
+    int nt = (N / 16 >= 2 * 148 || (K >= 4096 && N / 16 >= 148)) ? 2 : 1;
+    if (g_skinny_nt_override && N % (8 * g_skinny_nt_override) == 0 && (g_skinny_nt_override < 4 || M <= 16)) nt = g_skinny_nt_override;
     const int warps = pick_warps(K, N / (8 * nt), 128);
+    if (nt == 4)
+        return out_f32 ? launch_skinny<1, 4, 0, 0, float>(x, w, y, M, N, K, warps, nullptr, nullptr, nullptr, 0.f, stream)
+                       : launch_skinny<1, 4, 0, 0, bf16>(x, w, y, M, N, K, warps, nullptr, nullptr, nullptr, 0.f, stream);
     if (out_f32)
         return nt == 2 ? pick_mt<2, float>(x, w, y, M, N, K, warps, stream) : pick_mt<1, float>(x, w, y, M, N, K, warps, stream);
     return nt == 2 ? pick_mt<2, bf16>(x, w, y, M, N, K, warps, stream) : pick_mt<1, bf16>(x, w, y, M, N, K, warps, stream);
