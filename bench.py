@@ -148,7 +148,7 @@ TRACE_FILES = ["elementwise", "qk_norm_rope_kv", "attention_generic", "attention
                "skinny_gemm", "gemm_tcgen05", "attention_prefill_tcgen05"]
 
 
-def timeline(runner, batch, context, layers, prefill_tokens=0, vocab=1000) -> int:
+def timeline(runner, batch, context, layers, prefill_tokens=0, vocab=1000, mixed_tokens=0) -> int:
     """One replay of the captured decode step, clocked by the kernels themselves (thread 0 of
     each kernel's first CTA reads the global timer before and after its wait for the kernel
     before it).  "to next" is the time from a kernel's wait ending to the next kernel's wait
@@ -174,7 +174,24 @@ def timeline(runner, batch, context, layers, prefill_tokens=0, vocab=1000) -> in
         return sorted(recs)
 
     cache = runner.cache
-    if prefill_tokens:
+    if mixed_tokens:
+        # a mixed step: the decoding requests beside one portion of a prompt that has 1024 tokens behind it
+        ids = [f"t{b}" for b in range(batch)]
+        for r in ids:
+            cache.open(r)
+            assert cache.reserve(r, context)
+            cache.commit(r, context - 1)
+        cache.open("tp")
+        assert cache.reserve("tp", 1024 + mixed_tokens)
+        cache.commit("tp", 1024)
+        prompt = np.random.default_rng(0).integers(0, vocab, mixed_tokens).tolist()
+        entries = [StepEntry(r, [1 + i], [0]) for i, r in enumerate(ids)] + [StepEntry("tp", prompt, [])]
+        zeros = np.zeros(batch, dtype=np.float32)
+        runner.graph_step_tokens = batch + mixed_tokens
+        runner.step_and_sample(entries, zeros, zeros)
+        graph = runner._portion_graph(entries)
+        assert graph is not None, "the mixed step does not run as a captured step"
+    elif prefill_tokens:
         prompt = np.random.default_rng(0).integers(0, vocab, prefill_tokens).tolist()
         cache.open("tp")
         assert cache.reserve("tp", prefill_tokens)
@@ -207,6 +224,8 @@ def timeline(runner, batch, context, layers, prefill_tokens=0, vocab=1000) -> in
     per_layer = max(1, (len(rows) - 4) // max(1, layers))
     start = min(len(rows), 2 + per_layer * (layers // 2))
     what = f"prefill step, {prefill_tokens} tokens" if prefill_tokens else f"decode step, batch {batch}, context {context}"
+    if mixed_tokens:
+        what = f"mixed step, {batch} decoding at context {context} beside a portion of {mixed_tokens} tokens"
     print(f"{what}, {layers} layers: {len(rows)} kernels stamped, "
           f"{(recs[-1][0] - recs[0][0]) / 1e3:.1f} us from first to last")
     print(f"one layer from the middle:\n{'kernel':18s} {'at us':>9s} {'to next':>8s} {'in place':>8s}")
@@ -235,6 +254,8 @@ def main(argv=None) -> int:
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--timeline-prefill", action="store_true",
                     help="with --only timeline: the captured step of a 2048-token prompt portion instead of the decode step")
+    ap.add_argument("--timeline-mixed", type=int, default=0, metavar="TOKENS",
+                    help="with --only timeline: the decoding requests beside one prompt portion of this many tokens")
     ap.add_argument("--only", choices=["decode", "prefill", "timeline"], default=None,
                     help="run one part alone and print a short line (for profiling; not a bench record); "
                          "timeline: one captured decode step as the kernels themselves clocked it")
@@ -295,7 +316,7 @@ def main(argv=None) -> int:
             return 0
 
         if args.only == "timeline":
-            return timeline(runner, B, ctx, L, PREFILL_TOKENS if args.timeline_prefill else 0, V)
+            return timeline(runner, B, ctx, L, PREFILL_TOKENS if args.timeline_prefill else 0, V, args.timeline_mixed)
 
         # -- decode, on the device -------------------------------------------------------
         ms, launches = decode_point(runner, B, ctx, steps, warmup, clocks)

@@ -187,6 +187,35 @@ __global__ void attention_reduce_kernel(const float* part_o, const float* part_m
     for (int t = blockIdx.x; t < n_red; t += gridDim.x) {
         const int token = red[t * 4], first = red[t * 4 + 1], count = min(red[t * 4 + 2], RED_MAX_SPLITS), stride = red[t * 4 + 3];
         if (count <= 0) continue;
+        if (count <= 8 && ng == 1) {
+            // few splits (the usual case away from batch 1): every thread fetches the entry's (m, l) pairs and
+            // its own column of the partial rows in one trip, nothing goes through shared memory and no
+            // thread waits for another, so a CTA's entries follow one another at the pace of the loads
+            float2 ml[8];
+            float v[8], M = -CUDART_INF_F;
+            const float* po = part_o + ((size_t)first * nh + head) * hd + d;
+            const size_t s_stride = (size_t)stride * nh * hd;
+#pragma unroll
+            for (int s = 0; s < 8; s++) {
+                ml[s] = make_float2(-CUDART_INF_F, 0.f);
+                v[s] = 0.f;
+                if (s < count) {
+                    ml[s] = *reinterpret_cast<const float2*>(part_ml + ((size_t)(first + s * stride) * nh + head) * 2);
+                    v[s] = po[(size_t)s * s_stride];
+                }
+                M = fmaxf(M, ml[s].x);
+            }
+            float L = 0.f, o = 0.f;
+#pragma unroll
+            for (int s = 0; s < 8; s++) {
+                if (s >= count) break;
+                const float f = ml[s].x == -CUDART_INF_F ? 0.f : expf(ml[s].x - M);
+                L += ml[s].y * f;
+                o = fmaf(v[s], f, o);
+            }
+            out[((size_t)token * nh + head) * hd + d] = from_f32<T>(o * (L > 0.f ? 1.0f / L : 0.f));
+            continue;
+        }
         __syncthreads();       // the weights and sums of the entry before are no longer read
         if (threadIdx.x < 32) {
             // up to 8 splits a lane, their (m, l) pairs fetched together
@@ -278,6 +307,8 @@ PLLM_EXPORT int pllm_attention_reduce(int dtype, const float* part_o, const floa
     if (max_red <= 0) return PLLM_OK;
     const int groups = many_splits && RED_GROUPS * hd <= 1024 ? RED_GROUPS : 1;
     PLLM_DISPATCH_DTYPE(dtype, {
+        // (a captured step launches its capacity, and every CTA of it costs its start even with nothing to do:
+        // 256 x heads instead of 64 cost the 2048-token step 4 us a layer; the CTAs loop over the entries)
         dim3 grid(max_red < 64 ? max_red : 64, nh);
         launch_chained(attention_reduce_kernel<T>, grid, dim3(groups * hd), (size_t)groups * hd * sizeof(float), stream,
                        part_o, part_ml, red,

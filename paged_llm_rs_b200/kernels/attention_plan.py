@@ -26,6 +26,11 @@ SPLIT_ALIGN = 64   # split boundaries fall on multiples of the kernels' key tile
 # step of the 0.6B shape, batch 1, context 4096: 0.927 ms with 256, 0.947 with 128, 1.011 with 512).
 MIN_SPLIT_KEYS = 256
 MAX_SPLITS = 128   # the reduce kernel holds the weights of up to 256 splits in shared memory
+# A tile of many query tokens is cut only where every part still has this many keys: its partial results are
+# a tile of rows each, not one row (a 512-token portion behind 1024 tokens of context beside one decoded
+# token, 0.6B shape: cut in four from 256 keys on, the attention took 25 us a layer and the reduction 17;
+# whole, see profiles/prefill_2048_tokens.md).
+MULTI_MIN_SPLIT_KEYS = 2048
 
 
 def decode_cluster(n_tokens: int, ctas_per_item: int, target_ctas: int, max_cluster: int) -> int:
@@ -43,7 +48,8 @@ def decode_cluster(n_tokens: int, ctas_per_item: int, target_ctas: int, max_clus
 
 def plan_attention(segments: Sequence[Tuple[int, int, int]], tile_tokens: int, window: Optional[int],
                    ctas_per_item: int, target_ctas: int,
-                   min_split_keys: int = MIN_SPLIT_KEYS, cluster: int = 0) -> Tuple[np.ndarray, np.ndarray, int]:
+                   min_split_keys: int = MIN_SPLIT_KEYS, cluster: int = 0,
+                   multi_min_split_keys: int = MULTI_MIN_SPLIT_KEYS) -> Tuple[np.ndarray, np.ndarray, int]:
     """segments: (first token index, token count, position of the first token) per
     segment, in step order.  Returns (work [n, 8], red [m, 4], partial rows used).
     ``cluster`` > 1 (steps of single tokens only): every token gets exactly that many
@@ -101,7 +107,8 @@ def plan_attention(segments: Sequence[Tuple[int, int, int]], tile_tokens: int, w
         want = target_ctas // (n_tiles * ctas_per_item)
         if want < 2:
             want = 2 if int(qn.max()) == 1 else 1
-        splits = np.clip(np.minimum(want, keys // min_split_keys), 1, MAX_SPLITS)
+        floor = np.where(qn > 1, max(min_split_keys, multi_min_split_keys), min_split_keys)
+        splits = np.clip(np.minimum(want, keys // floor), 1, MAX_SPLITS)
     if (splits == 1).all():
         work = np.stack([seg, q0, qn, p0, kv_begin, kv_end, np.full(n_tiles, -1), np.zeros(n_tiles, np.int64)], 1)
         return work.astype(np.int32), np.zeros((0, 4), np.int32), 0

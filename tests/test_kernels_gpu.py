@@ -257,7 +257,7 @@ def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, c
     tile = ops.attention_tile_tokens(nh, nkv, dtype, hd, page, window or 0)
     # (splits from 128 keys on, shorter than the engine cuts them, so that the short contexts here have some)
     work, red, parts = attention_plan.plan_attention(segs, tile, window, nkv * (-(-(nh // nkv) // 16)), target_ctas,
-                                                     min_split_keys=128, cluster=cluster)
+                                                     min_split_keys=128, cluster=cluster, multi_min_split_keys=128)
     dev = lambda t: t.to(DEV)
     workd = dev(torch.from_numpy(np.ascontiguousarray(work)).reshape(-1, 8)) if len(work) else torch.zeros(1, 8, dtype=torch.int32, device=DEV)
     if idle_items:   # a list with room to spare, as a captured step's is

@@ -103,3 +103,39 @@ def test_cluster_plan_gives_every_token_whole_clusters_that_cover_its_keys():
             assert len(live) + len(empty) == C and (items[:len(live)] == live).all()   # the live ones come first
     with pytest.raises(ValueError):
         attention_plan.plan_attention([(0, 2, 10)], 8, None, 8, 296, cluster=4)
+
+
+def _covers(work, segs, tile):
+    """Every query token's keys 0 .. its position, each once, over the items that hold the token."""
+    seen = {}
+    for seg, q0, qn, p0, kb, ke, part, split in work.tolist():
+        for t in range(qn):
+            lo, hi = kb, min(ke, p0 + t + 1)
+            if hi > lo:
+                seen.setdefault(q0 + t, []).append((lo, hi))
+    for t0, n, p0 in segs:
+        for t in range(n):
+            runs = sorted(seen[t0 + t])
+            assert runs[0][0] == 0 and runs[-1][1] == p0 + t + 1
+            assert all(a[1] == b[0] for a, b in zip(runs, runs[1:]))
+
+
+def test_tiles_of_many_tokens_are_cut_only_where_the_parts_stay_long():
+    # one decoded token at 4095 beside a 512-token portion behind 1024 tokens: the single token is cut,
+    # the portion's tiles (1088 .. 1536 keys) are not; the same portion behind 15 000 tokens is
+    segs = [(0, 1, 4095), (1, 512, 1024)]
+    work, red, parts = attention_plan.plan_attention(segs, 64, None, 8, 296)
+    _covers(work, segs, 64)
+    single, multi = work[work[:, 2] == 1], work[work[:, 2] > 1]
+    assert len(single) == 4 and (single[:, 6] >= 0).all()          # 296 // (9 x 8) = 4 parts
+    assert len(multi) == 8 and (multi[:, 6] == -1).all() and (multi[:, 7] == 0).all()
+    assert len(red) == 1 and parts == 4
+    segs = [(0, 1, 4095), (1, 512, 15000)]
+    work, red, parts = attention_plan.plan_attention(segs, 64, None, 8, 296)
+    _covers(work, segs, 64)
+    multi = work[work[:, 2] > 1]
+    assert len(multi) == 8 * 4 and (multi[:, 6] >= 0).all()
+    assert ((multi[:, 5] - multi[:, 4]) >= attention_plan.MULTI_MIN_SPLIT_KEYS).all()
+    assert len(red) == 1 + 512
+    lim = attention_plan.plan_limits(513, 64, 296, 8, 2)
+    assert len(work) <= lim[0] and len(red) <= lim[1] and parts <= lim[2]
