@@ -248,6 +248,17 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kv_token_kernel(
     }
 }
 
+// From how many tokens on a warp takes a whole token (a setter for tuning runs).  Measured back to back,
+// 16 + 2 x 8 heads of 128: 512 tokens 5.0 us a warp an item pair against 8.4 a warp a token, 1024: 7.5 / 11.5,
+// 2048: 12.2 / 12.8, 4096: 21.9 / 19.8; inside the 2048-token step the warp a token is the faster one
+// (3.455 against 3.504 ms for the step).
+static int g_qk_token_threshold = 1536;
+PLLM_EXPORT int pllm_qk_set_token_threshold(int n) {
+    const int was = g_qk_token_threshold;
+    g_qk_token_threshold = n;
+    return was;
+}
+
 template <typename T, int LPH>
 static void launch_qk_vec(const void* qkv, void* q_out, const float* q_gain, const float* k_gain, float eps,
                           const float* cos_t, const float* sin_t, int max_pos, const int* positions, const int* slots,
@@ -255,7 +266,7 @@ static void launch_qk_vec(const void* qkv, void* q_out, const float* q_gain, con
                           int swizzle, int* status, cudaStream_t stream) {
     const long long items = (long long)n_tokens * (nh + 2 * nkv);
     const int per_block = 4 * (32 / LPH);
-    if (n_tokens >= 256) {
+    if (n_tokens >= g_qk_token_threshold) {
         // enough tokens to fill the GPU with a warp each
         launch_chained(qk_norm_rope_kv_token_kernel<T, LPH>, dim3((unsigned)((n_tokens + 3) / 4)), dim3(128), 0, stream,
                        (const T*)qkv, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, max_pos, positions, slots, (T*)k_pool,

@@ -96,7 +96,7 @@ def rope_ref(x, pos, theta, rotary_dim):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd,rot,page", [(6, 3, 48, 48, 8), (8, 1, 32, 16, 16), (16, 8, 128, 128, 64), (4, 4, 80, 80, 16),
                                                 (4, 2, 64, 64, 16), (3, 1, 256, 256, 8), (5, 5, 32, 32, 16)])
-@pytest.mark.parametrize("T", [21, 301])     # few tokens: a lane a chunk; many: a warp a token
+@pytest.mark.parametrize("T", [21, 301, 1601])     # a lane a chunk of a head (two kernels); very many: a warp a token
 def test_qk_norm_rope_kv_write(dtype, nh, nkv, hd, rot, page, T):
     from paged_llm_rs_b200.parts.base import Runtime
     from paged_llm_rs_b200.parts.position import RotaryEncoding
