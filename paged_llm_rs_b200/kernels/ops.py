@@ -273,6 +273,21 @@ def attention_tile_tokens(num_heads: int, num_kv_heads: int, dtype: torch.dtype 
     return lib().pllm_attention_generic_tile_tokens(num_heads, num_kv_heads)
 
 
+# PAGED_LLM_MIXED_BESIDE=0: in a step of decoded tokens beside prompt portions the tcgen05 kernel takes the
+# single tokens too (one launch) instead of the bulk-copy kernel running beside it on a second stream.
+MIXED_BESIDE = os.environ.get("PAGED_LLM_MIXED_BESIDE", "1") != "0"
+MIXED_BESIDE_MIN_REQUESTS = 9       # rows of the step's block tables (a captured step's capacity)
+MIXED_BESIDE_CALLS = 0              # how often that route was taken (for tests)
+_SIDE_STREAMS = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    key = torch.device(device).index or 0
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+    return _SIDE_STREAMS[key]
+
+
 def _many_splits(tokens: int, num_heads: int, num_kv_heads: int) -> int:
     """Whether a step of this many tokens is cut into eight splits or more a tile (the planner's
     arithmetic for single tokens: target CTAs over tiles x CTAs an item)."""
@@ -323,14 +338,35 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         # portions of several tokens go to the tcgen05 kernel where the layout allows it
         multi_tc = bool(kinds & 2) and swizzled and attention_prefill_uses_tcgen05(q.dtype, num_heads, num_kv_heads, head_dim,
                                                                                    page_size, int(window))
+        # (worth the two edges without programmatic launch from some eight requests on: 0.6B shape, a layer of a
+        # step of 1 / 8 / 64 decoded tokens at 4096 beside a portion: +9 / -3 / -10 us)
+        beside = bool(MIXED_BESIDE and multi_tc and kinds == 3 and tma_ok and (TMA_KINDS & 1) and cluster <= 1
+                      and block_tables.shape[0] >= MIXED_BESIDE_MIN_REQUESTS)
+        if beside:
+            # A step of decoded tokens beside prompt portions: the single tokens go to the bulk-copy kernel and
+            # the portions to the tcgen05 kernel, on two streams that meet again before the reduction.  Neither
+            # kernel reads what the other writes, a CTA of one does not fit an SM beside a CTA of the other, and
+            # the single tokens' long key ranges no longer queue behind tiles of 128 rows with two of them live.
+            global MIXED_BESIDE_CALLS
+            MIXED_BESIDE_CALLS += 1
+            main, side = torch.cuda.current_stream(), _side_stream(q.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                _check(L.pllm_attention_decode_tma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
+                                                   _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml),
+                                                   num_heads, num_kv_heads, head_dim, page_size, n_pages,
+                                                   block_tables.shape[-1], float(scale), 1, None, 0, _ptr(status),
+                                                   _stream()), "paged_attention (bulk copy, beside)")
         if multi_tc:
             _check(L.pllm_attention_prefill_tcgen05(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
                                                     _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml),
                                                     q.shape[0], num_heads, num_kv_heads, head_dim, page_size, n_pages,
-                                                    block_tables.shape[-1], float(scale), 1 if kinds == 3 else 0,
+                                                    block_tables.shape[-1], float(scale), 1 if (kinds == 3 and not beside) else 0,
                                                     _ptr(status), _stream()),
                    "paged_attention (tcgen05)")
-            # beside portions it takes the single decoded tokens too: one launch a layer, not two
+            if beside:
+                torch.cuda.current_stream().wait_stream(_side_stream(q.device))
+            # (else) beside portions it takes the single decoded tokens too: one launch a layer, not two
             kinds = 0 if kinds == 3 else kinds & ~2
         take = (kinds & TMA_KINDS) if tma_ok else 0
         rest = kinds & ~take

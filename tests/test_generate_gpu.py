@@ -90,6 +90,27 @@ def test_greedy_tiny_d_tensor_core_kernels(tmp_path, dtype):
     assert plain.generate(prompts, max_tokens=24) == outs          # captured and plain launches agree
 
 
+def test_greedy_many_requests_decoding_beside_prompt_portions(tmp_path):
+    # twelve requests under a token budget: from the ninth on, the decoded tokens of a mixed step run on the
+    # bulk-copy kernel beside the tcgen05 kernel that takes the portion (two streams that meet again)
+    from paged_llm_rs_b200 import Engine
+    from paged_llm_rs_b200.kernels import ops
+    cfg, seed = CONFIGS["D"]
+    model = write_model(tmp_path, "D")
+    prompts = prompts_for(cfg["vocab_size"], [70, 66, 90, 64, 130, 75, 68, 81, 99, 64, 72, 110], 23)
+    assert ops.MIXED_BESIDE
+    outs = {}
+    for graphs in (True, False):
+        eng = Engine(model, dtype="bfloat16", block_size=16, blocks=160, chunk=96, max_batch=16)
+        eng.runner.use_graphs = graphs
+        calls = ops.MIXED_BESIDE_CALLS
+        outs[graphs] = eng.generate(prompts, max_tokens=40)
+        check_greedy(model, prompts, outs[graphs], 40, "bfloat16")
+        assert eng.metrics()["mixed_steps"] >= 10
+        assert ops.MIXED_BESIDE_CALLS > calls          # (captured: once a layer at capture; plain: every such step)
+    assert outs[True] == outs[False]
+
+
 def test_greedy_with_splits_combined_in_clusters(tmp_path):
     # the option that combines a decoded token's splits inside a thread-block cluster, through the engine:
     # the packer cuts every token into whole clusters, the captured step launches them, no reduction runs

@@ -397,17 +397,21 @@ def _check_fused_combine(cases, bases, counters, nh, nkv, hd, page):
 
 @pytest.mark.parametrize("nh,nkv,hd,page", [(16, 8, 128, 16), (8, 1, 64, 8), (4, 4, 128, 64), (6, 3, 64, 32), (40, 2, 64, 16),
                                             (5, 1, 128, 16)])
-def test_prompt_portions_take_the_tcgen05_kernel(nh, nkv, hd, page):
+def test_prompt_portions_take_the_tcgen05_kernel(monkeypatch, nh, nkv, hd, page):
     # portions of many tokens, with and without context before them, ending on and off the edges of
     # the 64-key tiles and of the 128-row items; beside single decoded tokens (which it then takes too)
     assert ops.attention_prefill_uses_tcgen05(torch.bfloat16, nh, nkv, hd, page, 0)
     reqs = [(0, 300), (1000, 200), (37, 129), (63, 2), (500, 1), (0, 64), (64, 65), (0, 1)]
-    launches = ops.LAUNCHES
-    for target in (1, 10 ** 6):
-        res, _ = run_attention(torch.bfloat16, reqs, nh, nkv, hd, page, None, target)
-        for got, want in res:
-            torch.testing.assert_close(got, want, **tol(torch.bfloat16))
-    assert ops.LAUNCHES - launches == 4        # tcgen05 (the single tokens too) + reduction, twice
+    # the single tokens beside the portions: on the bulk-copy kernel on a second stream, or in the tcgen05 kernel too
+    for beside, expect in ((True, 6), (False, 4)):
+        monkeypatch.setattr(ops, "MIXED_BESIDE", beside)
+        monkeypatch.setattr(ops, "MIXED_BESIDE_MIN_REQUESTS", 1)
+        launches = ops.LAUNCHES
+        for target in (1, 10 ** 6):
+            res, _ = run_attention(torch.bfloat16, reqs, nh, nkv, hd, page, None, target)
+            for got, want in res:
+                torch.testing.assert_close(got, want, **tol(torch.bfloat16))
+        assert ops.LAUNCHES - launches == expect     # (bulk copy +) tcgen05 + reduction, twice
     # one key far back decides the row: its score stands out, and its value is unlike the others
     def craft(r, q, k, v):
         if r == 0:
