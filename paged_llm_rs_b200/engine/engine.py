@@ -22,13 +22,14 @@ from ..kernels import ops
 from ..sampling.sampler import SamplingParams, sample_host
 from .runner import ModelRunner
 from .scheduler import Finish, Outcome, Plan, Scheduler, Sequence
+from .step import StepEntry
 
 
 class Engine:
     def __init__(self, model: str, dtype="bfloat16", block_size: int = 16, cache_mib: int = 3584,
                  blocks: Optional[int] = None, max_batch: int = 16, chunk: Optional[int] = 128,
                  prefix_cache: bool = True, device: str = "cuda:0", max_requests: Optional[int] = None,
-                 max_prefill_seqs: int = 1):
+                 max_prefill_seqs: int = 1, lookahead: bool = True):
         if chunk is not None and chunk < 1:
             raise ConfigError("chunk 0 would carry nothing")
         self.runner = ModelRunner(model, dtype=dtype, page_size=block_size, num_pages=blocks,
@@ -42,6 +43,11 @@ class Engine:
         self._seqs: Dict[int, Sequence] = {}
         self._finish: Dict[int, Finish] = {}
         self.bytes_d2h = 0  # bytes the last step copied back to the host
+        # While a decode step runs on the GPU the host gets the next one ready (pages, positions, tables,
+        # attention work: everything but the token ids), so that between two steps the GPU waits only for
+        # the tokens to be read, checked for an ending, written into the buffer, and the replay.
+        self.lookahead = bool(lookahead)
+        self._inflight = None   # (plan, what _launch returned) of a step that runs and is not yet committed
 
     # -- requests ------------------------------------------------------------------------
     def submit(self, prompt: Seq[int], max_tokens: int = 512, temperature: float = 0.0,
@@ -65,24 +71,34 @@ class Engine:
 
     # -- one step ------------------------------------------------------------------------
     def step(self) -> Optional[Outcome]:
-        """Plan, run, sample and commit one step.  None when there is nothing to do."""
-        plan = self.scheduler.plan()
-        if plan.kind == "idle":
-            return None
-        if plan.kind in ("refused", "outgrown"):
-            out = self.scheduler.commit(plan, [])
-        else:
-            tokens = self._run(plan)
-            out = self.scheduler.commit(plan, tokens)
+        """Plan, run, sample and commit one step.  None when there is nothing to do.  On return the
+        step after it may already be running (a decode step that follows a decode step with the same
+        requests): its tokens come with the next call."""
+        if self._inflight is None:
+            plan = self.scheduler.plan()
+            if plan.kind == "idle":
+                return None
+            if plan.kind in ("refused", "outgrown"):
+                return self._note(self.scheduler.commit(plan, []))
+            self._inflight = (plan, self._launch(plan))
+        plan, ctx = self._inflight
+        ahead = self._prepare_next(plan, ctx)          # host work beside the GPU
+        tokens = self._collect(plan, ctx)              # waits for the step
+        self._inflight = None
+        if ahead is not None:
+            seqs, graph = ahead
+            if not self.scheduler.waiting and not any(self.scheduler.ends_with(s, t) for s, t in zip(seqs, tokens)):
+                self._inflight = self._launch_prepared(seqs, graph, tokens)
+        return self._note(self.scheduler.commit(plan, tokens))
+
+    def _note(self, out: Outcome) -> Outcome:
         for rid, why in out.finished:
             self._finish[rid] = why
         return out
 
-    def _run(self, plan: Plan) -> List[int]:
-        """The step and the choice of tokens: one packed copy to the device, the
-        model, the sampling kernel, one copy of status word and tokens back.  Rows
-        of requests with top-k or top-p are copied back as logits and drawn on the host."""
-        seqs = [self._seqs[rid] for rid in plan.ids]
+    def _sampling_rows(self, seqs):
+        """Temperatures for the sampling kernel, a uniform number for every row that draws (greedy rows
+        leave their generator alone, sampler.rs:119-121), and the rows drawn on the host instead."""
         n = len(seqs)
         temp = np.zeros(n, dtype=np.float32)
         uni = np.zeros(n, dtype=np.float32)
@@ -93,12 +109,23 @@ class Engine:
                 host_rows.append(i)
             elif not p.is_greedy:
                 temp[i] = p.temperature
-                uni[i] = s.rng.next_f32()   # greedy rows leave their generator alone (sampler.rs:119-121)
+                uni[i] = s.rng.next_f32()
+        return temp, uni, host_rows
+
+    def _launch(self, plan: Plan):
+        """One packed copy to the device, the model, the sampling kernel; nothing is waited for."""
+        seqs = [self._seqs[rid] for rid in plan.ids]
+        temp, uni, host_rows = self._sampling_rows(seqs)
         logits, tokens_dev = self.runner.step_and_sample(plan.entries, temp, uni)
+        return seqs, logits, tokens_dev, self.runner.tokens_host, host_rows
+
+    def _collect(self, plan: Plan, ctx) -> List[int]:
+        """The step's status word and tokens, one copy back.  Rows of requests with top-k or top-p are
+        copied back as logits and drawn on the host."""
+        seqs, logits, tokens_dev, back, host_rows = ctx
         if tokens_dev is None:
             self.bytes_d2h = 0
             return []
-        back = self.runner.tokens_host
         if back is not None:     # a captured step copies them to pinned memory itself
             torch.cuda.current_stream().synchronize()
         else:
@@ -113,6 +140,29 @@ class Engine:
             for r, i in zip(rows, host_rows):
                 tokens[i] = sample_host(r, seqs[i].sampling, seqs[i].rng)
         return tokens
+
+    def _prepare_next(self, plan: Plan, ctx):
+        """While ``plan`` runs: if the step after it will be the same requests decoding again, reserve
+        their pages and pack that step (all but the token ids).  Returns (requests, captured step) or None."""
+        if not self.lookahead or plan.kind != "decode" or ctx[4] or ctx[2] is None:
+            return None
+        seqs = self.scheduler.continuation(plan)
+        if seqs is None or any(not s.sampling.on_device for s in seqs):
+            return None
+        temp = np.asarray([0.0 if s.sampling.is_greedy else s.sampling.temperature for s in seqs], dtype=np.float32)
+        graph = self.runner.prepack_decode([StepEntry(s.id, [0], [0]) for s in seqs], temp)
+        return None if graph is None else (seqs, graph)
+
+    def _launch_prepared(self, seqs, graph, tokens: List[int]):
+        """The step ``_prepare_next`` packed, now that the tokens it starts from are known."""
+        uni = None       # (all rows greedy: nothing to draw, the buffer holds zeros)
+        if any(not s.sampling.is_greedy for s in seqs):
+            _, uni, _ = self._sampling_rows(seqs)
+        logits, tokens_dev = graph.launch_prepacked(tokens, uni)
+        self.scheduler.count_decode_step(len(seqs))
+        plan = Plan("decode", [s.id for s in seqs], [(s.id, 1) for s in seqs],
+                    [StepEntry(s.id, [t], [0]) for s, t in zip(seqs, tokens)])
+        return plan, (seqs, logits, tokens_dev, self.runner.tokens_host, [])
 
     # -- whole generations -----------------------------------------------------------------
     def run_until_done(self) -> None:

@@ -70,6 +70,7 @@ class _DecodeGraph:
         self.tokens = torch.zeros(1 + n_seg, dtype=torch.int32, device=runner.device)
         # the status word and the chosen tokens come back by a copy that is part of the captured step
         self.tokens_host = torch.zeros(1 + n_seg, dtype=torch.int32).pin_memory()
+        self.staging = None     # host buffer of a step packed ahead of time (prepack)
         # Warm up on a side stream (library handles, workspaces), then capture.
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -103,6 +104,32 @@ class _DecodeGraph:
         ops.sample(self.logits, self.state.temperature, self.state.uniform, self.tokens[1:])
         self.tokens[:1].copy_(r.rt.status)
         self.tokens_host.copy_(self.tokens, non_blocking=True)
+
+    # -- a decode step packed ahead of time (while the step before it runs) ---------------------------
+    def prepack(self, entries, temperature) -> None:
+        """Fill a host buffer of the step's layout for requests that each stand one token further than
+        their committed count; token ids and the sampling's uniform numbers come at launch."""
+        if self.staging is None:
+            self.pinned_np = self.pinned.numpy()
+            self.staging = np.zeros_like(self.pinned_np)
+        self.native.pack(entries, temperature, np.zeros(len(entries), dtype=np.float32) if temperature is not None else None,
+                         ahead=1, out=self.staging)
+
+    def launch_prepacked(self, tokens, uniform):
+        """Put the token ids (and uniform numbers) into the buffer ``prepack`` filled, and replay."""
+        r = self.runner
+        n = len(tokens)
+        o = self.layout["tokens"][0]
+        self.staging[o:o + n] = tokens
+        if uniform is not None:
+            o = self.layout["uniform"][0]
+            self.staging[o:o + n] = np.asarray(uniform, dtype=np.float32).view(np.int32)
+        np.copyto(self.pinned_np, self.staging)
+        self.graph.replay()
+        r.bytes_h2d = self.nbytes
+        r.last_launches = self.launches
+        r.tokens_host = self.tokens_host[:1 + n]
+        return self.logits[:n], self.tokens[:1 + n]
 
     def run(self, entries, temperature, uniform):
         r = self.runner
@@ -225,6 +252,19 @@ class ModelRunner:
         if check:
             self.check_status()
         return logits, tokens
+
+    def prepack_decode(self, entries: Sequence[StepEntry], temperature):
+        """Get the next decode step ready on the host while the current one runs: the captured step for
+        these requests, its buffer filled for positions one further than committed (pages reserved by the
+        caller).  Returns the step to ``launch_prepacked`` once the token ids are known, or None when such
+        steps are not captured."""
+        if not self.use_graphs or temperature is None:
+            return None
+        g = self._decode_graph(entries)
+        if g is None or g.native is None:
+            return None
+        g.prepack(entries, temperature)
+        return g
 
     # -- decode steps as CUDA graphs ------------------------------------------------------
     def _decode_graph(self, entries):

@@ -301,6 +301,34 @@ class Scheduler:
         return Plan("decode", [s.id for s in seqs], [(s.id, 1) for s in seqs],
                     [StepEntry(s.id, [s.pending[0]], [0]) for s in seqs])
 
+    # -- the decode step after a decode step, planned before that one is committed ----------------------
+    def continuation(self, plan: Plan) -> Optional[List[Sequence]]:
+        """While the decode step ``plan`` runs: the requests of the decode step after it, if that step
+        is sure to be the same rows again provided none of them ends (nobody waits, no prompt is in
+        flight, the step holds every running request), with the pages for one more token each reserved.
+        None: plan the next step the ordinary way, after this one is committed."""
+        if plan.kind != "decode" or self.waiting or len(self.running) != len(plan.ids) or len(plan.ids) > self.max_batch:
+            return None
+        for s, rid in zip(self.running, plan.ids):
+            if s.id != rid or s.finish is not None or s.prompt_left > 0 or len(s.pending) != 1:
+                return None
+        for s in self.running:
+            # (the step in flight is not committed: its token and the next one's both need their page)
+            if self.cache.blocks_needed(s.id, 2) > 0 and not self.cache.reserve(s.id, 2):
+                return None     # a dry pool: preemption is the ordinary plan's business
+        return list(self.running)
+
+    def ends_with(self, s: Sequence, token: int) -> bool:
+        """Whether ``commit`` will end request ``s`` when its step brings ``token``."""
+        return (s.finish is not None or token in s.stop_tokens or s.generated + 1 >= s.max_tokens
+                or (self.max_positions is not None and len(s.history) + 1 >= self.max_positions))
+
+    def count_decode_step(self, rows: int) -> None:
+        """The counters of a decode step that was not planned by ``plan`` (see ``continuation``)."""
+        self.metrics.steps += 1
+        self.metrics.decode_steps += 1
+        self.metrics.decode_rows += rows
+
     def _newest_evictable(self, protect: int) -> Optional[int]:
         for i in range(len(self.running) - 1, -1, -1):
             if i != protect and self.running[i].finish is None:

@@ -320,16 +320,22 @@ class NativeDecodePacker:
                       layout["temperature"][0], layout["uniform"][0], n_groups)
         self.out_ptr = out.ctypes.data
 
-    def pack(self, entries: Sequence[StepEntry], temperature, uniform) -> None:
+    def pack(self, entries: Sequence[StepEntry], temperature, uniform, ahead: int = 0,
+             out: Optional[np.ndarray] = None) -> None:
+        """``ahead``: the step is packed while the one before it still runs and is not yet committed: every
+        request stands ``ahead`` tokens further than its committed count says (its pages are reserved).
+        ``out``: a buffer of the pinned one's size to fill instead of it."""
         cache = self.packer.cache
         n = len(entries)
         if n > self.caps.tokens:
             raise ConfigError("the step does not fit the capacities it was given")
+        if out is not None and (out.dtype != np.int32 or len(out) != len(self.out) or not out.flags.c_contiguous):
+            raise ConfigError("the buffer to pack into does not match the step's")
         tables = []
         for i, e in enumerate(entries):
             rc = cache.get(e.request_id)
             self.tokens[i] = int(e.tokens[0])
-            self.positions[i] = rc.tokens
+            self.positions[i] = rc.tokens + ahead
             self.state_slots[i] = rc.state_slot
             tables.append(rc.tables)
         for gi in range(self.n_groups):
@@ -340,7 +346,8 @@ class NativeDecodePacker:
         if have:
             self.temperature[:n] = [float(t) for t in temperature]
             self.uniform[:n] = [float(u) for u in uniform]
-        code = self.fn(self.out_ptr, len(self.out), n, self.tokens, self.positions, self.state_slots,
+        code = self.fn(self.out_ptr if out is None else out.ctypes.data, len(self.out), n, self.tokens, self.positions,
+                       self.state_slots,
                        self.temperature if have else None, self.uniform if have else None, *self.fixed,
                        self.groups, ctypes.byref(self.err))
         if code != 0:

@@ -271,3 +271,54 @@ def test_window_model_runs_a_long_prompt_through_few_pages():
             break
         produced += step(s)[1].tokens
     assert len(produced) == 5 and cache.available() == 6
+
+
+def test_the_decode_step_after_a_decode_step_is_known_before_that_one_is_committed():
+    # what the engine asks while a decode step runs: the same requests again, pages for one more token
+    # each reserved; not when someone waits, a prompt is in flight, a request has ended or the pool is dry
+    s, cache = make(pages=16, page_size=4, chunk=8)
+    for i, n in enumerate((3, 4)):
+        s.submit(seq(i, n, max_tokens=6, start=10 * i))
+    while s.waiting or any(q.prompt_left for q in s.running):
+        step(s)
+    plan = s.plan()
+    assert plan.kind == "decode" and plan.ids == [0, 1]
+    before = cache.groups[0].allocator.in_use()
+    seqs = s.continuation(plan)                      # request 1 stands at 4 committed: tokens 5 and 6 need page 2
+    assert [q.id for q in seqs] == [0, 1]
+    assert all(cache.blocks_needed(q.id, 2) == 0 for q in seqs) and cache.groups[0].allocator.in_use() >= before
+    cache.check_invariants()
+    assert not s.ends_with(seqs[0], 9) and s.ends_with(seqs[0], 9) is False
+    stopper = Sequence(7, [1, 2], GREEDY, 5, [9])
+    assert s.ends_with(stopper, 9) and not s.ends_with(stopper, 8)
+    stopper.generated = 4
+    assert s.ends_with(stopper, 8)                   # the budget's last token
+    steps, rows = s.metrics.steps, s.metrics.decode_rows
+    s.count_decode_step(2)
+    assert (s.metrics.steps, s.metrics.decode_rows) == (steps + 1, rows + 2)
+    s.commit(plan, [9, 9])
+    cache.check_invariants()
+    # someone waits: the next step is a mixed one
+    plan = s.plan()
+    s.submit(seq(5, 3))
+    assert s.continuation(plan) is None
+    s.commit(plan, [9, 9])
+    # a prompt in flight
+    plan = s.plan()
+    assert plan.kind == "mixed" and s.continuation(plan) is None
+    s.commit(plan, [9, 9, 9])
+
+
+def test_no_continuation_from_a_dry_pool():
+    s, cache = make(pages=2, page_size=4)
+    s.submit(seq(0, 4, max_tokens=20))
+    step(s)                                           # the prompt fills page 0
+    plan = s.plan()                                   # the first decode takes page 1: positions 4 .. 7
+    assert plan.kind == "decode" and s.continuation(plan) is not None
+    s.commit(plan, [9])
+    for _ in range(2):
+        step(s)                                       # 7 tokens committed
+    plan = s.plan()                                   # position 7: fits; the one after it needs a third page
+    assert plan.kind == "decode" and s.continuation(plan) is None
+    s.commit(plan, [9])
+    cache.check_invariants()
