@@ -41,7 +41,12 @@ struct AttnWork { int seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slo
 
 namespace {
 
-constexpr int P_ROWS = 128, P_BK = 64, P_STAGES = 4, P_THREADS = 384;   // P_STAGES: key tiles, and as many value tiles, in flight
+// Key tiles (and as many value tiles) in flight.  The kernel's time does not follow it (8192 tokens: 360.8,
+// 358.0, 357.8 us with 2, 3, 4): the loads are not what bounds it.
+#ifndef PLLM_ATT_STAGES
+#define PLLM_ATT_STAGES 4
+#endif
+constexpr int P_ROWS = 128, P_BK = 64, P_STAGES = PLLM_ATT_STAGES, P_THREADS = 384;   // P_STAGES: key tiles, and as many value tiles, in flight
 constexpr int P_PLANE = P_BK * 128;            // 64 keys x 128 bytes
 constexpr float P_RESCALE = 8.0f;              // log2 units the running maximum may lag behind
 
