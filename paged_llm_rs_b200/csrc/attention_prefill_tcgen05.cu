@@ -46,7 +46,17 @@ namespace {
 #ifndef PLLM_ATT_STAGES
 #define PLLM_ATT_STAGES 4
 #endif
-constexpr int P_ROWS = 128, P_BK = 64, P_STAGES = PLLM_ATT_STAGES, P_THREADS = 384;   // P_STAGES: key tiles, and as many value tiles, in flight
+// Softmax groups (2 or 3) that take the key tiles in turn: four warps each, beside the four warps of producers and issuers.
+#ifndef PLLM_ATT_GROUPS
+#define PLLM_ATT_GROUPS 2
+#endif
+// P handed to the tensor cores in tensor memory (1) or in shared memory (0)
+#ifndef PLLM_ATT_P_TMEM
+#define PLLM_ATT_P_TMEM 1
+#endif
+constexpr int P_G = PLLM_ATT_GROUPS;
+constexpr int P_ROWS = 128, P_BK = 64, P_STAGES = PLLM_ATT_STAGES, P_THREADS = (4 * P_G + 4) * 32;
+constexpr int W_KEYS = 4 * P_G, W_SCORES = 4 * P_G + 1, W_VALUES = 4 * P_G + 2, W_SUMS = 4 * P_G + 3;   // the other four warps   // P_STAGES: key tiles, and as many value tiles, in flight
 constexpr int P_PLANE = P_BK * 128;            // 64 keys x 128 bytes
 constexpr float P_RESCALE = 8.0f;              // log2 units the running maximum may lag behind
 
@@ -67,7 +77,9 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     int tile_tokens, int take_single, int* status) {
     constexpr int NHALF = HD / 64;
     constexpr int Q_BYTES = NHALF * P_ROWS * 128, STAGE = NHALF * P_PLANE, P_BYTES = P_ROWS * 128;   // STAGE: a key (or value) tile
-    constexpr uint32_t TMEM_COLS = 256, S_COL = 0, O_COL = 128;
+    constexpr uint32_t S_COL = 0, O_COL = P_G * P_BK, P_COL = O_COL + HD;     // P: 32 columns a group (64 keys, two to a column)
+    constexpr uint32_t TMEM_USED = P_COL + (PLLM_ATT_P_TMEM ? P_G * 32 : 0), TMEM_COLS = TMEM_USED <= 256 ? 256 : 512;
+    constexpr int P_SMEM = PLLM_ATT_P_TMEM ? 0 : P_G * P_ROWS * 128;          // the P buffers in shared memory, if any
     if ((int)blockIdx.y >= *n_work_ptr) return;
     const AttnWork w = work[blockIdx.y];
     // single decoded tokens are another kernel's, unless this one is told to take them too (a step of
@@ -89,17 +101,17 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t q_s = smem_u32(smem);
     const uint32_t k_ring = q_s + Q_BYTES, v_ring = k_ring + P_STAGES * STAGE;
-    const uint32_t p_s = v_ring + P_STAGES * STAGE;            // two P buffers
+    const uint32_t p_s = v_ring + P_STAGES * STAGE;            // a P buffer a group
     constexpr int RINGS = 2 * P_STAGES * STAGE;
-    float* mstate = reinterpret_cast<float*>(smem + Q_BYTES + RINGS + 2 * P_BYTES);   // [128] a row's maximum in use
-    float* lpart = mstate + P_ROWS;                                                               // [2][128] the groups' sums
-    unsigned char* ctl = smem + Q_BYTES + RINGS + 2 * P_BYTES + 3 * P_ROWS * 4;
+    float* mstate = reinterpret_cast<float*>(smem + Q_BYTES + RINGS + P_SMEM);          // [128] a row's maximum in use
+    float* lpart = mstate + P_ROWS;                                                                 // [groups][128] the groups' sums
+    unsigned char* ctl = smem + Q_BYTES + RINGS + P_SMEM + (1 + P_G) * P_ROWS * 4;
     const uint32_t bars = smem_u32(ctl);
     const uint32_t q_full = bars, k_full = bars + 8, k_empty = k_full + 8 * P_STAGES, v_full = k_empty + 8 * P_STAGES,
                    v_empty = v_full + 8 * P_STAGES, s_full = v_empty + 8 * P_STAGES,
-                   p_full = s_full + 16, p_empty = p_full + 16, o_full = p_empty + 16, m_ready = o_full + 8,   // m_ready[2][4]
-                   s_free = m_ready + 64;
-    constexpr int N_BARS = 4 * P_STAGES + 1 + 2 + 2 + 2 + 1 + 8 + 2;
+                   p_full = s_full + 8 * P_G, p_empty = p_full + 8 * P_G, o_full = p_empty + 8 * P_G, m_ready = o_full + 8,   // m_ready[groups][4]
+                   s_free = m_ready + 32 * P_G;
+    constexpr int N_BARS = 4 * P_STAGES + 1 + 3 * P_G + 1 + 4 * P_G + P_G;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctl + 8 * N_BARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(ctl + 8 * N_BARS + 8);
 
@@ -109,7 +121,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             mbar_init(k_full + 8 * s, 1); mbar_init(k_empty + 8 * s, 1);
             mbar_init(v_full + 8 * s, 1); mbar_init(v_empty + 8 * s, 1);
         }
-        for (int b = 0; b < 2; b++) {
+        for (int b = 0; b < P_G; b++) {
             mbar_init(s_full + 8 * b, 1);
             mbar_init(p_full + 8 * b, 4);        // one arrival from each warp of the group
             mbar_init(p_empty + 8 * b, 1);
@@ -121,7 +133,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
         fence_async_smem();
     }
-    if (warp == 9) {
+    if (warp == W_SCORES) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
@@ -130,11 +142,11 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 8 || warp == 10) {
+    if (warp == W_KEYS || warp == W_VALUES) {
         // ---- producers: warp 8 the queries and the key tiles, warp 10 the value tiles, each with a ring
         // of its own (a key tile's place comes free when its scores are formed, two tiles before its
         // values' does; with one ring for both the keys would be fetched only two tiles ahead) --------
-        const bool keys = warp == 8;
+        const bool keys = warp == W_KEYS;
         pdl_wait(KID_ATT_TC, keys && lane == 0);           // the queries and this step's cache rows come from the kernel before
         if (keys && lane == 0) {
             mbar_expect_tx(q_full, (uint32_t)(NHALF * 128 * heads_per_cta * tile_tokens));
@@ -184,8 +196,8 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 for (int h = 0; h < NHALF; h++) tma_load_2d(st_base + h * P_PLANE + lane * slab_bytes, map, h * 64, row, full + 8 * s);
             }
         }
-    } else if (warp == 9) {
-        // ---- tensor-core issue, the scores: S[t & 1] = Q K_t^T.  (Two issuing threads, this one and
+    } else if (warp == W_SCORES) {
+        // ---- tensor-core issue, the scores: S[t % groups] = Q K_t^T.  (Two issuing threads, this one and
         // warp 11's for O += P V: each tile costs an issuing thread a handful of waits, instructions
         // and commits one after the other, and that, not the tensor cores' time, bounds the kernel.)
         if (lane == 0) {
@@ -196,38 +208,47 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             bool ok = mbar_wait(q_full, 0, abort_flag);
             for (int t = 0; t < n_tiles && ok; t++) {
                 const int s = t % P_STAGES;
-                // the group must have read the scores of two tiles ago out of this buffer
-                if (t >= 2 && !mbar_wait(s_free + 8 * (t & 1), ((t - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
+                // the group must have read its scores of the turn before out of this buffer
+                const int g = t % P_G;
+                if (t >= P_G && !mbar_wait(s_free + 8 * g, ((t - P_G) / P_G) & 1, abort_flag)) { ok = false; break; }
                 if (!mbar_wait(k_full + 8 * s, (t / P_STAGES) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint64_t kd = k_desc + (uint64_t)((s * STAGE) >> 4);
-                const uint32_t d = tmem + S_COL + (t & 1) * P_BK;
+                const uint32_t d = tmem + S_COL + g * P_BK;
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++)
                     mma_ss(d, q_desc + (uint64_t)(((ks / 4) * P_ROWS * 128 + (ks % 4) * 32) >> 4),
                            kd + (uint64_t)(((ks / 4) * P_PLANE + (ks % 4) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
                 mma_commit(k_empty + 8 * s);         // the key tile's place is free once these have read it
-                mma_commit(s_full + 8 * (t & 1));
+                mma_commit(s_full + 8 * g);
             }
         }
-    } else if (warp == 11) {
+    } else if (warp == W_SUMS) {
         // ---- tensor-core issue, the sums: O += P_t V_t --------------------------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc_pv = instr_desc(P_ROWS, HD, 1);
             const uint64_t p_desc = smem_desc(p_s), v_desc = smem_desc(v_ring, P_PLANE);
             bool ok = true;
             for (int t = 0; t < n_tiles && ok; t++) {
-                if (!mbar_wait(p_full + 8 * (t & 1), (t >> 1) & 1, abort_flag)) { ok = false; break; }
+                const int g = t % P_G;
+                if (!mbar_wait(p_full + 8 * g, (t / P_G) & 1, abort_flag)) { ok = false; break; }
                 if (!mbar_wait(v_full + 8 * (t % P_STAGES), (t / P_STAGES) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint64_t vd = v_desc + (uint64_t)(((t % P_STAGES) * STAGE) >> 4);
-                const uint64_t pd = p_desc + (uint64_t)(((t & 1) * P_BYTES) >> 4);
+                const uint64_t pd = p_desc + (uint64_t)((g * P_BYTES) >> 4);
 #pragma unroll
-                for (int ks = 0; ks < P_BK / 16; ks++)     // 16 keys = 2048 bytes down the value planes
+                for (int ks = 0; ks < P_BK / 16; ks++) {   // 16 keys = 2048 bytes down the value planes
+#if PLLM_ATT_P_TMEM
+                    mma_ts(tmem + O_COL, tmem + P_COL + g * 32 + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv,
+                           (t | ks) ? 1u : 0u);
+#else
                     mma_ss(tmem + O_COL, pd + (uint64_t)((ks * 32) >> 4), vd + (uint64_t)((ks * 2048) >> 4), idesc_pv,
                            (t | ks) ? 1u : 0u);
+#endif
+                }
+                (void)pd;
                 mma_commit(v_empty + 8 * (t % P_STAGES));    // the values of this tile are read
-                mma_commit(p_empty + 8 * (t & 1));           // and so is this group's P (and O holds the tile)
+                mma_commit(p_empty + 8 * g);                 // and so is this group's P (and O holds the tile)
             }
             if (ok) mma_commit(o_full);
         }
@@ -245,9 +266,10 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
         // this group's part of the row's sum, in units of 2^m_ref
         float m_ref = -CUDART_INF_F, l_run = 0.f;
         bool ok = true;
-        for (int t = grp; t < n_tiles; t += 2) {
+        const int grp_before = (grp + P_G - 1) % P_G;      // the group of the tile before this group's
+        for (int t = grp; t < n_tiles; t += P_G) {
             const int kv0 = w.kv_begin + t * P_BK;
-            if (!mbar_wait(s_full + 8 * grp, (t >> 1) & 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(s_full + 8 * grp, (t / P_G) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             uint32_t v0[32], v1[32];
             tmem_ld32(lane_base + S_COL + grp * P_BK, v0);
@@ -255,7 +277,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             tmem_wait_ld();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(s_free + 8 * grp);        // the buffer may take the scores of two tiles on
+            if (lane == 0) mbar_arrive(s_free + 8 * grp);        // the buffer may take the scores of this group's next tile
             // keys of this tile at or past vis are hidden from this row (only tiles on the diagonal have any)
             const int vis = hi - kv0;
             if (vis < P_BK) {
@@ -276,7 +298,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             // the maximum in use after the tile before this one, which the other group decided
             float m_prev = -CUDART_INF_F;
             if (t > 0) {
-                if (!mbar_wait(m_ready + 8 * (4 * (grp ^ 1) + wq), ((t - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(m_ready + 8 * (4 * grp_before + wq), ((t - 1) / P_G) & 1, abort_flag)) { ok = false; break; }
                 m_prev = mstate[row];
             }
             // it moves only when it grew by more than 2^8 (or is not set yet)
@@ -288,7 +310,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             if (t > 0 && __any_sync(0xffffffffu, grow)) {
                 // O is rescaled once the tile before this one is in it (this tile's is not issued before
                 // this group says so, nor the next one's before this tile's)
-                if (!mbar_wait(p_empty + 8 * (grp ^ 1), ((t - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(p_empty + 8 * grp_before, ((t - 1) / P_G) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const float alpha = (grow && m_prev > -CUDART_INF_F) ? ex2(m_prev - m_used) : (grow ? 0.f : 1.f);
 #pragma unroll
@@ -321,32 +343,38 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 s4[i & 3] += p0 + p1;
             }
             l_run += (s4[0] + s4[1]) + (s4[2] + s4[3]);
-            // this group's P of two tiles ago must be read out of shared memory before it is overwritten
-            if (t >= 2 && !mbar_wait(p_empty + 8 * grp, ((t - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
+            // this group's P of its tile before must be read out of shared memory before it is overwritten
+            if (t >= P_G && !mbar_wait(p_empty + 8 * grp, ((t - P_G) / P_G) & 1, abort_flag)) { ok = false; break; }
+#if PLLM_ATT_P_TMEM
+            // the row's 64 weights, two to a column, into this thread's lane of the group's P columns
+            tmem_st32(lane_base + P_COL + grp * 32, pw);
+            tmem_wait_st();
+#else
             // the row's 128 bytes, chunk c at c ^ (row & 7)
             unsigned char* prow = smem + Q_BYTES + RINGS + grp * P_BYTES + row * 128;
 #pragma unroll
             for (int c = 0; c < 8; c++)
                 *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pw[4 * c], pw[4 * c + 1], pw[4 * c + 2], pw[4 * c + 3]);
             fence_async_smem();          // the tensor cores read shared memory through the async proxy
+#endif
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full + 8 * grp);
         }
         // ---- the groups' sums meet; each group stores half of the columns -------------------------------
         if (!ok || *abort_flag) *abort_flag = 1;
-        asm volatile("bar.sync 1, 256;\n" ::: "memory");          // (the eight softmax warps; the others are elsewhere)
+        asm volatile("bar.sync 1, %0;\n" ::"n"(P_G * 128) : "memory");          // (the softmax warps; the others are elsewhere)
         const float m_fin = mstate[row];                           // after the last tile (every row has one)
         lpart[grp * P_ROWS + row] = (m_ref > -CUDART_INF_F && m_fin > -CUDART_INF_F) ? l_run * ex2(m_ref - m_fin) : 0.f;
-        asm volatile("bar.sync 1, 256;\n" ::: "memory");
-        const float l_tot = lpart[row] + lpart[P_ROWS + row];
+        asm volatile("bar.sync 1, %0;\n" ::"n"(P_G * 128) : "memory");
+        float l_tot = lpart[row];
+#pragma unroll
+        for (int g = 1; g < P_G; g++) l_tot += lpart[g * P_ROWS + row];
         if (!*abort_flag && mbar_wait(o_full, 0, abort_flag)) {
             tc_fence_after();
             const float inv = l_tot > 0.f ? 1.0f / l_tot : 0.f;
-            constexpr int HALF_CHUNKS = HD / 64;                   // chunks of 32 columns a group
-#pragma unroll
-            for (int cc = 0; cc < HALF_CHUNKS; cc++) {
-                const int c = grp * HALF_CHUNKS + cc;
+            // chunks of 32 columns, dealt to the groups
+            for (int c = grp; c < HD / 32; c += P_G) {
                 uint32_t o[32];
                 tmem_ld32(lane_base + O_COL + c * 32, o);
                 tmem_wait_ld();
@@ -380,7 +408,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     // ---- everyone meets; the allocating warp gives the tensor memory back ---------------------------
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == W_SCORES) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS));
     }
@@ -423,8 +451,9 @@ static int launch_prefill(const void* q, const void* k_pool, const void* v_pool,
         if (tensor_map(v_pool, 2, dp, sp, bp, false, &map_v) != 0) return PLLM_ERR_SIZE;
     }
     constexpr int NHALF = HD / 64;
-    const size_t smem = (size_t)NHALF * P_ROWS * 128 + (size_t)P_STAGES * 2 * NHALF * P_PLANE + 2 * P_ROWS * 128 +
-                        3 * P_ROWS * 4 + 8 * (4 * P_STAGES + 18) + 16 + 1024;
+    const size_t smem = (size_t)NHALF * P_ROWS * 128 + (size_t)P_STAGES * 2 * NHALF * P_PLANE +
+                        (PLLM_ATT_P_TMEM ? 0 : P_G * P_ROWS * 128) +
+                        (1 + P_G) * P_ROWS * 4 + 8 * (4 * P_STAGES + 2 + 8 * P_G) + 16 + 1024;
     cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_chained(attention_prefill_tcgen05_kernel<HD>, dim3(nkv * gparts, max_work), dim3(P_THREADS), smem, stream, map_q,
                    map_k, map_v, block_tables, (const AttnWork*)work, n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv,
