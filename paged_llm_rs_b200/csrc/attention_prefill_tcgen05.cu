@@ -9,14 +9,17 @@
 //   S = Q K^T     tcgen05.mma, 128 x 64, Q and the key tile in shared memory, S in tensor memory
 //   P = softmax   four warps, ONE ROW A THREAD (a thread's lane of tensor memory is its row, so
 //                 the row's maximum and sum need no shuffles): tcgen05.ld, scale, mask, exp2,
-//                 P rounded to bfloat16 into shared memory in the tensor cores' layout
-//   O += P V      tcgen05.mma, 128 x head_dim, O stays in tensor memory for the whole item
+//                 P rounded to bfloat16 back into tensor memory (tcgen05.st, two weights a column)
+//   O += P V      tcgen05.mma with P as its tensor-memory operand and the value tile in shared
+//                 memory, 128 x head_dim; O stays in tensor memory for the whole item
 //
 // Twelve warps: 0-3 and 4-7 are two softmax groups that take the key tiles in turn (even tiles
 // the first, odd the second: a group's warp w owns rows 32 w .. 32 w + 31 like its twin in
 // the other group), 8 and 10 are the producers (TMA: queries and key tiles; value tiles), one lane
 // of warp 9 issues the tcgen05.mma of the scores, one of warp 11's those of the sums; warp 9 also
-// allocates the tensor memory.  S and P have two buffers each, one a group, so the tensor cores
+// allocates the tensor memory.  (A third group is a build option: it measured slower, 387.8 against
+// 357.8 us at 8192 tokens, within the 128 registers that sixteen warps leave each thread.)
+// S and P have two buffers each, one a group, so the tensor cores
 // form the next tiles' scores and sums while the groups work on theirs, and two warps share
 // each scheduler (the exponentials of one hide the waits of the other).  A row's running
 // maximum is only moved when it grew by more than 2^8 (then O is rescaled in tensor memory),
@@ -54,6 +57,11 @@ namespace {
 #ifndef PLLM_ATT_P_TMEM
 #define PLLM_ATT_P_TMEM 1
 #endif
+// Q likewise (copied from shared memory into tensor memory once, by the first group's threads, a row each):
+// correct and no faster (8192 tokens: 343.1 against 339.6 us), so off.
+#ifndef PLLM_ATT_Q_TMEM
+#define PLLM_ATT_Q_TMEM 0
+#endif
 constexpr int P_G = PLLM_ATT_GROUPS;
 constexpr int P_ROWS = 128, P_BK = 64, P_STAGES = PLLM_ATT_STAGES, P_THREADS = (4 * P_G + 4) * 32;
 constexpr int W_KEYS = 4 * P_G, W_SCORES = 4 * P_G + 1, W_VALUES = 4 * P_G + 2, W_SUMS = 4 * P_G + 3;   // the other four warps   // P_STAGES: key tiles, and as many value tiles, in flight
@@ -78,7 +86,9 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     constexpr int NHALF = HD / 64;
     constexpr int Q_BYTES = NHALF * P_ROWS * 128, STAGE = NHALF * P_PLANE, P_BYTES = P_ROWS * 128;   // STAGE: a key (or value) tile
     constexpr uint32_t S_COL = 0, O_COL = P_G * P_BK, P_COL = O_COL + HD;     // P: 32 columns a group (64 keys, two to a column)
-    constexpr uint32_t TMEM_USED = P_COL + (PLLM_ATT_P_TMEM ? P_G * 32 : 0), TMEM_COLS = TMEM_USED <= 256 ? 256 : 512;
+    constexpr uint32_t Q_COL = P_COL + (PLLM_ATT_P_TMEM ? P_G * 32 : 0);      // Q: head_dim / 2 columns
+    constexpr uint32_t TMEM_USED = Q_COL + (PLLM_ATT_Q_TMEM ? HD / 2 : 0), TMEM_COLS = TMEM_USED <= 256 ? 256 : 512;
+    static_assert(TMEM_USED <= 512, "tensor memory has 512 columns");
     constexpr int P_SMEM = PLLM_ATT_P_TMEM ? 0 : P_G * P_ROWS * 128;          // the P buffers in shared memory, if any
     if ((int)blockIdx.y >= *n_work_ptr) return;
     const AttnWork w = work[blockIdx.y];
@@ -110,8 +120,8 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     const uint32_t q_full = bars, k_full = bars + 8, k_empty = k_full + 8 * P_STAGES, v_full = k_empty + 8 * P_STAGES,
                    v_empty = v_full + 8 * P_STAGES, s_full = v_empty + 8 * P_STAGES,
                    p_full = s_full + 8 * P_G, p_empty = p_full + 8 * P_G, o_full = p_empty + 8 * P_G, m_ready = o_full + 8,   // m_ready[groups][4]
-                   s_free = m_ready + 32 * P_G;
-    constexpr int N_BARS = 4 * P_STAGES + 1 + 3 * P_G + 1 + 4 * P_G + P_G;
+                   s_free = m_ready + 32 * P_G, q_tmem = s_free + 8 * P_G;
+    constexpr int N_BARS = 4 * P_STAGES + 1 + 3 * P_G + 1 + 4 * P_G + P_G + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctl + 8 * N_BARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(ctl + 8 * N_BARS + 8);
 
@@ -129,6 +139,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             for (int wq = 0; wq < 4; wq++) mbar_init(m_ready + 8 * (4 * b + wq), 1);
         }
         mbar_init(o_full, 1);
+        mbar_init(q_tmem, 4);                    // the first group's warps have put their rows of Q into tensor memory
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
         fence_async_smem();
@@ -205,7 +216,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             // descriptors differ only in their address field (bits 0-13, units of 16 bytes): the rest is
             // made once, and an address offset is one addition
             const uint64_t q_desc = smem_desc(q_s), k_desc = smem_desc(k_ring);
-            bool ok = mbar_wait(q_full, 0, abort_flag);
+            bool ok = mbar_wait(PLLM_ATT_Q_TMEM ? q_tmem : q_full, 0, abort_flag);
             for (int t = 0; t < n_tiles && ok; t++) {
                 const int s = t % P_STAGES;
                 // the group must have read its scores of the turn before out of this buffer
@@ -216,9 +227,15 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 const uint64_t kd = k_desc + (uint64_t)((s * STAGE) >> 4);
                 const uint32_t d = tmem + S_COL + g * P_BK;
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ks++)
+                for (int ks = 0; ks < HD / 16; ks++) {
+#if PLLM_ATT_Q_TMEM
+                    mma_ts(d, tmem + Q_COL + ks * 8, kd + (uint64_t)(((ks / 4) * P_PLANE + (ks % 4) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
+#else
                     mma_ss(d, q_desc + (uint64_t)(((ks / 4) * P_ROWS * 128 + (ks % 4) * 32) >> 4),
                            kd + (uint64_t)(((ks / 4) * P_PLANE + (ks % 4) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
+#endif
+                }
+                (void)q_desc;
                 mma_commit(k_empty + 8 * s);         // the key tile's place is free once these have read it
                 mma_commit(s_full + 8 * g);
             }
@@ -266,6 +283,29 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
         // this group's part of the row's sum, in units of 2^m_ref
         float m_ref = -CUDART_INF_F, l_run = 0.f;
         bool ok = true;
+#if PLLM_ATT_Q_TMEM
+        if (grp == 0) {
+            // this thread's row of Q out of shared memory (where TMA put it, 16-byte chunk c of a 64-value
+            // half at c ^ (row & 7)) into its lane of tensor memory, two values to a column: the scores'
+            // products then read only the keys from shared memory
+            ok = mbar_wait(q_full, 0, abort_flag);
+#pragma unroll
+            for (int h = 0; h < NHALF; h++) {
+                uint32_t qr[32];
+                const unsigned char* qrow = smem + h * P_ROWS * 128 + row * 128;
+#pragma unroll
+                for (int c = 0; c < 8; c++) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(qrow + ((c ^ (row & 7)) << 4));
+                    qr[4 * c] = v.x; qr[4 * c + 1] = v.y; qr[4 * c + 2] = v.z; qr[4 * c + 3] = v.w;
+                }
+                tmem_st32(lane_base + Q_COL + h * 32, qr);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(q_tmem);
+        }
+#endif
         const int grp_before = (grp + P_G - 1) % P_G;      // the group of the tile before this group's
         for (int t = grp; t < n_tiles; t += P_G) {
             const int kv0 = w.kv_begin + t * P_BK;
@@ -453,7 +493,7 @@ static int launch_prefill(const void* q, const void* k_pool, const void* v_pool,
     constexpr int NHALF = HD / 64;
     const size_t smem = (size_t)NHALF * P_ROWS * 128 + (size_t)P_STAGES * 2 * NHALF * P_PLANE +
                         (PLLM_ATT_P_TMEM ? 0 : P_G * P_ROWS * 128) +
-                        (1 + P_G) * P_ROWS * 4 + 8 * (4 * P_STAGES + 2 + 8 * P_G) + 16 + 1024;
+                        (1 + P_G) * P_ROWS * 4 + 8 * (4 * P_STAGES + 3 + 8 * P_G) + 16 + 1024;
     cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_chained(attention_prefill_tcgen05_kernel<HD>, dim3(nkv * gparts, max_work), dim3(P_THREADS), smem, stream, map_q,
                    map_k, map_v, block_tables, (const AttnWork*)work, n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv,
