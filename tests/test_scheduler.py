@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from paged_llm_rs_b200.cache import CacheManager
-from paged_llm_rs_b200.engine.scheduler import Finish, Scheduler, Sequence
+from paged_llm_rs_b200.engine.scheduler import Finish, Plan, Scheduler, Sequence
 from paged_llm_rs_b200.parts.base import KVNeed, StateNeed
 from paged_llm_rs_b200.sampling import SamplingParams
 
@@ -322,3 +322,68 @@ def test_no_continuation_from_a_dry_pool():
     assert plan.kind == "decode" and s.continuation(plan) is None
     s.commit(plan, [9])
     cache.check_invariants()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_traffic_with_steps_planned_ahead_loses_no_page(seed):
+    # requests of random lengths, budgets and stop tokens arrive at random times, some are cancelled; the
+    # driver does what the engine does (a decode step that follows a decode step is taken from
+    # continuation() before the one before it is committed).  After every commit the books balance, and in
+    # the end every page is free and every request got what its budget and its stop token allow.
+    import random
+    rng = random.Random(seed)
+    chunk = rng.choice([None, 6, 16])
+    s, cache = make(pages=rng.choice([10, 14, 40]), page_size=4, max_batch=rng.choice([3, 8]), chunk=chunk,
+                    max_positions=64)
+    todo = [Sequence(i, [rng.randrange(1, 50) for _ in range(rng.randrange(1, 14))], GREEDY, rng.randrange(1, 12),
+                     [rng.choice([3, 77])]) for i in range(14)]
+    seqs = {q.id: q for q in todo}
+    produced, ahead, used_ahead, guard = {}, None, 0, 0
+    while todo or s.has_work():
+        guard += 1
+        assert guard < 2000
+        while todo and rng.random() < 0.4:
+            s.submit(todo.pop())
+        if ahead is not None:
+            plan, ahead = ahead, None
+            used_ahead += 1
+        else:
+            plan = s.plan()
+            if plan.kind == "idle":
+                if not todo:
+                    assert not s.has_work() or s.waiting
+                    if s.waiting:      # a prompt that waits for pages that will never come cannot happen here:
+                        raise AssertionError("idle with requests waiting and nobody running")
+                    break
+                continue
+            if plan.kind in ("refused", "outgrown"):
+                s.commit(plan, [])
+                cache.check_invariants()
+                continue
+        tokens = [rng.randrange(1, 6) for _ in plan.ids]
+        # while the step "runs": the next one, if it is sure to be the same rows again
+        nxt = s.continuation(plan)
+        cache.check_invariants()
+        if rng.random() < 0.05 and s.running:
+            s.cancel(rng.choice(s.running).id)
+            cache.check_invariants()
+        goes_on = nxt is not None and not s.waiting and len(s.running) == len(plan.ids)
+        if goes_on and not any(s.ends_with(q, t) for q, t in zip(nxt, tokens)):
+            s.count_decode_step(len(nxt))
+            ahead = Plan("decode", [q.id for q in nxt], [(q.id, 1) for q in nxt], [])
+        out = s.commit(plan, tokens)
+        cache.check_invariants()
+        for rid, tok in out.tokens:
+            produced.setdefault(rid, []).append(tok)
+        if ahead is not None:
+            # what the step planned ahead assumed still holds after the commit: the same requests, none ended,
+            # each with its page for the token it will write
+            assert [q.id for q in s.running] == ahead.ids
+            assert all(q.finish is None and len(q.pending) == 1 and cache.blocks_needed(q.id, 1) == 0 for q in s.running)
+    assert cache.available() == cache.num_pages
+    cache.check_invariants()
+    assert used_ahead > 0
+    for q in seqs.values():
+        got = produced.get(q.id, [])
+        assert len(got) <= q.max_tokens and not (set(got) & q.stop_tokens)
+        assert got == q.output
