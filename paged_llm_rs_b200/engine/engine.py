@@ -82,9 +82,9 @@ class Engine:
                 return self._note(self.scheduler.commit(plan, []))
             self._inflight = (plan, self._launch(plan))
         plan, ctx = self._inflight
+        self._inflight = None                          # (whatever goes wrong below, this step is not collected twice)
         ahead = self._prepare_next(plan, ctx)          # host work beside the GPU
         tokens = self._collect(plan, ctx)              # waits for the step
-        self._inflight = None
         if ahead is not None:
             seqs, graph = ahead
             if not self.scheduler.waiting and not any(self.scheduler.ends_with(s, t) for s, t in zip(seqs, tokens)):

@@ -227,6 +227,32 @@ def test_packing_the_next_step_ahead_changes_nothing(tmp_path, dtype):
     assert with_it[2]["tokens"] == without[2]["tokens"]
 
 
+def test_cancel_while_the_next_step_already_runs(tmp_path):
+    # a request is cancelled between two calls of step(), when the engine has a decode step with it in flight:
+    # its pages go back at once, its token of that step is dropped, the others go on as if nothing had happened
+    from paged_llm_rs_b200 import Engine
+    from paged_llm_rs_b200.engine.scheduler import Finish
+    cfg, seed = CONFIGS["A"]
+    model = write_model(tmp_path, "A")
+    prompts = prompts_for(cfg["vocab_size"], [5, 9, 12], 17)
+    full = Engine(model, dtype="float32", block_size=16, blocks=32, chunk=8).generate(prompts, max_tokens=20)
+    eng = Engine(model, dtype="float32", block_size=16, blocks=32, chunk=8)
+    ids = [eng.submit(p, max_tokens=20) for p in prompts]
+    outs, cancelled_at = {i: [] for i in ids}, None
+    while eng.scheduler.has_work():
+        out = eng.step()
+        for rid, tok in out.tokens:
+            outs[rid].append(tok)
+        if cancelled_at is None and len(outs[ids[1]]) == 6:
+            assert eng._inflight is not None and ids[1] in eng._inflight[0].ids     # the step after is on its way
+            eng.cancel(ids[1])
+            cancelled_at = len(outs[ids[1]])
+    assert cancelled_at == 6 and outs[ids[1]] == full[1][:6]
+    assert outs[ids[0]] == full[0] and outs[ids[2]] == full[2]
+    assert eng._inflight is None and eng.metrics()["pages_free"] == 32
+    assert eng.finish_reason(ids[0]) == Finish.LENGTH
+
+
 def test_top_k_top_p_follow_the_reference_order(tmp_path):
     from paged_llm_rs_b200 import Engine
     cfg, seed = CONFIGS["A"]
