@@ -12,8 +12,12 @@
 // Same kernels and same result as pllm_sample; the scratch memory between its two
 // launches is a fixed array of PLLM_STATIC_SAMPLE_FLOATS floats in the library image
 // instead of a buffer from the caller.  Calls must not overlap on the GPU.  The first
-// call on a device should come before any stream capture.
+// call on a device should come before any stream capture.  The array that is used is
+// the CURRENT device's (cudaGetDevice at the call): ``stream`` must be a stream of that
+// device, or the kernels would be given another GPU's array.
 #pragma once
+
+#include <cuda_runtime_api.h>   // cudaStream_t: this header can be included on its own
 
 #define PLLM_STATIC_SAMPLE_MAX_ROWS 64
 #define PLLM_STATIC_SAMPLE_MAX_VOCAB (1 << 20)

@@ -12,12 +12,13 @@ max_batch 16, chunk 128 (None = "off": prompts run whole), prefix_cache on.
 
 from __future__ import annotations
 
+from collections import OrderedDict
 from typing import Dict, Iterable, List, Optional, Sequence as Seq
 
 import numpy as np
 import torch
 
-from ..errors import ConfigError
+from ..errors import ConfigError, EngineError
 from ..kernels import ops
 from ..sampling.sampler import SamplingParams, sample_host
 from .runner import ModelRunner
@@ -29,19 +30,23 @@ class Engine:
     def __init__(self, model: str, dtype="bfloat16", block_size: int = 16, cache_mib: int = 3584,
                  blocks: Optional[int] = None, max_batch: int = 16, chunk: Optional[int] = 128,
                  prefix_cache: bool = True, device: str = "cuda:0", max_requests: Optional[int] = None,
-                 max_prefill_seqs: int = 1, lookahead: bool = True):
+                 max_prefill_seqs: int = 1, lookahead: bool = True, runner=None):
+        """``runner``: something that steps like a ``ModelRunner`` (cache, spec, vocab_size,
+        step_and_sample, prepack_decode, check_status), to drive the loop without a model."""
         if chunk is not None and chunk < 1:
             raise ConfigError("chunk 0 would carry nothing")
-        self.runner = ModelRunner(model, dtype=dtype, page_size=block_size, num_pages=blocks,
-                                  cache_bytes=None if blocks is not None else cache_mib << 20,
-                                  max_requests=max_requests or max(256, 2 * max_batch), device=device,
-                                  prefix_cache=prefix_cache)
+        self.runner = runner if runner is not None else ModelRunner(
+            model, dtype=dtype, page_size=block_size, num_pages=blocks,
+            cache_bytes=None if blocks is not None else cache_mib << 20,
+            max_requests=max_requests or max(256, 2 * max_batch), device=device, prefix_cache=prefix_cache)
         self.runner.graph_step_tokens = chunk if (chunk is not None and chunk <= 8192) else None
         self.scheduler = Scheduler(self.runner.cache, max_batch=max_batch, chunk=chunk,
                                    max_positions=self.runner.spec.max_positions, max_prefill_seqs=max_prefill_seqs)
         self._next_id = 0
         self._seqs: Dict[int, Sequence] = {}
-        self._finish: Dict[int, Finish] = {}
+        # how the last FINISH_MEMORY requests ended (older ones are forgotten: an engine lives long)
+        self._finish: "OrderedDict[int, Finish]" = OrderedDict()
+        self.last_error: Optional[EngineError] = None   # what failed the last failed step
         self.bytes_d2h = 0  # bytes the last step copied back to the host
         # While a decode step runs on the GPU the host gets the next one ready (pages, positions, tables,
         # attention work: everything but the token ids), so that between two steps the GPU waits only for
@@ -66,34 +71,73 @@ class Engine:
         self.scheduler.submit(seq)
         return rid
 
+    FINISH_MEMORY = 4096
+
     def cancel(self, rid: int) -> None:
+        """End a request now; its pages go back at once.  A step that is already running may still
+        write the request's keys and values into those pages: it does so in stream order before any
+        step that is planned after this call, so a new owner of a page (which names the page only
+        after its own step is committed) never reads them.  When nothing is left to run, the step in
+        flight is waited for here and its status checked, so that no step outlives its requests."""
         self.scheduler.cancel(rid)
+        if self._inflight is not None and not self.scheduler.has_work():
+            plan, ctx = self._inflight
+            self._inflight = None
+            try:
+                self._collect(plan, ctx)               # its tokens belong to nobody any more
+            except EngineError as e:
+                self.last_error = e
 
     # -- one step ------------------------------------------------------------------------
     def step(self) -> Optional[Outcome]:
         """Plan, run, sample and commit one step.  None when there is nothing to do.  On return the
         step after it may already be running (a decode step that follows a decode step with the same
-        requests): its tokens come with the next call."""
+        requests): its tokens come with the next call.
+
+        A step that fails (a kernel refuses its arguments, or the status word says that a kernel
+        met an index out of range or a wait that ran out) ends every request that was in it with
+        ``Finish.ERROR``, since none of them can tell what was written before it stopped
+        (crates/pagedllm-server/src/engine.rs:338-348); their pages and state slots go back, the
+        other requests go on, and ``last_error`` holds the cause."""
         if self._inflight is None:
             plan = self.scheduler.plan()
             if plan.kind == "idle":
                 return None
             if plan.kind in ("refused", "outgrown"):
                 return self._note(self.scheduler.commit(plan, []))
-            self._inflight = (plan, self._launch(plan))
+            try:
+                self._inflight = (plan, self._launch(plan))
+            except EngineError as e:
+                return self._fail(plan, e)
         plan, ctx = self._inflight
         self._inflight = None                          # (whatever goes wrong below, this step is not collected twice)
-        ahead = self._prepare_next(plan, ctx)          # host work beside the GPU
-        tokens = self._collect(plan, ctx)              # waits for the step
+        try:
+            ahead = self._prepare_next(plan, ctx)      # host work beside the GPU
+            tokens = self._collect(plan, ctx)          # waits for the step
+        except EngineError as e:
+            return self._fail(plan, e)
         if ahead is not None:
             seqs, graph = ahead
             if not self.scheduler.waiting and not any(self.scheduler.ends_with(s, t) for s, t in zip(seqs, tokens)):
-                self._inflight = self._launch_prepared(seqs, graph, tokens)
+                try:
+                    self._inflight = self._launch_prepared(seqs, graph, tokens)
+                except EngineError as e:
+                    out = self._note(self.scheduler.commit(plan, tokens))
+                    failed = self._fail(Plan("decode", [s.id for s in seqs], [(s.id, 1) for s in seqs]), e)
+                    out.finished += failed.finished
+                    return out
         return self._note(self.scheduler.commit(plan, tokens))
+
+    def _fail(self, plan: Plan, error: EngineError) -> Outcome:
+        self.last_error = error
+        return self._note(self.scheduler.fail([rid for rid, _ in plan.advanced]))
 
     def _note(self, out: Outcome) -> Outcome:
         for rid, why in out.finished:
             self._finish[rid] = why
+            self._finish.move_to_end(rid)
+        while len(self._finish) > self.FINISH_MEMORY:
+            self._finish.popitem(last=False)
         return out
 
     def _sampling_rows(self, seqs):

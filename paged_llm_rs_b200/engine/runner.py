@@ -71,6 +71,12 @@ class _DecodeGraph:
         # the status word and the chosen tokens come back by a copy that is part of the captured step
         self.tokens_host = torch.zeros(1 + n_seg, dtype=torch.int32).pin_memory()
         self.staging = None     # host buffer of a step packed ahead of time (prepack)
+        # The pinned buffer is read by the replay's first node.  A caller that replays this step again
+        # without having waited for the replay before it (the engine waits: it needs the tokens) must
+        # not overwrite the buffer under a replay that has not started yet: an event marks each
+        # replay's end and is waited for (on the host) before the buffer is written again.
+        self._replayed = torch.cuda.Event()
+        self._pending = False
         # Warm up on a side stream (library handles, workspaces), then capture.
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -124,21 +130,33 @@ class _DecodeGraph:
         if uniform is not None:
             o = self.layout["uniform"][0]
             self.staging[o:o + n] = np.asarray(uniform, dtype=np.float32).view(np.int32)
+        self._before_write()
         np.copyto(self.pinned_np, self.staging)
-        self.graph.replay()
+        self._replay()
         r.bytes_h2d = self.nbytes
         r.last_launches = self.launches
         r.tokens_host = self.tokens_host[:1 + n]
         return self.logits[:n], self.tokens[:1 + n]
 
+    def _before_write(self):
+        if self._pending:
+            self._replayed.synchronize()
+            self._pending = False
+
+    def _replay(self):
+        self.graph.replay()
+        self._replayed.record()
+        self._pending = True
+
     def run(self, entries, temperature, uniform):
         r = self.runner
+        self._before_write()
         if self.native is not None:
             self.native.pack(entries, temperature, uniform)     # straight into the pinned buffer
         else:
             host, _, _ = r.packer.pack(entries, r._heads, self.caps, self.work_caps, temperature, uniform)
             self.pinned.numpy()[:] = host
-        self.graph.replay()
+        self._replay()
         r.bytes_h2d = self.nbytes
         r.last_launches = self.launches
         n = sum(len(e.want) for e in entries)
@@ -211,11 +229,17 @@ class ModelRunner:
         self.last_launches = 0    # kernels of this library the last step launched
 
     # -- the step ----------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry], check: bool = True) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], check: bool = True, trace: Optional[dict] = None) -> torch.Tensor:
         """Run one batch.  Returns float32 logits [wanted, vocab] on the device, in
         the order of the entries and of their ``want`` lists.  Pages for the new
-        tokens must have been reserved; nothing is committed."""
-        logits, _ = self.step_and_sample(entries, None, None, check=check)
+        tokens must have been reserved; nothing is committed.  With ``trace`` (a
+        dict) the parts store copies of what they leave at module boundaries
+        there, under the checkpoint's names (``Runtime.trace``)."""
+        self.rt.trace = trace
+        try:
+            logits, _ = self.step_and_sample(entries, None, None, check=check)
+        finally:
+            self.rt.trace = None
         return logits
 
     def step_and_sample(self, entries: Sequence[StepEntry], temperature, uniform, check: bool = False):
@@ -298,6 +322,8 @@ class ModelRunner:
         S = 1
         while S < len(entries):
             S *= 2
+        if sum(len(e.want) for e in entries) > S:
+            return None     # (generation wants one place a request at most; a step that wants more is launched plainly)
         width = max((len(self.cache.get(e.request_id).tables[gi].blocks) for e in entries
                      for gi in range(len(self.cache.groups))), default=1)
         W = 64

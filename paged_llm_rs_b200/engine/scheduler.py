@@ -37,6 +37,7 @@ from .step import StepEntry
 class Finish(enum.Enum):
     STOP = "stop"      # a stop token came, or the request was cancelled
     LENGTH = "length"  # max_tokens ran out, or the prompt can never fit
+    ERROR = "error"    # a step the request was in failed
 
 
 class Sequence:
@@ -375,6 +376,18 @@ class Scheduler:
                     s.finish = Finish.LENGTH  # the next token would sit past the last position
         if plan.kind == "refused":
             out.finished.append((plan.refused, Finish.LENGTH))
+        self._retire(out)
+        return out
+
+    def fail(self, ids) -> Outcome:
+        """A step with these requests failed: each ends with ``Finish.ERROR`` and gives back what it
+        holds (pages taken for the step that failed included); nothing of that step is committed
+        (crates/pagedllm-server/src/engine.rs:338-348)."""
+        ids = set(ids)
+        for s in self.running:
+            if s.id in ids and s.finish is None:
+                s.finish = Finish.ERROR
+        out = Outcome()
         self._retire(out)
         return out
 

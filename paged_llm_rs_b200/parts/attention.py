@@ -107,7 +107,13 @@ class GQAttention(Mixer):
         ops.paged_attention(q, k_pool, v_pool, g.block_tables, g.work, g.n_work, g.max_work, o, g.part_o, g.part_ml,
                             g.red, g.n_red, g.max_red, self.nh, self.nkv, self.hd, self.window or 0, self.scale,
                             self.rt.status, swizzled=swizzled, kinds=g.kinds, counters=g.counters, cluster=g.cluster)
-        return ops.linear(o, self.w_o, status=self.rt.status)
+        out = ops.linear(o, self.w_o, status=self.rt.status)
+        if self.rt.trace is not None:
+            qw, kw = self.nh * self.hd, self.nkv * self.hd
+            for leaf, t in (("q_proj.out", qkv[:, :qw]), ("k_proj.out", qkv[:, qw:qw + kw]), ("v_proj.out", qkv[:, qw + kw:]),
+                            ("o_proj.in", o), ("o_proj.out", out), ("out", out)):
+                self.rt.record(self._name(leaf), t)
+        return out
 
 
 register_mixer("gqa_attention", GQAttention)

@@ -33,10 +33,19 @@ class Runtime:
     dtype: torch.dtype
     # one int32 the kernels raise bits in when an index is out of range
     status: torch.Tensor = None
+    # While a step runs with a dict here, parts store copies of what they leave at their
+    # boundaries under "<tensor prefix>.<what>" ("model.layers.0.self_attn.o_proj.in"): the
+    # reference's Trace (crates/pagedllm/src/model/mod.rs:33-80).  Only what a kernel stores
+    # can be named: a fused kernel's intermediate values are not.
+    trace: Optional[Dict[str, torch.Tensor]] = None
 
     def __post_init__(self):
         if self.status is None:
             self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def record(self, name: str, tensor: torch.Tensor) -> None:
+        if self.trace is not None:
+            self.trace[name] = tensor.detach().clone()
 
 
 # --- what a mixer needs of the cache manager ------------------------------------
@@ -200,6 +209,7 @@ class Block:
     returns the same pair, so that the add can be fused into the next norm."""
 
     kind = ""
+    prefix = ""   # the layer's tensor prefix ("model.layers.3"), set by the decoder that builds it
 
     def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: Dict[str, Norm]):
         self.mixer, self.feed_forward, self.norms = mixer, feed_forward, norms

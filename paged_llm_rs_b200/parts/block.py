@@ -31,7 +31,11 @@ class PreNormResidualBlock(Block):
         residual = self._residual_after(h, r)
         h, r = self._normed(self.norms["feed_forward"], self.feed_forward, residual, a)
         out = self.feed_forward.forward(h, step)
-        return self._residual_after(h, r), out
+        residual = self._residual_after(h, r)
+        rt = self.mixer.rt
+        if rt.trace is not None and self.prefix:
+            rt.record(f"{self.prefix}.out", residual + out)      # (otherwise formed by the next norm's kernel)
+        return residual, out
 
 
 register_block("prenorm_residual", PreNormResidualBlock)

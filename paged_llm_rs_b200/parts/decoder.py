@@ -33,6 +33,7 @@ class DecoderModel:
             if ls.block not in BLOCKS:
                 raise KeyError(f"no block arrangement {ls.block!r} is registered; known: {sorted(BLOCKS)}")
             self.blocks.append(BLOCKS[ls.block](mixer, ff, norms))
+            self.blocks[-1].prefix = ls.prefix
         self.final_norm = make(NORMS, "norm", spec.final_norm, rt)
         self.head = make(HEADS, "head", spec.head, rt)
         self.schedule = list(spec.schedule)
@@ -72,7 +73,9 @@ class DecoderModel:
             # A portion in the middle of a prompt runs only to fill the cache (mod.rs:336-346).
             return torch.zeros((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
         h = self.final_norm.add_norm(residual, delta, rows=step.logit_rows)
-        return self.head.forward(h)
+        logits = self.head.forward(h)
+        self.rt.record("logits", logits)
+        return logits
 
 
 def tensor_specs_of(spec: ModelSpec) -> List[TensorSpec]:

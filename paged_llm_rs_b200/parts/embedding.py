@@ -27,7 +27,9 @@ class TokenEmbedding(Part):
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         out = torch.empty((tokens.numel(), self.hidden), dtype=self.table.dtype, device=self.table.device)
-        return ops.embed(tokens, self.table, out, self.rt.status)
+        ops.embed(tokens, self.table, out, self.rt.status)
+        self.rt.record(self._name("out"), out)
+        return out
 
 
 class LinearHead(Part):
@@ -54,7 +56,9 @@ class LinearHead(Part):
             raise WeightError(f"no {self._name('weight')}, and the config does not tie the embeddings")
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear(x, self.weight, out_dtype=torch.float32)
+        logits = ops.linear(x, self.weight, out_dtype=torch.float32)
+        self.rt.record(self._name("out"), logits)
+        return logits
 
 
 register_embedding("token_embedding", TokenEmbedding)

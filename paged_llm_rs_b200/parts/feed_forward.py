@@ -31,7 +31,13 @@ class SwiGLUMLP(FeedForward):
     takes_normed_input = True
 
     def forward(self, x, step):
-        return ops.linear(ops.linear_glu(x, self.w_gate_up, status=self.rt.status), self.w_down, status=self.rt.status)
+        act = ops.linear_glu(x, self.w_gate_up, status=self.rt.status)
+        out = ops.linear(act, self.w_down, status=self.rt.status)
+        if self.rt.trace is not None:
+            self.rt.record(self._name("down_proj.in"), act)
+            self.rt.record(self._name("down_proj.out"), out)
+            self.rt.record(self._name("out"), out)
+        return out
 
 
 register_feed_forward("swiglu_mlp", SwiGLUMLP)

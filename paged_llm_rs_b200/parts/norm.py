@@ -28,14 +28,18 @@ class RMSNorm(Norm):
     def forward(self, x, rows=None):
         n = rows.numel() if rows is not None else x.shape[0]
         out = torch.empty((n, self.width), dtype=x.dtype, device=x.device)
-        return ops.rmsnorm(x, self.gain, self.eps, out, rows=rows)
+        ops.rmsnorm(x, self.gain, self.eps, out, rows=rows)
+        self.rt.record(self._name("out"), out)
+        return out
 
     def add_norm(self, residual, delta, rows=None):
         n = rows.numel() if rows is not None else residual.shape[0]
         out = torch.empty((n, self.width), dtype=residual.dtype, device=residual.device)
         # With rows the sum is formed for those rows only and not stored.
-        return ops.rmsnorm(residual, self.gain, self.eps, out, delta=delta,
-                           residual_out=residual if (delta is not None and rows is None) else None, rows=rows)
+        ops.rmsnorm(residual, self.gain, self.eps, out, delta=delta,
+                    residual_out=residual if (delta is not None and rows is None) else None, rows=rows)
+        self.rt.record(self._name("out"), out)
+        return out
 
     def add_norm_deferred(self, residual, delta):
         # the few rows of a decode step in bfloat16: the product that follows does the add and the norm

@@ -48,7 +48,8 @@ def random_tensors(model_spec, seed: int, dtype: torch.dtype = torch.bfloat16, d
 
 
 def write_random_model(model_dir: str, config_dict: dict, seed: int, dtype: torch.dtype = torch.bfloat16,
-                       device="cpu", write_optional: bool = False) -> str:
+                       device="cpu", write_optional: bool = False, matrix_std: float = 0.02,
+                       gain_std: float = 0.1) -> str:
     """Make ``model_dir`` with config.json and model.safetensors.  Optional
     tensors (a tied head's own copy) are left out unless asked for."""
     arch = resolve_architecture(config_dict)
@@ -57,6 +58,7 @@ def write_random_model(model_dir: str, config_dict: dict, seed: int, dtype: torc
     os.makedirs(model_dir, exist_ok=True)
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(config_dict, f, indent=1)
-    tensors = random_tensors(spec, seed, dtype=dtype, device=device, write_optional=write_optional)
+    tensors = random_tensors(spec, seed, dtype=dtype, device=device, matrix_std=matrix_std, gain_std=gain_std,
+                             write_optional=write_optional)
     write_safetensors(os.path.join(model_dir, "model.safetensors"), tensors)
     return model_dir

@@ -21,13 +21,14 @@ from typing import Dict, List, Optional
 import torch
 
 
-def load_model(model_dir: str, dtype=torch.float32):
-    """config.json as a dict and every tensor of model.safetensors cast to ``dtype``."""
+def load_model(model_dir: str, dtype=torch.float32, device="cpu"):
+    """config.json as a dict and every tensor of model.safetensors cast to ``dtype``
+    (on ``device``: the functions below run wherever the weights are)."""
     from safetensors.torch import load_file
 
     with open(os.path.join(model_dir, "config.json")) as f:
         cfg = json.load(f)
-    w = {k: v.to(dtype) for k, v in load_file(os.path.join(model_dir, "model.safetensors")).items()}
+    w = {k: v.to(device=device, dtype=dtype) for k, v in load_file(os.path.join(model_dir, "model.safetensors")).items()}
     return cfg, w
 
 
@@ -68,7 +69,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return x @ weight.t()
 
 
-def rope_tables(head_dim: int, positions: int, theta: float, dtype=torch.float32):
+def rope_tables(head_dim: int, positions: int, theta: float, dtype=torch.float32, device="cpu"):
     """cos/sin [positions, head_dim]: inv_freq[i] = 1/theta^(2i/head_dim), the angle
     pos*inv_freq[i] in float64, each angle twice (once per half of the head)
     (crates/pagedllm/src/model/rope.rs:39-62)."""
@@ -76,7 +77,8 @@ def rope_tables(head_dim: int, positions: int, theta: float, dtype=torch.float32
     inv_freq = torch.tensor([1.0 / theta ** (2.0 * i / head_dim) for i in range(half)], dtype=torch.float64)
     angle = torch.arange(positions, dtype=torch.float64)[:, None] * inv_freq[None, :]
     angle = torch.cat([angle, angle], dim=-1)
-    return angle.cos().to(torch.float32).to(dtype), angle.sin().to(torch.float32).to(dtype)
+    return (angle.cos().to(torch.float32).to(device=device, dtype=dtype),
+            angle.sin().to(torch.float32).to(device=device, dtype=dtype))
 
 
 def rotate_half(x: torch.Tensor) -> torch.Tensor:
@@ -91,16 +93,16 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
     return x * cos + rotate_half(x) * sin
 
 
-def causal_mask(seq: int, window: Optional[int], dtype) -> torch.Tensor:
+def causal_mask(seq: int, window: Optional[int], dtype, device="cpu") -> torch.Tensor:
     """0 where key j <= query i, -inf past it (crates/pagedllm/src/model/attention.rs:255-275).
     With a window w, key j is also hidden when j <= i - w: a query sees itself and
     the w-1 keys before it (not in the reference, which has no window)."""
-    i = torch.arange(seq)[:, None]
-    j = torch.arange(seq)[None, :]
+    i = torch.arange(seq, device=device)[:, None]
+    j = torch.arange(seq, device=device)[None, :]
     hidden = j > i
     if window is not None:
         hidden = hidden | (j <= i - window)
-    return torch.zeros(seq, seq, dtype=dtype).masked_fill(hidden, float("-inf"))
+    return torch.zeros(seq, seq, dtype=dtype, device=device).masked_fill(hidden, float("-inf"))
 
 
 def softmax_last(x: torch.Tensor) -> torch.Tensor:
@@ -133,7 +135,7 @@ def attention(x, w: Dict[str, torch.Tensor], prefix: str, cfg, cos, sin, window,
     k = k.repeat_interleave(group, dim=0)  # head h reads kv head h // group
     v = v.repeat_interleave(group, dim=0)
     scores = q @ k.transpose(-1, -2) * (1.0 / math.sqrt(hd))
-    scores = scores + causal_mask(seq, window, scores.dtype)
+    scores = scores + causal_mask(seq, window, scores.dtype, scores.device)
     out = softmax_last(scores) @ v  # [nh, seq, hd]
     out = out.transpose(0, 1).reshape(seq, nh * hd)
     if trace is not None:
@@ -175,20 +177,23 @@ def block(x, w, layer: int, cfg, cos, sin, trace=None):
     return x
 
 
-def forward(cfg, w, tokens: List[int], trace: Optional[dict] = None) -> torch.Tensor:
+def forward(cfg, w, tokens: List[int], trace: Optional[dict] = None, rows: Optional[List[int]] = None) -> torch.Tensor:
     """Logits [len(tokens), vocab] of one sequence from position 0, every position
-    projected (model/mod.rs:271-303).  The head is lm_head.weight when stored, else
+    projected (model/mod.rs:271-303); with ``rows``, only those positions are normed
+    and projected (mod.rs:340-351).  The head is lm_head.weight when stored, else
     the embedding when tied, else an error (mod.rs:226-235)."""
     if not tokens:
         raise ValueError("cannot run a forward pass on no tokens")
-    dtype = w["model.embed_tokens.weight"].dtype
-    ids = torch.tensor(tokens, dtype=torch.long)
+    dtype, device = w["model.embed_tokens.weight"].dtype, w["model.embed_tokens.weight"].device
+    ids = torch.tensor(tokens, dtype=torch.long, device=device)
     x = embed(ids, w["model.embed_tokens.weight"])
     if trace is not None:
         trace["model.embed_tokens.out"] = x
-    cos, sin = rope_tables(cfg["head_dim"], len(tokens), rope_theta(cfg), dtype)
+    cos, sin = rope_tables(cfg["head_dim"], len(tokens), rope_theta(cfg), dtype, device)
     for layer in range(cfg["num_hidden_layers"]):
         x = block(x, w, layer, cfg, cos, sin, trace)
+    if rows is not None:
+        x = x[torch.tensor(list(rows), dtype=torch.long, device=device)]
     x = rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
     if "lm_head.weight" in w:
         head = w["lm_head.weight"]

@@ -10,7 +10,7 @@ from paged_llm_rs_b200 import (ConfigError, GenerationDefaults, Qwen3Config, Uns
                                register_architecture, resolve_architecture)
 from paged_llm_rs_b200.config import Architecture
 from paged_llm_rs_b200.models.qwen3 import describe_qwen3
-from tiny_configs import TINY_A, TINY_B
+from tiny_configs import TINY_A, TINY_B, TINY_W
 
 QWEN3_0_6B = dict(
     architectures=["Qwen3ForCausalLM"], attention_bias=False, attention_dropout=0.0, bos_token_id=151643,
@@ -30,12 +30,13 @@ def test_published_shape_parses():
 
 
 def test_round_trip_and_both_tiny_configs():
-    for d in (TINY_A, TINY_B):
+    for d in (TINY_A, TINY_B, TINY_W):
         c = Qwen3Config.from_dict(d)
         assert Qwen3Config.from_dict(c.to_dict()) == c
     b = Qwen3Config.from_dict(TINY_B)
     assert b.rope_theta == 1e6  # nested under rope_parameters
-    assert [b.window_of_layer(i) for i in range(3)] == [40, None, 40]
+    assert [b.window_of_layer(i) for i in range(3)] == [None, None, None]
+    assert [Qwen3Config.from_dict(TINY_W).window_of_layer(i) for i in range(3)] == [40, None, 40]
 
 
 @pytest.mark.parametrize("change,error", [
@@ -74,7 +75,7 @@ def test_registry(tmp_path):
         resolve_architecture({"architectures": ["MambaForCausalLM"], "model_type": "mamba"})
     with pytest.raises(ConfigError):
         resolve_architecture({})
-    (tmp_path / "config.json").write_text(json.dumps(TINY_B))
+    (tmp_path / "config.json").write_text(json.dumps(TINY_W))
     arch, cfg = load_config(str(tmp_path))
     spec = arch.describe(cfg)
     assert len(spec.layers) == 3 and spec.layers[0].mixer.params["window"] == 40

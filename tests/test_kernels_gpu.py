@@ -219,7 +219,7 @@ def attention_ref(q, k, v, scale, window):
 
 
 def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, craft=None, kinds=3, counters=None,
-                  raw=False, cluster=0, idle_items=0):
+                  raw=False, cluster=0, idle_items=0, min_split_keys=128, multi_min_split_keys=128):
     """reqs: list of (context before the step, query tokens).  Builds a paged cache
     with shuffled pages, runs the kernel, returns (got, want) per request."""
     g = torch.Generator().manual_seed(seed)
@@ -257,7 +257,8 @@ def run_attention(dtype, reqs, nh, nkv, hd, page, window, target_ctas, seed=0, c
     tile = ops.attention_tile_tokens(nh, nkv, dtype, hd, page, window or 0)
     # (splits from 128 keys on, shorter than the engine cuts them, so that the short contexts here have some)
     work, red, parts = attention_plan.plan_attention(segs, tile, window, nkv * (-(-(nh // nkv) // 16)), target_ctas,
-                                                     min_split_keys=128, cluster=cluster, multi_min_split_keys=128)
+                                                     min_split_keys=min_split_keys, cluster=cluster,
+                                                     multi_min_split_keys=multi_min_split_keys)
     dev = lambda t: t.to(DEV)
     workd = dev(torch.from_numpy(np.ascontiguousarray(work)).reshape(-1, 8)) if len(work) else torch.zeros(1, 8, dtype=torch.int32, device=DEV)
     if idle_items:   # a list with room to spare, as a captured step's is
@@ -521,6 +522,57 @@ def test_a_far_key_among_hundreds_decides(dtype):
         for r, (got, want) in enumerate(res):
             assert (got - (100.0 + r)).abs().max() < 0.6
             torch.testing.assert_close(got, want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("context", [4096, 16384, 40000])
+def test_a_far_key_decides_in_a_long_context(dtype, context):
+    # The reference's kernel holds a score per key in shared memory and stops at 12 160 keys
+    # (crates/pagedllm/src/kernels/paged_attention.rs:626-634); this one cuts the range into splits and
+    # combines them.  Contexts up to the 0.6B shape's 40 960 positions, cut as the engine cuts them
+    # (296 CTAs wanted, splits of at least 256 keys, up to 128 of them) and not cut at all: a key near
+    # the start of the context carries the answer, and the very first and the very last key carry
+    # louder wrong ones that the right one must still beat.
+    nh, nkv, hd, page = 4, 1, 128, 16
+
+    def craft(r, q, k, v):
+        far = 70 + 300 * r
+        q[:] = 0; q[:, :, 5] = 9.0 * hd ** 0.5
+        k[:, :, 5] = 0
+        k[far, :, 5] = 9.0; v[far] = 40.0 + r
+        k[0, :, 5] = 7.0; v[0] = -200.0
+        k[-1, :, 5] = 7.0; v[-1] = 300.0
+    reqs = [(context - 1, 1), (context - 1 - 77, 1)]
+    for target, splits in ((1, False), (296, True)):
+        res, n_red = run_attention(dtype, reqs, nh, nkv, hd, page, None, target, craft=craft, kinds=1,
+                                   min_split_keys=attention_plan.MIN_SPLIT_KEYS)
+        assert (n_red > 0) == splits
+        for r, (got, want) in enumerate(res):
+            assert (got - (40.0 + r)).abs().max() < 1.0
+            torch.testing.assert_close(got, want, **tol(dtype))
+
+
+def test_a_far_key_decides_for_a_long_portion_behind_a_long_context():
+    # 2048 tokens of a prompt behind 6000 that are already in the cache: the tcgen05 kernel's tiles of
+    # 128 rows walk some 8000 keys through the block table; a key in the cached part decides for one
+    # row, and one inside the portion for another
+    nh, nkv, hd, page = 4, 1, 128, 16
+    assert ops.attention_prefill_uses_tcgen05(torch.bfloat16, nh, nkv, hd, page, 0)
+
+    def craft(r, q, k, v):
+        k[:, :, 5] = 0
+        for row, far, mark in ((1500, 41, 30.0), (77, 6000 + 500, -20.0), (2047, 5999, 11.0)):
+            q[row] = 0; q[row, :, 5] = 9.0 * hd ** 0.5
+            k[far, :, 5] = 9.0; v[far] = mark
+    res, _ = run_attention(torch.bfloat16, [(6000, 2048)], nh, nkv, hd, page, None, 296, craft=craft, kinds=2,
+                           min_split_keys=attention_plan.MIN_SPLIT_KEYS,
+                           multi_min_split_keys=attention_plan.MULTI_MIN_SPLIT_KEYS)
+    got, want = res[0]
+    # row 77 (position 6077) sees the marked keys at 41 and 5999, which score alike: the mean of their
+    # values; rows 1500 and 2047 see the one at 6500 too
+    assert (got[77] - 20.5).abs().max() < 0.5
+    assert (got[1500] - 7.0).abs().max() < 0.5 and (got[2047] - 7.0).abs().max() < 0.5
+    torch.testing.assert_close(got, want, **tol(torch.bfloat16))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

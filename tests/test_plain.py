@@ -78,3 +78,28 @@ def test_sampler_distribution_and_top_k_top_p():
     assert all(P.sample(logits, 1.0, 1, None, P.PlainRng(s)) == 0 for s in range(20))
     # top_p 0.7: 0.5 does not reach it, 0.5 + 0.3 crosses and is kept; nothing else is
     assert {P.sample(logits, 1.0, None, 0.7, P.PlainRng(s)) for s in range(200)} == {0, 1}
+
+
+@pytest.mark.parametrize("name", ["A", "D"])
+def test_the_models_for_checks_on_tokens_let_attention_decide(tmp_path, name):
+    """Checks on generated tokens use folders drawn wider than N(0, 0.02) and with a head of their
+    own (tiny_configs.write_model(..., decisive=True)): there the next token changes when the
+    attention output is zeroed, and the model does not simply repeat its last token.  With
+    N(0, 0.02) and a tied head neither holds often enough for a token to say much about the cache."""
+    from tiny_configs import CONFIGS, write_model
+
+    cfg, seed = CONFIGS[name]
+    model = write_model(tmp_path, name, decisive=True)
+    c, w = P.load_model(model, torch.float64)
+    silent = {k: (v * 0 if "o_proj" in k else v) for k, v in w.items()}
+    rng = np.random.default_rng(9)
+    moved = echoes = total = 0
+    for n in (7, 19, 40):
+        seq = rng.integers(0, cfg["vocab_size"], n).tolist()
+        for _ in range(8):
+            a = int(P.forward(c, w, seq)[-1].argmax())
+            moved += a != int(P.forward(c, silent, seq)[-1].argmax())
+            echoes += a == seq[-1]
+            total += 1
+            seq.append(a)
+    assert moved >= 0.9 * total and echoes <= 0.5 * total, (moved, echoes, total)

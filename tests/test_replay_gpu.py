@@ -1,14 +1,16 @@
 """Trace replay against the plain implementation: the same requests whole, with
 the last 32 tokens decoded one by one, in portions of changing size, and mixed
 with other requests in a pool so small that pages are used again; long decoding;
-the first tokens of a sequence.  In float32 and in bfloat16, for two tiny
-configurations that differ in every size and option (the second with a window
-on two of its layers and a single kv head)."""
+the first tokens of a sequence; requests that share pages with equal prefixes;
+and the same work as captured and replayed CUDA graphs, the way generation runs
+it.  In float32 and in bfloat16, for two tiny configurations that differ in every
+size and option (A on pages of 16; B, with a single kv head, on pages of 8), and
+for two more with a window on some of their layers (W, D)."""
 
 import numpy as np
 import pytest
 
-from tiny_configs import CONFIGS, write_model
+from tiny_configs import CONFIGS, PAGE_SIZES, write_model
 from trace_tools import TraceBuilder, plain_logits, replay
 
 pytestmark = pytest.mark.gpu
@@ -91,18 +93,19 @@ def err(got, want):
     return float(np.abs(got - want).max() / max(1.0, np.abs(want).max()))
 
 
-@pytest.fixture(scope="module", params=[("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16"),
-                                        ("D", "float32"), ("D", "bfloat16")],
-                ids=lambda p: f"{p[0]}-{p[1]}")
+PARAMS = [(n, d) for n in ("A", "B", "W", "D") for d in ("float32", "bfloat16")]
+
+
+@pytest.fixture(scope="module", params=PARAMS, ids=lambda p: f"{p[0]}-{p[1]}")
 def run(request, tmp_path_factory):
     name, dtype = request.param
     cfg, seed = CONFIGS[name]
     model = write_model(tmp_path_factory.mktemp("models"), name)
-    V = cfg["vocab_size"]
+    V, ps = cfg["vocab_size"], PAGE_SIZES[name]
     tb, toks = build_trace(V, seed)
-    got = tb.collect(replay(model, dtype, tb.steps, 640, V))
+    got = tb.collect(replay(model, dtype, tb.steps, 640, V, page_size=ps))
     tbm, toksm = build_mixed(V, seed)
-    gotm = tbm.collect(replay(model, dtype, tbm.steps, 256, V))
+    gotm = tbm.collect(replay(model, dtype, tbm.steps, 256, V, page_size=ps))
     want = {k: plain_logits(model, t) for k, t in {**toks, **toksm}.items()}
     return dict(dtype=dtype, got={**got, **gotm}, want=want, name=name)
 
@@ -150,6 +153,157 @@ def test_mixed_batches_in_reused_pages(run):
         pos = sorted(have)
         assert len(pos) >= 3, k
         assert err(rows(have, pos), run["want"][k][pos]) <= TOL[run["dtype"]], k
+
+
+# --- as generation runs it: captured steps --------------------------------------------------------
+
+def build_served(vocab, seed, budget):
+    """Four requests as the scheduler would run them under a token budget, with given tokens
+    instead of sampled ones: every step carries the next token of each request whose prompt
+    is done (its logits wanted) and then one portion of the prompt in flight in the room
+    that is left (the logits of its last token wanted when the prompt ends there).  Steps of
+    single tokens replay the captured decode step (one, two, three and four requests: the
+    step for four also runs with three, padded); portions that fill more than half of the
+    budget replay the captured portion step; the rest are launched kernel by kernel."""
+    rng = np.random.default_rng(seed + 200)
+    prompt = dict(s0=90, s1=3, s2=130, s3=64)
+    total = dict(s0=90 + 40, s1=3 + 70, s2=130 + 25, s3=64 + 33)
+    toks = {k: rng.integers(0, vocab, n).tolist() for k, n in total.items()}
+    tb = TraceBuilder()
+    fed = {k: 0 for k in prompt}
+    waiting, running = list(prompt), []
+    while waiting or running:
+        entries, room = [], budget
+        for k in running:
+            if fed[k] >= prompt[k]:
+                entries.append((k, [toks[k][fed[k]]], [0]))
+                room -= 1
+        flying = [k for k in running if fed[k] < prompt[k]]
+        if not flying and waiting:
+            flying = [waiting.pop(0)]
+            running.append(flying[0])
+        if flying and room > 0:
+            k = flying[0]
+            n = min(room, prompt[k] - fed[k])
+            entries.append((k, toks[k][fed[k]:fed[k] + n], [n - 1] if fed[k] + n == prompt[k] else []))
+        for k, t, _ in entries:
+            fed[k] += len(t)
+        done = [k for k in running if fed[k] == total[k]]
+        tb.step(entries, end=done)
+        running = [k for k in running if k not in done]
+    return tb, toks
+
+
+@pytest.fixture(scope="module", params=PARAMS, ids=lambda p: f"{p[0]}-{p[1]}")
+def served(request, tmp_path_factory):
+    name, dtype = request.param
+    cfg, seed = CONFIGS[name]
+    model = write_model(tmp_path_factory.mktemp("models"), name)
+    V, ps = cfg["vocab_size"], PAGE_SIZES[name]
+    tb, toks = build_served(V, seed, 48)
+    kinds = [("decode" if all(len(e["tokens"]) == 1 for e in s["entries"]) else "portion") for s in tb.steps]
+    assert kinds.count("decode") >= 20 and kinds.count("portion") >= 6
+    captured = tb.collect(replay(model, dtype, tb.steps, 640, V, page_size=ps, graphs=True, step_tokens=48))
+    plain = tb.collect(replay(model, dtype, tb.steps, 640, V, page_size=ps))
+    want = {k: plain_logits(model, t) for k, t in toks.items()}
+    return dict(dtype=dtype, captured=captured, launched=plain, want=want)
+
+
+def test_captured_steps_give_the_plain_implementations_logits(served):
+    for k, have in served["captured"].items():
+        pos = sorted(have)
+        assert len(pos) >= 20, k
+        assert err(rows(have, pos), served["want"][k][pos]) <= TOL[served["dtype"]], k
+        if served["dtype"] == "float32":
+            assert (rows(have, pos).argmax(1) == served["want"][k][pos].argmax(1)).all(), k
+
+
+def test_captured_and_launched_steps_agree(served):
+    for k, have in served["captured"].items():
+        pos = sorted(have)
+        assert sorted(served["launched"][k]) == pos
+        assert err(rows(have, pos), rows(served["launched"][k], pos)) <= TOL_CUT[served["dtype"]], k
+
+
+# --- equal prefixes share pages (crates/pagedllm/tests/prefix.rs) ------------------------------------
+
+def build_shared(vocab, seed, ps):
+    """The reference's cases on pages of ``ps`` tokens, every request alone and ended before the
+    next starts, so that what it leaves behind is what the next one may take."""
+    rng = np.random.default_rng(seed + 300)
+    draw = lambda n: rng.integers(0, vocab, n).tolist()
+    tb, toks, expect = TraceBuilder(), {}, {}
+
+    def request(name, tokens, wanted, shares):
+        toks[name], expect[name] = tokens, shares
+        tb.step([(name, tokens, wanted)], end=[name])
+
+    # the same prompt twice: the second takes every page but the last (prefix.rs:88-107)
+    p = draw(50)
+    request("same1", p, [49], 0)
+    request("same2", p, [49], (50 - 1) // ps * ps)
+    # a common head of 32 tokens, then different tails (prefix.rs:115-139)
+    head = draw(32)
+    request("tail_a", head + draw(18), range(40, 50), 0)
+    request("tail_b", head + draw(18), range(40, 50), 32)
+    # the same page of tokens after a different first page is another page (prefix.rs:146-170)
+    middle = draw(ps)
+    request("after_x", draw(ps) + middle + [7], [2 * ps], 0)
+    request("after_y", draw(ps) + middle + [7], [2 * ps], 0)
+    # ... also when the first page is found, which takes three prompts to reach (prefix.rs:182-223)
+    head_a, head_c, mid = draw(ps), draw(ps), draw(ps)
+    request("other", head_c + mid + [7], [2 * ps], 0)
+    request("primer", head_a + draw(ps) + [7], [2 * ps], 0)
+    request("under_test", head_a + mid + [7], [2 * ps], ps)
+    return tb, toks, expect
+
+
+@pytest.fixture(scope="module", params=[(n, d) for n in ("A", "B") for d in ("float32", "bfloat16")],
+                ids=lambda p: f"{p[0]}-{p[1]}")
+def shared(request, tmp_path_factory):
+    name, dtype = request.param
+    cfg, seed = CONFIGS[name]
+    model = write_model(tmp_path_factory.mktemp("models"), name)
+    V, ps = cfg["vocab_size"], PAGE_SIZES[name]
+    tb, toks, expect = build_shared(V, seed, ps)
+    res = replay(model, dtype, tb.steps, 1024, V, page_size=ps, prefix_cache=True)
+    want = {k: plain_logits(model, t) for k, t in toks.items()}
+    return dict(dtype=dtype, got=tb.collect(res), prefix=res["prefix"], want=want, expect=expect, model=model, V=V, ps=ps)
+
+
+def test_requests_take_the_pages_of_equal_prefixes_and_only_those(shared):
+    assert shared["prefix"]["cached_tokens"] == shared["expect"]
+    assert shared["prefix"]["hits"] == sum(shared["expect"].values()) // shared["ps"]
+    assert shared["prefix"]["evictions"] == 0
+
+
+def test_logits_over_shared_pages_are_those_of_the_plain_implementation(shared):
+    for k, have in shared["got"].items():
+        pos = sorted(have)
+        assert err(rows(have, pos), shared["want"][k][pos]) <= TOL[shared["dtype"]], k
+    same1, same2 = shared["got"]["same1"][49], shared["got"]["same2"][49]
+    assert err(same2[None], same1[None]) <= TOL_CUT[shared["dtype"]]
+
+
+def test_a_prompt_answers_the_same_after_its_pages_lost_their_names(shared):
+    """prefix.rs:227-246: a pool that holds one prompt; a second prompt takes its pages and
+    their names with them; the first prompt, run again, is computed anew."""
+    V, ps = shared["V"], shared["ps"]
+    rng = np.random.default_rng(77)
+    p = rng.integers(0, V, 60).tolist()
+    other = [(t + 50) % V for t in p]
+    tb = TraceBuilder()
+    tb.step([("first", p, [59])], end=["first"])
+    tb.step([("other", other, [59])], end=["other"])
+    tb.step([("again", p, [59])], end=["again"])
+    res = replay(shared["model"], shared["dtype"], tb.steps, 64, V, page_size=ps, prefix_cache=True)
+    got = tb.collect(res)
+    assert res["prefix"]["evictions"] > 0
+    assert res["prefix"]["cached_tokens"]["other"] == 0
+    want = plain_logits(shared["model"], p)[59]
+    for k in ("first", "again"):
+        assert err(got[k][59][None], want[None]) <= TOL[shared["dtype"]], k
+    assert err(got["again"][59][None], got["first"][59][None]) <= TOL_CUT[shared["dtype"]]
 
 
 def test_trace_run_answers_step_by_step(tmp_path):

@@ -16,18 +16,30 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
 
 
-def replay(model_dir, dtype, steps, max_tokens, vocab):
-    """Run the steps through bin/trace_run in one process.  Returns {step: [wanted, vocab]}."""
+def replay(model_dir, dtype, steps, max_tokens, vocab, page_size=None, prefix_cache=False, graphs=False,
+           step_tokens=None):
+    """Run the steps through bin/trace_run in one process.  Returns {step: [wanted, vocab]};
+    with ``prefix_cache`` the key "prefix" holds what trace_run wrote about shared pages."""
     out = tempfile.mkdtemp(prefix="trace_out_")
     text = "".join(json.dumps(s) + "\n" for s in steps)
-    r = subprocess.run([sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", out,
-                        "--max-tokens", str(max_tokens)], input=text, capture_output=True, text=True, timeout=900)
+    cmd = [sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", out, "--max-tokens", str(max_tokens)]
+    if page_size is not None:
+        cmd += ["--page-size", str(page_size)]
+    if prefix_cache:
+        cmd += ["--prefix-cache", "on"]
+    if graphs:
+        cmd += ["--graphs", "on"] + (["--step-tokens", str(step_tokens)] if step_tokens else [])
+    r = subprocess.run(cmd, input=text, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, f"trace_run failed:\n{r.stdout[-2000:]}\n{r.stderr[-4000:]}"
     done = [l for l in r.stdout.splitlines() if l.startswith("done ")]
     assert [int(l.split()[1]) for l in done] == [s["step"] for s in steps]
     res = {}
     for f in os.listdir(out):
-        res[int(f[:-4])] = np.fromfile(os.path.join(out, f), dtype="<f4").reshape(-1, vocab)
+        if f.endswith(".f32"):
+            res[int(f[:-4])] = np.fromfile(os.path.join(out, f), dtype="<f4").reshape(-1, vocab)
+    if prefix_cache:
+        with open(os.path.join(out, "prefix.json")) as f:
+            res["prefix"] = json.load(f)
     return res
 
 
@@ -72,3 +84,8 @@ class TraceBuilder:
         for k, row, rid, pos in self.where:
             out.setdefault(rid, {})[pos] = results[k][row]
         return out
+
+    def retire(self, rid, new_name):
+        """Let a later request use the id ``rid`` again: what was collected under it so far is
+        kept under ``new_name``."""
+        self.where = [(k, row, new_name if r == rid else r, pos) for k, row, r, pos in self.where]
