@@ -9,8 +9,10 @@ size) form a group with pages, an allocator and tables of its own; a window
 group gives pages back as soon as the window has passed them.  Mixers that ask
 for a ``StateNeed`` get a slot of fixed size per request instead.
 
-One page holds ``page_size`` tokens of every layer of its group; layout of a
-layer's keys (and likewise values): [pages, kv_heads, page_size, head_dim].
+One page holds ``page_size`` tokens of every layer of its group.  How a page
+lies in memory is the need's business (``PagedNeed.pool_shape``): keys and
+values per kv head for a ``KVNeed`` (a layer's keys, and likewise values, as
+[pages, kv_heads, page_size, head_dim]), one row per token for a ``RowNeed``.
 """
 
 from __future__ import annotations
@@ -21,7 +23,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from ..errors import CacheError
-from ..parts.base import KVNeed, StateNeed
+from ..parts.base import PagedNeed, StateNeed
 from .allocator import BlockAllocator, block_hash
 
 FREED = -1  # a table entry whose page was given back (window groups only)
@@ -75,12 +77,11 @@ class BlockTable:
 
 @dataclass
 class CacheGroup:
-    need: KVNeed
+    need: PagedNeed
     entries: List[int]                 # schedule entries whose caches live here
     allocator: BlockAllocator
     page_size: int
-    pool: Optional[torch.Tensor] = None  # [entries, 2, pages, kv_heads, page_size, head_dim]
-    max_group_size: int = 1            # most query heads per kv head among the group's layers
+    pool: Optional[torch.Tensor] = None  # need.pool_shape(entries, pages, page_size)
 
     @property
     def window(self) -> Optional[int]:
@@ -103,9 +104,8 @@ class RequestCache:
 
 class CacheManager:
     def __init__(self, needs: Sequence[Optional[object]], page_size: int, num_pages: int, max_requests: int,
-                 dtype: torch.dtype, device, prefix_cache: bool = True, group_sizes: Optional[Sequence[int]] = None,
-                 allocate_device: bool = True):
-        """``needs[i]`` is what schedule entry i asks for (KVNeed, StateNeed or None).
+                 dtype: torch.dtype, device, prefix_cache: bool = True, allocate_device: bool = True):
+        """``needs[i]`` is what schedule entry i asks for (a PagedNeed, a StateNeed or None).
         Every group gets ``num_pages`` pages of ``page_size`` tokens."""
         if page_size < 1:
             raise CacheError("page_size must be at least 1")
@@ -116,7 +116,7 @@ class CacheManager:
         self._state_entries: Dict[int, StateNeed] = {}
         by_key: Dict[tuple, int] = {}
         for i, need in enumerate(needs):
-            if isinstance(need, KVNeed):
+            if isinstance(need, PagedNeed):
                 key = need.group_key()
                 if key not in by_key:
                     by_key[key] = len(self.groups)
@@ -124,8 +124,6 @@ class CacheManager:
                 g = self.groups[by_key[key]]
                 self._entry_group[i] = (by_key[key], len(g.entries))
                 g.entries.append(i)
-                if group_sizes is not None:
-                    g.max_group_size = max(g.max_group_size, int(group_sizes[i]))
             elif isinstance(need, StateNeed):
                 self._state_entries[i] = need
             elif need is not None:
@@ -141,27 +139,27 @@ class CacheManager:
             and all(g.window is None for g in self.groups)
         if allocate_device:
             for g in self.groups:
-                n = g.need
-                g.pool = torch.zeros((len(g.entries), 2, num_pages, n.num_kv_heads, page_size, n.head_dim),
-                                     dtype=dtype, device=device)
+                g.pool = torch.zeros(g.need.pool_shape(len(g.entries), num_pages, page_size),
+                                     dtype=g.need.dtype or dtype, device=device)
             for i, need in self._state_entries.items():
                 self._state[i] = torch.zeros((max_requests,) + tuple(need.shape), dtype=need.dtype, device=device)
 
     # -- what layers get -------------------------------------------------------------
     def layer_caches(self) -> List[object]:
-        """Per schedule entry what its mixer is handed: (k_pool, v_pool, group index),
-        a state tensor [max_requests, *shape], or None."""
+        """Per schedule entry what its mixer is handed: its view of the group's pool and the
+        group's number ((k_pool, v_pool, group) for a KVNeed), a state tensor
+        [max_requests, *shape], or None."""
         out: List[object] = [None] * self._n_entries
         for i, (gi, li) in self._entry_group.items():
-            pool = self.groups[gi].pool
-            out[i] = (pool[li, 0], pool[li, 1], gi) if pool is not None else (None, None, gi)
+            g = self.groups[gi]
+            out[i] = g.need.layer_view(g.pool, li) + (gi,) if g.pool is not None else (None, gi)
         for i, t in self._state.items():
             out[i] = t
         return out
 
     def bytes_per_token(self) -> int:
-        esz = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.entries) * 2 * g.need.num_kv_heads * g.need.head_dim * esz for g in self.groups)
+        return sum(len(g.entries) * g.need.bytes_per_token(torch.empty((), dtype=g.need.dtype or self.dtype).element_size())
+                   for g in self.groups)
 
     # -- requests ----------------------------------------------------------------------
     def open(self, request_id) -> RequestCache:

@@ -87,24 +87,6 @@ __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint3
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// Thread-block clusters: this CTA's rank, the barrier of all the cluster's threads, and a load from the
-// shared memory of the CTA of a given rank (at the same offset as `local` has here).
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release;\n" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire;\n" ::: "memory");
-}
-__device__ __forceinline__ float ld_cluster_f32(uint32_t local, uint32_t rank) {
-    uint32_t remote;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote) : "memory");
-    return v;
-}
 // An 8x8 block of 16-bit values held one row in four lanes, transposed across the warp.
 __device__ __forceinline__ uint32_t movmatrix_t(uint32_t a) {
     uint32_t d;
@@ -168,32 +150,20 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
     const int* __restrict__ block_tables, const AttnWork* __restrict__ work, const int* __restrict__ n_work_ptr,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     int nh, int nkv, int page_size, int page_shift, int n_pages, int table_width, float scale_log2,
-    int heads_per_cta, int kinds_mask, int* counters, int cluster_c, FusedQK fq, int* status) {
+    int heads_per_cta, int kinds_mask, FusedQK fq, int* status) {
     // The work items and block tables came from the host before the step, and the cache below
     // the step's own positions was written by earlier steps: neither depends on the kernels
     // just before this one.  So nobody waits for those kernels yet: the producer starts the
     // first tiles of old keys on their way at once, and waits only before a tile that may hold
     // a key of this step; the consumers wait before they read the queries.
-    //
-    // With cluster_c > 1 (single tokens only) the cluster_c CTAs of consecutive blockIdx.y form a cluster
-    // and hold the cluster_c items of one token, its key range cut in that many (some may be empty): they
-    // combine their partial results through one another's shared memory, no partial result goes through
-    // global memory and no kernel follows to add them up.  Every thread of such a CTA reaches the
-    // cluster's two barriers whatever happened to it before; whole clusters beyond the list leave here.
     if ((int)blockIdx.y >= *n_work_ptr) return;
-    AttnWork w = work[blockIdx.y];
-    const bool clustered = KEYS_AS_ROWS && cluster_c > 1;
-    bool bad_item = false;
-    if (!clustered) {
-        if (!(kinds_mask & (w.q_count == 1 ? 1 : 2))) return;   // another kernel's item
-        if (KEYS_AS_ROWS && w.q_count != 1) return;             // (this variant is for single tokens only)
-    }
-    if ((w.kv_begin & (TD_BK - 1)) || (clustered && w.q_count != 1)) {
+    const AttnWork w = work[blockIdx.y];
+    if (!(kinds_mask & (w.q_count == 1 ? 1 : 2))) return;   // another kernel's item
+    if (KEYS_AS_ROWS && w.q_count != 1) return;             // (this variant is for single tokens only)
+    if (w.kv_begin & (TD_BK - 1)) {
         // slabs and the swizzle need the range to start on a tile boundary
         if (threadIdx.x == 0) atomicOr(status, 32);
-        if (!clustered) return;
-        w = AttnWork{0, 0, 1, 0, 0, 0, -1, 0};   // nothing to read and (bad_item) nothing to write; the barriers are still kept
-        bad_item = true;
+        return;
     }
     const int group = nh / nkv;
     const int gparts = (group + heads_per_cta - 1) / heads_per_cta;
@@ -286,7 +256,6 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
                 }
             }
         }
-        if (clustered) { cluster_sync_all(); cluster_sync_all(); }   // the cluster's barriers count every thread
         return;
     }
 
@@ -357,8 +326,6 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
 
     float* o_s = reinterpret_cast<float*>(smem);          // [4][16][HD], once the ring is no longer read
     float* ml_s = o_s + TD_CONSUMERS * 16 * HD;           // [4][16][2]
-    float* c_o = ml_s + TD_CONSUMERS * 16 * 2 + TD_CONSUMERS * 128;   // [8][HD]: this CTA's result, for its cluster
-    float* c_ml = c_o + 8 * HD;                                       // [8][2]
     if constexpr (KEYS_AS_ROWS) {
     // ---- consumers, one query token of at most 8 heads: the KEYS are the 16 rows of the score block --------
     // and the heads its 8 columns, S^T = K q^T and O^T = V^T P^T.  A block of 16 keys costs 8 + HD / 16
@@ -468,9 +435,7 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
     asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
     if (*abort_flag) {
         if (threadIdx.x == 0) atomicOr(status, 16);
-        if (!clustered) return;
-        m_run[0] = m_run[1] = -CUDART_INF_F;   // counts for nothing; the status word says why
-        l_run[0] = l_run[1] = 0.f;
+        return;
     }
     // the four warps' results meet, head by head
     {
@@ -688,10 +653,7 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
             o += o_s[(size_t)(wi * 16 + r) * HD + c] * f;
         }
         const int head = head0 + r;
-        if (clustered) {
-            c_o[r * HD + c] = o;
-            if (c == 0) { c_ml[r * 2] = M; c_ml[r * 2 + 1] = L; }
-        } else if (w.part_slot < 0) {
+        if (w.part_slot < 0) {
             out[((size_t)w.q_token0 * nh + head) * HD + c] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
         } else {
             const size_t pr = (size_t)w.part_slot * nh + head;
@@ -701,102 +663,6 @@ __global__ void __launch_bounds__((TD_CONSUMERS + 1) * 32, 2) attention_decode_t
     }
     }
 
-    if (clustered) {
-        // ---- the cluster's CTAs hold the token's splits: each combines a share of the outputs -----------
-        // (rank j holds split j; they are added in that order whoever adds them)
-        cluster_sync_all();
-        const uint32_t rank = cluster_rank();
-        const int total = rows * HD;
-        const int per = (total + cluster_c - 1) / cluster_c;
-        const int stop = bad_item ? 0 : min(total, (int)(rank + 1) * per);
-        const uint32_t o_a = smem_u32(c_o), ml_a = smem_u32(c_ml);
-        for (int idx = (int)rank * per + threadIdx.x; idx < stop; idx += TD_CONSUMERS * 32) {
-            const int r = idx / HD, c = idx % HD;
-            float mj[8], M = -CUDART_INF_F;
-#pragma unroll
-            for (int j = 0; j < 8; j++) {
-                mj[j] = j < cluster_c ? ld_cluster_f32(ml_a + (r * 2) * 4, j) : -CUDART_INF_F;
-                M = fmaxf(M, mj[j]);
-            }
-            float L = 0.f, o = 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; j++) {
-                if (j >= cluster_c) break;
-                const float f = mj[j] == -CUDART_INF_F ? 0.f : exp2f(mj[j] - M);
-                L += ld_cluster_f32(ml_a + (r * 2 + 1) * 4, j) * f;
-                o += ld_cluster_f32(o_a + (r * HD + c) * 4, j) * f;
-            }
-            out[((size_t)w.q_token0 * nh + head0 + r) * HD + c] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
-        }
-        cluster_sync_all();   // nobody leaves while its results are being read
-        return;
-    }
-
-    // ---- the splits of a tile are combined by whichever of their CTAs finishes last ----------------
-    // (no kernel of its own for it, and no CTA waits for another: each adds one to the tile's
-    // counter after its partial results are out, and the one that brings it to the number of
-    // splits reads them all back, in the order of the splits whoever it is, with the arithmetic
-    // of attention_reduce_kernel.  It leaves the counter at zero for the next launch.)
-    if (counters == nullptr || w.part_slot < 0) return;
-    const int n_split = w.split >> 16, k_split = w.split & 0xffff;
-    int* last_s = reinterpret_cast<int*>(const_cast<int*>(abort_flag)) + 2;
-    __threadfence();
-    asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
-    if (threadIdx.x == 0) {
-        int* c = counters + (size_t)((int)blockIdx.y - k_split) * gridDim.x + blockIdx.x;
-        const int last = atomicAdd(c, 1) == n_split - 1;
-        if (last) *c = 0;
-        *last_s = last;
-    }
-    asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
-    if (!*last_s) return;
-    __threadfence();
-    float* wgt = reinterpret_cast<float*>(smem) + TD_CONSUMERS * 16 * HD + TD_CONSUMERS * 16 * 2 + warp * 128;   // [4][128]
-    const int first = w.part_slot - k_split * w.q_count, stride = w.q_count;
-    for (int r = warp; r < rows; r += TD_CONSUMERS) {
-        const int tq = r / n_heads, head = head0 + r % n_heads;
-        float M = -CUDART_INF_F;
-        for (int sp = lane; sp < n_split; sp += 32) M = fmaxf(M, __ldcg(part_ml + ((size_t)(first + sp * stride + tq) * nh + head) * 2));
-        M = warp_max(M);
-        float L = 0.f;
-        for (int sp = lane; sp < n_split; sp += 32) {
-            const size_t pr = (size_t)(first + sp * stride + tq) * nh + head;
-            const float ms = __ldcg(part_ml + pr * 2);
-            const float f = ms == -CUDART_INF_F ? 0.f : expf(ms - M);
-            wgt[sp] = f;
-            L += __ldcg(part_ml + pr * 2 + 1) * f;
-        }
-        L = warp_sum(L);
-        const float inv = L > 0.f ? 1.0f / L : 0.f;
-        __syncwarp();
-        // every lane owns HD / 32 outputs; the partial results of eight splits are fetched
-        // together (they come from L2, written by other SMs) and then added in the splits' order
-        constexpr int DPL = HD / 32;
-        float o[DPL];
-#pragma unroll
-        for (int j = 0; j < DPL; j++) o[j] = 0.f;
-        const float* po = part_o + ((size_t)(first + tq) * nh + head) * HD + lane;
-        const size_t sp_stride = (size_t)stride * nh * HD;
-        for (int sp0 = 0; sp0 < n_split; sp0 += 8) {
-            float v[8][DPL];
-#pragma unroll
-            for (int i = 0; i < 8; i++)
-#pragma unroll
-                for (int j = 0; j < DPL; j++)
-                    v[i][j] = sp0 + i < n_split ? __ldcg(po + (size_t)(sp0 + i) * sp_stride + 32 * j) : 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                if (sp0 + i >= n_split) break;
-                const float f = wgt[sp0 + i];
-#pragma unroll
-                for (int j = 0; j < DPL; j++) o[j] = fmaf(v[i][j], f, o[j]);
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < DPL; j++)
-            out[((size_t)(w.q_token0 + tq) * nh + head) * HD + lane + 32 * j] = __float2bfloat16_rn(o[j] * inv);
-        __syncwarp();
-    }
 }
 
 // Whether this kernel takes decode items of this shape and cache layout.
@@ -808,7 +674,7 @@ PLLM_EXPORT int pllm_attention_decode_tma_supports(int dtype, int nh, int nkv, i
 template <int HD>
 static int launch_tma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables, const int* work,
                       const int* n_work_ptr, int max_work, void* out, float* part_o, float* part_ml, int nh, int nkv,
-                      int page_size, int n_pages, int table_width, float scale, int kinds_mask, int* counters, int cluster_c,
+                      int page_size, int n_pages, int table_width, float scale, int kinds_mask,
                       FusedQK fq, int* status, cudaStream_t stream) {
     const int group = nh / nkv;
     const int heads_per_cta = group < 16 ? group : 16;
@@ -818,17 +684,6 @@ static int launch_tma(const void* q, const void* k_pool, const void* v_pool, con
     const size_t smem = (size_t)TD_STAGES * 2 * TD_BK * HD * 2 + TD_QROWS * HD * 2 + 16 * TD_STAGES + 16;
     const float scale_log2 = scale * 1.4426950408889634f;
     const dim3 block((TD_CONSUMERS + 1) * 32);
-    if (cluster_c > 1) {
-        // the list holds cluster_c items a token, one cluster each: single tokens of small groups only
-        if (group > 8 || kinds_mask != 1 || cluster_c > 8) return PLLM_ERR_SIZE;
-        const int rows_y = (max_work + cluster_c - 1) / cluster_c * cluster_c;
-        cudaFuncSetAttribute(attention_decode_tma_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_chained_cluster_y(attention_decode_tma_kernel<HD, true>, dim3(nkv * gparts, rows_y), block, smem, stream, cluster_c,
-                                 (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
-                                 n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
-                                 scale_log2, heads_per_cta, 1, (int*)nullptr, cluster_c, fq, status);
-        return launch_status();
-    }
     // single tokens of groups of at most 8 heads go to the variant with the keys as rows; what else the
     // caller asked for (several query tokens) to the other, as a launch of its own
     int rest = kinds_mask;
@@ -837,7 +692,7 @@ static int launch_tma(const void* q, const void* k_pool, const void* v_pool, con
         launch_chained(attention_decode_tma_kernel<HD, true>, dim3(nkv * gparts, max_work), block, smem,
                        stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
                        n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
-                       scale_log2, heads_per_cta, 1, counters, 0, fq, status);
+                       scale_log2, heads_per_cta, 1, fq, status);
         rest &= ~1;
     }
     if (rest) {
@@ -845,40 +700,32 @@ static int launch_tma(const void* q, const void* k_pool, const void* v_pool, con
         launch_chained(attention_decode_tma_kernel<HD, false>, dim3(nkv * gparts, max_work), block, smem,
                        stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, (const AttnWork*)work,
                        n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv, page_size, page_shift, n_pages, table_width,
-                       scale_log2, heads_per_cta, rest, counters, 0, fq, status);
+                       scale_log2, heads_per_cta, rest, fq, status);
     }
     return launch_status();
 }
 
 static int dispatch_tma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables, const int* work,
                         const int* n_work_ptr, int max_work, void* out, float* part_o, float* part_ml, int nh, int nkv,
-                        int hd, int page_size, int n_pages, int table_width, float scale, int kinds_mask, int* counters,
-                        int cluster_c, FusedQK fq, int* status, cudaStream_t stream) {
+                        int hd, int page_size, int n_pages, int table_width, float scale, int kinds_mask,
+                        FusedQK fq, int* status, cudaStream_t stream) {
     if (max_work <= 0) return PLLM_OK;
     if (!pllm_attention_decode_tma_supports(PLLM_BF16, nh, nkv, hd, page_size, 0)) return PLLM_ERR_SIZE;
     if (hd == 128)
         return launch_tma<128>(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv,
-                               page_size, n_pages, table_width, scale, kinds_mask, counters, cluster_c, fq, status, stream);
+                               page_size, n_pages, table_width, scale, kinds_mask, fq, status, stream);
     return launch_tma<64>(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv,
-                          page_size, n_pages, table_width, scale, kinds_mask, counters, cluster_c, fq, status, stream);
+                          page_size, n_pages, table_width, scale, kinds_mask, fq, status, stream);
 }
 
-// The largest cluster the kernel combines single tokens' splits in (0: it does not for this shape).
-PLLM_EXPORT int pllm_attention_decode_tma_max_cluster(int dtype, int nh, int nkv, int hd, int page_size, int window) {
-    if (!pllm_attention_decode_tma_supports(dtype, nh, nkv, hd, page_size, window)) return 0;
-    return nh / nkv <= 8 ? 8 : 0;
-}
-
-// cluster_c > 1: the list holds cluster_c items for every token (kinds_mask 1 only), combined inside the
-// kernel; part_o, part_ml and counters are not used then.
 PLLM_EXPORT int pllm_attention_decode_tma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables,
                                           const int* work, const int* n_work_ptr, int max_work, void* out,
                                           float* part_o, float* part_ml, int nh, int nkv, int hd, int page_size,
-                                          int n_pages, int table_width, float scale, int kinds_mask, int* counters,
-                                          int cluster_c, int* status, cudaStream_t stream) {
+                                          int n_pages, int table_width, float scale, int kinds_mask, int* status,
+                                          cudaStream_t stream) {
     FusedQK none = {};
     return dispatch_tma(q, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv, hd,
-                        page_size, n_pages, table_width, scale, kinds_mask, counters, cluster_c, none, status, stream);
+                        page_size, n_pages, table_width, scale, kinds_mask, none, status, stream);
 }
 
 // The same for a step of single decoded tokens, straight from the projection's output: the kernel
@@ -889,12 +736,11 @@ PLLM_EXPORT int pllm_attention_decode_tma_fused(const void* qkv, const float* q_
                                                 void* v_pool, const int* block_tables, const int* work,
                                                 const int* n_work_ptr, int max_work, void* out, float* part_o,
                                                 float* part_ml, int nh, int nkv, int hd, int page_size, int n_pages,
-                                                int table_width, float scale, int cluster_c, int* status,
-                                                cudaStream_t stream) {
+                                                int table_width, float scale, int* status, cudaStream_t stream) {
     if (qkv == nullptr || ((uintptr_t)qkv & 15)) return PLLM_ERR_ALIGN;
     FusedQK fq = {(const bf16*)qkv, q_gain, k_gain, cos_t, sin_t, (bf16*)k_pool, (bf16*)v_pool, eps, max_pos};
     return dispatch_tma(nullptr, k_pool, v_pool, block_tables, work, n_work_ptr, max_work, out, part_o, part_ml, nh, nkv, hd,
-                        page_size, n_pages, table_width, scale, 1, nullptr, cluster_c, fq, status, stream);
+                        page_size, n_pages, table_width, scale, 1, fq, status, stream);
 }
 
 PLLM_TRACE_EXPORT(attention_decode_tma)

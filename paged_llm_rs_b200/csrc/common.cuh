@@ -96,6 +96,18 @@ static inline int launch_status() {
     return e == cudaSuccess ? PLLM_OK : (int)e;
 }
 
+// Streaming multiprocessors of the current device (asked once; grids are sized by it).
+static inline int sm_count() {
+    static int count = 0;
+    if (count <= 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            return 148;       // (a B200; asked again next time)
+        count = n;
+    }
+    return count;
+}
+
 // ---- programmatic dependent launch -------------------------------------------------------
 // A decode step is a chain of a few hundred short kernels, each waiting for the one
 // before it.  Launched with the programmatic-serialization attribute, a kernel's CTAs

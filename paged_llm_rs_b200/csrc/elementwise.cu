@@ -16,6 +16,9 @@ int pllm_pdl_enabled = 0;
 
 // Switch programmatic dependent launch on (1) or off (0, the default) for every kernel
 // of the library; returns the former setting.
+// Streaming multiprocessors of the current device (what the kernels size their grids by).
+PLLM_EXPORT int pllm_sm_count() { return sm_count(); }
+
 PLLM_EXPORT int pllm_set_pdl(int on) {
     const int was = pllm_pdl_enabled;
     pllm_pdl_enabled = on ? 1 : 0;
@@ -235,12 +238,12 @@ PLLM_EXPORT int pllm_swiglu(int dtype, const void* in, void* out, int n_rows, in
         constexpr int N = Vec16<T>::N;
         if (inter % N == 0) {
             long long total = (long long)n_rows * (inter / N);
-            int blocks = (int)min((long long)148 * 16, (total + 255) / 256);
+            int blocks = (int)min((long long)sm_count() * 16, (total + 255) / 256);
             launch_chained(swiglu_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)in, (T*)out, inter, total,
                            inter / N);
         } else {
             long long total = (long long)n_rows * inter;
-            int blocks = (int)min((long long)148 * 16, (total + 255) / 256);
+            int blocks = (int)min((long long)sm_count() * 16, (total + 255) / 256);
             launch_chained(swiglu_scalar_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)in, (T*)out, inter,
                            total);
         }

@@ -14,20 +14,8 @@
 // deliver them: lane t (mod 4) holds k = 8t .. 8t+7 of both operands.
 // The warps of a CTA split K; their partial sums meet in shared memory.
 //
-// Two things a decode step does around its products are folded in, because at a
-// few rows every kernel costs its launch and a round trip through memory, not
-// its arithmetic:
-//   PRO = 1: x is the residual stream; the product is taken of
-//     rmsnorm(x + delta) * gain (crates/pagedllm/src/model/layers.rs:40-65 after
-//     the residual add of crates/pagedllm/src/model/mod.rs:131-132).  A warp's
-//     slice of K is then exactly 128 (K / 128 warps, so K <= 2048), and the step
-//     has at most 8 rows (the upper half of the 16-row operand is zero): with its
-//     weight loads in flight it forms h = x + delta (rounded to bfloat16, as the
-//     residual stream holds it) in registers and sums h^2; the warps exchange
-//     their sums through shared memory, and each then multiplies by
-//     h * (1/rms) * gain rounded to bfloat16, the very operand a norm kernel
-//     would have stored.  The first CTA stores h to residual_out, which must be
-//     a buffer of its own: the other CTAs still read x and delta.
+// One thing a decode step does after a product is folded in, because at a few rows
+// every kernel costs its launch and a round trip through memory, not its arithmetic:
 //   EPI = 1: W is [gate rows | up rows] of a gated feed-forward and y = silu(g) * u
 //     (crates/pagedllm/src/model/layers.rs:93-99): a CTA takes the same columns
 //     of both halves, so the activation needs neither a pass nor a buffer.
@@ -59,36 +47,9 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Two bfloat16 in each word.  h = x + d rounded to bfloat16 (x itself without d); its
-// squares are added to ss.
-__device__ __forceinline__ uint32_t add2(uint32_t x, uint32_t d, bool add, float& ss) {
-    float h0 = __uint_as_float(x << 16), h1 = __uint_as_float(x & 0xffff0000u);
-    if (add) {
-        h0 = __bfloat162float(__float2bfloat16_rn(h0 + __uint_as_float(d << 16)));
-        h1 = __bfloat162float(__float2bfloat16_rn(h1 + __uint_as_float(d & 0xffff0000u)));
-    }
-    ss += h0 * h0 + h1 * h1;
-    return (__float_as_uint(h0) >> 16) | (__float_as_uint(h1) & 0xffff0000u);
-}
-// h * inv * gain for the two values of a word, each rounded once.
-__device__ __forceinline__ uint32_t scale2(uint32_t h, float inv, float g0, float g1) {
-    __nv_bfloat162 a = __floats2bfloat162_rn(__uint_as_float(h << 16) * inv * g0,
-                                             __uint_as_float(h & 0xffff0000u) * inv * g1);
-    return *reinterpret_cast<uint32_t*>(&a);
-}
-
-// WMAX: the most warps a launch may have (16, or 8 with the promise of three CTAs to an SM,
-// which the forms with the norm need: a launch that fills the SMs only in a second wave
-// cannot start its weights while the kernel before it drains).
-template <int MT, int NT, int PRO, int EPI, typename OutT, int WMAX = 16>
-__global__ void __launch_bounds__(WMAX * 32, WMAX == 8 ? 3 : 1) skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w,
-                                                          OutT* __restrict__ y, int M, int N, int K,
-                                                          const bf16* delta, bf16* __restrict__ residual_out,
-                                                          const float* __restrict__ gain, float eps) {
-    static_assert(PRO == 0 || MT == 1, "the norm prologue is for up to 16 rows");
-    // PRO = 2 (the form that is launched): at most 8 rows, so that the upper half of the A
-    // operand is zero and costs no registers
-    constexpr int HS = PRO == 2 ? 1 : 2;
+template <int MT, int NT, int EPI, typename OutT>
+__global__ void __launch_bounds__(16 * 32, 1) skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w,
+                                                                 OutT* __restrict__ y, int M, int N, int K) {
     static_assert(!EPI || NT % 2 == 0, "the gated epilogue pairs tiles of gate and up");
     // k blocks of 32 whose loads are issued together
     constexpr int U = MT == 1 ? 4 : (MT == 2 ? 2 : 1);
@@ -123,78 +84,7 @@ __global__ void __launch_bounds__(WMAX * 32, WMAX == 8 ? 3 : 1) skinny_gemm_kern
             xrow[a][h] = x + (size_t)(xok[a][h] ? m : 0) * K + t * 8;
         }
     extern __shared__ float red[];  // [warps][MT*16][NT*8]
-    __shared__ float ssq[16][16];   // [warp][row]: sums of h^2 over the warp's slice of K
 
-    if constexpr (PRO) {
-        // ---- one group of 128 values of k a warp: add, norm and product -------------------------
-        const bool add = delta != nullptr;
-        const bool keep = residual_out != nullptr && blockIdx.x == 0;
-        uint4 wf[4][NT], hf[4][HS];
-#pragma unroll
-        for (int u = 0; u < 4; u++)
-#pragma unroll
-            for (int b = 0; b < NT; b++) wf[u][b] = ld_stream16(wrow[b] + k_begin + 32 * u);
-        if (PLLM_SKINNY_EARLY) pdl_launch_dependents();
-        pdl_wait(KID_GEMM);   // the weights do not depend on the kernel before this one; x and delta do
-        float ss[HS];
-        {
-            uint4 df[4][HS];
-#pragma unroll
-            for (int u = 0; u < 4; u++)
-#pragma unroll
-                for (int h = 0; h < HS; h++) {
-                    hf[u][h] = df[u][h] = make_uint4(0, 0, 0, 0);
-                    if (xok[0][h]) {
-                        hf[u][h] = ld_cached16(xrow[0][h] + k_begin + 32 * u);
-                        if (add) df[u][h] = ld_cached16(delta + (xrow[0][h] - x) + k_begin + 32 * u);
-                    }
-                }
-#pragma unroll
-            for (int h = 0; h < HS; h++) ss[h] = 0.f;
-#pragma unroll
-            for (int u = 0; u < 4; u++)
-#pragma unroll
-                for (int h = 0; h < HS; h++) {
-                    hf[u][h] = make_uint4(add2(hf[u][h].x, df[u][h].x, add, ss[h]), add2(hf[u][h].y, df[u][h].y, add, ss[h]),
-                                          add2(hf[u][h].z, df[u][h].z, add, ss[h]), add2(hf[u][h].w, df[u][h].w, add, ss[h]));
-                    if (keep && xok[0][h])
-                        *reinterpret_cast<uint4*>(residual_out + (size_t)(h * 8 + r) * K + k_begin + 32 * u + t * 8) = hf[u][h];
-                }
-        }
-#pragma unroll
-        for (int h = 0; h < HS; h++) {
-            float v = ss[h];
-            v += __shfl_xor_sync(0xffffffffu, v, 1);
-            v += __shfl_xor_sync(0xffffffffu, v, 2);
-            if (t == 0) ssq[warp][h * 8 + r] = v;
-        }
-        __syncthreads();
-        float inv[HS];
-#pragma unroll
-        for (int h = 0; h < HS; h++) {
-            float tot = 0.f;
-            for (int wi = 0; wi < ks_count; wi++) tot += ssq[wi][h * 8 + r];  // fixed order
-            inv[h] = 1.0f / sqrtf(tot / (float)K + eps);
-        }
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-            // the gain is fetched only now (it is in L1 or L2): held across the barrier it would
-            // cost the registers that let a fourth CTA onto the SM
-            const float4 g0 = __ldg(reinterpret_cast<const float4*>(gain + k_begin + 32 * u + t * 8));
-            const float4 g1 = __ldg(reinterpret_cast<const float4*>(gain + k_begin + 32 * u + t * 8 + 4));
-            const uint4 xa = make_uint4(scale2(hf[u][0].x, inv[0], g0.x, g0.y), scale2(hf[u][0].y, inv[0], g0.z, g0.w),
-                                        scale2(hf[u][0].z, inv[0], g1.x, g1.y), scale2(hf[u][0].w, inv[0], g1.z, g1.w));
-            uint4 xb = make_uint4(0, 0, 0, 0);
-            if (HS == 2)
-                xb = make_uint4(scale2(hf[u][HS - 1].x, inv[HS - 1], g0.x, g0.y), scale2(hf[u][HS - 1].y, inv[HS - 1], g0.z, g0.w),
-                                scale2(hf[u][HS - 1].z, inv[HS - 1], g1.x, g1.y), scale2(hf[u][HS - 1].w, inv[HS - 1], g1.z, g1.w));
-#pragma unroll
-            for (int b = 0; b < NT; b++) {
-                mma16816(acc[0][b], xa.x, xb.x, xa.y, xb.y, wf[u][b].x, wf[u][b].y);
-                mma16816(acc[0][b], xa.z, xb.z, xa.w, xb.w, wf[u][b].z, wf[u][b].w);
-            }
-        }
-    } else {
     for (int kb = k_begin; kb < k_end; kb += 32 * U) {
         // every load of the group is issued before the first is used: one trip to memory, not U
         uint4 wf[U][NT], xf[U][MT][2];
@@ -227,7 +117,6 @@ __global__ void __launch_bounds__(WMAX * 32, WMAX == 8 ? 3 : 1) skinny_gemm_kern
                 }
             }
         }
-    }
     }
 
     if (!PLLM_SKINNY_EARLY) pdl_launch_dependents();   // the weights are read: the next kernel may start on its own
@@ -291,33 +180,28 @@ PLLM_EXPORT int pllm_skinny_gemm_set_tiles(int nt) {
 PLLM_EXPORT int pllm_skinny_gemm_supports(int M, int N, int K) {
     return M >= 1 && M <= 64 && N % 16 == 0 && K % 128 == 0 && N >= 16 && K >= 128;
 }
-// The same for the forms with the norm before or the gate after (N: columns of y).
-// With the norm every warp holds a slice of exactly 128 values of k, so K is at most 16 x 128;
-// and at most 8 rows, since with 16 the operand's registers leave too few CTAs on an SM
-// (measured 10.3 us against 6.6 us for the norm kernel followed by the plain product).
-PLLM_EXPORT int pllm_skinny_gemm_fused_supports(int M, int N, int K, int normed) {
-    return M >= 1 && M <= 16 && N % 16 == 0 && K % 128 == 0 && N >= 16 && K >= 128 && (!normed || (K <= 2048 && M <= 8));
+// The same for the form with the gate after (N: columns of y).
+PLLM_EXPORT int pllm_skinny_gemm_glu_supports(int M, int N, int K) {
+    return M >= 1 && M <= 16 && N % 16 == 0 && K % 128 == 0 && N >= 16 && K >= 128;
 }
 
-template <int MT, int NT, int PRO, int EPI, typename OutT, int WMAX = 16>
-static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, int warps, const void* delta,
-                         void* residual_out, const float* gain, float eps, cudaStream_t stream) {
+template <int MT, int NT, int EPI, typename OutT>
+static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, int warps, cudaStream_t stream) {
     const size_t smem = (warps > 1 || EPI) ? (size_t)warps * MT * 16 * NT * 8 * sizeof(float) : 0;
     if (smem > 48 * 1024)
-        cudaFuncSetAttribute(skinny_gemm_kernel<MT, NT, PRO, EPI, OutT, WMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem);
+        cudaFuncSetAttribute(skinny_gemm_kernel<MT, NT, EPI, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     constexpr int out_cols = EPI ? 4 * NT : 8 * NT;
-    launch_chained(skinny_gemm_kernel<MT, NT, PRO, EPI, OutT, WMAX>, dim3(N / out_cols), dim3(warps * 32), smem, stream,
-                   (const bf16*)x, (const bf16*)w, (OutT*)y, M, N, K, (const bf16*)delta, (bf16*)residual_out, gain, eps);
+    launch_chained(skinny_gemm_kernel<MT, NT, EPI, OutT>, dim3(N / out_cols), dim3(warps * 32), smem, stream,
+                   (const bf16*)x, (const bf16*)w, (OutT*)y, M, N, K);
     return launch_status();
 }
 
 template <int NT, typename OutT>
 static int pick_mt(const void* x, const void* w, void* y, int M, int N, int K, int warps, cudaStream_t s) {
-    if (M <= 16) return launch_skinny<1, NT, 0, 0, OutT>(x, w, y, M, N, K, warps, nullptr, nullptr, nullptr, 0.f, s);
-    if (M <= 32) return launch_skinny<2, NT, 0, 0, OutT>(x, w, y, M, N, K, warps, nullptr, nullptr, nullptr, 0.f, s);
-    if (M <= 48) return launch_skinny<3, NT, 0, 0, OutT>(x, w, y, M, N, K, warps, nullptr, nullptr, nullptr, 0.f, s);
-    return launch_skinny<4, NT, 0, 0, OutT>(x, w, y, M, N, K, warps, nullptr, nullptr, nullptr, 0.f, s);
+    if (M <= 16) return launch_skinny<1, NT, 0, OutT>(x, w, y, M, N, K, warps, s);
+    if (M <= 32) return launch_skinny<2, NT, 0, OutT>(x, w, y, M, N, K, warps, s);
+    if (M <= 48) return launch_skinny<3, NT, 0, OutT>(x, w, y, M, N, K, warps, s);
+    return launch_skinny<4, NT, 0, OutT>(x, w, y, M, N, K, warps, s);
 }
 
 // K is split over the warps of a CTA.  A warp's loads of ``slice`` values of k are all
@@ -328,7 +212,7 @@ static int pick_mt(const void* x, const void* w, void* y, int M, int N, int K, i
 static int pick_warps(int K, int ctas, int slice) {
     int warps = 1;
     for (int wv = 2; wv <= 16; wv++)
-        if (K % (wv * 32) == 0 && K / wv >= slice && (long long)ctas * wv <= 148LL * 64) warps = wv;
+        if (K % (wv * 32) == 0 && K / wv >= slice && (long long)ctas * wv <= (long long)sm_count() * 64) warps = wv;
     if (g_skinny_warps_override > 0 && g_skinny_warps_override <= 16 && K % (g_skinny_warps_override * 32) == 0)
         warps = g_skinny_warps_override;
     return warps;
@@ -343,41 +227,24 @@ PLLM_EXPORT int pllm_skinny_gemm(const void* x, const void* w, void* y, int M, i
     // (With long rows, K >= 4096, a CTA has work enough for one tile of 16 to an SM to do, and every CTA reads
     // all of x from L2, as many bytes as 8 rows of W: measured at 8 rows, 4096 x 12288, 34.8 us with tiles of 8
     // and 26.6 with tiles of 16; 4096 x 4096, 19.5 and 16.4.)
-    int nt = (N / 16 >= 2 * 148 || (K >= 4096 && N / 16 >= 148)) ? 2 : 1;
+    const int sms = sm_count();
+    int nt = (N / 16 >= 2 * sms || (K >= 4096 && N / 16 >= sms)) ? 2 : 1;
     if (g_skinny_nt_override && N % (8 * g_skinny_nt_override) == 0 && (g_skinny_nt_override < 4 || M <= 16)) nt = g_skinny_nt_override;
     const int warps = pick_warps(K, N / (8 * nt), 128);
     if (nt == 4)
-        return out_f32 ? launch_skinny<1, 4, 0, 0, float>(x, w, y, M, N, K, warps, nullptr, nullptr, nullptr, 0.f, stream)
-                       : launch_skinny<1, 4, 0, 0, bf16>(x, w, y, M, N, K, warps, nullptr, nullptr, nullptr, 0.f, stream);
+        return out_f32 ? launch_skinny<1, 4, 0, float>(x, w, y, M, N, K, warps, stream)
+                       : launch_skinny<1, 4, 0, bf16>(x, w, y, M, N, K, warps, stream);
     if (out_f32)
         return nt == 2 ? pick_mt<2, float>(x, w, y, M, N, K, warps, stream) : pick_mt<1, float>(x, w, y, M, N, K, warps, stream);
     return nt == 2 ? pick_mt<2, bf16>(x, w, y, M, N, K, warps, stream) : pick_mt<1, bf16>(x, w, y, M, N, K, warps, stream);
 }
 
-// The forms with work folded in, for up to 16 rows, all bfloat16:
-//   gain != null (up to 8 rows, K <= 2048): y = (rmsnorm(x + delta) * gain) . W^T; delta may be null (no add);
-//     residual_out (may be null) receives x + delta and must not overlap x or delta.
-//   glu != 0: w is [2N, K], gate rows then up rows, and y[M, N] = silu(gate) * up.
-PLLM_EXPORT int pllm_skinny_gemm_fused(const void* x, const void* delta, void* residual_out, const float* gain, float eps,
-                                       const void* w, void* y, int M, int N, int K, int glu, cudaStream_t stream) {
-    if (!pllm_skinny_gemm_fused_supports(M, N, K, gain != nullptr)) return PLLM_ERR_SIZE;
-    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)delta | (uintptr_t)residual_out | (uintptr_t)gain) & 15)
-        return PLLM_ERR_ALIGN;
-    if (residual_out && (residual_out == x || residual_out == delta)) return PLLM_ERR_ALIGN;
-    const int pro = gain != nullptr;
-    if (!pro && !glu) return pllm_skinny_gemm(x, w, y, M, N, K, 0, stream);
-    // With the norm a CTA needs more registers and three fit an SM: tiles of 16 rows of W as
-    // soon as tiles of 8 would not all be resident at once.
-    const int nt = glu ? 2 : ((pro ? N / 8 > 3 * 148 : N / 16 >= 2 * 148) ? 2 : 1);
-    const int ctas = glu ? N / 8 : N / (8 * nt);
-    const int warps = pro ? K / 128 : pick_warps(K, ctas, 128);
-    if (!pro) return launch_skinny<1, 2, 0, 1, bf16>(x, w, y, M, N, K, warps, nullptr, nullptr, nullptr, 0.f, stream);
-#define PLLM_SKINNY_PRO(NT_, EPI_)                                                                                     \
-    (warps <= 8 ? launch_skinny<1, NT_, 2, EPI_, bf16, 8>(x, w, y, M, N, K, warps, delta, residual_out, gain, eps, stream) \
-                : launch_skinny<1, NT_, 2, EPI_, bf16>(x, w, y, M, N, K, warps, delta, residual_out, gain, eps, stream))
-    if (glu) return PLLM_SKINNY_PRO(2, 1);
-    return nt == 2 ? PLLM_SKINNY_PRO(2, 0) : PLLM_SKINNY_PRO(1, 0);
-#undef PLLM_SKINNY_PRO
+// w is [2N, K], gate rows then up rows, and y[M, N] = silu(x Wg^T) * (x Wu^T); up to 16 rows, all bfloat16.
+PLLM_EXPORT int pllm_skinny_gemm_glu(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
+    if (!pllm_skinny_gemm_glu_supports(M, N, K)) return PLLM_ERR_SIZE;
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return PLLM_ERR_ALIGN;
+    const int warps = pick_warps(K, N / 8, 128);
+    return launch_skinny<1, 2, 1, bf16>(x, w, y, M, N, K, warps, stream);
 }
 
 PLLM_TRACE_EXPORT(skinny_gemm)

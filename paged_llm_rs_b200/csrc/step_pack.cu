@@ -19,7 +19,7 @@ struct PllmGroupPack {
     int window;                 // 0: every key stays
     int ctas_per_item;          // CTAs the attention kernel launches per work item
     int max_work, max_red, max_parts;                                    // capacities of the captured step
-    int cluster;                // > 1: that many items for every request, combined inside the attention kernel
+    int plans;                  // 0: the group's mixers take no attention work items (the offsets of work and red are unused)
     int off_slots, off_tables, off_n_work, off_n_red, off_work, off_red; // offsets in int32 units
 };
 
@@ -77,6 +77,7 @@ PLLM_EXPORT int pllm_pack_decode_step(int* out, int out_len, int n, const int* t
             if (page < 0) { *err_request = i; return PLLM_PACK_FREED_PAGE; }
             slots[i] = page * page_size + p0 % page_size;
         }
+        if (!g.plans) continue;
         // ---- the attention work items: one tile a request, cut into splits when the step has
         // too few tiles to fill the GPU (kernels/attention_plan.py: plan_attention) -------------
         int* work = out + g.off_work;
@@ -92,25 +93,6 @@ PLLM_EXPORT int pllm_pack_decode_step(int* out, int out_len, int n, const int* t
             const int kv_end = p0 + 1;
             const int kv_begin = g.window > 0 ? (p0 - (g.window - 1) > 0 ? p0 - (g.window - 1) : 0) : 0;
             const int keys = kv_end - kv_begin;
-            if (g.cluster > 1) {
-                // exactly g.cluster items: as many as the range is worth hold keys, the rest are empty
-                int splits = keys / min_split_keys < g.cluster ? keys / min_split_keys : g.cluster;
-                if (splits < 1) splits = 1;
-                const int chunk = ceil_div(ceil_div(keys, splits), SPLIT_ALIGN) * SPLIT_ALIGN;
-                const int stop = ceil_div(kv_end, SPLIT_ALIGN) * SPLIT_ALIGN;
-                if (n_work + g.cluster > g.max_work) { *err_request = i; return PLLM_PACK_WORK; }
-                for (int k = 0; k < g.cluster; k++) {
-                    int* w = work + 8 * (n_work + k);
-                    int begin = kv_begin + k * chunk;
-                    if (begin > stop) begin = stop;
-                    int end = begin + chunk < kv_end ? begin + chunk : kv_end;
-                    if (end < begin) end = begin;
-                    w[0] = i; w[1] = i; w[2] = 1; w[3] = p0;
-                    w[4] = begin; w[5] = end; w[6] = -1; w[7] = (g.cluster << 16) | k;
-                }
-                n_work += g.cluster;
-                continue;
-            }
             int splits = 1;
             if (want > 1) {
                 splits = keys / min_split_keys < want ? keys / min_split_keys : want;

@@ -23,14 +23,13 @@ from ..cache.manager import CacheManager
 from ..config.registry import load_config
 from ..errors import ConfigError, KernelError
 from ..kernels import attention_plan, ops
-from ..parts.base import KVNeed, Runtime
+from ..parts.base import PagedNeed, Runtime
 from ..parts.decoder import DecoderModel
 from ..weights.loader import load_weights
 from .step import GroupPlanConfig, NativeDecodePacker, StepCaps, StepEntry, StepPacker
 
 DTYPES = {"float32": torch.float32, "f32": torch.float32, "fp32": torch.float32,
           "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
-SM_COUNT_TARGET = 2 * 148  # CTAs an attention launch should have before splits stop: one full wave at two CTAs an SM
 
 
 def parse_dtype(name) -> torch.dtype:
@@ -59,14 +58,14 @@ class _DecodeGraph:
         self.decode = segments is None
         n_seg = B if self.decode else segments
         self.caps = StepCaps(tokens=B, wanted=n_seg, segments=n_seg, table_width=W, kinds=1 if self.decode else 3)
-        self.work_caps = [attention_plan.plan_limits(B, p.tile_tokens, pk.target_ctas, p.ctas_per_item, n_seg)
+        self.work_caps = [None if p is None else attention_plan.plan_limits(B, p.tile_tokens, pk.target_ctas, p.ctas_per_item, n_seg)
                           for p in pk.plans]
-        host, self.layout, self.sizes = pk.pack([], runner._heads, self.caps, self.work_caps)
+        host, self.layout, self.sizes = pk.pack([], self.caps, self.work_caps)
         self.pinned = torch.from_numpy(host.copy()).pin_memory()
         self.native = NativeDecodePacker(pk, self.caps, self.work_caps, self.layout, self.pinned.numpy()) if self.decode else None
         self.dev = self.pinned.to(runner.device)
         self.nbytes = host.nbytes
-        self.state = pk.to_state(self.dev, self.layout, self.sizes, runner._heads, full=True)
+        self.state = pk.to_state(self.dev, self.layout, self.sizes, full=True)
         self.tokens = torch.zeros(1 + n_seg, dtype=torch.int32, device=runner.device)
         # the status word and the chosen tokens come back by a copy that is part of the captured step
         self.tokens_host = torch.zeros(1 + n_seg, dtype=torch.int32).pin_memory()
@@ -163,11 +162,11 @@ class _DecodeGraph:
             if self.native is not None:
                 self.native.pack(entries, temperature, uniform)     # straight into the pinned buffer
             else:
-                host, _, _ = r.packer.pack(entries, r._heads, self.caps, self.work_caps, temperature, uniform)
+                host, _, _ = r.packer.pack(entries, self.caps, self.work_caps, temperature, uniform)
                 self.pinned.numpy()[:] = host
             self._replay()
         else:
-            host, _, _ = r.packer.pack(entries, r._heads, self.caps, self.work_caps, temperature, uniform)
+            host, _, _ = r.packer.pack(entries, self.caps, self.work_caps, temperature, uniform)
             i = self._turn
             self._turn = (i + 1) % len(self._pinned)
             if self._copy_pending[i]:
@@ -207,10 +206,6 @@ class ModelRunner:
             self.model.bind(tensors)
             del tensors
         needs = self.model.cache_needs()
-        group_sizes = []
-        for e, need in zip(self.model.schedule, needs):
-            m = self.model.blocks[e.layer].mixer
-            group_sizes.append(getattr(m, "nh", 1) // max(1, getattr(m, "nkv", 1)) if isinstance(need, KVNeed) else 1)
         probe = CacheManager(needs, page_size, 1, 1, self.dtype, self.device, allocate_device=False)
         if num_pages is None:
             if cache_bytes is None:
@@ -218,20 +213,19 @@ class ModelRunner:
             # pages = budget / bytes per page, at least one (crates/pagedllm/src/batch.rs:53-57)
             num_pages = max(1, cache_bytes // max(1, page_size * probe.bytes_per_token()))
         self.cache = CacheManager(needs, page_size, num_pages, max_requests, self.dtype, self.device,
-                                  prefix_cache=prefix_cache, group_sizes=group_sizes)
+                                  prefix_cache=prefix_cache)
         self.caches = self.cache.layer_caches()
-        plans, self._heads = [], []
+        # How each group's attention is cut into work items is what its mixers wish (those of one group alike);
+        # a group whose mixers wish for nothing gets tables and slots only.
+        plans = []
         for g in self.cache.groups:
-            nkv = g.need.num_kv_heads
-            nh = nkv * g.max_group_size
-            tile = ops.attention_tile_tokens(nh, nkv, self.dtype, g.need.head_dim, page_size, g.window or 0)
-            gparts = -(-g.max_group_size // 16)
-            limit = min((self.model.blocks[self.model.schedule[i].layer].mixer.cluster_limit(page_size) for i in g.entries),
-                        default=0)
-            plans.append(GroupPlanConfig(tile, nkv * gparts, g.window, limit))
-            nh_max = max(getattr(self.model.blocks[self.model.schedule[i].layer].mixer, "nh", nh) for i in g.entries)
-            self._heads.append((nh_max, g.need.head_dim))
-        self.packer = StepPacker(self.cache, plans, SM_COUNT_TARGET, self.spec.vocab_size, self.spec.max_positions,
+            wishes = {self.model.blocks[self.model.schedule[i].layer].mixer.plan_wish(page_size) for i in g.entries}
+            if len(wishes) != 1:
+                raise ConfigError(f"the mixers that share a cache group wish for different attention plans: {sorted(map(str, wishes))}")
+            w = wishes.pop()
+            plans.append(None if w is None else GroupPlanConfig(w.tile_tokens, w.ctas_per_item, g.window, w.heads, w.head_dim))
+        # CTAs an attention launch should have before splits stop: one full wave at two CTAs an SM
+        self.packer = StepPacker(self.cache, plans, 2 * ops.sm_count(), self.spec.vocab_size, self.spec.max_positions,
                                  self.device)
         self.vocab_size = self.spec.vocab_size
         # A captured step replays fixed launches; a mixer that loops over the step on the
@@ -279,11 +273,11 @@ class ModelRunner:
                 g = self._portion_graph(entries)
             if g is not None:
                 return g.run(entries, temperature, uniform)
-        host, layout, sizes = self.packer.pack(entries, self._heads, temperature=temperature, uniform=uniform)
+        host, layout, sizes = self.packer.pack(entries, temperature=temperature, uniform=uniform)
         pinned = torch.from_numpy(host).pin_memory()
         dev = pinned.to(self.device, non_blocking=True)
         self.bytes_h2d = host.nbytes
-        state = self.packer.to_state(dev, layout, sizes, self._heads)
+        state = self.packer.to_state(dev, layout, sizes)
         tokens = None
         before = ops.LAUNCHES
         with torch.no_grad():

@@ -23,7 +23,7 @@ import torch
 from ..cache.manager import CacheManager, RequestCache
 from ..errors import CacheError, ConfigError
 from ..kernels import attention_plan
-from ..parts.base import GroupStep, StepState
+from ..parts.base import AttentionWork, GroupStep, StepState
 
 
 @dataclass
@@ -38,10 +38,14 @@ class StepEntry:
 
 @dataclass
 class GroupPlanConfig:
+    """How a cache group's attention is cut into work items (what its mixers wished: Mixer.plan_wish).
+    A group whose mixers read no work items has None in its place."""
+
     tile_tokens: int      # query tokens per attention work item
     ctas_per_item: int    # CTAs the kernel launches per item (kv heads x group parts)
     window: Optional[int]
-    max_cluster: int = 0  # items of one single token the kernel can combine in a thread-block cluster (0: none)
+    heads: int = 1        # partial results of split items are [rows, heads, head_dim]
+    head_dim: int = 1
 
 
 @dataclass
@@ -54,49 +58,30 @@ class StepCaps:
     segments: int
     table_width: int
     kinds: int = 1        # what the captured step's attention items may be (1: single tokens only, 3: anything)
-    # (a captured step of single tokens cuts its attention for ``tokens`` requests however many it holds: the
-    # cluster size is part of the launch)
 
 
 class StepPacker:
     """Lays out and fills the packed buffer of a step."""
 
-    def __init__(self, cache: CacheManager, plans: List[GroupPlanConfig], target_ctas: int, vocab_size: int,
+    def __init__(self, cache: CacheManager, plans: List[Optional[GroupPlanConfig]], target_ctas: int, vocab_size: int,
                  max_positions: int, device):
         self.cache, self.plans, self.target_ctas = cache, plans, target_ctas
         self.vocab_size, self.max_positions, self.device = vocab_size, max_positions, device
         self._scratch: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
-        self._counters: Dict[int, torch.Tensor] = {}
 
-    def scratch(self, gi: int, parts: int, nh_hd: Tuple[int, int]) -> Tuple[torch.Tensor, torch.Tensor]:
+    def scratch(self, gi: int, parts: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """Partial-result buffers of group gi for at least ``parts`` rows."""
-        nh, hd = nh_hd
+        nh, hd = self.plans[gi].heads, self.plans[gi].head_dim
         cur = self._scratch.get(gi)
-        if cur is None or cur[0].shape[0] < parts or cur[0].shape[1] != nh or cur[0].shape[2] != hd:
+        if cur is None or cur[0].shape[0] < parts:
             rows = max(parts, 1)
             cur = (torch.empty((rows, nh, hd), dtype=torch.float32, device=self.device),
                    torch.empty((rows, nh, 2), dtype=torch.float32, device=self.device))
             self._scratch[gi] = cur
         return cur
 
-    def cluster_for(self, gi: int, n_tokens: int) -> int:
-        """Items every token of a step of ``n_tokens`` single tokens gets in group gi, when the
-        group's kernel combines them in a cluster (0: the step is planned for the reduction kernel)."""
-        plan = self.plans[gi]
-        return attention_plan.decode_cluster(n_tokens, plan.ctas_per_item, self.target_ctas, plan.max_cluster)
-
-    def counters(self, gi: int, max_work: int) -> torch.Tensor:
-        """Zeros for the kernel that combines split items itself (one per work item and CTA of
-        it); the kernel leaves them zero, so they are made once and grown when needed."""
-        n = max(max_work, 1) * self.plans[gi].ctas_per_item
-        cur = self._counters.get(gi)
-        if cur is None or cur.numel() < n:
-            cur = torch.zeros(n, dtype=torch.int32, device=self.device)
-            self._counters[gi] = cur
-        return cur
-
-    def pack(self, entries: Sequence[StepEntry], heads: List[Tuple[int, int]],
-             caps: Optional[StepCaps] = None, work_caps: Optional[List[Tuple[int, int, int]]] = None,
+    def pack(self, entries: Sequence[StepEntry],
+             caps: Optional[StepCaps] = None, work_caps: Optional[List[Optional[Tuple[int, int, int]]]] = None,
              temperature: Optional[Sequence[float]] = None, uniform: Optional[Sequence[float]] = None):
         """Returns (host int32 array, layout dict, sizes) for the entries.  Pages
         must already be reserved for every token.  ``temperature`` / ``uniform``
@@ -169,24 +154,20 @@ class StepPacker:
                         raise CacheError(f"request {rc.request_id!r} writes into a page it gave back")
                     slots[t0:t0 + n] = page * ps + pp % ps
             plan = self.plans[gi]
-            # a step of single tokens whose splits the kernel combines in clusters: of the captured step's
-            # size when it is one (the cluster is part of its launches), else of this step's
-            cluster = 0
-            if caps is not None and caps.kinds == 1:
-                cluster = self.cluster_for(gi, caps.tokens)
-            elif caps is None and segs and all(n == 1 for (_, n, _, _) in segs):
-                cluster = self.cluster_for(gi, n_seg)
+            if plan is None:        # the group's mixers read tables and slots only
+                group_parts.append((slots, tables, None, None, 0, 0, 0, W))
+                continue
             # groups that cut their work alike (same tile, window, CTAs an item) share one plan
-            key = (plan.tile_tokens, plan.window, plan.ctas_per_item, cluster)
+            key = (plan.tile_tokens, plan.window, plan.ctas_per_item)
             if key not in planned:
                 planned[key] = attention_plan.plan_attention(
                     [(t0, n, p0) for (t0, n, p0, _) in segs], plan.tile_tokens, plan.window, plan.ctas_per_item,
-                    self.target_ctas, cluster=cluster if segs else 0)
+                    self.target_ctas)
             work, red, parts = planned[key]
             mw, mr, mp = (work_caps[gi] if work_caps else (len(work), len(red), parts))
             if len(work) > mw or len(red) > mr or parts > mp:
                 raise ConfigError("the step's attention work does not fit the capacities it was given")
-            group_parts.append((slots, tables, work, red, mp, mw, mr, W, cluster))
+            group_parts.append((slots, tables, work, red, mp, mw, mr, W))
 
         # layout: offsets in int32 units
         off = 0
@@ -199,10 +180,11 @@ class StepPacker:
 
         take("tokens", Tc); take("positions", Tc); take("logit_rows", max(nc, 1)); take("segments", max(sc, 1) * 4)
         take("temperature", max(nc, 1)); take("uniform", max(nc, 1))
-        for gi, (slots, tables, work, red, parts, mw, mr, W, _) in enumerate(group_parts):
+        for gi, (slots, tables, work, red, parts, mw, mr, W) in enumerate(group_parts):
             take(f"g{gi}.slots", Tc); take(f"g{gi}.tables", sc * W)
-            take(f"g{gi}.n_work", 1); take(f"g{gi}.n_red", 1)
-            take(f"g{gi}.work", max(mw, 1) * 8); take(f"g{gi}.red", max(mr, 1) * 4)
+            if work is not None:
+                take(f"g{gi}.n_work", 1); take(f"g{gi}.n_red", 1)
+                take(f"g{gi}.work", max(mw, 1) * 8); take(f"g{gi}.red", max(mr, 1) * 4)
         host = np.zeros(off, dtype=np.int32)
 
         def put(name, arr):
@@ -215,26 +197,32 @@ class StepPacker:
             put("temperature", np.asarray(temperature, dtype=np.float32).view(np.int32))
             put("uniform", np.asarray(uniform, dtype=np.float32).view(np.int32))
         put("segments", np.asarray(segs, dtype=np.int32).reshape(-1) if segs else [])
-        for gi, (slots, tables, work, red, parts, mw, mr, W, _) in enumerate(group_parts):
+        for gi, (slots, tables, work, red, parts, mw, mr, W) in enumerate(group_parts):
             put(f"g{gi}.slots", slots); put(f"g{gi}.tables", tables)
-            put(f"g{gi}.n_work", [len(work)]); put(f"g{gi}.n_red", [len(red)])
-            put(f"g{gi}.work", work); put(f"g{gi}.red", red)
+            if work is not None:
+                put(f"g{gi}.n_work", [len(work)]); put(f"g{gi}.n_red", [len(red)])
+                put(f"g{gi}.work", work); put(f"g{gi}.red", red)
         # What the work items are: bit 0 items of one query token (decoded tokens, but also the
         # last tile of a portion of 33 tokens), bit 1 items of several.  Read off the items, not
         # the segments.  A step packed to capacities is a captured decode step: single tokens only.
         kinds = 0
         for p in group_parts:
+            if p[2] is None:
+                continue
             counts = p[2][:, 2] if len(p[2]) else np.zeros(0, np.int32)
             kinds |= (1 if (counts == 1).any() else 0) | (2 if (counts > 1).any() else 0)
         if caps is not None:
             kinds = caps.kinds      # a captured step launches the same kernels whatever it holds
+        singles = bool(segs) and all(n == 1 for (_, n, _, _) in segs)
         sizes = dict(tokens=T, wanted=n_want, segments=n_seg, tokens_cap=Tc, wanted_cap=nc, segments_cap=sc, kinds=kinds,
-                     groups=[dict(parts=p[4], max_work=p[5], max_red=p[6], table_width=p[7], cluster=p[8]) for p in group_parts],
-                     host_segments=segs)
+                     groups=[dict(planned=p[2] is not None, parts=p[4], max_work=p[5], max_red=p[6], table_width=p[7])
+                             for p in group_parts],
+                     host_segments=segs,
+                     # (a captured step of single tokens is cut for its capacity's worth of requests at the least)
+                     plan_tokens=(caps.tokens if caps is not None and caps.kinds == 1 else n_seg) if (singles or caps) else 0)
         return host, layout, sizes
 
-    def to_state(self, dev: torch.Tensor, layout, sizes, heads: List[Tuple[int, int]],
-                 full: bool = False) -> StepState:
+    def to_state(self, dev: torch.Tensor, layout, sizes, full: bool = False) -> StepState:
         """Views of the packed device buffer as the parts see it.  ``full``: take
         the capacities rather than the live sizes (graph capture)."""
 
@@ -246,14 +234,16 @@ class StepPacker:
         nw = sizes["wanted_cap"] if full else sizes["wanted"]
         groups = []
         for gi, gs in enumerate(sizes["groups"]):
-            part_o, part_ml = self.scratch(gi, gs["parts"], heads[gi])
-            groups.append(GroupStep(
-                block_tables=view(f"g{gi}.tables").view(sizes["segments_cap"], gs["table_width"]),
-                slots=view(f"g{gi}.slots", T),
-                work=view(f"g{gi}.work").view(-1, 8), n_work=view(f"g{gi}.n_work"), max_work=gs["max_work"],
-                red=view(f"g{gi}.red").view(-1, 4), n_red=view(f"g{gi}.n_red"), max_red=gs["max_red"],
-                part_o=part_o, part_ml=part_ml, kinds=sizes["kinds"], counters=self.counters(gi, gs["max_work"]),
-                cluster=gs.get("cluster", 0)))
+            plan = None
+            if gs["planned"]:
+                part_o, part_ml = self.scratch(gi, gs["parts"])
+                many = sizes["kinds"] == 1 and attention_plan.many_splits(max(1, sizes["plan_tokens"]), self.plans[gi].ctas_per_item,
+                                                                           self.target_ctas)
+                plan = AttentionWork(work=view(f"g{gi}.work").view(-1, 8), n_work=view(f"g{gi}.n_work"), max_work=gs["max_work"],
+                                     red=view(f"g{gi}.red").view(-1, 4), n_red=view(f"g{gi}.n_red"), max_red=gs["max_red"],
+                                     part_o=part_o, part_ml=part_ml, kinds=sizes["kinds"], many_splits=many)
+            groups.append(GroupStep(block_tables=view(f"g{gi}.tables").view(sizes["segments_cap"], gs["table_width"]),
+                                    slots=view(f"g{gi}.slots", T), plan=plan))
         state = StepState(n_tokens=T, tokens=view("tokens", T), positions=view("positions", T), groups=groups,
                           logit_rows=view("logit_rows", nw), n_wanted=nw,
                           segments=view("segments").view(-1, 4), host_segments=list(sizes["host_segments"]))
@@ -267,7 +257,7 @@ class _GroupPack(ctypes.Structure):
     _fields_ = [("tables", ctypes.POINTER(ctypes.c_void_p)), ("table_len", ctypes.POINTER(ctypes.c_int)),
                 ("window", ctypes.c_int), ("ctas_per_item", ctypes.c_int),
                 ("max_work", ctypes.c_int), ("max_red", ctypes.c_int), ("max_parts", ctypes.c_int),
-                ("cluster", ctypes.c_int),
+                ("plans", ctypes.c_int),
                 ("off_slots", ctypes.c_int), ("off_tables", ctypes.c_int), ("off_n_work", ctypes.c_int),
                 ("off_n_red", ctypes.c_int), ("off_work", ctypes.c_int), ("off_red", ctypes.c_int)]
 
@@ -308,10 +298,11 @@ class NativeDecodePacker:
             g, plan = self.groups[gi], packer.plans[gi]
             g.tables = ctypes.cast(ptrs, ctypes.POINTER(ctypes.c_void_p))
             g.table_len = ctypes.cast(lens, ctypes.POINTER(ctypes.c_int))
-            g.window, g.ctas_per_item = int(plan.window or 0), plan.ctas_per_item
-            g.max_work, g.max_red, g.max_parts = work_caps[gi]
-            g.cluster = packer.cluster_for(gi, caps.tokens)
-            for name in ("slots", "tables", "n_work", "n_red", "work", "red"):
+            g.plans = 0 if plan is None else 1
+            if plan is not None:
+                g.window, g.ctas_per_item = int(plan.window or 0), plan.ctas_per_item
+                g.max_work, g.max_red, g.max_parts = work_caps[gi]
+            for name in ("slots", "tables") + (("n_work", "n_red", "work", "red") if plan is not None else ()):
                 setattr(g, f"off_{name}", layout[f"g{gi}.{name}"][0])
         self.n_groups = n_groups
         self.fixed = (caps.tokens, caps.wanted, caps.segments, caps.table_width, packer.cache.page_size, packer.vocab_size,

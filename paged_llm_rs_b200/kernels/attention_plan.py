@@ -33,48 +33,13 @@ MAX_SPLITS = 128   # the reduce kernel holds the weights of up to 256 splits in 
 MULTI_MIN_SPLIT_KEYS = 2048
 
 
-def decode_cluster(n_tokens: int, ctas_per_item: int, target_ctas: int, max_cluster: int) -> int:
-    """How many items every token of a step of ``n_tokens`` single tokens gets when the kernel
-    combines a token's splits inside a thread-block cluster of at most ``max_cluster`` CTAs: the
-    split count the planner would want, when a cluster can hold it (or nearly: up to twice the
-    cluster are cut into a full cluster instead); 0 when the step is not cut, or too finely."""
-    if max_cluster < 2 or n_tokens <= 0 or n_tokens * ctas_per_item >= target_ctas:
-        return 0
-    want = max(2, target_ctas // (n_tokens * ctas_per_item))
-    if want > 2 * max_cluster:
-        return 0
-    return min(want, max_cluster)
-
-
 def plan_attention(segments: Sequence[Tuple[int, int, int]], tile_tokens: int, window: Optional[int],
                    ctas_per_item: int, target_ctas: int,
-                   min_split_keys: int = MIN_SPLIT_KEYS, cluster: int = 0,
+                   min_split_keys: int = MIN_SPLIT_KEYS,
                    multi_min_split_keys: int = MULTI_MIN_SPLIT_KEYS) -> Tuple[np.ndarray, np.ndarray, int]:
     """segments: (first token index, token count, position of the first token) per
-    segment, in step order.  Returns (work [n, 8], red [m, 4], partial rows used).
-    ``cluster`` > 1 (steps of single tokens only): every token gets exactly that many
-    consecutive items, as many of them as the key range is worth holding keys and the rest
-    empty, for a kernel that combines them itself: no partial rows, no reductions."""
+    segment, in step order.  Returns (work [n, 8], red [m, 4], partial rows used)."""
     seg_ids, q0s, qns, p0s = [], [], [], []
-    if cluster > 1:
-        if not segments or any(c != 1 for _, c, _ in segments):
-            raise ValueError("a cluster plan is for steps of single tokens")
-        a = np.asarray(segments, dtype=np.int64)
-        n = len(a)
-        q0, p0 = a[:, 0], a[:, 2]
-        kv_end = p0 + 1
-        kv_begin = np.maximum(0, p0 - (window - 1)) if window else np.zeros_like(p0)
-        keys = kv_end - kv_begin
-        splits = np.clip(np.minimum(cluster, keys // min_split_keys), 1, cluster)
-        chunk = -(-keys // splits)
-        chunk = -(-chunk // SPLIT_ALIGN) * SPLIT_ALIGN
-        tile_of = np.repeat(np.arange(n), cluster)
-        k = np.tile(np.arange(cluster), n)
-        begin = np.minimum(kv_begin[tile_of] + k * chunk[tile_of], (kv_end[tile_of] + SPLIT_ALIGN - 1) // SPLIT_ALIGN * SPLIT_ALIGN)
-        end = np.maximum(begin, np.minimum(begin + chunk[tile_of], kv_end[tile_of]))
-        work = np.stack([tile_of, q0[tile_of], np.ones(n * cluster, np.int64), p0[tile_of], begin, end,
-                         np.full(n * cluster, -1), (cluster << 16) | k], 1)
-        return work.astype(np.int32), np.zeros((0, 4), np.int32), 0
     if segments and all(c == 1 for _, c, _ in segments):
         # a decode step: one tile per segment, no per-segment array work
         a = np.asarray(segments, dtype=np.int64)
@@ -127,7 +92,7 @@ def plan_attention(segments: Sequence[Tuple[int, int, int]], tile_tokens: int, w
     rows_of = np.where(is_split, n_split * qn, 0)                  # partial rows a tile uses
     base = np.cumsum(rows_of) - rows_of
     part = np.where(is_split[tile_of], base[tile_of] + k * qn[tile_of], -1)
-    # which split of how many: the kernel that combines a tile's splits itself counts them off
+    # which split of how many
     split = np.where(is_split[tile_of], (n_split[tile_of] << 16) | k, 0)
     work = np.stack([seg[tile_of], q0[tile_of], qn[tile_of], p0[tile_of], begin, end, part, split], 1)
     st = np.nonzero(is_split)[0]
@@ -156,3 +121,10 @@ def plan_limits(max_step_tokens: int, tile_tokens: int, target_ctas: int, ctas_p
     max_red = max_step_tokens
     max_parts = split_items * tile_tokens
     return max_work, max_red, max_parts
+
+
+def many_splits(n_tokens: int, ctas_per_item: int, target_ctas: int) -> bool:
+    """Whether a step of this many single tokens is cut into eight splits a tile or more (the
+    planner's arithmetic): the reduction kernel then shares an entry's splits out over four
+    groups of threads."""
+    return target_ctas // max(1, n_tokens * ctas_per_item) >= 8

@@ -49,26 +49,24 @@ def lib():
             "pllm_sample_scratch_floats": [c_int, c_int],
             "pllm_skinny_gemm_supports": [c_int, c_int, c_int],
             "pllm_skinny_gemm": [P, P, P, c_int, c_int, c_int, c_int, P],
-            "pllm_skinny_gemm_fused_supports": [c_int, c_int, c_int, c_int],
-            "pllm_skinny_gemm_fused": [P, P, P, P, c_float, P, P, c_int, c_int, c_int, c_int, P],
+            "pllm_skinny_gemm_glu_supports": [c_int, c_int, c_int],
+            "pllm_skinny_gemm_glu": [P, P, P, c_int, c_int, c_int, P],
+            "pllm_sm_count": [],
             "pllm_attention_mma_supports": [c_int, c_int, c_int, c_int],
             "pllm_attention_mma_tile_tokens": [c_int, c_int],
             "pllm_attention_mma": [P, P, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                                    c_int, c_float, c_int, c_int, P, P],
             "pllm_attention_decode_tma_supports": [c_int, c_int, c_int, c_int, c_int, c_int],
             "pllm_attention_decode_tma": [P, P, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
-                                          c_float, c_int, P, c_int, P, P],
-            "pllm_attention_decode_tma_max_cluster": [c_int, c_int, c_int, c_int, c_int, c_int],
+                                          c_float, c_int, P, P],
         }
         sig["pllm_set_pdl"] = [c_int]
-        sig["pllm_attention_decode_tma_fused"] = [P, P, P, c_float, P, P, c_int, P, P, P, P, P, c_int, P, P, P] + [c_int] * 6 + [c_float, c_int, P, P]
+        sig["pllm_attention_decode_tma_fused"] = [P, P, P, c_float, P, P, c_int, P, P, P, P, P, c_int, P, P, P] + [c_int] * 6 + [c_float, P, P]
         sig["pllm_attention_prefill_tcgen05_tile_tokens"] = [c_int, c_int]
         sig["pllm_attention_prefill_tcgen05_supports"] = [c_int] * 6
         sig["pllm_attention_prefill_tcgen05"] = [P] * 10 + [c_int] * 7 + [c_float, c_int, P, P]
         sig["pllm_gemm_tcgen05_supports"] = [c_int, c_int, c_int, c_int]
         sig["pllm_gemm_tcgen05"] = [P, P, P, c_int, c_int, c_int, c_int, P, P]
-        sig["pllm_gemm_tcgen05_qkv_supports"] = [c_int] * 6
-        sig["pllm_gemm_tcgen05_qkv"] = [P, P, P, P, P, c_float, P, P, c_int, P, P, P, P] + [c_int] * 8 + [P, P]
         sig["pllm_pack_decode_step"] = [P, c_int, c_int, P, P, P, P, P] + [c_int] * 16 + [P, P]
         for name, args in sig.items():
             fn = getattr(L, name)
@@ -288,31 +286,23 @@ def _side_stream(device) -> "torch.cuda.Stream":
     return _SIDE_STREAMS[key]
 
 
-def _many_splits(tokens: int, num_heads: int, num_kv_heads: int) -> int:
-    """Whether a step of this many tokens is cut into eight splits or more a tile (the planner's
-    arithmetic for single tokens: target CTAs over tiles x CTAs an item)."""
-    group = num_heads // num_kv_heads
-    ctas_per_item = num_kv_heads * -(-group // min(group, 16))
-    return 1 if 2 * 148 // max(1, tokens * ctas_per_item) >= 8 else 0
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device (the kernels size their grids by it)."""
+    return int(lib().pllm_sm_count())
 
 
-def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
-                    work: torch.Tensor, n_work: torch.Tensor, max_work: int, out: torch.Tensor,
-                    part_o: torch.Tensor, part_ml: torch.Tensor, red: torch.Tensor, n_red: torch.Tensor,
-                    max_red: int, num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
-                    status: torch.Tensor, swizzled: bool = False, kinds: int = 3,
-                    counters: Optional[torch.Tensor] = None, cluster: int = 0) -> torch.Tensor:
+def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor, w,
+                    out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
+                    status: torch.Tensor, swizzled: bool = False) -> torch.Tensor:
     """Attention of the step's tokens over the paged cache, then the reduction of
-    split items.  ``work`` is int32 [>=max_work, 8], ``red`` int32 [>=max_red, 4];
-    n_work / n_red are int32 scalars on the device saying how many are live.
-    ``swizzled`` says how the pools are laid out (see ``pool_is_swizzled``);
-    ``kinds`` what the work items are: 1 single decoded tokens only, 2 portions of
-    several tokens only, 3 both, so that only the kernels with work are launched.
-    ``counters`` (int32 zeros, max_work x CTAs an item, left zero): with them the
-    bulk-copy kernel, where it takes all the work, combines the splits itself and
-    the reduction kernel is not launched.  ``cluster`` > 1: the list was planned with
-    that many items for every (single) token, which the bulk-copy kernel combines
-    inside a thread-block cluster; nothing else takes such a list."""
+    split items.  ``w`` is the group's ``AttentionWork`` (parts/base.py): work items
+    int32 [>=max_work, 8], reductions int32 [>=max_red, 4], how many are live as
+    int32 scalars on the device, the scratch for partial results, and ``kinds``,
+    what the work items are (1 single decoded tokens only, 2 portions of several
+    tokens only, 3 both), so that only the kernels with work are launched.
+    ``swizzled`` says how the pools are laid out (see ``pool_is_swizzled``)."""
+    work, n_work, max_work, red, n_red, max_red = w.work, w.n_work, w.max_work, w.red, w.n_red, w.max_red
+    part_o, part_ml, kinds = w.part_o, w.part_ml, w.kinds
     _dev(q, k_pool, v_pool, block_tables, work, n_work, out, part_o, part_ml, red, n_red, status)
     for t, n in ((block_tables, "block_tables"), (work, "work"), (n_work, "n_work"), (red, "red"), (n_red, "n_red")):
         _i32(t, n)
@@ -327,6 +317,8 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         raise KernelError(f"paged_attention: {num_heads} heads do not group over {num_kv_heads} kv heads")
     if work.numel() < max_work * 8 or red.numel() < max_red * 4:
         raise KernelError("paged_attention: work / red lists shorter than their maxima")
+    if part_o.shape[1:] != (num_heads, head_dim) or part_ml.shape[1:] != (num_heads, 2):
+        raise KernelError("paged_attention: the scratch for partial results is not [rows, heads, head_dim] and [rows, heads, 2]")
     n_pages, page_size = k_pool.shape[0], k_pool.shape[2]
     L = lib()
     if attention_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim):
@@ -340,7 +332,7 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                                                                                    page_size, int(window))
         # (worth the two edges without programmatic launch from some eight requests on: 0.6B shape, a layer of a
         # step of 1 / 8 / 64 decoded tokens at 4096 beside a portion: +9 / -3 / -10 us)
-        beside = bool(MIXED_BESIDE and multi_tc and kinds == 3 and tma_ok and (TMA_KINDS & 1) and cluster <= 1
+        beside = bool(MIXED_BESIDE and multi_tc and kinds == 3 and tma_ok and (TMA_KINDS & 1)
                       and block_tables.shape[0] >= MIXED_BESIDE_MIN_REQUESTS)
         if beside:
             # A step of decoded tokens beside prompt portions: the single tokens go to the bulk-copy kernel and
@@ -355,8 +347,8 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                 _check(L.pllm_attention_decode_tma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
                                                    _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml),
                                                    num_heads, num_kv_heads, head_dim, page_size, n_pages,
-                                                   block_tables.shape[-1], float(scale), 1, None, 0, _ptr(status),
-                                                   _stream()), "paged_attention (bulk copy, beside)")
+                                                   block_tables.shape[-1], float(scale), 1, _ptr(status), _stream()),
+                       "paged_attention (bulk copy, beside)")
         if multi_tc:
             _check(L.pllm_attention_prefill_tcgen05(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
                                                     _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml),
@@ -370,30 +362,11 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
             kinds = 0 if kinds == 3 else kinds & ~2
         take = (kinds & TMA_KINDS) if tma_ok else 0
         rest = kinds & ~take
-        if cluster > 1:
-            if take != 1 or rest or multi_tc or cluster > attention_max_cluster(q.dtype, num_heads, num_kv_heads, head_dim,
-                                                                                page_size, int(window), swizzled):
-                raise KernelError("paged_attention: a list planned for clusters, and no kernel here that combines in clusters")
-            _check(L.pllm_attention_decode_tma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
-                                               _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml),
-                                               num_heads, num_kv_heads, head_dim, page_size, n_pages,
-                                               block_tables.shape[-1], float(scale), 1, None, int(cluster),
-                                               _ptr(status), _stream()),
-                   "paged_attention (bulk copy, clusters)")
-            return out
-        group = num_heads // num_kv_heads
-        ctas_per_item = num_kv_heads * -(-group // min(group, 16))
-        fused = bool(FUSE_REDUCE and take and not rest and not multi_tc and counters is not None
-                     and counters.numel() >= max_work * ctas_per_item)
-        if fused:
-            _dev(counters)
-            _i32(counters, "counters")
         if take:
             _check(L.pllm_attention_decode_tma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
                                                _ptr(n_work), max_work, _ptr(out), _ptr(part_o), _ptr(part_ml),
                                                num_heads, num_kv_heads, head_dim, page_size, n_pages,
-                                               block_tables.shape[-1], float(scale), take,
-                                               _ptr(counters) if fused else None, 0, _ptr(status), _stream()),
+                                               block_tables.shape[-1], float(scale), take, _ptr(status), _stream()),
                    "paged_attention (bulk copy)")
         if rest:
             _check(L.pllm_attention_mma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _ptr(work),
@@ -401,11 +374,7 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                                         num_kv_heads, head_dim, page_size, n_pages, block_tables.shape[-1], int(window),
                                         float(scale), 1 if swizzled else 0, rest, _ptr(status), _stream()),
                    "paged_attention (mma)")
-        if fused:
-            return out
     else:
-        if cluster > 1:
-            raise KernelError("paged_attention: a list planned for clusters, and no kernel here that combines in clusters")
         if swizzled:
             raise KernelError("paged_attention: the generic kernel reads plain pools, not swizzled ones")
         _check(L.pllm_attention_generic(_code(q), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables),
@@ -414,31 +383,8 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                                         block_tables.shape[-1], int(window), float(scale), _ptr(status), _stream()),
                "paged_attention")
     _check(L.pllm_attention_reduce(_code(q), _ptr(part_o), _ptr(part_ml), _ptr(red), _ptr(n_red), max_red,
-                                   _ptr(out), num_heads, head_dim, _many_splits(q.shape[0], num_heads, num_kv_heads),
-                                   _stream()), "attention_reduce")
+                                   _ptr(out), num_heads, head_dim, 1 if w.many_splits else 0, _stream()), "attention_reduce")
     return out
-
-
-# PAGED_LLM_CLUSTER=1: steps of single tokens whose splits fit a thread-block cluster are combined inside the
-# attention kernel, through the cluster's shared memory, instead of through global memory and the reduction
-# kernel.  Off by default: it measured no faster (0.6B shape, context 4096, a captured step: batch 8 1.386 ms
-# against 1.390, batch 16 2.041 against 2.037, batch 4 with clusters of 8 1.29 against 1.07).  The reduction
-# kernel's 3.7 us a layer go, but a cluster starts only when all its CTAs find room in one GPC at once, so the
-# attention's CTAs no longer trickle in behind the product before them, and the two cluster barriers and the
-# remote reads add 2 us to the attention itself.
-CLUSTER_COMBINE = os.environ.get("PAGED_LLM_CLUSTER", "0") == "1"
-
-
-def attention_max_cluster(dtype, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
-                          swizzled: bool = True) -> int:
-    """The most items of one single token that ``paged_attention`` / ``decode_attention_fused`` can combine
-    inside a cluster for this shape (0: none; the planner then cuts as for the reduction kernel)."""
-    if not CLUSTER_COMBINE or not swizzled or not (TMA_KINDS & 1) or dtype != torch.bfloat16:
-        return 0
-    if not attention_uses_tensor_cores(dtype, num_heads, num_kv_heads, head_dim):
-        return 0
-    return int(lib().pllm_attention_decode_tma_max_cluster(_BF16, num_heads, num_kv_heads, head_dim, int(page_size),
-                                                           int(window or 0)))
 
 
 # A step of single decoded tokens: the q/k norm, the rotation and the cache write are done by the
@@ -459,15 +405,15 @@ def decode_attention_fuses(dtype, num_heads: int, num_kv_heads: int, head_dim: i
 
 
 def decode_attention_fused(qkv: torch.Tensor, q_gain, k_gain, eps: float, cos, sin, k_pool: torch.Tensor,
-                           v_pool: torch.Tensor, block_tables: torch.Tensor, work: torch.Tensor, n_work: torch.Tensor,
-                           max_work: int, out: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
-                           red: torch.Tensor, n_red: torch.Tensor, max_red: int, num_heads: int, num_kv_heads: int,
-                           head_dim: int, scale: float, status: torch.Tensor, cluster: int = 0) -> torch.Tensor:
+                           v_pool: torch.Tensor, block_tables: torch.Tensor, w, out: torch.Tensor, num_heads: int,
+                           num_kv_heads: int, head_dim: int, scale: float, status: torch.Tensor) -> torch.Tensor:
     """Attention of a step of single decoded tokens straight from the projection's output
     ``qkv`` [tokens, (heads + 2 kv heads) * head_dim]: per-head norm of q and k, rotation at each
     token's position (the work item's), the token's key and value written to its cache slot
-    (found through the block table), attention over the cache, reduction of split items
-    (``cluster`` > 1: the list holds that many items a token, combined inside the kernel)."""
+    (found through the block table), attention over the cache, reduction of split items.
+    ``w``: the group's ``AttentionWork``."""
+    work, n_work, max_work, red, n_red, max_red, part_o, part_ml = (w.work, w.n_work, w.max_work, w.red, w.n_red, w.max_red,
+                                                                    w.part_o, w.part_ml)
     _dev(qkv, k_pool, v_pool, block_tables, work, n_work, out, part_o, part_ml, red, n_red, status, q_gain, k_gain, cos, sin)
     _f32(q_gain, "q_gain"); _f32(k_gain, "k_gain"); _f32(cos, "cos"); _f32(sin, "sin")
     _f32(part_o, "part_o"); _f32(part_ml, "part_ml")
@@ -485,14 +431,10 @@ def decode_attention_fused(qkv: torch.Tensor, q_gain, k_gain, eps: float, cos, s
                                              cos.shape[0] if cos is not None else 0, _ptr(k_pool), _ptr(v_pool),
                                              _ptr(block_tables), _ptr(work), _ptr(n_work), max_work, _ptr(out),
                                              _ptr(part_o), _ptr(part_ml), num_heads, num_kv_heads, head_dim, page_size,
-                                             n_pages, block_tables.shape[-1], float(scale), int(cluster), _ptr(status),
-                                             _stream()),
+                                             n_pages, block_tables.shape[-1], float(scale), _ptr(status), _stream()),
            "decode_attention_fused")
-    if cluster > 1:
-        return out
     _check(L.pllm_attention_reduce(_code(out), _ptr(part_o), _ptr(part_ml), _ptr(red), _ptr(n_red), max_red,
-                                   _ptr(out), num_heads, head_dim, _many_splits(qkv.shape[0], num_heads, num_kv_heads),
-                                   _stream()), "attention_reduce")
+                                   _ptr(out), num_heads, head_dim, 1 if w.many_splits else 0, _stream()), "attention_reduce")
     return out
 
 
@@ -512,18 +454,8 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
     return tokens
 
 
-# Split items combined by the last CTA of each tile inside the bulk-copy kernel instead of by the
-# reduction kernel (PAGED_LLM_FUSE_REDUCE=1).  Off: the combining CTA's round trips to L2 come after
-# the attention instead of beside it, and a captured step of the 0.6B shape at 4096 tokens of context
-# was slower (batch 1: 1.011 against 0.948 ms, batch 8: 1.564 against 1.537; batch 64: 6.44 against 6.47).
-FUSE_REDUCE = os.environ.get("PAGED_LLM_FUSE_REDUCE", "0") == "1"
 SKINNY_GEMM = True  # few rows in bfloat16 go to this library's weight-streaming kernel
-# ... which can also take the residual add and the norm before it (PAGED_LLM_FUSE_NORM=1).  Off: in a
-# captured step of the 0.6B shape it saves two launches a layer but its CTAs need more registers, and
-# the step was no faster (batch 1: 0.956 against 0.950 ms, batch 4: 1.200 against 1.141, batch 8: 1.527
-# against 1.524).
-FUSE_NORM = os.environ.get("PAGED_LLM_FUSE_NORM", "0") == "1"
-FUSE_GLU = os.environ.get("PAGED_LLM_FUSE_GLU", "1") != "0"     # ... and the gated activation after it
+FUSE_GLU = os.environ.get("PAGED_LLM_FUSE_GLU", "1") != "0"     # ... with the gated activation in its epilogue
 
 
 def skinny_gemm_takes(x: torch.Tensor, weight: torch.Tensor, k: Optional[int] = None) -> bool:
@@ -586,157 +518,25 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, glu: bool = False, statu
     return out
 
 
-# PAGED_LLM_FUSE_QKV_GEMM=1: the attention's input projection for the many rows of a prompt portion with the
-# per-head norm, the rotation and the cache write in the product's epilogue, instead of the library product
-# and then the q/k kernel over its output.  Off by default: it measured slower (2048 tokens of the 0.6B
-# shape: 43 us alone with cold caches against 21 + 19, and 36 us against 17 + 11 inside the step, 3.64 ms
-# against 3.41 for the prompt).  The product itself is 25 us here against the library's 21, and the epilogue
-# of four warps takes 17 us for a tile of 256 columns with the norm and the rotation (4 us plain), of which
-# only the first of a CTA's two tiles hides behind the tensor cores.
-FUSE_QKV_GEMM = os.environ.get("PAGED_LLM_FUSE_QKV_GEMM", "0") == "1"
-
-
-def qkv_projection_fuses(x, weight: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
-                         rotary_dim: int) -> bool:
-    """Whether ``qkv_projection_fused`` takes this step: bfloat16, enough rows for the tensor-core tiles,
-    heads of 64 or 128 values rotated over their whole width or not at all."""
-    if not FUSE_QKV_GEMM or not TCGEN05_GEMM or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+def skinny_glu_takes(x, weight: torch.Tensor, n_out: int) -> bool:
+    """Whether the weight-streaming kernel takes the gate/up product with the activation in its epilogue."""
+    if not SKINNY_GEMM or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or x.dim() != 2:
         return False
-    if x.shape[0] < TCGEN05_MIN_M or not weight.is_contiguous() or weight.shape[0] != (num_heads + 2 * num_kv_heads) * head_dim:
-        return False
-    return bool(lib().pllm_gemm_tcgen05_qkv_supports(x.shape[0], weight.shape[1], num_heads, num_kv_heads, head_dim,
-                                                     int(rotary_dim)))
+    return n_out <= SKINNY_MAX_N and bool(lib().pllm_skinny_gemm_glu_supports(x.shape[0], n_out, weight.shape[1]))
 
 
-def qkv_projection_fused(x, weight: torch.Tensor, q_out: torch.Tensor, q_gain, k_gain, eps: float, cos, sin,
-                         positions: torch.Tensor, slots: Optional[torch.Tensor], k_pool: Optional[torch.Tensor],
-                         v_pool: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int,
-                         status: torch.Tensor, swizzled: bool = False) -> torch.Tensor:
-    """q_out = rope(norm(x Wq^T)), and with pools: rope(norm(x Wk^T)) and x Wv^T into the cache rows that
-    ``slots`` names (-1: none), all from one product on the tcgen05 tensor cores whose epilogue threads
-    each hold one token's heads.  ``weight`` is [q rows; k rows; v rows]; without pools only q is made."""
-    x = as_tensor(x)
-    if not qkv_projection_fuses(x, weight, num_heads, num_kv_heads, head_dim, head_dim if cos is not None else 0):
-        raise KernelError(f"qkv_projection_fused: does not take x {tuple(x.shape)} {x.dtype}, W {tuple(weight.shape)}")
-    _dev(x, weight, q_out, q_gain, k_gain, cos, sin, positions, slots, k_pool, v_pool, status)
-    _f32(q_gain, "q_gain"); _f32(k_gain, "k_gain"); _f32(cos, "cos"); _f32(sin, "sin")
-    _i32(positions, "positions")
-    if slots is not None:
-        _i32(slots, "slots")
-    M, K = x.shape
-    if not x.is_contiguous() or weight.shape[1] != K or q_out.shape != (M, num_heads * head_dim) or q_out.dtype != torch.bfloat16 \
-            or not q_out.is_contiguous() or positions.numel() < M or (slots is not None and slots.numel() < M):
-        raise KernelError("qkv_projection_fused: shapes do not fit")
-    if (cos is None) != (sin is None) or (cos is not None and cos.shape[-1] * 2 != head_dim):
-        raise KernelError("qkv_projection_fused: the rotation must span the whole head (or be absent)")
-    keep = k_pool is not None
-    if keep and (v_pool is None or slots is None or k_pool.shape != v_pool.shape or k_pool.dtype != torch.bfloat16
-                 or k_pool.dim() != 4 or k_pool.shape[1] != num_kv_heads or k_pool.shape[3] != head_dim):
-        raise KernelError(f"qkv_projection_fused: pools must be bfloat16 [pages, {num_kv_heads}, page_size, {head_dim}]")
-    _check(lib().pllm_gemm_tcgen05_qkv(_ptr(x), _ptr(weight), _ptr(q_out), _ptr(q_gain), _ptr(k_gain), float(eps),
-                                       _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0, _ptr(positions),
-                                       _ptr(slots) if keep else None, _ptr(k_pool) if keep else None,
-                                       _ptr(v_pool) if keep else None, M, K, num_heads, num_kv_heads, head_dim,
-                                       k_pool.shape[2] if keep else 1, k_pool.shape[0] if keep else 0,
-                                       1 if swizzled else 0, _ptr(status), _stream()), "qkv_projection_fused")
-    return q_out
-
-
-class NormedInput:
-    """rmsnorm(residual + delta) * gain, not yet formed: what a norm hands to a part
-    whose first operation is a product (``linear`` or ``linear_glu``), so that the
-    add, the norm and the product can be one kernel.  ``residual_out`` is where
-    residual + delta is stored (a buffer of its own, or ``residual`` itself when
-    there is no delta); it is valid once the input was consumed or ``tensor()``
-    was called."""
-
-    def __init__(self, residual: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor, eps: float):
-        self.residual, self.delta, self.gain, self.eps = residual, delta, gain, float(eps)
-        self.residual_out = residual if delta is None else torch.empty_like(residual)
-        self.consumed = False
-        self._tensor: Optional[torch.Tensor] = None
-
-    @property
-    def shape(self):
-        return self.residual.shape
-
-    @property
-    def dtype(self):
-        return self.residual.dtype
-
-    @property
-    def device(self):
-        return self.residual.device
-
-    def tensor(self) -> torch.Tensor:
-        """The normed rows as a tensor (the norm kernel runs now, once)."""
-        if self._tensor is None:
-            out = torch.empty_like(self.residual)
-            rmsnorm(self.residual, self.gain, self.eps, out, delta=self.delta,
-                    residual_out=self.residual_out if self.delta is not None else None)
-            self._tensor, self.consumed = out, True
-        return self._tensor
-
-
-def deferred_norm_pays(rows: int, width: int, dtype: torch.dtype) -> bool:
-    """Whether a product's kernel would take the add and the norm for rows of this
-    shape (few rows of a decode step in bfloat16); otherwise the norm kernel is
-    the better route and the norm should run at once."""
-    return SKINNY_GEMM and FUSE_NORM and dtype == torch.bfloat16 \
-        and bool(lib().pllm_skinny_gemm_fused_supports(rows, 16, width, 1))
-
-
-def as_tensor(x) -> torch.Tensor:
-    """A part that does anything but a product with its input first calls this."""
-    return x.tensor() if isinstance(x, NormedInput) else x
-
-
-def fused_linear_takes(x, weight: torch.Tensor, n_out: int) -> bool:
-    """Whether the product's kernel can take the norm before it or the gate after."""
-    if not SKINNY_GEMM or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or len(x.shape) != 2:
-        return False
-    normed = isinstance(x, NormedInput) and x._tensor is None
-    return n_out <= SKINNY_MAX_N and bool(lib().pllm_skinny_gemm_fused_supports(x.shape[0], n_out, weight.shape[1],
-                                                                                1 if normed else 0))
-
-
-def _fused(x, weight: torch.Tensor, n_out: int, glu: bool) -> torch.Tensor:
-    M, K = x.shape
-    out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
-    if isinstance(x, NormedInput) and x._tensor is None:
-        _dev(x.residual, x.delta, x.gain, weight)
-        _f32(x.gain, "gain")
-        res_out = x.residual_out if x.delta is not None else None
-        _check(lib().pllm_skinny_gemm_fused(_ptr(x.residual), _ptr(x.delta), _ptr(res_out), _ptr(x.gain), x.eps,
-                                            _ptr(weight), _ptr(out), M, n_out, K, 1 if glu else 0, _stream()),
-               "skinny_gemm_fused")
-        x.consumed = True
-    else:
-        x = as_tensor(x)
-        _dev(x, weight)
-        _check(lib().pllm_skinny_gemm_fused(_ptr(x), None, None, None, 0.0, _ptr(weight), _ptr(out), M, n_out, K,
-                                            1 if glu else 0, _stream()), "skinny_gemm_fused")
-    return out
-
-
-def linear(x, weight: torch.Tensor, out: Optional[torch.Tensor] = None, gated: bool = False,
+def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None, gated: bool = False,
            out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y = x W^T with W stored [out, in].
 
     Few rows (a decode step) in bfloat16 run this library's weight-streaming
-    kernel, which also takes a ``NormedInput`` (add, norm and product in one
-    kernel).  With ``gated`` the input is [g | u] of twice W's width and the
+    kernel.  With ``gated`` the input is [g | u] of twice W's width and the
     product is taken of silu(g) * u, formed by the activation kernel first.
     Everything else is the library matrix product (cuBLAS through torch), which
     is where the reference uses a library too
     (crates/pagedllm/src/model/layers.rs:27-35).  float32 inputs run in true
     float32: the engine switches TF32 off."""
     N, K = weight.shape
-    if isinstance(x, NormedInput):
-        if not gated and out is None and out_dtype in (None, torch.bfloat16) and fused_linear_takes(x, weight, N) \
-                and x.shape[-1] == K:
-            return _fused(x, weight, N, glu=False)
-        x = x.tensor()
     if not x.is_cuda:
         raise KernelError("linear: input is not on a CUDA device: there is no CPU path")
     if x.shape[-1] != (2 * K if gated else K):
@@ -769,22 +569,26 @@ def linear(x, weight: torch.Tensor, out: Optional[torch.Tensor] = None, gated: b
     return torch.matmul(x, weight.t(), out=out) if out is not None else torch.matmul(x, weight.t())
 
 
-def linear_glu(x, w_gate_up: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+def linear_glu(x: torch.Tensor, w_gate_up: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """silu(x Wg^T) * (x Wu^T) for W = [Wg; Wu] stacked [2I, K]: the gated
     feed-forward's first half (crates/pagedllm/src/model/layers.rs:93-99).  Few
-    rows in bfloat16: one kernel whose CTAs hold the same columns of both halves
-    (and which takes a ``NormedInput``); otherwise the product, then the
-    activation kernel."""
+    rows in bfloat16: one kernel whose CTAs hold the same columns of both halves;
+    many rows: the tcgen05 product with the activation in its epilogue; otherwise
+    the product, then the activation kernel."""
     two_i, K = w_gate_up.shape
     if two_i % 2:
         raise KernelError("linear_glu: the stacked weight needs an even number of rows")
     inter = two_i // 2
     if x.shape[-1] != K:
         raise KernelError(f"linear_glu: input width {x.shape[-1]} does not fit a weight of {tuple(w_gate_up.shape)}")
-    if FUSE_GLU and fused_linear_takes(x, w_gate_up, inter):
-        return _fused(x, w_gate_up, inter, glu=True)
-    if TCGEN05_GEMM >= 1 and x.shape[0] >= TCGEN05_MIN_M and gemm_tcgen05_takes(as_tensor(x), w_gate_up, inter, True):
-        return gemm_tcgen05(as_tensor(x), w_gate_up, glu=True, status=status)
+    if FUSE_GLU and skinny_glu_takes(x, w_gate_up, inter):
+        _dev(x, w_gate_up)
+        out = torch.empty((x.shape[0], inter), dtype=torch.bfloat16, device=x.device)
+        _check(lib().pllm_skinny_gemm_glu(_ptr(x), _ptr(w_gate_up), _ptr(out), x.shape[0], inter, K, _stream()),
+               "skinny_gemm_glu")
+        return out
+    if TCGEN05_GEMM >= 1 and x.shape[0] >= TCGEN05_MIN_M and gemm_tcgen05_takes(x, w_gate_up, inter, True):
+        return gemm_tcgen05(x, w_gate_up, glu=True, status=status)
     gu = linear(x, w_gate_up)
     act = torch.empty((gu.shape[0], inter), dtype=gu.dtype, device=gu.device)
     return swiglu(gu, act)

@@ -13,7 +13,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .base import KVNeed, Mixer, register_mixer
+from .base import KVNeed, Mixer, PlanWish, register_mixer
 from .spec import TensorSpec
 
 
@@ -56,47 +56,32 @@ class GQAttention(Mixer):
     def cache_need(self):
         if self._need is None:
             swizzled = self.rt.device.type == "cuda" and ops.pool_is_swizzled(self.rt.dtype, self.nh, self.nkv, self.hd)
-            self._need = KVNeed("window" if self.window else "full", self.nkv, self.hd, self.window, swizzled)
+            self._need = KVNeed("window" if self.window else "full", self.nkv, self.hd, self.window, swizzled,
+                                group_size=self.nh // self.nkv)
         return self._need
 
-    takes_normed_input = True
-
-    def cluster_limit(self, page_size: int) -> int:
-        if self.rt.device.type != "cuda":
-            return 0
-        return ops.attention_max_cluster(self.rt.dtype, self.nh, self.nkv, self.hd, page_size, self.window or 0,
-                                         self.cache_need().swizzled)
+    def plan_wish(self, page_size: int):
+        group = self.nh // self.nkv
+        tile = ops.attention_tile_tokens(self.nh, self.nkv, self.rt.dtype, self.hd, page_size, self.window or 0)
+        # CTAs an item: one for every kv head and every 16 query heads of its group
+        return PlanWish(tile, self.nkv * -(-group // 16), self.nh, self.hd)
 
     def forward(self, x, step, cache, writes_cache=True):
         k_pool, v_pool, gi = cache
         g = step.groups[gi]
+        w = g.plan
         T = x.shape[0]
         rot = self.position.rotary() if self.position is not None else None
         cos, sin, rdim = rot if rot is not None else (None, None, 0)
         swizzled = self.cache_need().swizzled
-        if ops.qkv_projection_fuses(x, self.w_qkv, self.nh, self.nkv, self.hd, rdim):
-            # many rows (a prompt portion): the product's epilogue norms and rotates q and k and writes
-            # the cache rows; the [tokens, q + k + v] intermediate is never stored
-            q = torch.empty((T, self.nh * self.hd), dtype=x.dtype, device=x.device)
-            ops.qkv_projection_fused(x, self.w_qkv, q, self.q_gain, self.k_gain, self.qk_norm_eps or 0.0, cos, sin,
-                                     step.positions, g.slots, k_pool if writes_cache else None,
-                                     v_pool if writes_cache else None, self.nh, self.nkv, self.hd, self.rt.status,
-                                     swizzled=swizzled)
-            o = torch.empty_like(q)
-            ops.paged_attention(q, k_pool, v_pool, g.block_tables, g.work, g.n_work, g.max_work, o, g.part_o, g.part_ml,
-                                g.red, g.n_red, g.max_red, self.nh, self.nkv, self.hd, self.window or 0, self.scale,
-                                self.rt.status, swizzled=swizzled, kinds=g.kinds, counters=g.counters, cluster=g.cluster)
-            return ops.linear(o, self.w_o, status=self.rt.status)
         qkv = ops.linear(x, self.w_qkv, status=self.rt.status)
-        if writes_cache and g.kinds == 1 and ops.decode_attention_fuses(x.dtype, self.nh, self.nkv, self.hd, k_pool.shape[2],
+        if writes_cache and w.kinds == 1 and ops.decode_attention_fuses(x.dtype, self.nh, self.nkv, self.hd, k_pool.shape[2],
                                                                           self.window or 0, rdim, swizzled):
             # a step of single decoded tokens: the attention kernel norms and rotates q and k and
             # writes the cache rows itself, straight from the projection's output
             o = torch.empty((T, self.nh * self.hd), dtype=x.dtype, device=x.device)
             ops.decode_attention_fused(qkv, self.q_gain, self.k_gain, self.qk_norm_eps or 0.0, cos, sin, k_pool, v_pool,
-                                       g.block_tables, g.work, g.n_work, g.max_work, o, g.part_o, g.part_ml, g.red,
-                                       g.n_red, g.max_red, self.nh, self.nkv, self.hd, self.scale, self.rt.status,
-                                       cluster=g.cluster)
+                                       g.block_tables, w, o, self.nh, self.nkv, self.hd, self.scale, self.rt.status)
             return ops.linear(o, self.w_o, status=self.rt.status)
         q = torch.empty((T, self.nh * self.hd), dtype=x.dtype, device=x.device)
         ops.qk_norm_rope_kv(qkv, q, self.q_gain, self.k_gain, self.qk_norm_eps or 0.0, cos, sin, rdim,
@@ -104,9 +89,8 @@ class GQAttention(Mixer):
                             v_pool if writes_cache else None, self.nh, self.nkv, self.hd, self.rt.status,
                             swizzled=swizzled)
         o = torch.empty_like(q)
-        ops.paged_attention(q, k_pool, v_pool, g.block_tables, g.work, g.n_work, g.max_work, o, g.part_o, g.part_ml,
-                            g.red, g.n_red, g.max_red, self.nh, self.nkv, self.hd, self.window or 0, self.scale,
-                            self.rt.status, swizzled=swizzled, kinds=g.kinds, counters=g.counters, cluster=g.cluster)
+        ops.paged_attention(q, k_pool, v_pool, g.block_tables, w, o, self.nh, self.nkv, self.hd, self.window or 0,
+                            self.scale, self.rt.status, swizzled=swizzled)
         out = ops.linear(o, self.w_o, status=self.rt.status)
         if self.rt.trace is not None:
             qw, kw = self.nh * self.hd, self.nkv * self.hd

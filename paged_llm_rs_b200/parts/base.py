@@ -50,10 +50,31 @@ class Runtime:
 
 # --- what a mixer needs of the cache manager ------------------------------------
 
+class PagedNeed:
+    """Something kept for every token of a request, in pages that the cache manager hands out and
+    takes back.  kind "full": everything stays until the request ends; "window": only the last
+    ``window`` tokens are ever read, so older pages are given back.  A need says how its pages lie
+    in memory; needs with equal ``group_key()`` share pages, an allocator and block tables.
+    Every need has the fields ``kind``, ``window`` and ``dtype`` (None: the model's dtype)."""
+
+    def group_key(self) -> tuple:
+        raise NotImplementedError
+
+    def pool_shape(self, entries: int, pages: int, page_size: int) -> Tuple[int, ...]:
+        """The shape of the one tensor that holds the pages of ``entries`` runs of layers."""
+        raise NotImplementedError
+
+    def layer_view(self, pool: torch.Tensor, index: int) -> tuple:
+        """What run ``index`` of the group's layers is handed of the pool (the cache manager adds the group's number)."""
+        raise NotImplementedError
+
+    def bytes_per_token(self, element_size: int) -> int:
+        raise NotImplementedError
+
+
 @dataclass(frozen=True)
-class KVNeed:
-    """Paged keys and values.  kind "full": every key stays; "window": only the
-    last ``window`` keys of a request are ever read, so older pages are given back."""
+class KVNeed(PagedNeed):
+    """Paged keys and values, a layer's keys (and likewise values) as [pages, kv_heads, page_size, head_dim]."""
 
     kind: str
     num_kv_heads: int
@@ -62,9 +83,43 @@ class KVNeed:
     # rows stored with their 16-byte chunks XOR-ed by the offset in the page (what the
     # tensor-core attention kernels read); the mixer that reads the pool decides
     swizzled: bool = False
+    group_size: int = 1          # query heads to a kv head
+    dtype: Optional[torch.dtype] = None
 
     def group_key(self) -> tuple:
-        return (self.kind, self.window, self.num_kv_heads, self.head_dim, self.swizzled)
+        return ("kv", self.kind, self.window, self.num_kv_heads, self.head_dim, self.swizzled, self.group_size, self.dtype)
+
+    def pool_shape(self, entries, pages, page_size):
+        return (entries, 2, pages, self.num_kv_heads, page_size, self.head_dim)
+
+    def layer_view(self, pool, index):
+        return (pool[index, 0], pool[index, 1])
+
+    def bytes_per_token(self, element_size):
+        return 2 * self.num_kv_heads * self.head_dim * element_size
+
+
+@dataclass(frozen=True)
+class RowNeed(PagedNeed):
+    """One row of ``width`` values for every token (a latent vector, say), a layer's rows as
+    [pages, page_size, width]: the page of a mixer that does not keep keys and values per head."""
+
+    width: int
+    kind: str = "full"
+    window: Optional[int] = None
+    dtype: Optional[torch.dtype] = None
+
+    def group_key(self) -> tuple:
+        return ("rows", self.kind, self.window, self.width, self.dtype)
+
+    def pool_shape(self, entries, pages, page_size):
+        return (entries, pages, page_size, self.width)
+
+    def layer_view(self, pool, index):
+        return (pool[index],)
+
+    def bytes_per_token(self, element_size):
+        return self.width * element_size
 
 
 @dataclass(frozen=True)
@@ -76,15 +131,25 @@ class StateNeed:
     dtype: torch.dtype = torch.float32
 
 
+@dataclass(frozen=True)
+class PlanWish:
+    """What a mixer whose kernels read attention work items asks of the step packer: items of at
+    most ``tile_tokens`` query tokens, for a kernel that launches ``ctas_per_item`` CTAs an item
+    and leaves partial results of ``heads`` x ``head_dim`` a token where a key range was split."""
+
+    tile_tokens: int
+    ctas_per_item: int
+    heads: int
+    head_dim: int
+
+
 # --- the step as parts see it ---------------------------------------------------
 
 @dataclass
-class GroupStep:
-    """One cache group's share of a step: where tokens are written and what the
-    attention kernels read (see engine/step.py for how it is made)."""
+class AttentionWork:
+    """A step's attention cut into work items for a cache group (kernels/attention_plan.py), with
+    the scratch for split items: made only for groups whose mixers wish for it (Mixer.plan_wish)."""
 
-    block_tables: torch.Tensor  # int32 [segments, table_width]; -1 where a page was given back
-    slots: torch.Tensor         # int32 [tokens]: page * page_size + offset for each token
     work: torch.Tensor          # int32 [max_work, 8] attention work items
     n_work: torch.Tensor        # int32 [1]
     max_work: int
@@ -94,10 +159,17 @@ class GroupStep:
     part_o: torch.Tensor        # float32 scratch for split items
     part_ml: torch.Tensor
     kinds: int = 3              # what the work items are: 1 single tokens only, 2 portions only, 3 both
-    counters: Optional[torch.Tensor] = None   # int32 zeros [max_work * CTAs an item]: a kernel that combines
-                                              # the splits itself counts them off here and leaves zeros
-    cluster: int = 0            # > 1: the list holds that many items for every (single) token, which the
-                                # attention kernel combines inside a thread-block cluster; red is empty
+    many_splits: bool = False   # the step is cut into eight splits a tile or more (the reduction then shares them out)
+
+
+@dataclass
+class GroupStep:
+    """One cache group's share of a step: where each token is written and where its request's
+    pages lie (see engine/step.py for how it is made)."""
+
+    block_tables: torch.Tensor  # int32 [segments, table_width]; -1 where a page was given back
+    slots: torch.Tensor         # int32 [tokens]: page * page_size + offset for each token
+    plan: Optional[AttentionWork] = None
 
 
 @dataclass
@@ -154,13 +226,6 @@ class Norm(Part):
                 return self.forward(residual.index_select(0, rows.long()) + delta.index_select(0, rows.long()))
         return self.forward(residual, rows)
 
-    def add_norm_deferred(self, residual: torch.Tensor, delta: Optional[torch.Tensor]):
-        """The same as ``add_norm`` but not yet run: an object that the kernels'
-        products take in place of a tensor (ops.NormedInput), whose ``residual_out``
-        is the new residual stream; or None when this norm has no such form for
-        these rows.  Only handed to parts with ``takes_normed_input``."""
-        return None
-
 
 class PositionEncoding(Part):
     """Built once per model and handed to the mixers that name it."""
@@ -172,9 +237,6 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    # True when forward() hands x straight to a product (ops.linear / ops.linear_glu), so
-    # that the block may pass a norm that is not yet formed (ops.NormedInput) instead of a tensor.
-    takes_normed_input = False
     # True when forward() only launches kernels whose arguments do not depend on the
     # step's contents, so that a decode step can be captured once and replayed.
     graph_safe = False
@@ -183,22 +245,22 @@ class Mixer(Part):
         """KVNeed, StateNeed or None."""
         return None
 
-    def cluster_limit(self, page_size: int) -> int:
-        """For a mixer that reads its group's attention work items: the most items of one single
-        token it can take as a cluster (GroupStep.cluster), 0 when it wants split items with
-        partial rows and reductions.  The packer plans a group for the least of its mixers."""
-        return 0
+    def plan_wish(self, page_size: int) -> Optional[PlanWish]:
+        """For a mixer that reads attention work items (``GroupStep.plan``): how it wants the step's
+        attention cut for pages of ``page_size`` tokens.  None (the default): its group gets block
+        tables and slots only.  The mixers that share a cache group must wish alike."""
+        return None
 
     def forward(self, x: torch.Tensor, step: StepState, cache, writes_cache: bool = True) -> torch.Tensor:
-        """x [tokens, hidden] -> [tokens, hidden].  ``cache`` is what the cache
-        manager made for this run of the layer: (k_pool, v_pool, group index) for a
-        KVNeed, the state tensor [slots, *shape] for a StateNeed, None otherwise."""
+        """x [tokens, hidden] -> [tokens, hidden].  ``cache`` is what the cache manager made for
+        this run of the layer: for a paged need its ``layer_view`` and the group's number
+        ((k_pool, v_pool, group) for a KVNeed, (rows, group) for a RowNeed; the group's
+        tables and slots are ``step.groups[group]``), the state tensor [slots, *shape] for a
+        StateNeed, None otherwise."""
         raise NotImplementedError
 
 
 class FeedForward(Part):
-    takes_normed_input = False   # as for Mixer
-
     def forward(self, x: torch.Tensor, step: StepState) -> torch.Tensor:
         raise NotImplementedError
 

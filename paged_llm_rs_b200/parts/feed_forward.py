@@ -28,8 +28,6 @@ class SwiGLUMLP(FeedForward):
         self.w_gate_up = torch.cat([tensors[self._name("gate_proj.weight")], tensors[self._name("up_proj.weight")]], 0)
         self.w_down = tensors[self._name("down_proj.weight")]
 
-    takes_normed_input = True
-
     def forward(self, x, step):
         act = ops.linear_glu(x, self.w_gate_up, status=self.rt.status)
         out = ops.linear(act, self.w_down, status=self.rt.status)

@@ -1,7 +1,6 @@
 """RMSNorm (crates/pagedllm/src/model/layers.rs:40-65): x / sqrt(mean(x^2) + eps)
 times a gain, the statistic in float.  ``add_norm`` fuses the residual add that
-precedes it (crates/pagedllm/src/model/mod.rs:131-132) into the same kernel;
-``add_norm_deferred`` leaves both to the product that follows (a decode step)."""
+precedes it (crates/pagedllm/src/model/mod.rs:131-132) into the same kernel."""
 
 from __future__ import annotations
 
@@ -40,12 +39,6 @@ class RMSNorm(Norm):
                     residual_out=residual if (delta is not None and rows is None) else None, rows=rows)
         self.rt.record(self._name("out"), out)
         return out
-
-    def add_norm_deferred(self, residual, delta):
-        # the few rows of a decode step in bfloat16: the product that follows does the add and the norm
-        if not ops.deferred_norm_pays(residual.shape[0], self.width, residual.dtype):
-            return None
-        return ops.NormedInput(residual, delta, self.gain, self.eps)
 
 
 register_norm("rmsnorm", RMSNorm)

@@ -153,49 +153,6 @@ def test_greedy_many_requests_decoding_beside_prompt_portions(tmp_path):
     assert outs[True] == outs[False]
 
 
-def test_greedy_with_splits_combined_in_clusters(tmp_path):
-    # the option that combines a decoded token's splits inside a thread-block cluster, through the engine:
-    # the packer cuts every token into whole clusters, the captured step launches them, no reduction runs
-    from paged_llm_rs_b200 import Engine
-    from paged_llm_rs_b200.kernels import ops
-    cfg, seed = CONFIGS["D"]
-    model = write_model(tmp_path, "D")
-    prompts = prompts_for(cfg["vocab_size"], [90, 3, 130, 64], 21)
-    was, ops.CLUSTER_COMBINE = ops.CLUSTER_COMBINE, True
-    try:
-        for graphs in (True, False):
-            eng = Engine(model, dtype="bfloat16", block_size=16, blocks=64, chunk=48)
-            eng.runner.use_graphs = graphs
-            pk = eng.runner.packer
-            assert pk.plans[0].max_cluster == 8
-            pk.target_ctas = 4 * 4 * pk.plans[0].ctas_per_item          # four requests: clusters of four
-            assert pk.cluster_for(0, 4) == 4
-            outs = eng.generate(prompts, max_tokens=24)
-            check_greedy(model, prompts, outs, 24, "bfloat16")
-            if graphs:
-                g = eng.runner._graphs[(4, 64)]
-                assert g.state.groups[0].cluster == 4
-    finally:
-        ops.CLUSTER_COMBINE = was
-
-
-def test_greedy_with_the_input_projection_that_norms_rotates_and_writes_the_cache(tmp_path, monkeypatch):
-    # the option that folds the q/k norm, the rotation and the cache write into the product's epilogue,
-    # through the engine: prompts long enough for the tensor-core tiles, then decoding from what it wrote
-    from paged_llm_rs_b200 import Engine
-    from paged_llm_rs_b200.kernels import ops
-    cfg, seed = CONFIGS["D"]
-    model = write_model(tmp_path, "D")
-    prompts = prompts_for(cfg["vocab_size"], [90, 130, 64], 22)
-    monkeypatch.setattr(ops, "FUSE_QKV_GEMM", True)
-    eng = Engine(model, dtype="bfloat16", block_size=16, blocks=64, chunk=None)
-    m = eng.runner.model.blocks[0].mixer
-    x = torch.zeros(90, m.w_qkv.shape[1], dtype=torch.bfloat16, device="cuda:0")
-    assert ops.qkv_projection_fuses(x, m.w_qkv, m.nh, m.nkv, m.hd, m.hd)
-    outs = eng.generate(prompts, max_tokens=12)
-    check_greedy(model, prompts, outs, 12, "bfloat16")
-
-
 def vocab_order_choice(logits64, temperature, u):
     """The engine's device draw: ids upward, the first id whose running sum reaches u * total."""
     p = torch.softmax(logits64 / temperature, -1)

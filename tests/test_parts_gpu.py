@@ -121,14 +121,17 @@ def test_attention_part_alone_in_portions(dtype, window):
     w = {k: v.to(dtype) if "norm" not in k else v for k, v in attention_weights(cfg, "a", 10).items()}
     att.bind({k: v.to(DEV) for k, v in w.items()})
     cache = CacheManager([att.cache_need()], 8, 12, 4, dtype, DEV, prefix_cache=False)
-    packer = StepPacker(cache, [GroupPlanConfig(ops.attention_tile_tokens(nh, nkv, dtype, hd), nkv, window)], 296, 1000, 64, DEV)
+    wish = att.plan_wish(8)
+    assert (wish.heads, wish.head_dim, wish.ctas_per_item) == (nh, hd, nkv)
+    packer = StepPacker(cache, [GroupPlanConfig(wish.tile_tokens, wish.ctas_per_item, window, wish.heads, wish.head_dim)],
+                        296, 1000, 64, DEV)
     x = rand((40, H), 20).to(dtype)
     cache.open("r")
     outs, p = [], 0
     for n in (13, 2, 24, 1):
         assert cache.reserve("r", n)
-        host, layout, sizes = packer.pack([StepEntry("r", [0] * n, [])], [(nh, hd)])
-        state = packer.to_state(torch.from_numpy(host).to(DEV), layout, sizes, [(nh, hd)])
+        host, layout, sizes = packer.pack([StepEntry("r", [0] * n, [])])
+        state = packer.to_state(torch.from_numpy(host).to(DEV), layout, sizes)
         outs.append(att.forward(x[p:p + n].to(DEV).contiguous(), state, cache.layer_caches()[0]))
         cache.commit("r", n)
         p += n
@@ -268,3 +271,116 @@ def test_toy_mixer_and_schedule_without_touching_the_framework(tmp_path, dtype):
         assert np.abs(g - want[r]).max() / max(1.0, np.abs(want[r]).max()) <= t, r
     cache.close("a"); cache.close("b")
     cache.check_invariants()
+
+
+# --- a second toy mixer: one latent row per token, kept in pages of its own shape ---------------
+
+class LatentMeanMixer(Mixer):
+    """c_t = W_c x_t (``latent`` values) is cached for every token, in pages, as one row a token:
+    not keys and values per head.  y_t = W_o mean(c_0 .. c_t).  It asks for no attention work
+    items: the group's block tables and write slots are all it reads of the step."""
+
+    def __init__(self, spec, rt, position_encodings=None):
+        super().__init__(spec, rt)
+        self.hidden, self.latent = spec.params["hidden_size"], spec.params["latent"]
+
+    def tensors(self):
+        return [TensorSpec(self._name("down.weight"), (self.latent, self.hidden)),
+                TensorSpec(self._name("up.weight"), (self.hidden, self.latent))]
+
+    def bind(self, tensors):
+        self.w_c, self.w_o = tensors[self._name("down.weight")], tensors[self._name("up.weight")]
+
+    def cache_need(self):
+        return base.RowNeed(self.latent)
+
+    def forward(self, x, step, cache, writes_cache=True):
+        rows, gi = cache                                     # [pages, page_size, latent]
+        g = step.groups[gi]
+        assert g.plan is None
+        c = x @ self.w_c.t()
+        flat = rows.view(-1, self.latent)
+        if writes_cache:
+            flat[g.slots[:x.shape[0]].long()] = c
+        out = torch.empty_like(x)
+        ps = rows.shape[1]
+        for si, (t0, n, before, slot) in enumerate(step.host_segments):
+            total = before + n
+            pages = g.block_tables[si, :-(-total // ps)].long()
+            seen = rows[pages].reshape(-1, self.latent)[:total].float()
+            mean = torch.cumsum(seen, 0)[before:] / torch.arange(before + 1, total + 1, device=x.device)[:, None]
+            out[t0:t0 + n] = mean.to(x.dtype) @ self.w_o.t()
+        return out
+
+
+def describe_latent(cfg: Qwen3Config) -> ModelSpec:
+    spec = describe_qwen3(cfg)
+    spec.layers[1].mixer = PartSpec("latent_mean", dict(hidden_size=cfg.hidden_size, latent=40), "model.layers.1.latent")
+    return spec
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_mixer_that_caches_one_latent_row_a_token_in_pages(tmp_path, dtype):
+    register_mixer("latent_mean", LatentMeanMixer, replace=True)
+    register_architecture(Architecture("ToyLatentForCausalLM", parse=parse_toy, describe=describe_latent), replace=True)
+    cfg = dict(TINY_C, architectures=["ToyLatentForCausalLM"], model_type="toy_latent")
+    model = write_random_model(str(tmp_path / "latent"), cfg, 5)
+    runner = ModelRunner(model, dtype=dtype, page_size=8, num_pages=12, max_requests=4)
+    cache = runner.cache
+    # two groups with pages of different shapes: keys and values per head, and rows of 40 values
+    assert [type(g.need).__name__ for g in cache.groups] == ["KVNeed", "RowNeed"]
+    assert cache.groups[1].pool.shape == (1, 12, 8, 40) and runner.packer.plans[1] is None
+    esz = 4 if dtype == "float32" else 2
+    assert cache.bytes_per_token() == (2 * 3 * 48 + 40) * esz
+    assert not runner.use_graphs                              # (the toy loops over the step on the host)
+
+    c64, w = P.load_model(model, torch.float64)
+
+    def plain(tokens):
+        n = len(tokens)
+        x = P.embed(torch.tensor(tokens), w["model.embed_tokens.weight"])
+        cos, sin = P.rope_tables(c64["head_dim"], n, c64["rope_theta"], torch.float64)
+        eps = c64["rms_norm_eps"]
+
+        def latent(h):
+            c = h @ w["model.layers.1.latent.down.weight"].t()
+            mean = torch.cumsum(c, 0) / torch.arange(1, n + 1, dtype=c.dtype)[:, None]
+            return mean @ w["model.layers.1.latent.up.weight"].t()
+
+        for layer, mixer in ((0, lambda h: P.attention(h, w, "model.layers.0.self_attn", c64, cos, sin, None)), (1, latent)):
+            p = f"model.layers.{layer}"
+            x = x + mixer(P.rms_norm(x, w[f"{p}.input_layernorm.weight"], eps))
+            x = x + P.swiglu_mlp(P.rms_norm(x, w[f"{p}.post_attention_layernorm.weight"], eps), w, f"{p}.mlp")
+        return P.linear(P.rms_norm(x, w["model.norm.weight"], eps), w["model.embed_tokens.weight"]).numpy()
+
+    rng = np.random.default_rng(1)
+    toks = {r: rng.integers(0, 1000, n).tolist() for r, n in (("a", 30), ("b", 21), ("c", 9))}
+    got, fed = {r: {} for r in toks}, {r: 0 for r in toks}
+
+    def run(parts, end=()):
+        entries = []
+        for r, n in parts:
+            if not cache.has(r):
+                cache.open(r)
+            assert cache.reserve(r, n)
+            entries.append(StepEntry(r, toks[r][fed[r]:fed[r] + n], list(range(n))))
+        logits = runner.step(entries).cpu().numpy()
+        row = 0
+        for e in entries:
+            for i in range(len(e.tokens)):
+                got[e.request_id][fed[e.request_id] + i] = logits[row]; row += 1
+            cache.commit(e.request_id, len(e.tokens))
+            fed[e.request_id] += len(e.tokens)
+        for r in end:
+            cache.close(r)
+
+    # portions beside single tokens; "c" runs in the pages that "b" gave back
+    run([("a", 11)]); run([("a", 2), ("b", 9)]); run([("a", 1), ("b", 1)]); run([("b", 11), ("a", 16)], end=["b"])
+    run([("c", 7)]); run([("c", 2)], end=["c", "a"])
+    t = 2e-5 if dtype == "float32" else 3e-2
+    for r in toks:
+        want = plain(toks[r])
+        have = np.stack([got[r][i] for i in range(len(toks[r]))])
+        assert np.abs(have - want).max() / max(1.0, np.abs(want).max()) <= t, r
+    cache.check_invariants()
+    assert cache.available() == 12
