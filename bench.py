@@ -280,7 +280,7 @@ def decode_point(runner, batch, context, steps, warmup, clocks, repeats=9):
     uni = np.zeros(batch, dtype=np.float32)
     runner.step_and_sample(entries, temp, uni)          # packs the step, captures the graph on first use
     graph = runner._decode_graph(entries)
-    ms, span, spread = time_on_device(graph.graph.replay, steps, warmup, repeats)
+    ms, span, spread = time_on_device(graph.replay, steps, warmup, repeats)
     clocks.region(*span)
     launches = graph.launches
     for r in ids:
@@ -312,7 +312,7 @@ def mixed_point(runner, decoding, context, portion, behind, vocab, steps, warmup
         runner.step_and_sample(entries, zeros, zeros)
         graph = runner._portion_graph(entries)
         assert graph is not None, "the mixed step does not run as a captured step"
-        ms, span, spread = time_on_device(graph.graph.replay, steps, warmup, repeats)
+        ms, span, spread = time_on_device(graph.replay, steps, warmup, repeats)
     finally:
         runner.graph_step_tokens = was
     clocks.region(*span)
@@ -486,10 +486,10 @@ def timeline(runner, batch, context, layers, prefill_tokens=0, vocab=1000, mixed
         runner.step_and_sample(entries, zeros, zeros)
         graph = runner._decode_graph(entries)
     for _ in range(5):
-        graph.graph.replay()
+        graph.replay()
     torch.cuda.synchronize()
     read()
-    graph.graph.replay()
+    graph.replay()
     torch.cuda.synchronize()
     recs = read()
     rows = []

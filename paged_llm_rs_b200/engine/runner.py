@@ -92,7 +92,11 @@ class _DecodeGraph:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         before = ops.LAUNCHES
-        self.graph = torch.cuda.CUDAGraph()
+        # The step is one captured graph, or, where mixers are not ``graph_safe``, graphs with those
+        # mixers between them: ("graph", CUDAGraph) and ("eager", fn, buffer) in the order they run.
+        self.pieces = []
+        self._ctx = None
+        piecewise = not all(getattr(b.mixer, "graph_safe", False) for b in runner.model.blocks)
         # The collector must not run inside the capture: freeing an older engine's graphs
         # there (they die in reference cycles, at a time of the collector's choosing) is a
         # call the capture forbids, and the capture would be invalidated.
@@ -100,23 +104,68 @@ class _DecodeGraph:
         collecting = gc.isenabled()
         gc.disable()
         try:
-            # one memory pool for all of this runner's captured steps: they never run at the same time, so
-            # the activations of one may lie where another's did (a 2048-token step holds some 150 MB)
-            with torch.cuda.graph(self.graph, pool=runner.graph_pool), torch.no_grad():
-                self._body()
+            with torch.no_grad():
+                self._begin_piece()
+                self._body(self._outside if piecewise else None)
+                self._end_piece()
         finally:
             if collecting:
                 gc.enable()
+        self.graph = self.pieces[0][1] if len(self.pieces) == 1 else None     # (the whole step, when it is one graph)
         self.launches = ops.LAUNCHES - before
 
-    def _body(self):
+    def _begin_piece(self):
+        # one memory pool for all of this runner's captured steps: they never run at the same time, so
+        # the activations of one may lie where another's did (a 2048-token step holds some 150 MB)
+        g = torch.cuda.CUDAGraph()
+        self._ctx = torch.cuda.graph(g, pool=self.runner.graph_pool)
+        self._ctx.__enter__()
+        self.pieces.append(("graph", g))
+
+    def _end_piece(self):
+        self._ctx.__exit__(None, None, None)
+        self._ctx = None
+
+    def _outside(self, fn, like):
+        """A mixer that cannot be captured: the capture ends before it and begins again behind it; the
+        mixer reads what the graph before it left (fixed addresses) and its result is copied into a
+        fixed buffer that the graph behind it reads."""
+        self._end_piece()
+        buf = torch.empty_like(like)
+        buf.copy_(fn())
+        self.pieces.append(("eager", fn, buf))
+        self._begin_piece()
+        return buf
+
+    def replay(self):
+        if self.graph is not None:
+            self.graph.replay()
+            return
+        with torch.no_grad():
+            for piece in self.pieces:
+                if piece[0] == "graph":
+                    piece[1].replay()
+                else:
+                    piece[2].copy_(piece[1]())
+
+    def _body(self, outside=None):
         r = self.runner
         if self.decode:
             self.dev.copy_(self.pinned, non_blocking=True)  # the step's packed buffer: the graph's first node
-        self.logits = r.model.forward(self.state, r.caches)
+        self.logits = r.model.forward(self.state, r.caches, outside)
         ops.sample(self.logits, self.state.temperature, self.state.uniform, self.tokens[1:])
         self.tokens[:1].copy_(r.rt.status)
         self.tokens_host.copy_(self.tokens, non_blocking=True)
+
+    def _segments_of(self, entries, ahead=0):
+        """(first token, tokens, tokens in the cache before, state slot) of every request of the step: what
+        mixers that loop over the step on the host read (the captured pieces read the packed buffer)."""
+        cache, segs, t0 = self.runner.cache, [], 0
+        for e in entries:
+            rc = cache.get(e.request_id)
+            segs.append((t0, len(e.tokens), rc.tokens + ahead, rc.state_slot))
+            t0 += len(e.tokens)
+        return segs
 
     # -- a decode step packed ahead of time (while the step before it runs) ---------------------------
     def prepack(self, entries, temperature) -> None:
@@ -127,6 +176,7 @@ class _DecodeGraph:
             self.staging = np.zeros_like(self.pinned_np)
         self.native.pack(entries, temperature, np.zeros(len(entries), dtype=np.float32) if temperature is not None else None,
                          ahead=1, out=self.staging)
+        self._staged_segments = self._segments_of(entries, ahead=1) if self.graph is None else None
 
     def launch_prepacked(self, tokens, uniform):
         """Put the token ids (and uniform numbers) into the buffer ``prepack`` filled, and replay."""
@@ -139,6 +189,8 @@ class _DecodeGraph:
             self.staging[o:o + n] = np.asarray(uniform, dtype=np.float32).view(np.int32)
         self._before_write()
         np.copyto(self.pinned_np, self.staging)
+        if self.graph is None:
+            self.state.host_segments = self._staged_segments
         self._replay()
         r.bytes_h2d = self.nbytes
         r.last_launches = self.launches
@@ -151,12 +203,14 @@ class _DecodeGraph:
             self._pending = False
 
     def _replay(self):
-        self.graph.replay()
+        self.replay()
         self._replayed.record()
         self._pending = True
 
     def run(self, entries, temperature, uniform):
         r = self.runner
+        if self.graph is None:
+            self.state.host_segments = self._segments_of(entries)
         if self.decode:
             self._before_write()
             if self.native is not None:
@@ -175,7 +229,7 @@ class _DecodeGraph:
             self.dev.copy_(self._pinned[i], non_blocking=True)
             self._copied[i].record()
             self._copy_pending[i] = True
-            self.graph.replay()
+            self.replay()
         r.bytes_h2d = self.nbytes
         r.last_launches = self.launches
         n = sum(len(e.want) for e in entries)
@@ -228,9 +282,10 @@ class ModelRunner:
         self.packer = StepPacker(self.cache, plans, 2 * ops.sm_count(), self.spec.vocab_size, self.spec.max_positions,
                                  self.device)
         self.vocab_size = self.spec.vocab_size
-        # A captured step replays fixed launches; a mixer that loops over the step on the
-        # host (it says so by graph_safe = False) keeps the engine on plain launches.
-        self.use_graphs = use_graphs and all(getattr(b.mixer, "graph_safe", False) for b in self.model.blocks)
+        # A captured step replays fixed launches.  A mixer that loops over the step on the host (it says
+        # so by graph_safe = False) is left out of the capture and launched between the captured pieces,
+        # where its block can be run in halves around it; else it keeps the engine on plain launches.
+        self.use_graphs = use_graphs and self.model.capturable()
         self.max_graph_batch = max_graph_batch
         self._graphs = {}
         self.graph_pool = torch.cuda.graph_pool_handle()

@@ -279,6 +279,16 @@ class Block:
     def forward(self, residual, delta, step: StepState, cache, writes_cache: bool):
         raise NotImplementedError
 
+    # An arrangement may also give its forward in two halves around the mixer:
+    #   h = pre_mixer(residual, delta);  a = mixer.forward(h, step, cache, writes_cache);
+    #   residual, delta = post_mixer(residual, a, step)
+    # Then a step is still captured and replayed when the mixer is not ``graph_safe``: the
+    # capture ends before the mixer and begins again behind it, and the mixer alone is launched
+    # kernel by kernel at every replay.  Without them such a mixer keeps the whole model on
+    # plain launches.
+    pre_mixer = None
+    post_mixer = None
+
 
 # --- registries -------------------------------------------------------------------
 

@@ -61,14 +61,28 @@ class DecoderModel:
         return [None if e.reads_cache_of is not None else self.blocks[e.layer].mixer.cache_need()
                 for e in self.schedule]
 
-    def forward(self, step: StepState, caches: List[object]) -> torch.Tensor:
-        """Run the step's tokens; return float32 logits [step.n_wanted, vocab]."""
+    def capturable(self) -> bool:
+        """Whether a step of this model can be captured and replayed: every mixer either launches
+        fixed kernels only (``graph_safe``) or sits in a block that can be run in halves around it."""
+        return all(getattr(b.mixer, "graph_safe", False) or (b.pre_mixer is not None and b.post_mixer is not None)
+                   for b in self.blocks)
+
+    def forward(self, step: StepState, caches: List[object], outside=None) -> torch.Tensor:
+        """Run the step's tokens; return float32 logits [step.n_wanted, vocab].  ``outside``
+        (for a step that is being captured): called as outside(fn, like) for every mixer that is
+        not ``graph_safe``; it runs fn() outside the capture, now and at every replay, and returns
+        a tensor shaped like ``like`` that holds fn()'s result each time."""
         residual = self.embedding.forward(step.tokens)
         delta = None
         for i, e in enumerate(self.schedule):
             own = e.reads_cache_of is None
-            residual, delta = self.blocks[e.layer].forward(residual, delta, step,
-                                                           caches[i if own else e.reads_cache_of], own)
+            blk, cache = self.blocks[e.layer], caches[i if own else e.reads_cache_of]
+            if outside is not None and not getattr(blk.mixer, "graph_safe", False):
+                h = blk.pre_mixer(residual, delta)
+                a = outside(lambda blk=blk, h=h, cache=cache, own=own: blk.mixer.forward(h, step, cache, own), h)
+                residual, delta = blk.post_mixer(residual, a, step)
+                continue
+            residual, delta = blk.forward(residual, delta, step, cache, own)
         if step.n_wanted == 0:
             # A portion in the middle of a prompt runs only to fill the cache (mod.rs:336-346).
             return torch.zeros((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)

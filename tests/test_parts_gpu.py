@@ -301,7 +301,9 @@ class LatentMeanMixer(Mixer):
         c = x @ self.w_c.t()
         flat = rows.view(-1, self.latent)
         if writes_cache:
-            flat[g.slots[:x.shape[0]].long()] = c
+            slots = g.slots[:x.shape[0]].long()
+            live = slots >= 0                                # (a captured step's padding has slot -1: nothing is written)
+            flat[slots[live]] = c[live]
         out = torch.empty_like(x)
         ps = rows.shape[1]
         for si, (t0, n, before, slot) in enumerate(step.host_segments):
@@ -332,7 +334,7 @@ def test_a_mixer_that_caches_one_latent_row_a_token_in_pages(tmp_path, dtype):
     assert cache.groups[1].pool.shape == (1, 12, 8, 40) and runner.packer.plans[1] is None
     esz = 4 if dtype == "float32" else 2
     assert cache.bytes_per_token() == (2 * 3 * 48 + 40) * esz
-    assert not runner.use_graphs                              # (the toy loops over the step on the host)
+    assert runner.use_graphs                                  # (captured around the toy, which loops over the step on the host)
 
     c64, w = P.load_model(model, torch.float64)
 
@@ -384,3 +386,48 @@ def test_a_mixer_that_caches_one_latent_row_a_token_in_pages(tmp_path, dtype):
         assert np.abs(have - want).max() / max(1.0, np.abs(want).max()) <= t, r
     cache.check_invariants()
     assert cache.available() == 12
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_step_is_captured_around_a_mixer_that_cannot_be(tmp_path, dtype):
+    """The toy mixer with state loops over the step on the host (graph_safe is False).  The step is
+    captured all the same: the capture ends before each such mixer and begins again behind it, and at
+    every replay the mixer alone is launched between the captured pieces.  Three requests decode through
+    the step captured for four (one row of padding), against the plain implementation."""
+    register_mixer("running_mean", RunningMeanMixer, replace=True)
+    register_architecture(Architecture("ToyStateForCausalLM", parse=parse_toy, describe=describe_toy), replace=True)
+    model = write_random_model(str(tmp_path / "toy"), TOY, 3)
+    runner = ModelRunner(model, dtype=dtype, page_size=8, num_pages=24, max_requests=4)
+    assert runner.use_graphs and runner.model.capturable()
+    cache = runner.cache
+    rng = np.random.default_rng(2)
+    lens, steps = dict(a=19, b=3, c=30), 6
+    toks = {r: rng.integers(0, 1000, n + steps).tolist() for r, n in lens.items()}
+    for r, n in lens.items():
+        cache.open(r)
+        assert cache.reserve(r, n)
+        runner.step([StepEntry(r, toks[r][:n], [])])
+        cache.commit(r, n)
+    want = {r: plain_toy(model, t) for r, t in toks.items()}
+    zeros = np.zeros(3, dtype=np.float32)
+    t = 2e-5 if dtype == "float32" else 3e-2
+    for i in range(steps):
+        entries = [StepEntry(r, [toks[r][lens[r] + i]], [0]) for r in lens]
+        for r in lens:
+            assert cache.reserve(r, 1)
+        logits, tokens = runner.step_and_sample(entries, zeros, zeros)
+        logits = logits.cpu().numpy()
+        graph = runner._decode_graph(entries)
+        kinds = [p[0] for p in graph.pieces]
+        # layers 0, toy, 0 again, toy: graph, toy, graph, toy, graph
+        assert graph.B == 4 and kinds == ["graph", "eager", "graph", "eager", "graph"]
+        runner.check_status()
+        assert (tokens.cpu().numpy()[1:] == logits.argmax(1)).all()
+        for row, r in enumerate(lens):
+            w = want[r][lens[r] + i]
+            assert np.abs(logits[row] - w).max() / max(1.0, np.abs(w).max()) <= t, (r, i)
+        for r in lens:
+            cache.commit(r, 1)
+    for r in lens:
+        cache.close(r)
+    cache.check_invariants()
