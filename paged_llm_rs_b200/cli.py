@@ -55,6 +55,11 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--prompt-ids", action="append", default=[], metavar="1,2,3",
                    help="one prompt as comma-separated token ids; may be given several times")
     g.add_argument("--prompts-file", help="JSON file with a list of prompts, each a list of token ids")
+    g.add_argument("--prompt-len", type=int, action="append", default=[], metavar="N",
+                   help="one prompt of N uniform-random token ids drawn from --seed; may be given several times")
+    g.add_argument("--reference-draw-order", action="store_true",
+                   help="draw plain temperature requests on the host in the reference's order (falling probability), "
+                        "so that a seed gives the reference's tokens; default: on the device, token ids upward")
     g.add_argument("--temperature", type=float, default=None)
     g.add_argument("--top-k", type=int, default=None)
     g.add_argument("--top-p", type=float, default=None)
@@ -94,8 +99,8 @@ def main(argv=None) -> int:
     if args.prompts_file:
         with open(args.prompts_file) as f:
             prompts += json.load(f)
-    if not prompts:
-        print("no prompt: give --prompt-ids or --prompts-file", file=sys.stderr)
+    if not prompts and not args.prompt_len:
+        print("no prompt: give --prompt-ids, --prompts-file or --prompt-len", file=sys.stderr)
         return 2
     dtype = args.dtype
     if dtype == "auto":  # the checkpoint's own dtype, read from the embedding (model/mod.rs:175)
@@ -110,7 +115,11 @@ def main(argv=None) -> int:
     stop = [int(x) for x in args.stop_ids.split(",") if x.strip()] or list(defaults.eos_token_ids)
     engine = Engine(args.model, dtype=dtype, block_size=args.block_size, cache_mib=args.cache_mib, blocks=args.blocks,
                     max_batch=args.max_batch, chunk=args.chunk, prefix_cache=args.prefix_cache,
-                    max_prefill_seqs=args.max_prefill_seqs)
+                    max_prefill_seqs=args.max_prefill_seqs, reference_draw_order=args.reference_draw_order)
+    if args.prompt_len:
+        import numpy as np
+        rng = np.random.default_rng(args.seed)
+        prompts += [rng.integers(0, engine.runner.vocab_size, n).tolist() for n in args.prompt_len]
     cache = engine.runner.cache
     print(f"model {args.model}  dtype {dtype}  cache {cache.num_pages} pages of {cache.page_size} tokens, "
           f"{cache.bytes_per_token()} bytes a token  chunk {args.chunk or 'off'}  "

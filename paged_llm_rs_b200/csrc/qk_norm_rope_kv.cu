@@ -160,9 +160,11 @@ __global__ void qk_norm_rope_kv_vec_kernel(
     v.store(dst + (c ^ xr) * N);
 }
 
-// The same for the many tokens of a prompt portion: one warp takes a whole token, 32 / LPH
-// heads at a time, so that the token's rotation angles and the two gains are fetched once a
-// warp and not once a head, and four heads' loads are in flight together.
+// The same for the many tokens of a prompt portion: the four warps of a CTA share one token, each
+// taking every fourth run of its heads, 32 / LPH heads at a time, so that the token's rotation
+// angles and the two gains are fetched once a warp and not once a head, four heads' loads are in
+// flight together, and an SM holds some fifty warps (with a warp a token it held fourteen, and the
+// kernel waited on its loads: 15.0 us for the 2048 tokens of the 0.6B shape).
 template <typename T, int LPH>
 __global__ void __launch_bounds__(128) qk_norm_rope_kv_token_kernel(
     const T* qkv, T* __restrict__ q_out, const float* __restrict__ q_gain,
@@ -173,7 +175,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kv_token_kernel(
     pdl_launch_dependents();
     pdl_wait(KID_QK);
     const int lane = threadIdx.x & 31, sub = lane / LPH, c = lane % LPH;
-    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     if (t >= n_tokens) return;
     const int heads = nh + 2 * nkv;
     float cs[N], sn[N], gq[N], gk[N];
@@ -197,7 +199,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kv_token_kernel(
     }
     const int xr = swizzle ? (off & 7) : 0;
     const T* src = qkv + (size_t)t * heads * HD + c * N;
-    for (int h0 = 0; h0 < heads; h0 += HPW * UNR) {
+    for (int h0 = warp * HPW * UNR; h0 < heads; h0 += warps * HPW * UNR) {
         Vec16<T> v[UNR];
 #pragma unroll
         for (int u = 0; u < UNR; u++) {
@@ -248,11 +250,10 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kv_token_kernel(
     }
 }
 
-// From how many tokens on a warp takes a whole token (a setter for tuning runs).  Measured back to back,
-// 16 + 2 x 8 heads of 128: 512 tokens 5.0 us a warp an item pair against 8.4 a warp a token, 1024: 7.5 / 11.5,
-// 2048: 12.2 / 12.8, 4096: 21.9 / 19.8; inside the 2048-token step the warp a token is the faster one
-// (3.455 against 3.504 ms for the step).
-static int g_qk_token_threshold = 1536;
+// From how many tokens on a CTA takes a whole token (a setter for tuning runs).  Measured back to back in a
+// captured loop, 16 + 2 x 8 heads of 128, microseconds a CTA a token / a warp a pair of heads: 512 tokens
+// 5.1 / 5.0, 1024: 6.1 / 7.4, 2048: 10.7 / 12.1, 4096: 19.2 / 21.8.
+static int g_qk_token_threshold = 768;
 PLLM_EXPORT int pllm_qk_set_token_threshold(int n) {
     const int was = g_qk_token_threshold;
     g_qk_token_threshold = n;
@@ -268,7 +269,7 @@ static void launch_qk_vec(const void* qkv, void* q_out, const float* q_gain, con
     const int per_block = 4 * (32 / LPH);
     if (n_tokens >= g_qk_token_threshold) {
         // enough tokens to fill the GPU with a warp each
-        launch_chained(qk_norm_rope_kv_token_kernel<T, LPH>, dim3((unsigned)((n_tokens + 3) / 4)), dim3(128), 0, stream,
+        launch_chained(qk_norm_rope_kv_token_kernel<T, LPH>, dim3((unsigned)n_tokens), dim3(128), 0, stream,
                        (const T*)qkv, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, max_pos, positions, slots, (T*)k_pool,
                        (T*)v_pool, n_tokens, nh, nkv, page_size, n_pages, swizzle, status);
         return;

@@ -30,8 +30,11 @@ class Engine:
     def __init__(self, model: str, dtype="bfloat16", block_size: int = 16, cache_mib: int = 3584,
                  blocks: Optional[int] = None, max_batch: int = 16, chunk: Optional[int] = 128,
                  prefix_cache: bool = True, device: str = "cuda:0", max_requests: Optional[int] = None,
-                 max_prefill_seqs: int = 1, lookahead: bool = True, runner=None):
-        """``runner``: something that steps like a ``ModelRunner`` (cache, spec, vocab_size,
+                 max_prefill_seqs: int = 1, lookahead: bool = True, reference_draw_order: bool = False, runner=None):
+        """``reference_draw_order``: temperature requests without top-k / top-p are drawn on the host
+        in the reference's order (falling probability) instead of on the device (token ids upward):
+        the same distribution, and for a given seed the reference's tokens.
+        ``runner``: something that steps like a ``ModelRunner`` (cache, spec, vocab_size,
         step_and_sample, prepack_decode, check_status), to drive the loop without a model."""
         if chunk is not None and chunk < 1:
             raise ConfigError("chunk 0 would carry nothing")
@@ -42,6 +45,7 @@ class Engine:
         self.runner.graph_step_tokens = chunk if (chunk is not None and chunk <= 8192) else None
         self.scheduler = Scheduler(self.runner.cache, max_batch=max_batch, chunk=chunk,
                                    max_positions=self.runner.spec.max_positions, max_prefill_seqs=max_prefill_seqs)
+        self.reference_draw_order = bool(reference_draw_order)
         self._next_id = 0
         self._seqs: Dict[int, Sequence] = {}
         # how the last FINISH_MEMORY requests ended (older ones are forgotten: an engine lives long)
@@ -60,7 +64,7 @@ class Engine:
                stop_tokens: Iterable[int] = ()) -> int:
         if temperature <= 0.0:
             top_k = top_p = None  # an explicit greedy request drops the nucleus settings (routes.rs:106-126)
-        params = SamplingParams(float(temperature), top_k, top_p)
+        params = SamplingParams(float(temperature), top_k, top_p, self.reference_draw_order)
         V = self.runner.vocab_size
         if any((not 0 <= int(t) < V) for t in prompt):
             raise ConfigError(f"a prompt token lies outside the vocabulary of {V}")

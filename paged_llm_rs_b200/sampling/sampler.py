@@ -46,6 +46,10 @@ class SamplingParams:
     temperature: float = 0.0
     top_k: Optional[int] = None
     top_p: Optional[float] = None
+    # True: a plain temperature request is drawn on the host too, in the reference's order (falling
+    # probability, sampler.rs:143-183), so that a seed gives the reference's tokens; the device walks
+    # token ids upward: the same distribution, another token for the same uniform number
+    reference_order: bool = False
 
     def __post_init__(self):
         t = self.temperature
@@ -68,7 +72,9 @@ class SamplingParams:
     @property
     def on_device(self) -> bool:
         """Greedy and plain temperature are drawn by the kernel."""
-        return self.is_greedy or (self.top_k is None and (self.top_p is None or self.top_p >= 1.0))
+        if self.is_greedy:
+            return True
+        return not self.reference_order and self.top_k is None and (self.top_p is None or self.top_p >= 1.0)
 
 
 def argmax_first(logits: np.ndarray) -> int:

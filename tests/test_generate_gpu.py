@@ -293,6 +293,25 @@ def test_top_k_top_p_follow_the_reference_order(tmp_path):
             assert tok == P.sample(logits, 0.9, 20, 0.9, rng), i
 
 
+def test_temperature_in_the_reference_order_when_asked(tmp_path):
+    # the device draws by walking token ids upward; with reference_draw_order the host draws by falling
+    # probability (crates/pagedllm/src/sampler.rs:143-183), which for a seed gives the reference's tokens
+    from paged_llm_rs_b200 import Engine
+    cfg, seed = CONFIGS["A"]
+    model = write_model(tmp_path, "A")
+    prompts = prompts_for(cfg["vocab_size"], [5, 9], 13)
+    outs = Engine(model, dtype="float32", blocks=32, reference_draw_order=True).generate(
+        prompts, max_tokens=10, temperature=0.9, seed=3)
+    c, w = P.load_model(model, torch.float64)
+    for p, o in zip(prompts, outs):
+        rng = P.PlainRng(3)
+        for i, tok in enumerate(o):
+            logits = P.forward(c, w, p + o[:i])[-1].float()
+            assert tok == P.sample(logits, 0.9, None, None, rng), i
+    other = Engine(model, dtype="float32", blocks=32).generate(prompts, max_tokens=10, temperature=0.9, seed=3)
+    assert other != outs         # (the device's order: other tokens for the same seed)
+
+
 def test_shared_prefix_gives_the_same_tokens(tmp_path):
     # crates/pagedllm/tests/prefix.rs:88-139: shared equals computed
     from paged_llm_rs_b200 import Engine

@@ -123,3 +123,13 @@ def test_sharded_checkpoint(tmp_path):
     os.remove(os.path.join(d, "model.safetensors"))
     sharded = load_weights(d, specs(TINY_A), torch.float32, "cpu")
     assert all(torch.equal(whole[k], sharded[k]) for k in whole)
+
+
+@pytest.mark.gpu
+def test_random_weights_do_not_depend_on_the_device_they_are_drawn_on(tmp_path):
+    # every value is a function of (seed, tensor name, index) computed in integers: a folder written on the
+    # GPU (the bench) holds the bytes of one written on the CPU (the tests)
+    a = write_random_model(str(tmp_path / "cpu"), TINY_B, 5, device="cpu")
+    b = write_random_model(str(tmp_path / "gpu"), TINY_B, 5, device="cuda")
+    with open(a + "/model.safetensors", "rb") as f, open(b + "/model.safetensors", "rb") as g:
+        assert f.read() == g.read()
