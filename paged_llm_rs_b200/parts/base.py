@@ -5,7 +5,8 @@ prefix of its tensors; it states the tensors it needs (``tensors()``), receives
 them (``bind``) and then runs (``forward``).  No part knows which model it is in.
 
   Norm               forward(x) and add_norm(residual, delta)
-  PositionEncoding   what a mixer needs to place tokens (rotary tables here)
+  PositionEncoding   what a mixer needs to place tokens (rotary tables here), and what it adds
+                     to the residual stream behind the embedding (nothing here)
   Mixer              forward(x, step, cache): mixes tokens of a request; says what
                      cache it needs (paged keys/values, or a slot of fixed-size state)
   FeedForward        forward(x, step): acts on each token alone
@@ -234,6 +235,12 @@ class PositionEncoding(Part):
         """(cos, sin, rotary_dim) with float32 tables [max_positions, rotary_dim/2],
         or None when this encoding does not rotate."""
         return None
+
+    def at_embedding(self, hidden: torch.Tensor, step: "StepState") -> torch.Tensor:
+        """What the encoding does to the residual stream right behind the embedding (learned
+        absolute positions add a row for ``step.positions`` here); the default leaves it as it is.
+        It runs inside a captured step, so it may launch kernels over the step's device tensors only."""
+        return hidden
 
 
 class Mixer(Part):

@@ -73,6 +73,8 @@ class DecoderModel:
         not ``graph_safe``; it runs fn() outside the capture, now and at every replay, and returns
         a tensor shaped like ``like`` that holds fn()'s result each time."""
         residual = self.embedding.forward(step.tokens)
+        for encoding in self.position_encodings.values():
+            residual = encoding.at_embedding(residual, step)
         delta = None
         for i, e in enumerate(self.schedule):
             own = e.reads_cache_of is None
