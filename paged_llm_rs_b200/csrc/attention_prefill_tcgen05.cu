@@ -13,11 +13,12 @@
 //   O += P V      tcgen05.mma with P as its tensor-memory operand and the value tile in shared
 //                 memory, 128 x head_dim; O stays in tensor memory for the whole item
 //
-// Twelve warps: 0-3 and 4-7 are two softmax groups that take the key tiles in turn (even tiles
+// Sixteen warps: 0-3 and 4-7 are two softmax groups that take the key tiles in turn (even tiles
 // the first, odd the second: a group's warp w owns rows 32 w .. 32 w + 31 like its twin in
-// the other group), 8 and 10 are the producers (TMA: queries and key tiles; value tiles), one lane
-// of warp 9 issues the tcgen05.mma of the scores, one of warp 11's those of the sums; warp 9 also
-// allocates the tensor memory.  (A third group is a build option: it measured slower, 387.8 against
+// the other group), 8 and 10 are the producers of the even tiles (TMA: queries and key tiles; value
+// tiles), 12 and 13 those of the odd tiles, one lane of warp 9 issues the tcgen05.mma of the scores, one
+// of warp 11's those of the sums; warp 9 also allocates the tensor memory.  The softmax warps take 192
+// registers a thread and leave the others 64 (setmaxnreg).  (A third group is a build option: it measured slower, 387.8 against
 // 357.8 us at 8192 tokens, within the 128 registers that sixteen warps leave each thread.)
 // S and P have two buffers each, one a group, so the tensor cores
 // form the next tiles' scores and sums while the groups work on theirs, and two warps share
@@ -27,13 +28,18 @@
 // memory, tile by tile, each keeping its own part of the row's sum.
 //
 // Shared-memory layouts.  A tile for the tensor cores has rows of 128 bytes (64 values) with
-// the 128-byte swizzle (tcgen05.cuh).  The cache stores a key's or value's row (head_dim
-// values) with its 16-byte chunk c at c ^ (offset in page & 7), which within each half of 64
-// values IS that swizzle; so a page's rows are fetched by TMA tile loads WITHOUT hardware
-// swizzle, one per half, and land as planes [64 keys][64 values] the tensor cores read
-// directly: K-major for Q K^T, MN-major (rows are the k of the product) for P V.  Q comes
-// from the step's plain [tokens, heads, head_dim] buffer through a three-dimensional map
-// with the hardware swizzle.
+// the 128-byte swizzle (tcgen05.cuh), in groups of 8 rows (1024 bytes).  The cache stores a key's
+// or value's row (head_dim values) with its 16-byte chunk c at c ^ (offset in page & 7), which
+// within each half of 64 values IS that swizzle.  A page's rows of one kv head are fetched by ONE
+// TMA tile load without hardware swizzle, through a four-dimensional view of the pool (64 values,
+// 8 rows, the halves of a row, groups of 8 rows): it lands as [group of 8 keys][half][8 rows][128
+// bytes], which the tensor cores read directly with a stride of NHALF * 1024 bytes from one group
+// of 8 rows to the next: K-major for Q K^T (the other half of the head 1024 bytes further), MN-major
+// (rows are the k of the product) for P V (the other 64 columns of the head 1024 bytes further).
+// A request to the copy engine costs the issuing warp some 110 clocks whatever it moves; one a page
+// instead of one a page and half brought the producers from 890 to half of that a tile of 64 keys,
+// below what the threads that issue the products need.  Q comes from the step's plain [tokens,
+// heads, head_dim] buffer through a three-dimensional map with the hardware swizzle.
 //
 // Every wait is bounded (status bit 128 when one ran out).
 #include "tcgen05.cuh"
@@ -63,9 +69,10 @@ namespace {
 #define PLLM_ATT_Q_TMEM 0
 #endif
 constexpr int P_G = PLLM_ATT_GROUPS;
-constexpr int P_ROWS = 128, P_BK = 64, P_STAGES = PLLM_ATT_STAGES, P_THREADS = (4 * P_G + 4) * 32;
-constexpr int W_KEYS = 4 * P_G, W_SCORES = 4 * P_G + 1, W_VALUES = 4 * P_G + 2, W_SUMS = 4 * P_G + 3;   // the other four warps   // P_STAGES: key tiles, and as many value tiles, in flight
-constexpr int P_PLANE = P_BK * 128;            // 64 keys x 128 bytes
+constexpr int P_ROWS = 128, P_BK = 64, P_STAGES = PLLM_ATT_STAGES, P_THREADS = (4 * P_G + 8) * 32;
+constexpr int W_KEYS = 4 * P_G, W_SCORES = 4 * P_G + 1, W_VALUES = 4 * P_G + 2, W_SUMS = 4 * P_G + 3;
+constexpr int W_KEYS2 = 4 * P_G + 4, W_VALUES2 = 4 * P_G + 5;    // the producers of the odd tiles (the last two warps have no work)
+static_assert(P_G == 2 && P_STAGES % 2 == 0, "the register split and the producers' turns are laid out for two groups and an even ring");   // the other four warps   // P_STAGES: key tiles, and as many value tiles, in flight
 constexpr float P_RESCALE = 8.0f;              // log2 units the running maximum may lag behind
 
 __device__ __forceinline__ float ex2(float x) {
@@ -76,6 +83,31 @@ __device__ __forceinline__ float ex2(float x) {
 
 }  // namespace
 
+// A build for finding who waits for whom (-DPLLM_ATT_CLOCKS=1): one thread of each role adds up the
+// clocks it spends in each of its waits and in its own work, and leaves the sums in a buffer that
+// pllm_attention_prefill_clocks_read copies out: [work item < 64][role][slot], for kv head 0.
+#ifdef PLLM_ATT_CLOCKS
+static __device__ long long g_att_clocks[64][8][8];
+static __device__ long long g_att_events[8][128][4];      // [role][tile][event] clock of work item 0, kv head 0
+#define EVT(role, tile, slot) { if (blockIdx.y == 0 && blockIdx.x == 0 && (tile) < 128) g_att_events[role][tile][slot] = clock64(); }
+PLLM_EXPORT int pllm_attention_prefill_events_read(long long* out) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(out, g_att_events, sizeof(g_att_events));
+}
+#define CLK_BEGIN long long clk_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long clk_t = clock64();
+#define CLK(slot) { const long long clk_n = clock64(); clk_acc[slot] += clk_n - clk_t; clk_t = clk_n; }
+#define CLK_END(role) if (blockIdx.y < 64 && blockIdx.x == 0) { for (int ci = 0; ci < 8; ci++) g_att_clocks[blockIdx.y][role][ci] = clk_acc[ci]; }
+PLLM_EXPORT int pllm_attention_prefill_clocks_read(long long* out) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(out, g_att_clocks, sizeof(g_att_clocks));
+}
+#else
+#define CLK_BEGIN
+#define CLK(slot)
+#define CLK_END(role)
+#define EVT(role, tile, slot) {}
+#endif
+
 template <int HD>
 __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -84,8 +116,9 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     int nh, int nkv, int page_size, int page_shift, int n_pages, int table_width, float scale_log2, int heads_per_cta,
     int tile_tokens, int take_single, int* status) {
     constexpr int NHALF = HD / 64;
-    constexpr int Q_BYTES = NHALF * P_ROWS * 128, STAGE = NHALF * P_PLANE, P_BYTES = P_ROWS * 128;   // STAGE: a key (or value) tile
-    constexpr uint32_t S_COL = 0, O_COL = P_G * P_BK, P_COL = O_COL + HD;     // P: 32 columns a group (64 keys, two to a column)
+    constexpr int GROUP = NHALF * 1024;            // 8 keys (or values): [half][8 rows][128 bytes]
+    constexpr int Q_BYTES = NHALF * P_ROWS * 128, STAGE = (P_BK / 8) * GROUP, P_BYTES = P_ROWS * 128;   // STAGE: a key (or value) tile
+    constexpr uint32_t S_COL = 0, O_COL = P_G * P_BK, P_COL = O_COL + P_G * HD;     // O: head_dim columns a group; P: 32 columns a group (64 keys, two to a column)
     constexpr uint32_t Q_COL = P_COL + (PLLM_ATT_P_TMEM ? P_G * 32 : 0);      // Q: head_dim / 2 columns
     constexpr uint32_t TMEM_USED = Q_COL + (PLLM_ATT_Q_TMEM ? HD / 2 : 0), TMEM_COLS = TMEM_USED <= 256 ? 256 : 512;
     static_assert(TMEM_USED <= 512, "tensor memory has 512 columns");
@@ -113,15 +146,15 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     const uint32_t k_ring = q_s + Q_BYTES, v_ring = k_ring + P_STAGES * STAGE;
     const uint32_t p_s = v_ring + P_STAGES * STAGE;            // a P buffer a group
     constexpr int RINGS = 2 * P_STAGES * STAGE;
-    float* mstate = reinterpret_cast<float*>(smem + Q_BYTES + RINGS + P_SMEM);          // [128] a row's maximum in use
-    float* lpart = mstate + P_ROWS;                                                                 // [groups][128] the groups' sums
-    unsigned char* ctl = smem + Q_BYTES + RINGS + P_SMEM + (1 + P_G) * P_ROWS * 4;
+    float* mstate = reinterpret_cast<float*>(smem + Q_BYTES + RINGS + P_SMEM);          // [groups][128] the groups' maxima at the end
+    float* lpart = mstate + P_G * P_ROWS;                                                           // [groups][128] the groups' sums
+    unsigned char* ctl = smem + Q_BYTES + RINGS + P_SMEM + 2 * P_G * P_ROWS * 4;
     const uint32_t bars = smem_u32(ctl);
     const uint32_t q_full = bars, k_full = bars + 8, k_empty = k_full + 8 * P_STAGES, v_full = k_empty + 8 * P_STAGES,
                    v_empty = v_full + 8 * P_STAGES, s_full = v_empty + 8 * P_STAGES,
-                   p_full = s_full + 8 * P_G, p_empty = p_full + 8 * P_G, o_full = p_empty + 8 * P_G, m_ready = o_full + 8,   // m_ready[groups][4]
-                   s_free = m_ready + 32 * P_G, q_tmem = s_free + 8 * P_G;
-    constexpr int N_BARS = 4 * P_STAGES + 1 + 3 * P_G + 1 + 4 * P_G + P_G + 1;
+                   p_full = s_full + 8 * P_G, p_empty = p_full + 8 * P_G, o_full = p_empty + 8 * P_G,
+                   s_free = o_full + 8, q_tmem = s_free + 8 * P_G;
+    constexpr int N_BARS = 4 * P_STAGES + 1 + 3 * P_G + 1 + P_G + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctl + 8 * N_BARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(ctl + 8 * N_BARS + 8);
 
@@ -136,7 +169,6 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             mbar_init(p_full + 8 * b, 4);        // one arrival from each warp of the group
             mbar_init(p_empty + 8 * b, 1);
             mbar_init(s_free + 8 * b, 4);        // the group has its scores in registers
-            for (int wq = 0; wq < 4; wq++) mbar_init(m_ready + 8 * (4 * b + wq), 1);
         }
         mbar_init(o_full, 1);
         mbar_init(q_tmem, 4);                    // the first group's warps have put their rows of Q into tensor memory
@@ -153,13 +185,21 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == W_KEYS || warp == W_VALUES) {
+    // Registers follow the work: the softmax threads hold a row of scores and weights each, the other
+    // eight warps a few addresses (512 threads start with 128 registers each).
+    // (The two halves of the CTA below each begin with their setmaxnreg: the compiler then knows the budget of
+    // the code behind it, and the four warps of a group execute one and the same instruction.)
+    if (warp >= 4 * P_G) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;\n" ::);
+    if (warp == W_KEYS || warp == W_VALUES || warp == W_KEYS2 || warp == W_VALUES2) {
         // ---- producers: warp 8 the queries and the key tiles, warp 10 the value tiles, each with a ring
         // of its own (a key tile's place comes free when its scores are formed, two tiles before its
         // values' does; with one ring for both the keys would be fetched only two tiles ahead) --------
-        const bool keys = warp == W_KEYS;
-        pdl_wait(KID_ATT_TC, keys && lane == 0);           // the queries and this step's cache rows come from the kernel before
-        if (keys && lane == 0) {
+        // (a request costs the issuing warp 135 clocks, 540 a tile of four pages: two warps a ring, taking the tiles in turn)
+        const bool keys = warp == W_KEYS || warp == W_KEYS2;
+        const int first = (warp == W_KEYS || warp == W_VALUES) ? 0 : 1;
+        pdl_wait(KID_ATT_TC, warp == W_KEYS && lane == 0);           // the queries and this step's cache rows come from the kernel before
+        if (warp == W_KEYS && lane == 0) {
             mbar_expect_tx(q_full, (uint32_t)(NHALF * 128 * heads_per_cta * tile_tokens));
             for (int h = 0; h < NHALF; h++) tma_load_3d(q_s + h * P_ROWS * 128, &map_q, h * 64, head0, w.q_token0, q_full);
         }
@@ -168,12 +208,13 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
         unsigned char* ring_ptr = smem + Q_BYTES + (keys ? 0 : P_STAGES * STAGE);
         const int slab_rows = page_size < P_BK ? page_size : P_BK;
         const int slabs = P_BK / slab_rows;                  // at most 8
-        const uint32_t slab_bytes = (uint32_t)slab_rows * 128;
+        const uint32_t slab_bytes = (uint32_t)(slab_rows / 8) * GROUP;   // a page's rows of this tile, both halves
         const int* table = block_tables + (size_t)w.seg * table_width;
         // the table entries of the key range, 32 at a time, one in each lane, fetched ahead
         int win0 = w.kv_begin >> page_shift;
         int tbl = (win0 + lane < table_width) ? table[win0 + lane] : -1;
-        for (int t = 0; t < n_tiles; t++) {
+        CLK_BEGIN
+        for (int t = first; t < n_tiles; t += 2) {
             const int s = t % P_STAGES;
             const int kv0 = w.kv_begin + t * P_BK;
             if (((kv0 + P_BK - 1) >> page_shift) >= win0 + 32) {
@@ -185,7 +226,10 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             int page = __shfl_sync(0xffffffffu, tbl, ((jl >> page_shift) - win0) & 31);
             if (lane >= slabs || jl >= w.kv_end) page = -1;
             if (page >= n_pages) { atomicOr(status, 8); page = -1; }
+            CLK(1)
             if (t >= P_STAGES && !mbar_wait(empty + 8 * s, ((t / P_STAGES) - 1) & 1, abort_flag)) break;
+            CLK(0)
+            if (lane == 0) EVT(keys ? 4 : 5, t, 0)
             const uint32_t have = __ballot_sync(0xffffffffu, page >= 0) & ((1u << slabs) - 1);
             const uint32_t st_base = ring + s * STAGE;
             unsigned char* st_ptr = ring_ptr + s * STAGE;
@@ -193,20 +237,24 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 // slabs with no page behind them are zeroed by hand: nothing stale is multiplied
                 for (int i = 0; i < slabs; i++) {
                     if (have & (1u << i)) continue;
-                    for (int pl = 0; pl < NHALF; pl++)
-                        for (int o = lane * 16; o < (int)slab_bytes; o += 32 * 16)
-                            *reinterpret_cast<uint4*>(st_ptr + pl * P_PLANE + i * slab_bytes + o) = make_uint4(0, 0, 0, 0);
+                    for (int o = lane * 16; o < (int)slab_bytes; o += 32 * 16)
+                        *reinterpret_cast<uint4*>(st_ptr + i * slab_bytes + o) = make_uint4(0, 0, 0, 0);
                 }
                 fence_async_smem();
                 __syncwarp();
             }
-            if (lane == 0) mbar_expect_tx(full + 8 * s, NHALF * slab_bytes * __popc(have));
+            if (lane == 0) mbar_expect_tx(full + 8 * s, slab_bytes * __popc(have));
             __syncwarp();
+            CLK(2)
+            // (One request a lane in one instruction: the same requests one after the other from an elected lane took
+            //  the warp 277 clocks each, against 135 this way.)
             if (lane < slabs && page >= 0) {
                 const int row = (page * nkv + kh) * page_size + (jl & (page_size - 1));
-                for (int h = 0; h < NHALF; h++) tma_load_2d(st_base + h * P_PLANE + lane * slab_bytes, map, h * 64, row, full + 8 * s);
+                tma_load_4d(st_base + lane * slab_bytes, map, 0, 0, 0, row >> 3, full + 8 * s);     // (a page starts on a multiple of 8 rows)
             }
+            if (lane == 0) EVT(keys ? 4 : 5, t, 1)
         }
+        if (lane == 0) { CLK(1) CLK_END((keys ? 4 : 5) + 2 * first) }
     } else if (warp == W_SCORES) {
         // ---- tensor-core issue, the scores: S[t % groups] = Q K_t^T.  (Two issuing threads, this one and
         // warp 11's for O += P V: each tile costs an issuing thread a handful of waits, instructions
@@ -215,63 +263,113 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             constexpr uint32_t idesc_qk = instr_desc(P_ROWS, P_BK);
             // descriptors differ only in their address field (bits 0-13, units of 16 bytes): the rest is
             // made once, and an address offset is one addition
-            const uint64_t q_desc = smem_desc(q_s), k_desc = smem_desc(k_ring);
+            const uint64_t q_desc = smem_desc(q_s), k_desc = smem_desc(k_ring, 16, GROUP);
             bool ok = mbar_wait(PLLM_ATT_Q_TMEM ? q_tmem : q_full, 0, abort_flag);
-            for (int t = 0; t < n_tiles && ok; t++) {
+            CLK_BEGIN
+            // With two groups and an even ring, key tiles t and t + 1 (t even) lie back to back in shared memory
+            // and their scores in neighbouring columns: ONE set of products 128 keys wide makes both (an
+            // instruction costs this thread some 85 clocks to issue, as much as the tensor cores need for
+            // three of the narrow ones).
+#ifndef PLLM_ATT_PAIRS
+#define PLLM_ATT_PAIRS 1
+#endif
+            constexpr bool PAIRS = PLLM_ATT_PAIRS && P_G == 2 && P_STAGES % 2 == 0;
+            constexpr uint32_t idesc_qk2 = instr_desc(P_ROWS, 2 * P_BK);
+            for (int t = 0; t < n_tiles && ok; t += PAIRS ? 2 : 1) {
                 const int s = t % P_STAGES;
-                // the group must have read its scores of the turn before out of this buffer
+                const bool two = PAIRS && t + 1 < n_tiles;
+                // the group(s) must have read their scores of the turn before out of the buffer(s)
                 const int g = t % P_G;
+#ifndef PLLM_ATT_LOADS_ONLY
                 if (t >= P_G && !mbar_wait(s_free + 8 * g, ((t - P_G) / P_G) & 1, abort_flag)) { ok = false; break; }
+                if (two && t >= P_G && !mbar_wait(s_free + 8 * (g + 1), ((t - P_G) / P_G) & 1, abort_flag)) { ok = false; break; }
+#endif
+                CLK(0)
+                EVT(0, t, 0)
                 if (!mbar_wait(k_full + 8 * s, (t / P_STAGES) & 1, abort_flag)) { ok = false; break; }
+                if (two && !mbar_wait(k_full + 8 * (s + 1), (t / P_STAGES) & 1, abort_flag)) { ok = false; break; }
+                CLK(1)
+                EVT(0, t, 1)
                 tc_fence_after();
+#ifdef PLLM_ATT_LOADS_ONLY
+                mbar_arrive(k_empty + 8 * s); if (two) mbar_arrive(k_empty + 8 * (s + 1)); CLK(2) (void)k_desc; (void)q_desc; (void)idesc_qk; (void)idesc_qk2;
+                continue;
+#endif
                 const uint64_t kd = k_desc + (uint64_t)((s * STAGE) >> 4);
                 const uint32_t d = tmem + S_COL + g * P_BK;
+                const uint32_t idesc = two ? idesc_qk2 : idesc_qk;
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {
 #if PLLM_ATT_Q_TMEM
-                    mma_ts(d, tmem + Q_COL + ks * 8, kd + (uint64_t)(((ks / 4) * P_PLANE + (ks % 4) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
+                    mma_ts(d, tmem + Q_COL + ks * 8, kd + (uint64_t)(((ks / 4) * 1024 + (ks % 4) * 32) >> 4), idesc, ks ? 1u : 0u);
 #else
                     mma_ss(d, q_desc + (uint64_t)(((ks / 4) * P_ROWS * 128 + (ks % 4) * 32) >> 4),
-                           kd + (uint64_t)(((ks / 4) * P_PLANE + (ks % 4) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
+                           kd + (uint64_t)(((ks / 4) * 1024 + (ks % 4) * 32) >> 4), idesc, ks ? 1u : 0u);
 #endif
                 }
                 (void)q_desc;
-                mma_commit(k_empty + 8 * s);         // the key tile's place is free once these have read it
+                mma_commit(k_empty + 8 * s);         // the key tiles' places are free once these have read them
+                if (two) mma_commit(k_empty + 8 * (s + 1));
                 mma_commit(s_full + 8 * g);
+                if (two) mma_commit(s_full + 8 * (g + 1));
+                CLK(2)
+                EVT(0, t, 2)
             }
+            CLK_END(0)
         }
     } else if (warp == W_SUMS) {
         // ---- tensor-core issue, the sums: O += P_t V_t --------------------------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc_pv = instr_desc(P_ROWS, HD, 1);
-            const uint64_t p_desc = smem_desc(p_s), v_desc = smem_desc(v_ring, P_PLANE);
+            const uint64_t p_desc = smem_desc(p_s), v_desc = smem_desc(v_ring, 1024, GROUP);
             bool ok = true;
+            CLK_BEGIN
             for (int t = 0; t < n_tiles && ok; t++) {
                 const int g = t % P_G;
+#ifndef PLLM_ATT_LOADS_ONLY
                 if (!mbar_wait(p_full + 8 * g, (t / P_G) & 1, abort_flag)) { ok = false; break; }
+#endif
+                CLK(0)
+                EVT(1, t, 0)
                 if (!mbar_wait(v_full + 8 * (t % P_STAGES), (t / P_STAGES) & 1, abort_flag)) { ok = false; break; }
+                CLK(1)
+                EVT(1, t, 1)
                 tc_fence_after();
+#ifdef PLLM_ATT_LOADS_ONLY
+                mbar_arrive(v_empty + 8 * (t % P_STAGES)); CLK(2) (void)v_desc; (void)p_desc; (void)idesc_pv;
+                continue;
+#endif
                 const uint64_t vd = v_desc + (uint64_t)(((t % P_STAGES) * STAGE) >> 4);
                 const uint64_t pd = p_desc + (uint64_t)((g * P_BYTES) >> 4);
 #pragma unroll
-                for (int ks = 0; ks < P_BK / 16; ks++) {   // 16 keys = 2048 bytes down the value planes
+                for (int ks = 0; ks < P_BK / 16; ks++) {   // 16 keys = two groups of 8 rows
 #if PLLM_ATT_P_TMEM
-                    mma_ts(tmem + O_COL, tmem + P_COL + g * 32 + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv,
-                           (t | ks) ? 1u : 0u);
+                    mma_ts(tmem + O_COL + g * HD, tmem + P_COL + g * 32 + ks * 8, vd + (uint64_t)((ks * 2 * GROUP) >> 4), idesc_pv,
+                           (t >= P_G || ks) ? 1u : 0u);
 #else
-                    mma_ss(tmem + O_COL, pd + (uint64_t)((ks * 32) >> 4), vd + (uint64_t)((ks * 2048) >> 4), idesc_pv,
-                           (t | ks) ? 1u : 0u);
+                    mma_ss(tmem + O_COL + g * HD, pd + (uint64_t)((ks * 32) >> 4), vd + (uint64_t)((ks * 2 * GROUP) >> 4), idesc_pv,
+                           (t >= P_G || ks) ? 1u : 0u);
 #endif
                 }
                 (void)pd;
                 mma_commit(v_empty + 8 * (t % P_STAGES));    // the values of this tile are read
                 mma_commit(p_empty + 8 * g);                 // and so is this group's P (and O holds the tile)
+                CLK(2)
+                EVT(1, t, 2)
             }
+            CLK_END(1)
+#ifndef PLLM_ATT_LOADS_ONLY
             if (ok) mma_commit(o_full);
+#endif
         }
+    }       // (the last two warps have no work)
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 192;\n" ::);
         // ---- softmax, one row a thread, the two groups taking the tiles in turn; then the epilogue ----
         pdl_launch_dependents();
+#ifdef PLLM_ATT_LOADS_ONLY
+        if (true) goto done;
+#endif
         const int grp = warp >> 2, wq = warp & 3;
         const int row = wq * 32 + lane;
         const int tq = row / heads_per_cta, hh = row % heads_per_cta;
@@ -306,10 +404,12 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             if (lane == 0) mbar_arrive(q_tmem);
         }
 #endif
-        const int grp_before = (grp + P_G - 1) % P_G;      // the group of the tile before this group's
+        CLK_BEGIN
         for (int t = grp; t < n_tiles; t += P_G) {
             const int kv0 = w.kv_begin + t * P_BK;
             if (!mbar_wait(s_full + 8 * grp, (t / P_G) & 1, abort_flag)) { ok = false; break; }
+            CLK(0)
+            if (wq == 0 && lane == 0) EVT(2 + grp, t, 0)
             tc_fence_after();
             uint32_t v0[32], v1[32];
             tmem_ld32(lane_base + S_COL + grp * P_BK, v0);
@@ -318,6 +418,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_free + 8 * grp);        // the buffer may take the scores of this group's next tile
+            CLK(1)
             // keys of this tile at or past vis are hidden from this row (only tiles on the diagonal have any)
             const int vis = hi - kv0;
             if (vis < P_BK) {
@@ -335,35 +436,31 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 for (int k = 0; k < 4; k++) m4[k] = fmaxf(m4[k], fmaxf(__uint_as_float(v0[i + k]), __uint_as_float(v1[i + k])));
             }
             const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scale_log2;   // the scale is positive
-            // the maximum in use after the tile before this one, which the other group decided
-            float m_prev = -CUDART_INF_F;
-            if (t > 0) {
-                if (!mbar_wait(m_ready + 8 * (4 * grp_before + wq), ((t - 1) / P_G) & 1, abort_flag)) { ok = false; break; }
-                m_prev = mstate[row];
-            }
-            // it moves only when it grew by more than 2^8 (or is not set yet)
+            // the maximum this group has in use; it moves only when it grew by more than 2^8 (or is not set yet)
+            const float m_prev = m_ref;
+            CLK(2)
             const bool grow = mx > m_prev + P_RESCALE || (m_prev == -CUDART_INF_F && mx > -CUDART_INF_F);
             const float m_used = grow ? mx : m_prev;
-            mstate[row] = m_used;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(m_ready + 8 * (4 * grp + wq));      // the other group may go on with its tile
-            if (t > 0 && __any_sync(0xffffffffu, grow)) {
-                // O is rescaled once the tile before this one is in it (this tile's is not issued before
-                // this group says so, nor the next one's before this tile's)
-                if (!mbar_wait(p_empty + 8 * grp_before, ((t - 1) / P_G) & 1, abort_flag)) { ok = false; break; }
+            CLK(3)
+            if (wq == 0 && lane == 0) EVT(2 + grp, t, 1)
+            if (t >= P_G && __any_sync(0xffffffffu, grow)) {
+                // this group's O is rescaled once its tile before this one is in it (this tile's is not issued
+                // before the group has stored its weights)
+                if (!mbar_wait(p_empty + 8 * grp, ((t - P_G) / P_G) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const float alpha = (grow && m_prev > -CUDART_INF_F) ? ex2(m_prev - m_used) : (grow ? 0.f : 1.f);
 #pragma unroll
                 for (int c = 0; c < HD / 32; c++) {
                     uint32_t o[32];
-                    tmem_ld32(lane_base + O_COL + c * 32, o);
+                    tmem_ld32(lane_base + O_COL + grp * HD + c * 32, o);
                     tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_st32(lane_base + O_COL + c * 32, o);
+                    tmem_st32(lane_base + O_COL + grp * HD + c * 32, o);
                 }
                 tmem_wait_st();
             }
+            CLK(4)
             // this group's sum so far, brought to the maximum now in use
             if (m_ref != m_used) {
                 l_run = m_ref > -CUDART_INF_F ? l_run * ex2(m_ref - m_used) : 0.f;
@@ -383,8 +480,11 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 s4[i & 3] += p0 + p1;
             }
             l_run += (s4[0] + s4[1]) + (s4[2] + s4[3]);
+            CLK(5)
+            if (wq == 0 && lane == 0) EVT(2 + grp, t, 2)
             // this group's P of its tile before must be read out of shared memory before it is overwritten
             if (t >= P_G && !mbar_wait(p_empty + 8 * grp, ((t - P_G) / P_G) & 1, abort_flag)) { ok = false; break; }
+            CLK(6)
 #if PLLM_ATT_P_TMEM
             // the row's 64 weights, two to a column, into this thread's lane of the group's P columns
             tmem_st32(lane_base + P_COL + grp * 32, pw);
@@ -400,16 +500,26 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full + 8 * grp);
+            CLK(7)
+            if (wq == 0 && lane == 0) EVT(2 + grp, t, 3)
         }
-        // ---- the groups' sums meet; each group stores half of the columns -------------------------------
+        if (wq == 0 && lane == 0) { CLK_END(2 + grp) }
+        // ---- the groups meet: each has a maximum, a sum and an O of its own (the even tiles', the odd tiles'),
+        // brought to the larger maximum here; each group stores half of the columns ------------------------
         if (!ok || *abort_flag) *abort_flag = 1;
+        mstate[grp * P_ROWS + row] = m_ref;
+        lpart[grp * P_ROWS + row] = l_run;
         asm volatile("bar.sync 1, %0;\n" ::"n"(P_G * 128) : "memory");          // (the softmax warps; the others are elsewhere)
-        const float m_fin = mstate[row];                           // after the last tile (every row has one)
-        lpart[grp * P_ROWS + row] = (m_ref > -CUDART_INF_F && m_fin > -CUDART_INF_F) ? l_run * ex2(m_ref - m_fin) : 0.f;
-        asm volatile("bar.sync 1, %0;\n" ::"n"(P_G * 128) : "memory");
-        float l_tot = lpart[row];
+        float m_fin = mstate[row];
 #pragma unroll
-        for (int g = 1; g < P_G; g++) l_tot += lpart[g * P_ROWS + row];
+        for (int g = 1; g < P_G; g++) m_fin = fmaxf(m_fin, mstate[g * P_ROWS + row]);
+        float share[P_G], l_tot = 0.f;        // 2^(a group's maximum - the row's): 0 for a group that saw no key of this row
+#pragma unroll
+        for (int g = 0; g < P_G; g++) {
+            const float mg = mstate[g * P_ROWS + row], lg = lpart[g * P_ROWS + row];
+            share[g] = (g < n_tiles && mg > -CUDART_INF_F && lg > 0.f) ? ex2(mg - m_fin) : 0.f;
+            l_tot += share[g] > 0.f ? lg * share[g] : 0.f;
+        }
         if (!*abort_flag && mbar_wait(o_full, 0, abort_flag)) {
             tc_fence_after();
             const float inv = l_tot > 0.f ? 1.0f / l_tot : 0.f;
@@ -418,6 +528,18 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 uint32_t o[32];
                 tmem_ld32(lane_base + O_COL + c * 32, o);
                 tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; i++) o[i] = __float_as_uint(share[0] > 0.f ? __uint_as_float(o[i]) * share[0] : 0.f);
+#pragma unroll
+                for (int g = 1; g < P_G; g++) {
+                    if (g >= n_tiles) continue;          // (a group without a tile never wrote its O)
+                    uint32_t og[32];
+                    tmem_ld32(lane_base + O_COL + g * HD + c * 32, og);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        if (share[g] > 0.f) o[i] = __float_as_uint(__uint_as_float(o[i]) + __uint_as_float(og[i]) * share[g]);
+                }
                 if (!live) continue;
                 const int head = head0 + hh;
                 if (w.part_slot < 0) {
@@ -446,6 +568,9 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
         }
     }
     // ---- everyone meets; the allocating warp gives the tensor memory back ---------------------------
+#ifdef PLLM_ATT_LOADS_ONLY
+done:
+#endif
     tc_fence_before();
     __syncthreads();
     if (warp == W_SCORES) {
@@ -485,15 +610,21 @@ static int launch_prefill(const void* q, const void* k_pool, const void* v_pool,
         const long long dq[3] = {HD, nh, n_tokens}, sq[2] = {2LL * HD, 2LL * HD * nh};
         const int bq[3] = {64, heads_per_cta, tile_tokens};
         if (tensor_map(q, 3, dq, sq, bq, true, &map_q) != 0) return PLLM_ERR_SIZE;
-        const long long dp[2] = {HD, (long long)n_pages * nkv * page_size}, sp[1] = {2LL * HD};
-        const int bp[2] = {64, slab_rows};
-        if (tensor_map(k_pool, 2, dp, sp, bp, false, &map_k) != 0) return PLLM_ERR_SIZE;
-        if (tensor_map(v_pool, 2, dp, sp, bp, false, &map_v) != 0) return PLLM_ERR_SIZE;
+        // the pool as (64 values, 8 rows, the halves of a row, groups of 8 rows): a box lands as [group][half][8 rows][128 bytes]
+        const long long dp[4] = {64, 8, HD / 64, (long long)n_pages * nkv * page_size / 8}, sp[3] = {2LL * HD, 128, 16LL * HD};
+        const int bp[4] = {64, 8, HD / 64, slab_rows / 8};
+#ifdef PLLM_ATT_PROBE_SWIZZLE
+        if (tensor_map(k_pool, 4, dp, sp, bp, true, &map_k) != 0) return PLLM_ERR_SIZE;
+        if (tensor_map(v_pool, 4, dp, sp, bp, true, &map_v) != 0) return PLLM_ERR_SIZE;
+#else
+        if (tensor_map(k_pool, 4, dp, sp, bp, false, &map_k) != 0) return PLLM_ERR_SIZE;
+        if (tensor_map(v_pool, 4, dp, sp, bp, false, &map_v) != 0) return PLLM_ERR_SIZE;
+#endif
     }
     constexpr int NHALF = HD / 64;
-    const size_t smem = (size_t)NHALF * P_ROWS * 128 + (size_t)P_STAGES * 2 * NHALF * P_PLANE +
+    const size_t smem = (size_t)NHALF * P_ROWS * 128 + (size_t)P_STAGES * 2 * NHALF * P_BK * 128 +
                         (PLLM_ATT_P_TMEM ? 0 : P_G * P_ROWS * 128) +
-                        (1 + P_G) * P_ROWS * 4 + 8 * (4 * P_STAGES + 3 + 8 * P_G) + 16 + 1024;
+                        2 * P_G * P_ROWS * 4 + 8 * (4 * P_STAGES + 3 + 4 * P_G) + 16 + 1024;
     cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_chained(attention_prefill_tcgen05_kernel<HD>, dim3(nkv * gparts, max_work), dim3(P_THREADS), smem, stream, map_q,
                    map_k, map_v, block_tables, (const AttnWork*)work, n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv,

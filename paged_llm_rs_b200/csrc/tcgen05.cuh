@@ -44,7 +44,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Waits until the barrier's phase `parity` is over; gives up after a bounded number of polls
-// or when another thread has given up.  Returns false then.
+// or when another thread has given up.  Returns false then.  (Polling with test_wait, which never
+// suspends the thread, measured no faster in the tcgen05 attention.)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     for (int spin = 0; spin < SPIN_LIMIT; spin++) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -60,9 +61,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16),
 // stored with the 128-byte swizzle in groups of 8 rows (1024 bytes): start address, leading
 // byte offset 1 (unused with a swizzle), stride byte offset 1024, version 1, layout 2.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t leading_bytes = 16) {
+// (stride_bytes: from one group of 8 rows to the next, 1024 when the groups lie back to back)
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t leading_bytes = 16, uint32_t stride_bytes = 1024) {
     return (uint64_t)((addr >> 4) & 0x3fff) | ((uint64_t)((leading_bytes >> 4) & 0x3fff) << 16) |
-           ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+           ((uint64_t)((stride_bytes >> 4) & 0x3fff) << 32) | (1ull << 46) | (2ull << 61);
 }
 // Instruction descriptor: float accumulator, bfloat16 A and B, both K-major, M x N.
 __host__ __device__ constexpr uint32_t instr_desc(int m, int n, int b_mn_major = 0) {
@@ -107,6 +109,10 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, int w, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&r)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
                  "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -123,22 +129,25 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 // ---- host: tensor maps (bfloat16), kept by what they describe -----------------------------------
 
 struct MapKey {
-    const void* ptr; int rank; long long dims[3]; long long strides[2]; int box[3]; int swizzle;
+    const void* ptr; int rank; long long dims[4]; long long strides[3]; int box[4]; int swizzle;
     bool operator<(const MapKey& o) const {
-        return std::tie(ptr, rank, dims[0], dims[1], dims[2], strides[0], strides[1], box[0], box[1], box[2], swizzle) <
-               std::tie(o.ptr, o.rank, o.dims[0], o.dims[1], o.dims[2], o.strides[0], o.strides[1], o.box[0], o.box[1], o.box[2], o.swizzle);
+        return std::tie(ptr, rank, dims[0], dims[1], dims[2], dims[3], strides[0], strides[1], strides[2], box[0], box[1], box[2], box[3], swizzle) <
+               std::tie(o.ptr, o.rank, o.dims[0], o.dims[1], o.dims[2], o.dims[3], o.strides[0], o.strides[1], o.strides[2], o.box[0], o.box[1],
+                        o.box[2], o.box[3], o.swizzle);
     }
 };
 
-// dims: elements, innermost first; strides: bytes of dims 1.. ; box: elements.  swizzle128: the
+// dims: elements, innermost first (rank 2 to 4); strides: bytes of dims 1.. ; box: elements.  swizzle128: the
 // hardware stores the box with the 128-byte swizzle (the box's innermost extent is then 64 elements).
 inline int tensor_map(const void* ptr, int rank, const long long* dims, const long long* strides, const int* box,
                       bool swizzle128, CUtensorMap* out) {
     static std::map<MapKey, CUtensorMap> maps;
     static std::mutex lock;
     std::lock_guard<std::mutex> hold(lock);
-    MapKey key{ptr, rank, {dims[0], dims[1], rank > 2 ? dims[2] : 1}, {strides[0], rank > 2 ? strides[1] : 0},
-               {box[0], box[1], rank > 2 ? box[2] : 1}, swizzle128 ? 1 : 0};
+    if (rank < 2 || rank > 4) return -1;
+    MapKey key{ptr, rank, {1, 1, 1, 1}, {0, 0, 0}, {1, 1, 1, 1}, swizzle128 ? 1 : 0};
+    for (int i = 0; i < rank; i++) { key.dims[i] = dims[i]; key.box[i] = box[i]; }
+    for (int i = 0; i + 1 < rank; i++) key.strides[i] = strides[i];
     auto it = maps.find(key);
     if (it != maps.end()) { *out = it->second; return 0; }
     // the driver's encoder is looked up at run time: the library then loads on a machine without a
@@ -154,10 +163,10 @@ inline int tensor_map(const void* ptr, int rank, const long long* dims, const lo
             return -1;
         encode = (EncodeFn)fn;
     }
-    cuuint64_t d[3] = {(cuuint64_t)dims[0], (cuuint64_t)dims[1], (cuuint64_t)(rank > 2 ? dims[2] : 1)};
-    cuuint64_t st[2] = {(cuuint64_t)strides[0], (cuuint64_t)(rank > 2 ? strides[1] : 0)};
-    cuuint32_t b[3] = {(cuuint32_t)box[0], (cuuint32_t)box[1], (cuuint32_t)(rank > 2 ? box[2] : 1)};
-    cuuint32_t e[3] = {1, 1, 1};
+    cuuint64_t d[4], st[3];
+    cuuint32_t b[4], e[4] = {1, 1, 1, 1};
+    for (int i = 0; i < 4; i++) { d[i] = (cuuint64_t)key.dims[i]; b[i] = (cuuint32_t)key.box[i]; }
+    for (int i = 0; i < 3; i++) st[i] = (cuuint64_t)key.strides[i];
     const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(ptr), d, st, b, e,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

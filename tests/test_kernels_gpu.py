@@ -45,11 +45,13 @@ def test_embed(dtype, hidden, vocab):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("width,eps", [(96, 1e-5), (1000, 1e-6), (4096, 1e-6), (50, 1e-3)])
-def test_rmsnorm_plain_fused_and_gathered(dtype, width, eps):
+@pytest.mark.parametrize("n", [19, 1100])     # few rows: a CTA a row; many: teams of one to eight warps a row
+@pytest.mark.parametrize("width,eps", [(96, 1e-5), (1000, 1e-6), (1024, 1e-6), (2056, 1e-5), (4096, 1e-6), (5120, 1e-6),
+                                       (9000, 1e-6), (50, 1e-3)])
+def test_rmsnorm_plain_fused_and_gathered(dtype, n, width, eps):
     g = torch.Generator(device=DEV).manual_seed(1)
-    x = (torch.randn(19, width, device=DEV, generator=g) * 3).to(dtype)
-    d = torch.randn(19, width, device=DEV, generator=g).to(dtype)
+    x = (torch.randn(n, width, device=DEV, generator=g) * 3).to(dtype)
+    d = torch.randn(n, width, device=DEV, generator=g).to(dtype)
     gain = 1 + 0.1 * torch.randn(width, device=DEV, generator=g)
 
     def ref(v):
@@ -66,12 +68,12 @@ def test_rmsnorm_plain_fused_and_gathered(dtype, width, eps):
     assert torch.equal(res, summed)
     torch.testing.assert_close(out.float(), ref(summed), **tol(dtype))
     # gathered rows with a pending add, nothing stored
-    rows = torch.tensor([18, 0, 7], dtype=torch.int32, device=DEV)
+    rows = torch.randperm(n, device=DEV, generator=g)[:max(3, n // 2)].to(torch.int32)
     res2 = x.clone()
-    out3 = torch.empty(3, width, device=DEV, dtype=dtype)
-    ops.rmsnorm(res2, gain, eps, out3, delta=d, rows=rows)
-    assert torch.equal(res2, x)
-    torch.testing.assert_close(out3.float(), ref(summed[rows.long()]), **tol(dtype))
+    out3 = torch.full((rows.numel() + 1, width), 7.0, device=DEV, dtype=dtype)
+    ops.rmsnorm(res2, gain, eps, out3[:-1], delta=d, rows=rows)
+    assert torch.equal(res2, x) and (out3[-1] == 7).all()
+    torch.testing.assert_close(out3[:-1].float(), ref(summed[rows.long()]), **tol(dtype))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
