@@ -6,26 +6,41 @@
 // tokens (kernels/attention_plan.py).  A CTA takes one item and one kv head: up to 128 rows
 // = query tokens x the heads of the group, and walks the item's keys 64 at a time:
 //
-//   S = Q K^T     tcgen05.mma, 128 x 64, Q and the key tile in shared memory, S in tensor memory
+//   S = Q K^T     tcgen05.mma, 128 x 64 (x 128 for two tiles at once), Q and the key tile in shared memory, S in tensor memory
 //   P = softmax   four warps, ONE ROW A THREAD (a thread's lane of tensor memory is its row, so
 //                 the row's maximum and sum need no shuffles): tcgen05.ld, scale, mask, exp2,
 //                 P rounded to bfloat16 back into tensor memory (tcgen05.st, two weights a column)
 //   O += P V      tcgen05.mma with P as its tensor-memory operand and the value tile in shared
-//                 memory, 128 x head_dim; O stays in tensor memory for the whole item
+//                 memory, 128 x head_dim; a group's O stays in tensor memory for the whole item
 //
 // Sixteen warps: 0-3 and 4-7 are two softmax groups that take the key tiles in turn (even tiles
-// the first, odd the second: a group's warp w owns rows 32 w .. 32 w + 31 like its twin in
-// the other group), 8 and 10 are the producers of the even tiles (TMA: queries and key tiles; value
-// tiles), 12 and 13 those of the odd tiles, one lane of warp 9 issues the tcgen05.mma of the scores, one
-// of warp 11's those of the sums; warp 9 also allocates the tensor memory.  The softmax warps take 192
-// registers a thread and leave the others 64 (setmaxnreg).  (A third group is a build option: it measured slower, 387.8 against
-// 357.8 us at 8192 tokens, within the 128 registers that sixteen warps leave each thread.)
-// S and P have two buffers each, one a group, so the tensor cores
-// form the next tiles' scores and sums while the groups work on theirs, and two warps share
-// each scheduler (the exponentials of one hide the waits of the other).  A row's running
-// maximum is only moved when it grew by more than 2^8 (then O is rescaled in tensor memory),
-// which is exact after the final division; the groups hand it to one another through shared
-// memory, tile by tile, each keeping its own part of the row's sum.
+// the first, odd the second: a group's warp w owns rows 32 w .. 32 w + 31), 8 and 10 are the producers
+// of the even tiles (TMA: queries and key tiles; value tiles), 12 and 13 those of the odd tiles, one
+// lane of warp 9 issues the tcgen05.mma of the scores, one of warp 11's those of the sums; warp 9 also
+// allocates the tensor memory; warps 14 and 15 have no work.  The softmax warps take 192 registers a
+// thread and leave the others 64 (setmaxnreg).
+// Each group has a maximum, a sum and an O of its own for its half of the tiles (like two splits of the
+// key range): nothing passes between the groups tile by tile, and they meet once, in the epilogue.  A
+// row's running maximum is only moved when it grew by more than 2^8 (then the group's O is rescaled in
+// tensor memory), which is exact after the final division.  S and P have a buffer a group; the scores of
+// tiles t and t + 1 (t even) are formed by ONE set of products 128 keys wide, since the two tiles lie
+// back to back in the ring and their scores in neighbouring columns.
+//
+// What was measured on the way (2048 tokens, 16 heads over 8 kv heads of 128; one CTA's clocks a tile of
+// 64 keys; -DPLLM_ATT_CLOCKS=1 builds the counters).  A request to the copy engine costs the issuing warp
+// 110-160 clocks whatever it moves, and 277 when one lane issues them one after the other: so a page is one
+// request, the lanes of a warp issue a tile's pages in one instruction, and two warps share a ring (the
+// loads alone then take 430 clocks a tile, 780 with one warp a ring).  A tcgen05.mma or a commit costs its
+// lone thread some 85 clocks and a wait on a barrier that is long over 100-200 beside eight busy warps, so
+// the scores of two tiles are one set of instructions and a thread waits first for what is surely there.
+// With everything a tile takes 1250 clocks: a group's turn (600 of them exponentials, two warps to a
+// scheduler) and the round trip from the groups to the issuing thread and back bound it about equally.
+// 8192 tokens: 328 -> 293 us (940 TFLOP/s); 2048 tokens: 29.6 -> 28.8 us with the reduction's launch.
+// Tried and no faster: three groups; rings of 2 or 3 tiles; steps of 128 keys in one group; Q in tensor
+// memory; polling with test_wait; two buffers of scores with P written over the scores it came from (the
+// next scores then wait for the P V before last: the same loop, longer); two buffers of scores AND of
+// weights with one O and the pair's maximum exchanged between twin warps (the groups' turn then bounds it
+// alone, at 2700 clocks a pair).
 //
 // Shared-memory layouts.  A tile for the tensor cores has rows of 128 bytes (64 values) with
 // the 128-byte swizzle (tcgen05.cuh), in groups of 8 rows (1024 bytes).  The cache stores a key's
@@ -36,10 +51,8 @@
 // bytes], which the tensor cores read directly with a stride of NHALF * 1024 bytes from one group
 // of 8 rows to the next: K-major for Q K^T (the other half of the head 1024 bytes further), MN-major
 // (rows are the k of the product) for P V (the other 64 columns of the head 1024 bytes further).
-// A request to the copy engine costs the issuing warp some 110 clocks whatever it moves; one a page
-// instead of one a page and half brought the producers from 890 to half of that a tile of 64 keys,
-// below what the threads that issue the products need.  Q comes from the step's plain [tokens,
-// heads, head_dim] buffer through a three-dimensional map with the hardware swizzle.
+// Q comes from the step's plain [tokens, heads, head_dim] buffer through a three-dimensional map with
+// the hardware swizzle.
 //
 // Every wait is bounded (status bit 128 when one ran out).
 #include "tcgen05.cuh"
@@ -50,15 +63,12 @@ struct AttnWork { int seg, q_token0, q_count, q_pos0, kv_begin, kv_end, part_slo
 
 namespace {
 
-// Key tiles (and as many value tiles) in flight.  The kernel's time does not follow it (8192 tokens: 360.8,
-// 358.0, 357.8 us with 2, 3, 4): the loads are not what bounds it.
+// Key tiles (and as many value tiles) in flight: an even number, two tiles are used at a time.
 #ifndef PLLM_ATT_STAGES
 #define PLLM_ATT_STAGES 4
 #endif
-// Softmax groups (2 or 3) that take the key tiles in turn: four warps each, beside the four warps of producers and issuers.
-#ifndef PLLM_ATT_GROUPS
+// Softmax groups that take the key tiles in turn: four warps each.
 #define PLLM_ATT_GROUPS 2
-#endif
 // P handed to the tensor cores in tensor memory (1) or in shared memory (0)
 #ifndef PLLM_ATT_P_TMEM
 #define PLLM_ATT_P_TMEM 1
@@ -270,31 +280,24 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             // and their scores in neighbouring columns: ONE set of products 128 keys wide makes both (an
             // instruction costs this thread some 85 clocks to issue, as much as the tensor cores need for
             // three of the narrow ones).
-#ifndef PLLM_ATT_PAIRS
-#define PLLM_ATT_PAIRS 1
-#endif
-            constexpr bool PAIRS = PLLM_ATT_PAIRS && P_G == 2 && P_STAGES % 2 == 0;
+            constexpr bool PAIRS = P_G == 2 && P_STAGES % 2 == 0;
             constexpr uint32_t idesc_qk2 = instr_desc(P_ROWS, 2 * P_BK);
             for (int t = 0; t < n_tiles && ok; t += PAIRS ? 2 : 1) {
                 const int s = t % P_STAGES;
                 const bool two = PAIRS && t + 1 < n_tiles;
                 // the group(s) must have read their scores of the turn before out of the buffer(s)
                 const int g = t % P_G;
-#ifndef PLLM_ATT_LOADS_ONLY
-                if (t >= P_G && !mbar_wait(s_free + 8 * g, ((t - P_G) / P_G) & 1, abort_flag)) { ok = false; break; }
-                if (two && t >= P_G && !mbar_wait(s_free + 8 * (g + 1), ((t - P_G) / P_G) & 1, abort_flag)) { ok = false; break; }
-#endif
-                CLK(0)
-                EVT(0, t, 0)
+                // (the key tiles first: they are there long before the groups have read the last scores, and a
+                // wait on a barrier that is over still costs this thread a hundred clocks or two)
                 if (!mbar_wait(k_full + 8 * s, (t / P_STAGES) & 1, abort_flag)) { ok = false; break; }
                 if (two && !mbar_wait(k_full + 8 * (s + 1), (t / P_STAGES) & 1, abort_flag)) { ok = false; break; }
                 CLK(1)
                 EVT(0, t, 1)
+                if (t >= P_G && !mbar_wait(s_free + 8 * g, ((t - P_G) / P_G) & 1, abort_flag)) { ok = false; break; }
+                if (two && t >= P_G && !mbar_wait(s_free + 8 * (g + 1), ((t - P_G) / P_G) & 1, abort_flag)) { ok = false; break; }
+                CLK(0)
+                EVT(0, t, 0)
                 tc_fence_after();
-#ifdef PLLM_ATT_LOADS_ONLY
-                mbar_arrive(k_empty + 8 * s); if (two) mbar_arrive(k_empty + 8 * (s + 1)); CLK(2) (void)k_desc; (void)q_desc; (void)idesc_qk; (void)idesc_qk2;
-                continue;
-#endif
                 const uint64_t kd = k_desc + (uint64_t)((s * STAGE) >> 4);
                 const uint32_t d = tmem + S_COL + g * P_BK;
                 const uint32_t idesc = two ? idesc_qk2 : idesc_qk;
@@ -326,19 +329,13 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             CLK_BEGIN
             for (int t = 0; t < n_tiles && ok; t++) {
                 const int g = t % P_G;
-#ifndef PLLM_ATT_LOADS_ONLY
-                if (!mbar_wait(p_full + 8 * g, (t / P_G) & 1, abort_flag)) { ok = false; break; }
-#endif
-                CLK(0)
-                EVT(1, t, 0)
-                if (!mbar_wait(v_full + 8 * (t % P_STAGES), (t / P_STAGES) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(v_full + 8 * (t % P_STAGES), (t / P_STAGES) & 1, abort_flag)) { ok = false; break; }      // (the values first, likewise)
                 CLK(1)
                 EVT(1, t, 1)
+                if (!mbar_wait(p_full + 8 * g, (t / P_G) & 1, abort_flag)) { ok = false; break; }
+                CLK(0)
+                EVT(1, t, 0)
                 tc_fence_after();
-#ifdef PLLM_ATT_LOADS_ONLY
-                mbar_arrive(v_empty + 8 * (t % P_STAGES)); CLK(2) (void)v_desc; (void)p_desc; (void)idesc_pv;
-                continue;
-#endif
                 const uint64_t vd = v_desc + (uint64_t)(((t % P_STAGES) * STAGE) >> 4);
                 const uint64_t pd = p_desc + (uint64_t)((g * P_BYTES) >> 4);
 #pragma unroll
@@ -358,18 +355,13 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 EVT(1, t, 2)
             }
             CLK_END(1)
-#ifndef PLLM_ATT_LOADS_ONLY
             if (ok) mma_commit(o_full);
-#endif
         }
     }       // (the last two warps have no work)
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 192;\n" ::);
         // ---- softmax, one row a thread, the two groups taking the tiles in turn; then the epilogue ----
         pdl_launch_dependents();
-#ifdef PLLM_ATT_LOADS_ONLY
-        if (true) goto done;
-#endif
         const int grp = warp >> 2, wq = warp & 3;
         const int row = wq * 32 + lane;
         const int tq = row / heads_per_cta, hh = row % heads_per_cta;
@@ -568,9 +560,6 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
         }
     }
     // ---- everyone meets; the allocating warp gives the tensor memory back ---------------------------
-#ifdef PLLM_ATT_LOADS_ONLY
-done:
-#endif
     tc_fence_before();
     __syncthreads();
     if (warp == W_SCORES) {
@@ -613,13 +602,8 @@ static int launch_prefill(const void* q, const void* k_pool, const void* v_pool,
         // the pool as (64 values, 8 rows, the halves of a row, groups of 8 rows): a box lands as [group][half][8 rows][128 bytes]
         const long long dp[4] = {64, 8, HD / 64, (long long)n_pages * nkv * page_size / 8}, sp[3] = {2LL * HD, 128, 16LL * HD};
         const int bp[4] = {64, 8, HD / 64, slab_rows / 8};
-#ifdef PLLM_ATT_PROBE_SWIZZLE
-        if (tensor_map(k_pool, 4, dp, sp, bp, true, &map_k) != 0) return PLLM_ERR_SIZE;
-        if (tensor_map(v_pool, 4, dp, sp, bp, true, &map_v) != 0) return PLLM_ERR_SIZE;
-#else
         if (tensor_map(k_pool, 4, dp, sp, bp, false, &map_k) != 0) return PLLM_ERR_SIZE;
         if (tensor_map(v_pool, 4, dp, sp, bp, false, &map_v) != 0) return PLLM_ERR_SIZE;
-#endif
     }
     constexpr int NHALF = HD / 64;
     const size_t smem = (size_t)NHALF * P_ROWS * 128 + (size_t)P_STAGES * 2 * NHALF * P_BK * 128 +
