@@ -183,12 +183,22 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kv_token_kernel(
     if (cos_t) {
         int pos = positions[t];
         if (pos < 0 || pos >= max_pos) { if (lane == 0) atomicOr(status, 4); pos = 0; }
+        // (N values = 16 or 32 bytes from a multiple of N: vector loads)
         const size_t o = (size_t)pos * (HD / 2) + (upper ? c - LPH / 2 : c) * N;
 #pragma unroll
-        for (int k = 0; k < N; k++) { cs[k] = cos_t[o + k]; sn[k] = upper ? sin_t[o + k] : -sin_t[o + k]; }
+        for (int k = 0; k < N; k += 4) {
+            const float4 a = *reinterpret_cast<const float4*>(cos_t + o + k), b = *reinterpret_cast<const float4*>(sin_t + o + k);
+            cs[k] = a.x; cs[k + 1] = a.y; cs[k + 2] = a.z; cs[k + 3] = a.w;
+            sn[k] = upper ? b.x : -b.x; sn[k + 1] = upper ? b.y : -b.y; sn[k + 2] = upper ? b.z : -b.z; sn[k + 3] = upper ? b.w : -b.w;
+        }
     }
 #pragma unroll
-    for (int k = 0; k < N; k++) { gq[k] = q_gain ? q_gain[c * N + k] : 1.f; gk[k] = k_gain ? k_gain[c * N + k] : 1.f; }
+    for (int k = 0; k < N; k += 4) {
+        const float4 a = q_gain ? *reinterpret_cast<const float4*>(q_gain + c * N + k) : make_float4(1.f, 1.f, 1.f, 1.f);
+        const float4 b = k_gain ? *reinterpret_cast<const float4*>(k_gain + c * N + k) : make_float4(1.f, 1.f, 1.f, 1.f);
+        gq[k] = a.x; gq[k + 1] = a.y; gq[k + 2] = a.z; gq[k + 3] = a.w;
+        gk[k] = b.x; gk[k + 1] = b.y; gk[k + 2] = b.z; gk[k + 3] = b.w;
+    }
     // where this token's keys and values go
     const int slot = slots[t];
     const bool write_kv = k_pool && slot >= 0;
@@ -251,9 +261,9 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kv_token_kernel(
 }
 
 // From how many tokens on a CTA takes a whole token (a setter for tuning runs).  Measured back to back in a
-// captured loop, 16 + 2 x 8 heads of 128, microseconds a CTA a token / a warp a pair of heads: 512 tokens
-// 5.1 / 5.0, 1024: 6.1 / 7.4, 2048: 10.7 / 12.1, 4096: 19.2 / 21.8.
-static int g_qk_token_threshold = 768;
+// captured loop, 16 + 2 x 8 heads of 128, microseconds a CTA a token / a warp a pair of heads: 128 tokens
+// 3.6 / 3.2, 256: 4.2 / 4.5, 512: 4.4 / 5.0, 1024: 5.7 / 7.5, 2048: 9.8 / 12.1, 4096: 17.8 / 21.8.
+static int g_qk_token_threshold = 256;
 PLLM_EXPORT int pllm_qk_set_token_threshold(int n) {
     const int was = g_qk_token_threshold;
     g_qk_token_threshold = n;
