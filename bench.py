@@ -409,6 +409,10 @@ def other_shape(key, layers, pk, clocks, steps, warmup):
             flops = 2 * 576 * z["L"] * z["layer_params"] + 2 * 64 * z["V"] * z["H"]
             bound = max(read / (pk["hbm_gbs"] * 1e9), flops / (pk["bf16_tflops"] * 1e12))
             out["8b_mixed_frac_of_slower_bound"] = round(bound / (mms / 1e3), 4)
+            # (both bounds: the decoded tokens' attention streams the cache while the tensor cores idle, the products
+            # of 576 rows keep the tensor cores busy while little streams, and a layer runs them one after the other)
+            out["8b_mixed_hbm_bound_ms"] = round(read / (pk["hbm_gbs"] * 1e9) * 1e3, 3)
+            out["8b_mixed_flop_bound_ms"] = round(flops / (pk["bf16_tflops"] * 1e12) * 1e3, 3)
         del eng, runner
     finally:
         shutil.rmtree(tmp, ignore_errors=True)
