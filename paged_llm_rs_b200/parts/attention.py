@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import torch
 
+from ..errors import KernelError
 from ..kernels import ops
 from .base import KVNeed, Mixer, PlanWish, register_mixer
 from .spec import TensorSpec
@@ -34,6 +35,9 @@ class GQAttention(Mixer):
             raise KeyError(f"position encoding {name!r} is not among the model's")
         if self.nh % self.nkv:
             raise ValueError(f"{self.nh} heads do not group over {self.nkv} kv heads")
+        if self.hd % 16 or not 16 <= self.hd <= 256:
+            # said when the model is built, not by the first step's kernel
+            raise KernelError(f"head_dim {self.hd}: the attention kernels take multiples of 16 from 16 to 256")
         self.w_qkv = self.w_o = self.q_gain = self.k_gain = None
         self._need = None
 

@@ -111,3 +111,20 @@ def test_generation_defaults(tmp_path):
         dict(eos_token_id=[5, 6], temperature=0.6, top_p=0.95, top_k=20)))
     g = GenerationDefaults.from_dir(str(tmp_path))
     assert g.eos_token_ids == (5, 6) and g.temperature == pytest.approx(0.6) and g.top_k == 20
+
+
+def test_a_head_size_no_kernel_takes_is_refused_when_the_model_is_described():
+    """head_dim 24 is a valid config; the attention part says at once that its kernels take multiples
+    of 16 only (the model is never built with a size that would first fail in a step)."""
+    import torch
+    from paged_llm_rs_b200 import KernelError
+    from paged_llm_rs_b200.models.qwen3 import describe_qwen3
+    from paged_llm_rs_b200.parts.base import Runtime
+    from paged_llm_rs_b200.parts.decoder import DecoderModel
+
+    d = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_act="silu", hidden_size=48, intermediate_size=64,
+             num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1, head_dim=24, rms_norm_eps=1e-6,
+             vocab_size=50, max_position_embeddings=64, tie_word_embeddings=True, rope_theta=10000.0)
+    spec = describe_qwen3(Qwen3Config.from_dict(d))
+    with pytest.raises(KernelError, match="head_dim 24"):
+        DecoderModel(spec, Runtime(torch.device("cpu"), torch.float32))
