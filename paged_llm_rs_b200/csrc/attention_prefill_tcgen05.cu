@@ -37,7 +37,7 @@
 // scheduler) and the round trip from the groups to the issuing thread and back bound it about equally.
 // 8192 tokens: 328 -> 293 us (940 TFLOP/s); 2048 tokens: 29.6 -> 28.8 us with the reduction's launch.
 // Tried and no faster: three groups; rings of 2 or 3 tiles; steps of 128 keys in one group; Q in tensor
-// memory; polling with test_wait; two buffers of scores with P written over the scores it came from (the
+// memory; polling with test_wait; the issuing loops run by their whole warps with an elected lane; two buffers of scores with P written over the scores it came from (the
 // next scores then wait for the P V before last: the same loop, longer); two buffers of scores AND of
 // weights with one O and the pair's maximum exchanged between twin warps (the groups' turn then bounds it
 // alone, at 2700 clocks a pair).
