@@ -209,10 +209,12 @@ static int pick_mt(const void* x, const void* w, void* y, int M, int N, int K, i
 // give each such a slice (at most 16, and K must divide evenly into slices that are
 // multiples of 32), unless the launch would then exceed what the SMs hold at once
 // several times over.
-static int pick_warps(int K, int ctas, int slice) {
+// (warps_an_sm: how many warps the launch may have for every SM there is)
+static int pick_warps(int K, int ctas, int slice, int warps_an_sm = 64, int max_warps = 16) {
     int warps = 1;
-    for (int wv = 2; wv <= 16; wv++)
-        if (K % (wv * 32) == 0 && K / wv >= slice && (long long)ctas * wv <= (long long)sm_count() * 64) warps = wv;
+    // (2, 4, 8 or 16: 10 warps of 128 registers leave an SM room for one CTA where 8 leave it room for two)
+    for (int wv = 2; wv <= max_warps; wv *= 2)
+        if (K % (wv * 32) == 0 && K / wv >= slice && (long long)ctas * wv <= (long long)sm_count() * warps_an_sm) warps = wv;
     if (g_skinny_warps_override > 0 && g_skinny_warps_override <= 16 && K % (g_skinny_warps_override * 32) == 0)
         warps = g_skinny_warps_override;
     return warps;
@@ -223,14 +225,32 @@ PLLM_EXPORT int pllm_skinny_gemm(const void* x, const void* w, void* y, int M, i
                                  cudaStream_t stream) {
     if (!pllm_skinny_gemm_supports(M, N, K)) return PLLM_ERR_SIZE;
     if (((uintptr_t)x | (uintptr_t)w) & 15) return PLLM_ERR_ALIGN;
-    // Tiles of 16 rows of W while that still gives every SM several CTAs, else of 8.
-    // (With long rows, K >= 4096, a CTA has work enough for one tile of 16 to an SM to do, and every CTA reads
-    // all of x from L2, as many bytes as 8 rows of W: measured at 8 rows, 4096 x 12288, 34.8 us with tiles of 8
-    // and 26.6 with tiles of 16; 4096 x 4096, 19.5 and 16.4.)
+    // More than 16 rows: tiles of 16 rows of W while that still gives every SM several CTAs, else of 8.
     const int sms = sm_count();
     int nt = (N / 16 >= 2 * sms || (K >= 4096 && N / 16 >= sms)) ? 2 : 1;
+    int warps_an_sm = 64;
+    int max_warps = 16;
+    if (M <= 16) {
+        // Up to 16 rows (a decode step).  Every CTA reads all of x from L2, and a wider tile of W does it for more
+        // rows of W; but a CTA of 32-row tiles holds 128 registers a thread (with 16 warps it would fill an SM's
+        // register file alone, and the kernels around it could not take their places beside it) and streams 64 K
+        // bytes of W.  The rule below was decided by the decode step's time with ONE product's tiles and warps
+        // changed at a time, at the 0.6B, 8B and 32B shapes (timed back to back on their own the same products
+        // rank otherwise: a 32-row tile with 16 warps wins there, and loses 4 to 17 us a layer in the step):
+        //   tiles of 32 rows and up to 8 warps  where that gives every SM a CTA and rows are at most 4096 long
+        //                                        (6144 x 4096: 5 us a layer better than 16 rows with 16 warps);
+        //   else tiles of 16 rows               where that gives every SM a CTA, with 16 warps where the rows are
+        //                                        at least as long as there are rows (the o and down products:
+        //                                        4096 x 12288 17 us better than 32 rows, 5120 x 25600 35 us), with
+        //                                        8 where there are more rows than they are long (10240 x 5120: 13 us
+        //                                        better than with 16, 30 better than 32-row tiles with 4);
+        //   else tiles of 8 rows with 16 warps  (1024 x 2048, 1024 x 3072: the best of eight).
+        nt = 1;
+        if (N % 32 == 0 && N / 32 >= sms && K <= 4096) { nt = 4; max_warps = 8; warps_an_sm = 16; }
+        else if (N % 16 == 0 && N / 16 >= sms) { nt = 2; max_warps = N > K ? 8 : 16; }
+    }
     if (g_skinny_nt_override && N % (8 * g_skinny_nt_override) == 0 && (g_skinny_nt_override < 4 || M <= 16)) nt = g_skinny_nt_override;
-    const int warps = pick_warps(K, N / (8 * nt), 128);
+    const int warps = pick_warps(K, N / (8 * nt), 128, warps_an_sm, max_warps);
     if (nt == 4)
         return out_f32 ? launch_skinny<1, 4, 0, float>(x, w, y, M, N, K, warps, stream)
                        : launch_skinny<1, 4, 0, bf16>(x, w, y, M, N, K, warps, stream);
@@ -243,6 +263,17 @@ PLLM_EXPORT int pllm_skinny_gemm(const void* x, const void* w, void* y, int M, i
 PLLM_EXPORT int pllm_skinny_gemm_glu(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
     if (!pllm_skinny_gemm_glu_supports(M, N, K)) return PLLM_ERR_SIZE;
     if (((uintptr_t)x | (uintptr_t)w) & 15) return PLLM_ERR_ALIGN;
+    // Tiles of 16 columns of y (16 gate rows and 16 up rows of W) where that gives four fifths of the SMs a CTA and
+    // either the rows are long or the tiles are few enough to be in place at once; else of 8.  Measured at 8 rows,
+    // microseconds with tiles of 8 / of 16: 3072 x 1024 4.6 / 3.6, 12288 x 4096 38.6 / 36.6, 25600 x 5120 91.3 / 82.6,
+    // 9728 x 2560 22.2 / 23.6 (the one that stays with 8).
+    const int sms = sm_count();
+    int nt = (N % 16 == 0 && N / 16 >= sms * 4 / 5 && (K >= 4096 || N / 16 <= 2 * sms)) ? 4 : 2;
+    if ((g_skinny_nt_override == 4 && N % 16 == 0) || g_skinny_nt_override == 2) nt = g_skinny_nt_override;
+    if (nt == 4) {
+        const int warps = pick_warps(K, N / 16, 128);
+        return launch_skinny<1, 4, 1, bf16>(x, w, y, M, N, K, warps, stream);
+    }
     const int warps = pick_warps(K, N / 8, 128);
     return launch_skinny<1, 2, 1, bf16>(x, w, y, M, N, K, warps, stream);
 }
