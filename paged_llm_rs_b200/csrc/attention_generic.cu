@@ -178,14 +178,20 @@ __global__ void attention_reduce_kernel(const float* part_o, const float* part_m
     __shared__ float inv_s;
     extern __shared__ float gsum[];     // [RED_GROUPS][hd]
     pdl_launch_dependents();
-    pdl_wait(KID_ATT_REDUCE);
+    // The list of reductions is the host's (part of the step's packed buffer): how many there are and this
+    // CTA's first entry are fetched before the wait for the attention kernel, two trips to L2 that then
+    // lie beside that kernel's end and not behind it.
     const int head = blockIdx.y, n_red = *n_red_ptr;
+    int4 entry = make_int4(0, 0, 0, 0);
+    if ((int)blockIdx.x < n_red) entry = make_int4(red[blockIdx.x * 4], red[blockIdx.x * 4 + 1], red[blockIdx.x * 4 + 2], red[blockIdx.x * 4 + 3]);   // (the list need not lie on a 16-byte boundary)
+    pdl_wait(KID_ATT_REDUCE);
     const int ng = blockDim.x / hd;                               // groups of hd threads: 1 or RED_GROUPS
     const int grp = threadIdx.x / hd, d = threadIdx.x % hd;
     // a CTA takes entries blockIdx.x, blockIdx.x + gridDim.x, ...: a captured step launches a grid for
     // the most entries a step could have, and CTAs with nothing to do must be few
     for (int t = blockIdx.x; t < n_red; t += gridDim.x) {
-        const int token = red[t * 4], first = red[t * 4 + 1], count = min(red[t * 4 + 2], RED_MAX_SPLITS), stride = red[t * 4 + 3];
+        if (t != (int)blockIdx.x) entry = make_int4(red[t * 4], red[t * 4 + 1], red[t * 4 + 2], red[t * 4 + 3]);
+        const int token = entry.x, first = entry.y, count = min(entry.z, RED_MAX_SPLITS), stride = entry.w;
         if (count <= 0) continue;
         if (count <= 8 && ng == 1) {
             // few splits (the usual case away from batch 1): every thread fetches the entry's (m, l) pairs and

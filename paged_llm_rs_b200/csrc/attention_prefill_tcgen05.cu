@@ -208,11 +208,6 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
         // (a request costs the issuing warp 135 clocks, 540 a tile of four pages: two warps a ring, taking the tiles in turn)
         const bool keys = warp == W_KEYS || warp == W_KEYS2;
         const int first = (warp == W_KEYS || warp == W_VALUES) ? 0 : 1;
-        pdl_wait(KID_ATT_TC, warp == W_KEYS && lane == 0);           // the queries and this step's cache rows come from the kernel before
-        if (warp == W_KEYS && lane == 0) {
-            mbar_expect_tx(q_full, (uint32_t)(NHALF * 128 * heads_per_cta * tile_tokens));
-            for (int h = 0; h < NHALF; h++) tma_load_3d(q_s + h * P_ROWS * 128, &map_q, h * 64, head0, w.q_token0, q_full);
-        }
         const CUtensorMap* map = keys ? &map_k : &map_v;
         const uint32_t ring = keys ? k_ring : v_ring, full = keys ? k_full : v_full, empty = keys ? k_empty : v_empty;
         unsigned char* ring_ptr = smem + Q_BYTES + (keys ? 0 : P_STAGES * STAGE);
@@ -223,6 +218,12 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
         // the table entries of the key range, 32 at a time, one in each lane, fetched ahead
         int win0 = w.kv_begin >> page_shift;
         int tbl = (win0 + lane < table_width) ? table[win0 + lane] : -1;
+        // (the block table is the host's: fetched before the wait)
+        pdl_wait(KID_ATT_TC, warp == W_KEYS && lane == 0);           // the queries and this step's cache rows come from the kernel before
+        if (warp == W_KEYS && lane == 0) {
+            mbar_expect_tx(q_full, (uint32_t)(NHALF * 128 * heads_per_cta * tile_tokens));
+            for (int h = 0; h < NHALF; h++) tma_load_3d(q_s + h * P_ROWS * 128, &map_q, h * 64, head0, w.q_token0, q_full);
+        }
         CLK_BEGIN
         for (int t = first; t < n_tiles; t += 2) {
             const int s = t % P_STAGES;

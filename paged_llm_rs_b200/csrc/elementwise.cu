@@ -71,25 +71,37 @@ PLLM_EXPORT int pllm_embed(int dtype, const int* tokens, const void* table, void
 //   y[i] = v / sqrt(mean(v^2) + eps) * gain
 // x and residual_out may be the same buffer.
 template <typename T>
-__global__ void rmsnorm_kernel(const T* x, const T* delta, T* residual_out,   // x, delta: just written, no __restrict__
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(const T* x, const T* delta, T* residual_out,   // x, delta: just written, no __restrict__
                                const float* __restrict__ gain, T* __restrict__ y, const int* __restrict__ rows,
                                int width, float eps) {
     __shared__ float scratch[32];
     pdl_launch_dependents();
-    pdl_wait(KID_RMSNORM);
     const int i = blockIdx.x;
+    constexpr int N = Vec16<T>::N;
+    const bool vec = (width % N == 0);
+    // Rows of up to RMS_HELD vectors a thread stay in registers between the two passes; wider rows
+    // (and rows that are not whole vectors) are read back.
+    constexpr int RMS_HELD = 4;
+    const bool held = vec && width <= (int)blockDim.x * N * RMS_HELD;
+    // the gain of a thread's first vector (a weight; all of the row when it is at most a vector a thread wide)
+    // and the row's number (the step's buffer) are fetched before the wait for the kernel before
+    float g0[N];
+    {
+        const int c = threadIdx.x * N;
+#pragma unroll
+        for (int k = 0; k < N; k += 4) {
+            const float4 q = (held && c < width) ? *reinterpret_cast<const float4*>(gain + c + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            g0[k] = q.x; g0[k + 1] = q.y; g0[k + 2] = q.z; g0[k + 3] = q.w;
+        }
+    }
     const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+    pdl_wait(KID_RMSNORM);
     const T* xr = x + r * width;
     const T* dr = delta ? delta + r * width : nullptr;
     T* rr = residual_out ? residual_out + r * width : nullptr;
     T* yr = y + (size_t)i * width;
-    constexpr int N = Vec16<T>::N;
-    const bool vec = (width % N == 0);
     float ss = 0.f;
-    // Rows of up to RMS_HELD vectors a thread stay in registers between the two passes; wider rows
-    // (and rows that are not whole vectors) are read back.
-    constexpr int RMS_HELD = 4;
-    if (vec && width <= (int)blockDim.x * N * RMS_HELD) {
+    if (held) {
         float f[RMS_HELD][N];
 #pragma unroll
         for (int j = 0; j < RMS_HELD; j++) {
@@ -115,11 +127,11 @@ __global__ void rmsnorm_kernel(const T* x, const T* delta, T* residual_out,   //
         for (int j = 0; j < RMS_HELD; j++) {
             const int c = (threadIdx.x + j * blockDim.x) * N;
             if (c >= width) break;
-            const float4 g0 = *reinterpret_cast<const float4*>(gain + c);
-            float gg[8] = {g0.x, g0.y, g0.z, g0.w, 0.f, 0.f, 0.f, 0.f};
-            if (N == 8) {
-                const float4 g1 = *reinterpret_cast<const float4*>(gain + c + 4);
-                gg[4] = g1.x; gg[5] = g1.y; gg[6] = g1.z; gg[7] = g1.w;
+            float gg[N];
+#pragma unroll
+            for (int k = 0; k < N; k += 4) {
+                const float4 q = j == 0 ? make_float4(g0[k], g0[k + 1], g0[k + 2], g0[k + 3]) : *reinterpret_cast<const float4*>(gain + c + k);
+                gg[k] = q.x; gg[k + 1] = q.y; gg[k + 2] = q.z; gg[k + 3] = q.w;
             }
 #pragma unroll
             for (int k = 0; k < N; k++) f[j][k] = f[j][k] * inv * gg[k];

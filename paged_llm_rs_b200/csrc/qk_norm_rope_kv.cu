@@ -104,7 +104,6 @@ __global__ void qk_norm_rope_kv_vec_kernel(
     T* __restrict__ v_pool, int n_tokens, int nh, int nkv, int page_size, int n_pages, int swizzle, int* status) {
     constexpr int N = Vec16<T>::N, HD = LPH * N, HPW = 32 / LPH;
     pdl_launch_dependents();
-    pdl_wait(KID_QK);
     const int lane = threadIdx.x & 31, sub = lane / LPH, c = lane % LPH;
     const int heads = nh + 2 * nkv;
     const long long total = (long long)n_tokens * heads;
@@ -114,6 +113,24 @@ __global__ void qk_norm_rope_kv_vec_kernel(
     const int t = (int)(item / heads), h = (int)(item % heads);
     const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
     const float* gain = is_q ? q_gain : (is_k ? k_gain : nullptr);
+    // What does not come from the kernel before (the token's position and slot out of the step's buffer, the
+    // rotation's table, the gain) is fetched before the wait for it: two trips to memory beside its end.
+    constexpr int HALF = HD / 2;
+    const bool upper = c >= LPH / 2;
+    float cs[N], sn[N], gn[N];
+    if (cos_t) {
+        int pos = positions[t];
+        if (pos < 0 || pos >= max_pos) { if (c == 0 && live) atomicOr(status, 4); pos = 0; }
+        const size_t o = (size_t)pos * HALF + (upper ? c - LPH / 2 : c) * N;
+#pragma unroll
+        for (int k = 0; k < N; k++) { cs[k] = cos_t[o + k]; sn[k] = sin_t[o + k]; }
+    }
+    if (gain) {
+#pragma unroll
+        for (int k = 0; k < N; k++) gn[k] = gain[c * N + k];
+    }
+    const int slot = (live && !is_q && k_pool) ? slots[t] : -1;
+    pdl_wait(KID_QK);
 
     Vec16<T> v;
     v.load(qkv + (size_t)t * heads * HD + (size_t)h * HD + c * N);
@@ -127,15 +144,9 @@ __global__ void qk_norm_rope_kv_vec_kernel(
     if (gain) {
         const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
 #pragma unroll
-        for (int k = 0; k < N; k++) f[k] = f[k] * inv * gain[c * N + k];
+        for (int k = 0; k < N; k++) f[k] = f[k] * inv * gn[k];
     }
     if (cos_t) {
-        int pos = positions[t];
-        if (pos < 0 || pos >= max_pos) { if (c == 0 && live) atomicOr(status, 4); pos = 0; }
-        constexpr int HALF = HD / 2;
-        const bool upper = c >= LPH / 2;
-        const float* cs = cos_t + (size_t)pos * HALF + (upper ? c - LPH / 2 : c) * N;
-        const float* sn = sin_t + (size_t)pos * HALF + (upper ? c - LPH / 2 : c) * N;
 #pragma unroll
         for (int k = 0; k < N; k++) {
             const float other = __shfl_xor_sync(0xffffffffu, f[k], LPH / 2);
@@ -148,7 +159,6 @@ __global__ void qk_norm_rope_kv_vec_kernel(
     if (is_q) {
         dst = q_out + (size_t)t * nh * HD + (size_t)h * HD;
     } else {
-        const int slot = slots[t];
         if (!k_pool || slot < 0) return;
         const int page = slot / page_size, off = slot % page_size;
         if (page >= n_pages) { if (c == 0) atomicOr(status, 2); return; }
@@ -173,7 +183,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kv_token_kernel(
     T* __restrict__ v_pool, int n_tokens, int nh, int nkv, int page_size, int n_pages, int swizzle, int* status) {
     constexpr int N = Vec16<T>::N, HD = LPH * N, HPW = 32 / LPH, UNR = 4;
     pdl_launch_dependents();
-    pdl_wait(KID_QK);
+    // (position, slot, rotation table and gains do not come from the kernel before: they are fetched before the wait for it)
     const int lane = threadIdx.x & 31, sub = lane / LPH, c = lane % LPH;
     const int t = blockIdx.x, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     if (t >= n_tokens) return;
@@ -209,6 +219,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kv_token_kernel(
     }
     const int xr = swizzle ? (off & 7) : 0;
     const T* src = qkv + (size_t)t * heads * HD + c * N;
+    pdl_wait(KID_QK);
     for (int h0 = warp * HPW * UNR; h0 < heads; h0 += warps * HPW * UNR) {
         Vec16<T> v[UNR];
 #pragma unroll
