@@ -22,9 +22,11 @@ from typing import List, Optional, Sequence, Tuple
 import numpy as np
 
 SPLIT_ALIGN = 64   # split boundaries fall on multiples of the kernels' key tiles (32 and 64)
-# A split shorter than this costs more in the reduction than it saves in the attention (a captured
-# step of the 0.6B shape, batch 1, context 4096: 0.927 ms with 256, 0.947 with 128, 1.011 with 512).
-MIN_SPLIT_KEYS = 256
+# The shortest split: one tile of keys.  Measured on captured steps of the 0.6B shape (decoded tokens a second
+# with 64 / 128 / 256 / 512 keys): batch 1 at context 4096: 1343 / 1266 / 1267 / 1081; batch 1 at context 512:
+# 1478 / 1480 / 1450 / 1266; batch 8 at context 512: 10484 / 10490 / 9700 / 8648.  (Before the reduction's list
+# was fetched ahead of its wait and the products' tiles were chosen anew, 256 was the best of these.)
+MIN_SPLIT_KEYS = 64
 MAX_SPLITS = 128   # the reduce kernel holds the weights of up to 256 splits in shared memory
 # A tile of many query tokens is cut only where every part still has this many keys: its partial results are
 # a tile of rows each, not one row (a 512-token portion behind 1024 tokens of context beside one decoded
