@@ -19,6 +19,9 @@ next token.  One JSON line is printed:
   points       decode tokens a second at batch 1 and 64 at the same context, and at batch 1, 8 and 64
                at context 512 (right after the baseline's 512-token prompts), each with its fraction
                of the HBM roofline
+  generate     whole generations through Engine.generate by the wall clock: 64 prompts of 512 tokens,
+               128 new tokens each, steps of at most 2048 tokens (the first call, which captures its
+               steps, is not counted)
   repeats      the spread of the timed region: it is repeated ten times (median, min, max)
   shapes       the same figures at the baseline's 8B shape (36 of 36 layers; with its mixed step: 64
                requests decoding at context 4096 beside a 512-token portion) and at the 32B shape's
@@ -345,6 +348,38 @@ def prefill_point(runner, vocab, clocks, repeats=9):
     return spread["median_ms"], spread
 
 
+def generate_point(model_dir, vocab, clocks, requests=64, prompt=512, new=128, repeats=3):
+    """Whole generations through ``Engine.generate``: ``requests`` random prompts of ``prompt`` tokens, ``new``
+    tokens each, greedy, no stop token; host token lists in and out, by the wall clock.  The first call
+    captures the steps it needs and is not counted.  What the scheduler, the portions under the token
+    budget, the step packing and the copies cost shows as the gap to the device-timed points."""
+    import numpy as np
+    import torch
+    from paged_llm_rs_b200 import Engine
+    eng = Engine(model_dir, dtype="bfloat16", block_size=PAGE, blocks=requests * ((prompt + new) // PAGE + 2) + 64,
+                 max_batch=requests, chunk=PREFILL_TOKENS, prefix_cache=False,
+                 max_prefill_seqs=max(1, PREFILL_TOKENS // prompt))    # (the token budget decides, not the count)
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, vocab, prompt).tolist() for _ in range(requests)]
+    eng.generate(prompts, max_tokens=new, stop_tokens=())
+    torch.cuda.synchronize()
+    per = []
+    for _ in range(repeats):
+        t0 = time.time()
+        outs = eng.generate(prompts, max_tokens=new, stop_tokens=())
+        torch.cuda.synchronize()
+        t1 = time.time()
+        clocks.region(t0, t1)
+        assert all(len(o) == new for o in outs)
+        per.append((t1 - t0) * 1e3)
+    ms = statistics.median(per)
+    m = eng.scheduler.metrics
+    return dict(requests=requests, prompt_tokens=prompt, new_tokens=new, ms=round(ms, 1), min_ms=round(min(per), 1),
+                max_ms=round(max(per), 1), generated_tokens_s=round(requests * new / (ms / 1e3), 1),
+                all_tokens_s=round(requests * (prompt + new) / (ms / 1e3), 1), step_token_budget=PREFILL_TOKENS,
+                steps_per_call=m.steps // (repeats + 1))
+
+
 def shape_sizes(shape):
     L, H, I = shape["num_hidden_layers"], shape["hidden_size"], shape["intermediate_size"]
     nh, nkv, hd, V = shape["num_attention_heads"], shape["num_key_value_heads"], shape["head_dim"], shape["vocab_size"]
@@ -621,7 +656,6 @@ def main(argv=None) -> int:
         pages = max(most, B) * (ctx // PAGE + 4) + PREFILL_TOKENS // PAGE + 64
         eng = Engine(model_dir, dtype="bfloat16", block_size=PAGE, blocks=pages, max_batch=max(most, B),
                      chunk=PREFILL_TOKENS, prefix_cache=False)
-        shutil.rmtree(tmp, ignore_errors=True)
         runner = eng.runner
         for g in runner.cache.groups:       # cache contents for the device-timed points: random, not zeros
             g.pool.normal_(0.0, 1.0)
@@ -706,6 +740,17 @@ def main(argv=None) -> int:
         gc.collect()
         torch.cuda.empty_cache()
 
+        # -- whole generations: 64 requests from their prompts to their last token ---------------
+        generate_out = {}
+        if not args.no_points:
+            try:
+                generate_out = generate_point(model_dir, V, clocks)
+            except Exception as e:     # noqa: BLE001
+                generate_out = {"error": f"{type(e).__name__}: {e}"[:200]}
+            gc.collect()
+            torch.cuda.empty_cache()
+        shutil.rmtree(tmp, ignore_errors=True)
+
         # -- the baseline's other shapes, and the reference's own kernel -------------------------------
         shapes, ref_kernel = {}, {}
         if not args.no_shapes and args.shape == "0.6b" and not args.layers:
@@ -745,6 +790,8 @@ def main(argv=None) -> int:
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
     }
+    if generate_out:
+        line["generate"] = generate_out
     if shapes:
         line["shapes"] = shapes
     if ref_kernel:

@@ -32,9 +32,12 @@ def test_the_reference_kernel_comparison_runs_and_agrees():
 
 
 def test_a_short_bench_run_prints_the_record():
-    out = run_bench("--steps", "3", "--warmup", "3", "--layers", "2", "--no-points")
-    for key in ("metric", "value", "ms_per_step", "e2e", "gpu_launches", "clocks", "prefill", "roofline", "config"):
+    out = run_bench("--steps", "3", "--warmup", "3", "--layers", "2", "--no-shapes")
+    for key in ("metric", "value", "ms_per_step", "e2e", "gpu_launches", "clocks", "prefill", "roofline", "config",
+                "points", "generate"):
         assert key in out, key
     assert out["config"]["layers"] == 2 and out["config"]["layers_of_shape"] == 28
     assert out["gpu_launches"] > 0 and out["e2e"]["h2d_bytes_per_step"] > 0 and out["e2e"]["d2h_bytes_per_step"] > 0
     assert 0 < out["roofline"]["frac"] < 1.2 and 0 < out["prefill"]["frac"] < 1.2
+    assert out["points"]["decode_b1"] > 0 and out["points"]["decode_b64"] > out["points"]["decode_b1"]
+    assert "error" not in out["generate"] and out["generate"]["generated_tokens_s"] > 0
