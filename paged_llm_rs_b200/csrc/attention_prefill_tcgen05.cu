@@ -81,7 +81,8 @@ namespace {
 constexpr int P_G = PLLM_ATT_GROUPS;
 constexpr int P_ROWS = 128, P_BK = 64, P_STAGES = PLLM_ATT_STAGES, P_THREADS = (4 * P_G + 8) * 32;
 constexpr int W_KEYS = 4 * P_G, W_SCORES = 4 * P_G + 1, W_VALUES = 4 * P_G + 2, W_SUMS = 4 * P_G + 3;
-constexpr int W_KEYS2 = 4 * P_G + 4, W_VALUES2 = 4 * P_G + 5;    // the producers of the odd tiles (the last two warps have no work)
+constexpr int W_KEYS2 = 4 * P_G + 4, W_VALUES2 = 4 * P_G + 5;    // the producers of the odd tiles
+constexpr int W_SCORES2 = 4 * P_G + 6, W_SUMS2 = 4 * P_G + 7;   // the second group's issuing threads
 static_assert(P_G == 2 && P_STAGES % 2 == 0, "the register split and the producers' turns are laid out for two groups and an even ring");   // the other four warps   // P_STAGES: key tiles, and as many value tiles, in flight
 constexpr float P_RESCALE = 8.0f;              // log2 units the running maximum may lag behind
 
@@ -97,7 +98,7 @@ __device__ __forceinline__ float ex2(float x) {
 // clocks it spends in each of its waits and in its own work, and leaves the sums in a buffer that
 // pllm_attention_prefill_clocks_read copies out: [work item < 64][role][slot], for kv head 0.
 #ifdef PLLM_ATT_CLOCKS
-static __device__ long long g_att_clocks[64][8][8];
+static __device__ long long g_att_clocks[64][10][8];
 static __device__ long long g_att_events[8][128][4];      // [role][tile][event] clock of work item 0, kv head 0
 #define EVT(role, tile, slot) { if (blockIdx.y == 0 && blockIdx.x == 0 && (tile) < 128) g_att_events[role][tile][slot] = clock64(); }
 PLLM_EXPORT int pllm_attention_prefill_events_read(long long* out) {
@@ -156,15 +157,18 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     const uint32_t k_ring = q_s + Q_BYTES, v_ring = k_ring + P_STAGES * STAGE;
     const uint32_t p_s = v_ring + P_STAGES * STAGE;            // a P buffer a group
     constexpr int RINGS = 2 * P_STAGES * STAGE;
-    float* mstate = reinterpret_cast<float*>(smem + Q_BYTES + RINGS + P_SMEM);          // [groups][128] the groups' maxima at the end
-    float* lpart = mstate + P_G * P_ROWS;                                                           // [groups][128] the groups' sums
-    unsigned char* ctl = smem + Q_BYTES + RINGS + P_SMEM + 2 * P_G * P_ROWS * 4;
+    // [groups][128] the groups' maxima and sums at the end, in the queries' place: written only when every
+    // product has run (o_full)
+    float* mstate = reinterpret_cast<float*>(smem);
+    float* lpart = mstate + P_G * P_ROWS;
+    static_assert(2 * P_G * P_ROWS * 4 <= Q_BYTES, "the groups' maxima and sums lie in the queries' place");
+    unsigned char* ctl = smem + Q_BYTES + RINGS + P_SMEM;
     const uint32_t bars = smem_u32(ctl);
     const uint32_t q_full = bars, k_full = bars + 8, k_empty = k_full + 8 * P_STAGES, v_full = k_empty + 8 * P_STAGES,
                    v_empty = v_full + 8 * P_STAGES, s_full = v_empty + 8 * P_STAGES,
                    p_full = s_full + 8 * P_G, p_empty = p_full + 8 * P_G, o_full = p_empty + 8 * P_G,
-                   s_free = o_full + 8, q_tmem = s_free + 8 * P_G;
-    constexpr int N_BARS = 4 * P_STAGES + 1 + 3 * P_G + 1 + P_G + 1;
+                   s_free = o_full + 8, q_tmem = s_free + 8 * P_G, turn = q_tmem + 8;
+    constexpr int N_BARS = 4 * P_STAGES + 1 + 3 * P_G + 1 + P_G + 1 + P_G;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctl + 8 * N_BARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(ctl + 8 * N_BARS + 8);
 
@@ -179,8 +183,9 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             mbar_init(p_full + 8 * b, 4);        // one arrival from each warp of the group
             mbar_init(p_empty + 8 * b, 1);
             mbar_init(s_free + 8 * b, 4);        // the group has its scores in registers
+            mbar_init(turn + 8 * b, 4);          // the other group is through with its exponentials
         }
-        mbar_init(o_full, 1);
+        mbar_init(o_full, P_G);                  // each group's issuing thread, after its last product
         mbar_init(q_tmem, 4);                    // the first group's warps have put their rows of Q into tensor memory
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
@@ -266,70 +271,59 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             if (lane == 0) EVT(keys ? 4 : 5, t, 1)
         }
         if (lane == 0) { CLK(1) CLK_END((keys ? 4 : 5) + 2 * first) }
-    } else if (warp == W_SCORES) {
-        // ---- tensor-core issue, the scores: S[t % groups] = Q K_t^T.  (Two issuing threads, this one and
-        // warp 11's for O += P V: each tile costs an issuing thread a handful of waits, instructions
-        // and commits one after the other, and that, not the tensor cores' time, bounds the kernel.)
+    } else if (warp == W_SCORES || warp == W_SCORES2) {
+        // ---- tensor-core issue, the scores of one group's tiles: S[g] = Q K_t^T for t = g, g + 2, ...  Each
+        // group has issuing threads of its own (this one and one for O += P V), so that nothing ties one
+        // group's turn to the other's: they drift apart until one computes its exponentials while the
+        // other loads, stores and waits.
         if (lane == 0) {
+            const int g = warp == W_SCORES ? 0 : 1;
             constexpr uint32_t idesc_qk = instr_desc(P_ROWS, P_BK);
             // descriptors differ only in their address field (bits 0-13, units of 16 bytes): the rest is
             // made once, and an address offset is one addition
             const uint64_t q_desc = smem_desc(q_s), k_desc = smem_desc(k_ring, 16, GROUP);
             bool ok = mbar_wait(PLLM_ATT_Q_TMEM ? q_tmem : q_full, 0, abort_flag);
             CLK_BEGIN
-            // With two groups and an even ring, key tiles t and t + 1 (t even) lie back to back in shared memory
-            // and their scores in neighbouring columns: ONE set of products 128 keys wide makes both (an
-            // instruction costs this thread some 85 clocks to issue, as much as the tensor cores need for
-            // three of the narrow ones).
-            constexpr bool PAIRS = P_G == 2 && P_STAGES % 2 == 0;
-            constexpr uint32_t idesc_qk2 = instr_desc(P_ROWS, 2 * P_BK);
-            for (int t = 0; t < n_tiles && ok; t += PAIRS ? 2 : 1) {
+            for (int t = g; t < n_tiles && ok; t += P_G) {
                 const int s = t % P_STAGES;
-                const bool two = PAIRS && t + 1 < n_tiles;
-                // the group(s) must have read their scores of the turn before out of the buffer(s)
-                const int g = t % P_G;
-                // (the key tiles first: they are there long before the groups have read the last scores, and a
+                // (the key tile first: it is there long before the group has read its last scores, and a
                 // wait on a barrier that is over still costs this thread a hundred clocks or two)
                 if (!mbar_wait(k_full + 8 * s, (t / P_STAGES) & 1, abort_flag)) { ok = false; break; }
-                if (two && !mbar_wait(k_full + 8 * (s + 1), (t / P_STAGES) & 1, abort_flag)) { ok = false; break; }
                 CLK(1)
                 EVT(0, t, 1)
+                // the group must have read its scores of the turn before out of the buffer
                 if (t >= P_G && !mbar_wait(s_free + 8 * g, ((t - P_G) / P_G) & 1, abort_flag)) { ok = false; break; }
-                if (two && t >= P_G && !mbar_wait(s_free + 8 * (g + 1), ((t - P_G) / P_G) & 1, abort_flag)) { ok = false; break; }
                 CLK(0)
                 EVT(0, t, 0)
                 tc_fence_after();
                 const uint64_t kd = k_desc + (uint64_t)((s * STAGE) >> 4);
                 const uint32_t d = tmem + S_COL + g * P_BK;
-                const uint32_t idesc = two ? idesc_qk2 : idesc_qk;
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {
 #if PLLM_ATT_Q_TMEM
-                    mma_ts(d, tmem + Q_COL + ks * 8, kd + (uint64_t)(((ks / 4) * 1024 + (ks % 4) * 32) >> 4), idesc, ks ? 1u : 0u);
+                    mma_ts(d, tmem + Q_COL + ks * 8, kd + (uint64_t)(((ks / 4) * 1024 + (ks % 4) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
 #else
                     mma_ss(d, q_desc + (uint64_t)(((ks / 4) * P_ROWS * 128 + (ks % 4) * 32) >> 4),
-                           kd + (uint64_t)(((ks / 4) * 1024 + (ks % 4) * 32) >> 4), idesc, ks ? 1u : 0u);
+                           kd + (uint64_t)(((ks / 4) * 1024 + (ks % 4) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
 #endif
                 }
                 (void)q_desc;
-                mma_commit(k_empty + 8 * s);         // the key tiles' places are free once these have read them
-                if (two) mma_commit(k_empty + 8 * (s + 1));
+                mma_commit(k_empty + 8 * s);         // the key tile's place is free once these have read it
                 mma_commit(s_full + 8 * g);
-                if (two) mma_commit(s_full + 8 * (g + 1));
                 CLK(2)
                 EVT(0, t, 2)
             }
-            CLK_END(0)
+            CLK_END(g ? 8 : 0)
         }
-    } else if (warp == W_SUMS) {
-        // ---- tensor-core issue, the sums: O += P_t V_t --------------------------------------------------
+    } else if (warp == W_SUMS || warp == W_SUMS2) {
+        // ---- tensor-core issue, the sums of one group's tiles: O[g] += P_t V_t --------------------------
         if (lane == 0) {
+            const int g = warp == W_SUMS ? 0 : 1;
             constexpr uint32_t idesc_pv = instr_desc(P_ROWS, HD, 1);
             const uint64_t p_desc = smem_desc(p_s), v_desc = smem_desc(v_ring, 1024, GROUP);
             bool ok = true;
             CLK_BEGIN
-            for (int t = 0; t < n_tiles && ok; t++) {
-                const int g = t % P_G;
+            for (int t = g; t < n_tiles && ok; t += P_G) {
                 if (!mbar_wait(v_full + 8 * (t % P_STAGES), (t / P_STAGES) & 1, abort_flag)) { ok = false; break; }      // (the values first, likewise)
                 CLK(1)
                 EVT(1, t, 1)
@@ -355,10 +349,10 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 CLK(2)
                 EVT(1, t, 2)
             }
-            CLK_END(1)
-            if (ok) mma_commit(o_full);
+            CLK_END(g ? 9 : 1)
+            if (ok) mma_commit(o_full);                      // (one arrival from each group's thread)
         }
-    }       // (the last two warps have no work)
+    }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 192;\n" ::);
         // ---- softmax, one row a thread, the two groups taking the tiles in turn; then the epilogue ----
@@ -397,6 +391,10 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             if (lane == 0) mbar_arrive(q_tmem);
         }
 #endif
+        // The exponentials of the two groups take turns (they share one unit, and left alone the groups fall
+        // into step: both compute theirs at once, at half speed each, and then both wait): a group computes
+        // its tile's when the other is through with those of the tile before, and meanwhile loads, stores and waits.
+        if (grp == 1 && lane == 0) mbar_arrive(turn);
         CLK_BEGIN
         for (int t = grp; t < n_tiles; t += P_G) {
             const int kv0 = w.kv_begin + t * P_BK;
@@ -459,10 +457,14 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 l_run = m_ref > -CUDART_INF_F ? l_run * ex2(m_ref - m_used) : 0.f;
                 m_ref = m_used;
             }
+            if (!mbar_wait(turn + 8 * grp, (t / P_G) & 1, abort_flag)) { ok = false; break; }
             // weights 2^(s * scale - m): one multiply-add and one exponential each; a hidden key's -inf gives 0
             const float neg_m = m_used > -CUDART_INF_F ? -m_used : 0.f;
             uint32_t pw[32];
-            float s4[4] = {0.f, 0.f, 0.f, 0.f};
+            // (eight sums side by side, each weight added to one of them directly: with four, and a pair's sum
+            //  formed first, a warp alone on its scheduler took 1083 clocks for these 64 weights instead of 704,
+            //  which is what the 64 exponentials take by themselves)
+            float s8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < 32; i++) {
                 const uint32_t a = i < 16 ? v0[2 * i] : v1[2 * i - 32], b2 = i < 16 ? v0[2 * i + 1] : v1[2 * i - 31];
@@ -470,9 +472,12 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 const float p1 = ex2(fmaf(__uint_as_float(b2), scale_log2, neg_m));
                 __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                 pw[i] = *reinterpret_cast<uint32_t*>(&h);
-                s4[i & 3] += p0 + p1;
+                s8[2 * (i & 3)] += p0;
+                s8[2 * (i & 3) + 1] += p1;
             }
-            l_run += (s4[0] + s4[1]) + (s4[2] + s4[3]);
+            l_run += ((s8[0] + s8[1]) + (s8[2] + s8[3])) + ((s8[4] + s8[5]) + (s8[6] + s8[7]));
+            __syncwarp();
+            if (lane == 0 && t + 1 < n_tiles) mbar_arrive(turn + 8 * (grp ^ 1));
             CLK(5)
             if (wq == 0 && lane == 0) EVT(2 + grp, t, 2)
             // this group's P of its tile before must be read out of shared memory before it is overwritten
@@ -500,6 +505,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
         // ---- the groups meet: each has a maximum, a sum and an O of its own (the even tiles', the odd tiles'),
         // brought to the larger maximum here; each group stores half of the columns ------------------------
         if (!ok || *abort_flag) *abort_flag = 1;
+        const bool have_o = !*abort_flag && mbar_wait(o_full, 0, abort_flag);      // (the last product has read Q, the keys and the values)
         mstate[grp * P_ROWS + row] = m_ref;
         lpart[grp * P_ROWS + row] = l_run;
         asm volatile("bar.sync 1, %0;\n" ::"n"(P_G * 128) : "memory");          // (the softmax warps; the others are elsewhere)
@@ -513,7 +519,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             share[g] = (g < n_tiles && mg > -CUDART_INF_F && lg > 0.f) ? ex2(mg - m_fin) : 0.f;
             l_tot += share[g] > 0.f ? lg * share[g] : 0.f;
         }
-        if (!*abort_flag && mbar_wait(o_full, 0, abort_flag)) {
+        if (have_o && !*abort_flag) {
             tc_fence_after();
             const float inv = l_tot > 0.f ? 1.0f / l_tot : 0.f;
             // chunks of 32 columns, dealt to the groups
@@ -609,7 +615,7 @@ static int launch_prefill(const void* q, const void* k_pool, const void* v_pool,
     constexpr int NHALF = HD / 64;
     const size_t smem = (size_t)NHALF * P_ROWS * 128 + (size_t)P_STAGES * 2 * NHALF * P_BK * 128 +
                         (PLLM_ATT_P_TMEM ? 0 : P_G * P_ROWS * 128) +
-                        2 * P_G * P_ROWS * 4 + 8 * (4 * P_STAGES + 3 + 4 * P_G) + 16 + 1024;
+                        8 * (4 * P_STAGES + 3 + 5 * P_G) + 16 + 1024;
     cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_chained(attention_prefill_tcgen05_kernel<HD>, dim3(nkv * gparts, max_work), dim3(P_THREADS), smem, stream, map_q,
                    map_k, map_v, block_tables, (const AttnWork*)work, n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv,
