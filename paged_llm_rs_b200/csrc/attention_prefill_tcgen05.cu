@@ -69,14 +69,9 @@ namespace {
 #endif
 // Softmax groups that take the key tiles in turn: four warps each.
 #define PLLM_ATT_GROUPS 2
-// P handed to the tensor cores in tensor memory (1) or in shared memory (0)
-#ifndef PLLM_ATT_P_TMEM
-#define PLLM_ATT_P_TMEM 1
-#endif
-// Q likewise (copied from shared memory into tensor memory once, by the first group's threads, a row each):
-// correct and no faster (8192 tokens: 343.1 against 339.6 us), so off.
-#ifndef PLLM_ATT_Q_TMEM
-#define PLLM_ATT_Q_TMEM 0
+// After how many of a tile's 32 pairs of weights a group lets the other begin with its exponentials
+#ifndef PLLM_ATT_HANDOVER
+#define PLLM_ATT_HANDOVER 32
 #endif
 constexpr int P_G = PLLM_ATT_GROUPS;
 constexpr int P_ROWS = 128, P_BK = 64, P_STAGES = PLLM_ATT_STAGES, P_THREADS = (4 * P_G + 8) * 32;
@@ -128,12 +123,12 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     int tile_tokens, int take_single, int* status) {
     constexpr int NHALF = HD / 64;
     constexpr int GROUP = NHALF * 1024;            // 8 keys (or values): [half][8 rows][128 bytes]
-    constexpr int Q_BYTES = NHALF * P_ROWS * 128, STAGE = (P_BK / 8) * GROUP, P_BYTES = P_ROWS * 128;   // STAGE: a key (or value) tile
-    constexpr uint32_t S_COL = 0, O_COL = P_G * P_BK, P_COL = O_COL + P_G * HD;     // O: head_dim columns a group; P: 32 columns a group (64 keys, two to a column)
-    constexpr uint32_t Q_COL = P_COL + (PLLM_ATT_P_TMEM ? P_G * 32 : 0);      // Q: head_dim / 2 columns
-    constexpr uint32_t TMEM_USED = Q_COL + (PLLM_ATT_Q_TMEM ? HD / 2 : 0), TMEM_COLS = TMEM_USED <= 256 ? 256 : 512;
+    constexpr int Q_BYTES = NHALF * P_ROWS * 128, STAGE = (P_BK / 8) * GROUP;   // STAGE: a key (or value) tile
+    // Tensor memory: two buffers of scores a group (64 columns each; the tile's weights, two to a column, are
+    // written over the first 32 of the scores they came from), then head_dim columns of O a group.
+    constexpr uint32_t S_COL = 0, O_COL = 2 * P_G * P_BK;
+    constexpr uint32_t TMEM_USED = O_COL + P_G * HD, TMEM_COLS = TMEM_USED <= 256 ? 256 : 512;
     static_assert(TMEM_USED <= 512, "tensor memory has 512 columns");
-    constexpr int P_SMEM = PLLM_ATT_P_TMEM ? 0 : P_G * P_ROWS * 128;          // the P buffers in shared memory, if any
     if ((int)blockIdx.y >= *n_work_ptr) return;
     const AttnWork w = work[blockIdx.y];
     // single decoded tokens are another kernel's, unless this one is told to take them too (a step of
@@ -155,20 +150,19 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t q_s = smem_u32(smem);
     const uint32_t k_ring = q_s + Q_BYTES, v_ring = k_ring + P_STAGES * STAGE;
-    const uint32_t p_s = v_ring + P_STAGES * STAGE;            // a P buffer a group
     constexpr int RINGS = 2 * P_STAGES * STAGE;
     // [groups][128] the groups' maxima and sums at the end, in the queries' place: written only when every
     // product has run (o_full)
     float* mstate = reinterpret_cast<float*>(smem);
     float* lpart = mstate + P_G * P_ROWS;
     static_assert(2 * P_G * P_ROWS * 4 <= Q_BYTES, "the groups' maxima and sums lie in the queries' place");
-    unsigned char* ctl = smem + Q_BYTES + RINGS + P_SMEM;
+    unsigned char* ctl = smem + Q_BYTES + RINGS;
     const uint32_t bars = smem_u32(ctl);
     const uint32_t q_full = bars, k_full = bars + 8, k_empty = k_full + 8 * P_STAGES, v_full = k_empty + 8 * P_STAGES,
-                   v_empty = v_full + 8 * P_STAGES, s_full = v_empty + 8 * P_STAGES,
-                   p_full = s_full + 8 * P_G, p_empty = p_full + 8 * P_G, o_full = p_empty + 8 * P_G,
-                   s_free = o_full + 8, q_tmem = s_free + 8 * P_G, turn = q_tmem + 8;
-    constexpr int N_BARS = 4 * P_STAGES + 1 + 3 * P_G + 1 + P_G + 1 + P_G;
+                   v_empty = v_full + 8 * P_STAGES, s_full = v_empty + 8 * P_STAGES,      // s_full, p_full, p_empty: [group][buffer]
+                   p_full = s_full + 16 * P_G, p_empty = p_full + 16 * P_G, o_full = p_empty + 16 * P_G,
+                   turn = o_full + 8;
+    constexpr int N_BARS = 4 * P_STAGES + 1 + 6 * P_G + 1 + P_G;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctl + 8 * N_BARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(ctl + 8 * N_BARS + 8);
 
@@ -178,15 +172,13 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             mbar_init(k_full + 8 * s, 1); mbar_init(k_empty + 8 * s, 1);
             mbar_init(v_full + 8 * s, 1); mbar_init(v_empty + 8 * s, 1);
         }
-        for (int b = 0; b < P_G; b++) {
+        for (int b = 0; b < 2 * P_G; b++) {
             mbar_init(s_full + 8 * b, 1);
             mbar_init(p_full + 8 * b, 4);        // one arrival from each warp of the group
             mbar_init(p_empty + 8 * b, 1);
-            mbar_init(s_free + 8 * b, 4);        // the group has its scores in registers
-            mbar_init(turn + 8 * b, 4);          // the other group is through with its exponentials
         }
+        for (int b = 0; b < P_G; b++) mbar_init(turn + 8 * b, 4);          // the other group is through with its exponentials
         mbar_init(o_full, P_G);                  // each group's issuing thread, after its last product
-        mbar_init(q_tmem, 4);                    // the first group's warps have put their rows of Q into tensor memory
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
         fence_async_smem();
@@ -282,34 +274,30 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             // descriptors differ only in their address field (bits 0-13, units of 16 bytes): the rest is
             // made once, and an address offset is one addition
             const uint64_t q_desc = smem_desc(q_s), k_desc = smem_desc(k_ring, 16, GROUP);
-            bool ok = mbar_wait(PLLM_ATT_Q_TMEM ? q_tmem : q_full, 0, abort_flag);
+            bool ok = mbar_wait(q_full, 0, abort_flag);
             CLK_BEGIN
             for (int t = g; t < n_tiles && ok; t += P_G) {
                 const int s = t % P_STAGES;
-                // (the key tile first: it is there long before the group has read its last scores, and a
-                // wait on a barrier that is over still costs this thread a hundred clocks or two)
+                const int k = t / P_G, buf = g * 2 + (k & 1);        // the group's k-th tile, into the buffer of its parity
+                // (the key tile first: it is there long before, and a wait on a barrier that is over still
+                // costs this thread a hundred clocks or two)
                 if (!mbar_wait(k_full + 8 * s, (t / P_STAGES) & 1, abort_flag)) { ok = false; break; }
                 CLK(1)
                 EVT(0, t, 1)
-                // the group must have read its scores of the turn before out of the buffer
-                if (t >= P_G && !mbar_wait(s_free + 8 * g, ((t - P_G) / P_G) & 1, abort_flag)) { ok = false; break; }
+                // the buffer held the scores and then the weights of the group's tile before last: those weights
+                // must have gone into O.  (The scores are thus formed a whole turn of the group ahead.)
+                if (k >= 2 && !mbar_wait(p_empty + 8 * buf, ((k >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
                 CLK(0)
                 EVT(0, t, 0)
                 tc_fence_after();
                 const uint64_t kd = k_desc + (uint64_t)((s * STAGE) >> 4);
-                const uint32_t d = tmem + S_COL + g * P_BK;
+                const uint32_t d = tmem + S_COL + buf * P_BK;
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ks++) {
-#if PLLM_ATT_Q_TMEM
-                    mma_ts(d, tmem + Q_COL + ks * 8, kd + (uint64_t)(((ks / 4) * 1024 + (ks % 4) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
-#else
+                for (int ks = 0; ks < HD / 16; ks++)
                     mma_ss(d, q_desc + (uint64_t)(((ks / 4) * P_ROWS * 128 + (ks % 4) * 32) >> 4),
                            kd + (uint64_t)(((ks / 4) * 1024 + (ks % 4) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
-#endif
-                }
-                (void)q_desc;
                 mma_commit(k_empty + 8 * s);         // the key tile's place is free once these have read it
-                mma_commit(s_full + 8 * g);
+                mma_commit(s_full + 8 * buf);
                 CLK(2)
                 EVT(0, t, 2)
             }
@@ -320,32 +308,25 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
         if (lane == 0) {
             const int g = warp == W_SUMS ? 0 : 1;
             constexpr uint32_t idesc_pv = instr_desc(P_ROWS, HD, 1);
-            const uint64_t p_desc = smem_desc(p_s), v_desc = smem_desc(v_ring, 1024, GROUP);
+            const uint64_t v_desc = smem_desc(v_ring, 1024, GROUP);
             bool ok = true;
             CLK_BEGIN
             for (int t = g; t < n_tiles && ok; t += P_G) {
+                const int k = t / P_G, buf = g * 2 + (k & 1);
                 if (!mbar_wait(v_full + 8 * (t % P_STAGES), (t / P_STAGES) & 1, abort_flag)) { ok = false; break; }      // (the values first, likewise)
                 CLK(1)
                 EVT(1, t, 1)
-                if (!mbar_wait(p_full + 8 * g, (t / P_G) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(p_full + 8 * buf, (k >> 1) & 1, abort_flag)) { ok = false; break; }
                 CLK(0)
                 EVT(1, t, 0)
                 tc_fence_after();
                 const uint64_t vd = v_desc + (uint64_t)(((t % P_STAGES) * STAGE) >> 4);
-                const uint64_t pd = p_desc + (uint64_t)((g * P_BYTES) >> 4);
 #pragma unroll
-                for (int ks = 0; ks < P_BK / 16; ks++) {   // 16 keys = two groups of 8 rows
-#if PLLM_ATT_P_TMEM
-                    mma_ts(tmem + O_COL + g * HD, tmem + P_COL + g * 32 + ks * 8, vd + (uint64_t)((ks * 2 * GROUP) >> 4), idesc_pv,
-                           (t >= P_G || ks) ? 1u : 0u);
-#else
-                    mma_ss(tmem + O_COL + g * HD, pd + (uint64_t)((ks * 32) >> 4), vd + (uint64_t)((ks * 2 * GROUP) >> 4), idesc_pv,
-                           (t >= P_G || ks) ? 1u : 0u);
-#endif
-                }
-                (void)pd;
+                for (int ks = 0; ks < P_BK / 16; ks++)    // 16 keys = two groups of 8 rows
+                    mma_ts(tmem + O_COL + g * HD, tmem + S_COL + buf * P_BK + ks * 8, vd + (uint64_t)((ks * 2 * GROUP) >> 4), idesc_pv,
+                           (k || ks) ? 1u : 0u);
                 mma_commit(v_empty + 8 * (t % P_STAGES));    // the values of this tile are read
-                mma_commit(p_empty + 8 * g);                 // and so is this group's P (and O holds the tile)
+                mma_commit(p_empty + 8 * buf);               // and so are the weights: O holds the tile, the buffer may take new scores
                 CLK(2)
                 EVT(1, t, 2)
             }
@@ -368,29 +349,6 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
         // this group's part of the row's sum, in units of 2^m_ref
         float m_ref = -CUDART_INF_F, l_run = 0.f;
         bool ok = true;
-#if PLLM_ATT_Q_TMEM
-        if (grp == 0) {
-            // this thread's row of Q out of shared memory (where TMA put it, 16-byte chunk c of a 64-value
-            // half at c ^ (row & 7)) into its lane of tensor memory, two values to a column: the scores'
-            // products then read only the keys from shared memory
-            ok = mbar_wait(q_full, 0, abort_flag);
-#pragma unroll
-            for (int h = 0; h < NHALF; h++) {
-                uint32_t qr[32];
-                const unsigned char* qrow = smem + h * P_ROWS * 128 + row * 128;
-#pragma unroll
-                for (int c = 0; c < 8; c++) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(qrow + ((c ^ (row & 7)) << 4));
-                    qr[4 * c] = v.x; qr[4 * c + 1] = v.y; qr[4 * c + 2] = v.z; qr[4 * c + 3] = v.w;
-                }
-                tmem_st32(lane_base + Q_COL + h * 32, qr);
-            }
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(q_tmem);
-        }
-#endif
         // The exponentials of the two groups take turns (they share one unit, and left alone the groups fall
         // into step: both compute theirs at once, at half speed each, and then both wait): a group computes
         // its tile's when the other is through with those of the tile before, and meanwhile loads, stores and waits.
@@ -398,17 +356,15 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
         CLK_BEGIN
         for (int t = grp; t < n_tiles; t += P_G) {
             const int kv0 = w.kv_begin + t * P_BK;
-            if (!mbar_wait(s_full + 8 * grp, (t / P_G) & 1, abort_flag)) { ok = false; break; }
+            const int k = t / P_G, buf = grp * 2 + (k & 1);      // the group's k-th tile, in the buffer of its parity
+            if (!mbar_wait(s_full + 8 * buf, (k >> 1) & 1, abort_flag)) { ok = false; break; }
             CLK(0)
             if (wq == 0 && lane == 0) EVT(2 + grp, t, 0)
             tc_fence_after();
             uint32_t v0[32], v1[32];
-            tmem_ld32(lane_base + S_COL + grp * P_BK, v0);
-            tmem_ld32(lane_base + S_COL + grp * P_BK + 32, v1);
+            tmem_ld32(lane_base + S_COL + buf * P_BK, v0);
+            tmem_ld32(lane_base + S_COL + buf * P_BK + 32, v1);
             tmem_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_free + 8 * grp);        // the buffer may take the scores of this group's next tile
             CLK(1)
             // keys of this tile at or past vis are hidden from this row (only tiles on the diagonal have any)
             const int vis = hi - kv0;
@@ -434,10 +390,10 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
             const float m_used = grow ? mx : m_prev;
             CLK(3)
             if (wq == 0 && lane == 0) EVT(2 + grp, t, 1)
-            if (t >= P_G && __any_sync(0xffffffffu, grow)) {
+            if (k >= 1 && __any_sync(0xffffffffu, grow)) {
                 // this group's O is rescaled once its tile before this one is in it (this tile's is not issued
                 // before the group has stored its weights)
-                if (!mbar_wait(p_empty + 8 * grp, ((t - P_G) / P_G) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(p_empty + 8 * (buf ^ 1), ((k - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const float alpha = (grow && m_prev > -CUDART_INF_F) ? ex2(m_prev - m_used) : (grow ? 0.f : 1.f);
 #pragma unroll
@@ -474,30 +430,23 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 pw[i] = *reinterpret_cast<uint32_t*>(&h);
                 s8[2 * (i & 3)] += p0;
                 s8[2 * (i & 3) + 1] += p1;
+                if (i == PLLM_ATT_HANDOVER - 1) {
+                    // the other group may begin: it takes a hundred clocks or two to notice
+                    __syncwarp();
+                    if (lane == 0 && t + 1 < n_tiles) mbar_arrive(turn + 8 * (grp ^ 1));
+                }
             }
             l_run += ((s8[0] + s8[1]) + (s8[2] + s8[3])) + ((s8[4] + s8[5]) + (s8[6] + s8[7]));
-            __syncwarp();
-            if (lane == 0 && t + 1 < n_tiles) mbar_arrive(turn + 8 * (grp ^ 1));
             CLK(5)
             if (wq == 0 && lane == 0) EVT(2 + grp, t, 2)
-            // this group's P of its tile before must be read out of shared memory before it is overwritten
-            if (t >= P_G && !mbar_wait(p_empty + 8 * grp, ((t - P_G) / P_G) & 1, abort_flag)) { ok = false; break; }
             CLK(6)
-#if PLLM_ATT_P_TMEM
-            // the row's 64 weights, two to a column, into this thread's lane of the group's P columns
-            tmem_st32(lane_base + P_COL + grp * 32, pw);
+            // the row's 64 weights, two to a column, over the first 32 of the scores they came from (this thread's
+            // lane: nobody else's scores)
+            tmem_st32(lane_base + S_COL + buf * P_BK, pw);
             tmem_wait_st();
-#else
-            // the row's 128 bytes, chunk c at c ^ (row & 7)
-            unsigned char* prow = smem + Q_BYTES + RINGS + grp * P_BYTES + row * 128;
-#pragma unroll
-            for (int c = 0; c < 8; c++)
-                *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pw[4 * c], pw[4 * c + 1], pw[4 * c + 2], pw[4 * c + 3]);
-            fence_async_smem();          // the tensor cores read shared memory through the async proxy
-#endif
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full + 8 * grp);
+            if (lane == 0) mbar_arrive(p_full + 8 * buf);
             CLK(7)
             if (wq == 0 && lane == 0) EVT(2 + grp, t, 3)
         }
@@ -614,8 +563,7 @@ static int launch_prefill(const void* q, const void* k_pool, const void* v_pool,
     }
     constexpr int NHALF = HD / 64;
     const size_t smem = (size_t)NHALF * P_ROWS * 128 + (size_t)P_STAGES * 2 * NHALF * P_BK * 128 +
-                        (PLLM_ATT_P_TMEM ? 0 : P_G * P_ROWS * 128) +
-                        8 * (4 * P_STAGES + 3 + 5 * P_G) + 16 + 1024;
+                        8 * (4 * P_STAGES + 2 + 7 * P_G) + 16 + 1024;
     cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_chained(attention_prefill_tcgen05_kernel<HD>, dim3(nkv * gparts, max_work), dim3(P_THREADS), smem, stream, map_q,
                    map_k, map_v, block_tables, (const AttnWork*)work, n_work_ptr, (bf16*)out, part_o, part_ml, nh, nkv,
