@@ -296,8 +296,8 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 for (int ks = 0; ks < HD / 16; ks++)
                     mma_ss(d, q_desc + (uint64_t)(((ks / 4) * P_ROWS * 128 + (ks % 4) * 32) >> 4),
                            kd + (uint64_t)(((ks / 4) * 1024 + (ks % 4) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
-                mma_commit(k_empty + 8 * s);         // the key tile's place is free once these have read it
                 mma_commit(s_full + 8 * buf);
+                mma_commit(k_empty + 8 * s);         // the key tile's place is free once these have read it
                 CLK(2)
                 EVT(0, t, 2)
             }
@@ -325,8 +325,8 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                 for (int ks = 0; ks < P_BK / 16; ks++)    // 16 keys = two groups of 8 rows
                     mma_ts(tmem + O_COL + g * HD, tmem + S_COL + buf * P_BK + ks * 8, vd + (uint64_t)((ks * 2 * GROUP) >> 4), idesc_pv,
                            (k || ks) ? 1u : 0u);
-                mma_commit(v_empty + 8 * (t % P_STAGES));    // the values of this tile are read
-                mma_commit(p_empty + 8 * buf);               // and so are the weights: O holds the tile, the buffer may take new scores
+                mma_commit(p_empty + 8 * buf);               // the weights are read: O holds the tile, the buffer may take new scores
+                mma_commit(v_empty + 8 * (t % P_STAGES));    // and so are the values of this tile
                 CLK(2)
                 EVT(1, t, 2)
             }
