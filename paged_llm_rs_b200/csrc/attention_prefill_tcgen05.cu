@@ -6,41 +6,57 @@
 // tokens (kernels/attention_plan.py).  A CTA takes one item and one kv head: up to 128 rows
 // = query tokens x the heads of the group, and walks the item's keys 64 at a time:
 //
-//   S = Q K^T     tcgen05.mma, 128 x 64 (x 128 for two tiles at once), Q and the key tile in shared memory, S in tensor memory
+//   S = Q K^T     tcgen05.mma, 128 x 64, Q and the key tile in shared memory, S in tensor memory
 //   P = softmax   four warps, ONE ROW A THREAD (a thread's lane of tensor memory is its row, so
 //                 the row's maximum and sum need no shuffles): tcgen05.ld, scale, mask, exp2,
-//                 P rounded to bfloat16 back into tensor memory (tcgen05.st, two weights a column)
+//                 P rounded to bfloat16 back into tensor memory (tcgen05.st, two weights a column,
+//                 over the first half of the scores they came from)
 //   O += P V      tcgen05.mma with P as its tensor-memory operand and the value tile in shared
 //                 memory, 128 x head_dim; a group's O stays in tensor memory for the whole item
 //
 // Sixteen warps: 0-3 and 4-7 are two softmax groups that take the key tiles in turn (even tiles
 // the first, odd the second: a group's warp w owns rows 32 w .. 32 w + 31), 8 and 10 are the producers
-// of the even tiles (TMA: queries and key tiles; value tiles), 12 and 13 those of the odd tiles, one
-// lane of warp 9 issues the tcgen05.mma of the scores, one of warp 11's those of the sums; warp 9 also
-// allocates the tensor memory; warps 14 and 15 have no work.  The softmax warps take 192 registers a
-// thread and leave the others 64 (setmaxnreg).
+// of the even tiles (TMA: queries and key tiles; value tiles), 12 and 13 those of the odd tiles.  Each
+// group has two issuing threads of its own: one lane of warp 9 (14 for the second group) issues the
+// tcgen05.mma of its scores, one of warp 11 (15) those of its sums; warp 9 also allocates the tensor
+// memory.  The softmax warps take 192 registers a thread and leave the others 64 (setmaxnreg).
 // Each group has a maximum, a sum and an O of its own for its half of the tiles (like two splits of the
 // key range): nothing passes between the groups tile by tile, and they meet once, in the epilogue.  A
 // row's running maximum is only moved when it grew by more than 2^8 (then the group's O is rescaled in
-// tensor memory), which is exact after the final division.  S and P have a buffer a group; the scores of
-// tiles t and t + 1 (t even) are formed by ONE set of products 128 keys wide, since the two tiles lie
-// back to back in the ring and their scores in neighbouring columns.
+// tensor memory), which is exact after the final division.
+// Tensor memory: two buffers of scores a group (4 x 64 columns), then head_dim columns of O a group
+// (512 columns at head_dim 128).  A buffer takes the scores of the group's tile after next once the
+// products that read this tile's weights out of it are over, so a tile's scores are formed while the
+// group is busy with the tile before.
+// The two groups share one unit for the exponentials, and left alone they fall into step: both compute
+// their exponentials at once, at half speed each, and then both load, store and wait at once (started
+// half a turn apart they were in step again within forty tiles).  So the exponentials take turns: a group
+// begins its tile's when the other is through with those of the tile before (a barrier a group).
 //
-// What was measured on the way (2048 tokens, 16 heads over 8 kv heads of 128; one CTA's clocks a tile of
-// 64 keys; -DPLLM_ATT_CLOCKS=1 builds the counters).  A request to the copy engine costs the issuing warp
-// 110-160 clocks whatever it moves, and 277 when one lane issues them one after the other: so a page is one
-// request, the lanes of a warp issue a tile's pages in one instruction, and two warps share a ring (the
-// loads alone then take 430 clocks a tile, 780 with one warp a ring).  A tcgen05.mma or a commit costs its
-// lone thread some 85 clocks and a wait on a barrier that is long over 100-200 beside eight busy warps, so
-// the scores of two tiles are one set of instructions and a thread waits first for what is surely there.
-// With everything a tile takes 1250 clocks: a group's turn (600 of them exponentials, two warps to a
-// scheduler) and the round trip from the groups to the issuing thread and back bound it about equally.
-// 8192 tokens: 328 -> 293 us (940 TFLOP/s); 2048 tokens: 29.6 -> 28.8 us with the reduction's launch.
-// Tried and no faster: three groups; rings of 2 or 3 tiles; steps of 128 keys in one group; Q in tensor
-// memory; polling with test_wait; the issuing loops run by their whole warps with an elected lane; two buffers of scores with P written over the scores it came from (the
-// next scores then wait for the P V before last: the same loop, longer); two buffers of scores AND of
-// weights with one O and the pair's maximum exchanged between twin warps (the groups' turn then bounds it
-// alone, at 2700 clocks a pair).
+// What was measured on the way (16 heads over 8 kv heads of 128; one CTA's clocks a tile of 64 keys;
+// -DPLLM_ATT_CLOCKS=1 builds the counters and a table of who saw what when).  A request to the copy engine
+// costs the issuing warp 110-160 clocks whatever it moves, and 277 when one lane issues them one after the
+// other: so a page is one request, the lanes of a warp issue a tile's pages in one instruction, and two
+// warps share a ring (the loads alone then take 430 clocks a tile, 780 with one warp a ring).  A
+// tcgen05.mma or a commit costs its lone thread some 85 clocks and a wait on a barrier that is long over
+// 100-200 beside eight busy warps, so a thread waits first for what is surely there.  The 64 exponentials
+// of a row's tile take a warp alone on its scheduler 704 clocks (512 would be the unit's rate), 1083 with
+// the sums formed pairwise first, and two warps on one scheduler 1127 each.
+// 8192 tokens: 295.6 us with one issuing thread for the scores of both groups (two tiles to one set of
+// products) and one for the sums, the groups in step, a tile every 1250 clocks; 268.8 with issuing threads
+// a group and the exponentials by turns; 255.1 (1077 TFLOP/s) with the scores buffered twice.  2048 tokens:
+// 28.7 -> 26.1 us with the reduction's launch.  What bounds it now is the chain from a tile's weights to
+// the scores of the tile after next (a wake-up, four products and a commit, a wake-up, eight products and
+// a commit, a wake-up: some 2100 clocks for a group's turn): without the maximum it takes 246, with half of
+// the exponentials 251.
+// Tried and no faster: three groups; rings of 2, 3 or 6 tiles; Q in tensor memory; polling with test_wait
+// or with a time to stay suspended (319); the issuing loops run by their whole warps with an elected lane;
+// one issuing thread a group for scores and sums (293); four issuing threads, each issuing a tile's sums
+// and then the scores of the tile after next without a wait in between (283); turns of 128 keys with the
+// weights through shared memory and the scores buffered once (276: the exponentials then take 19 clocks
+// each instead of 14); two buffers of scores AND of weights with one O and the pair's maximum exchanged
+// between twin warps (2700 clocks a pair); a part of the exponentials as a polynomial on the multiply-add
+// units (a quarter: 929 clocks for the 64 against 704).
 //
 // Shared-memory layouts.  A tile for the tensor cores has rows of 128 bytes (64 values) with
 // the 128-byte swizzle (tcgen05.cuh), in groups of 8 rows (1024 bytes).  The cache stores a key's
@@ -81,6 +97,11 @@ constexpr int W_SCORES2 = 4 * P_G + 6, W_SUMS2 = 4 * P_G + 7;   // the second gr
 static_assert(P_G == 2 && P_STAGES % 2 == 0, "the register split and the producers' turns are laid out for two groups and an even ring");   // the other four warps   // P_STAGES: key tiles, and as many value tiles, in flight
 constexpr float P_RESCALE = 8.0f;              // log2 units the running maximum may lag behind
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float y;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+    return y;
+}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -375,12 +396,12 @@ __global__ void __launch_bounds__(P_THREADS, 1) attention_prefill_tcgen05_kernel
                     if (i + 32 >= vis) v1[i] = 0xff800000u;
                 }
             }
-            // the row's maximum, four chains side by side
+            // the row's maximum, four chains side by side, three numbers to an instruction
             float m4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
 #pragma unroll
-                for (int k = 0; k < 4; k++) m4[k] = fmaxf(m4[k], fmaxf(__uint_as_float(v0[i + k]), __uint_as_float(v1[i + k])));
+                for (int c = 0; c < 4; c++) m4[c] = max3(m4[c], __uint_as_float(v0[i + c]), __uint_as_float(v1[i + c]));
             }
             const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scale_log2;   // the scale is positive
             // the maximum this group has in use; it moves only when it grew by more than 2^8 (or is not set yet)
