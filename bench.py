@@ -380,6 +380,46 @@ def generate_point(model_dir, vocab, clocks, requests=64, prompt=512, new=128, r
                 steps_per_call=m.steps // (repeats + 1))
 
 
+def long_prompt_points(runner, sizes, total, clocks):
+    """A prompt of ``total`` tokens through the step function in portions of 2048: each portion's device time, and
+    the fraction of the tensor peak its flops make (the products of 2048 rows, and the attention over everything
+    before the portion and half of itself)."""
+    import numpy as np
+    import torch
+    from paged_llm_rs_b200.engine.step import StepEntry
+    T, cache, pk = PREFILL_TOKENS, runner.cache, peaks()
+    L, nh, hd, V, H = sizes["L"], sizes["nh"], sizes["hd"], sizes["V"], sizes["H"]
+    products = sizes["prefill_flops"] - 2 * V * H - 2 * T * T * nh * hd * L        # of a portion's 2048 rows
+    prompt = np.random.default_rng(0).integers(0, V, total).tolist()
+    zero = np.zeros(1, dtype=np.float32)
+    out = {}
+    for rep in range(2):                         # (the first pass captures the steps)
+        cache.open("long")
+        events = []
+        t0 = time.time()
+        for c in range(0, total, T):
+            assert cache.reserve("long", T)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            runner.step_and_sample([StepEntry("long", prompt[c:c + T], [T - 1])], zero, zero)
+            b.record()
+            events.append((c, a, b))
+            cache.commit("long", T)
+        torch.cuda.synchronize()
+        clocks.region(t0, time.time())
+        cache.close("long")
+    for c, a, b in events:
+        if c % 8192 == 0 or c == total - T:
+            ms = a.elapsed_time(b)
+            attention = 4 * T * (c + T / 2) * nh * hd * L
+            flops = products + attention + 2 * V * H
+            out[f"portion_at_{c}"] = dict(ms=round(ms, 3), tokens_s=round(T / ms * 1e3, 1), attention_share_of_flops=round(attention / flops, 3),
+                                          bf16_frac=round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4))
+    out["whole_prompt_ms"] = round(sum(a.elapsed_time(b) for _, a, b in events), 1)
+    out["tokens"] = total
+    return out
+
+
 def shape_sizes(shape):
     L, H, I = shape["num_hidden_layers"], shape["hidden_size"], shape["intermediate_size"]
     nh, nkv, hd, V = shape["num_attention_heads"], shape["num_key_value_heads"], shape["head_dim"], shape["vocab_size"]
@@ -609,8 +649,9 @@ def main(argv=None) -> int:
                     help="with --only timeline: the captured step of a 2048-token prompt portion instead of the decode step")
     ap.add_argument("--timeline-mixed", type=int, default=0, metavar="TOKENS",
                     help="with --only timeline: the decoding requests beside one prompt portion of this many tokens")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "reference-kernel", "plain-cpu"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "long-prompt", "timeline", "reference-kernel", "plain-cpu"], default=None,
                     help="run one part alone and print a short line (for profiling; not a bench record); "
+                         "long-prompt: a prompt of --context tokens in portions of 2048, each portion timed; "
                          "timeline: one captured decode step as the kernels themselves clocked it; reference-kernel: "
                          "the reference's CUDA kernel against this engine's decode attention; plain-cpu: the plain "
                          "float32 implementation timed on the CPU (needs no GPU)")
@@ -654,6 +695,8 @@ def main(argv=None) -> int:
         model_dir = write_random_model(os.path.join(tmp, "model"), shape, 0, device="cuda")
         most = 1 if (args.no_points or args.only) else 64
         pages = max(most, B) * (ctx // PAGE + 4) + PREFILL_TOKENS // PAGE + 64
+        if args.only == "long-prompt":
+            pages = ctx // PAGE + 64
         eng = Engine(model_dir, dtype="bfloat16", block_size=PAGE, blocks=pages, max_batch=max(most, B),
                      chunk=PREFILL_TOKENS, prefix_cache=False)
         runner = eng.runner
@@ -676,6 +719,12 @@ def main(argv=None) -> int:
                 runner.cache.close("prefill")
             torch.cuda.synchronize()
             print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "steps": steps}))
+            return 0
+
+        if args.only == "long-prompt":
+            out = long_prompt_points(runner, z, max(PREFILL_TOKENS, ctx // PREFILL_TOKENS * PREFILL_TOKENS), clocks)
+            out.update(only="long-prompt", shape=shape_name, layers=L, clocks=clocks.stop())
+            print(json.dumps(out))
             return 0
 
         if args.only == "timeline":

@@ -41,3 +41,11 @@ def test_a_short_bench_run_prints_the_record():
     assert 0 < out["roofline"]["frac"] < 1.2 and 0 < out["prefill"]["frac"] < 1.2
     assert out["points"]["decode_b1"] > 0 and out["points"]["decode_b64"] > out["points"]["decode_b1"]
     assert "error" not in out["generate"] and out["generate"]["generated_tokens_s"] > 0
+
+
+def test_the_long_prompt_mode_times_every_portion():
+    out = run_bench("--only", "long-prompt", "--context", "6144", "--layers", "2")
+    assert out["tokens"] == 6144 and out["whole_prompt_ms"] > 0
+    first, last = out["portion_at_0"], out["portion_at_4096"]
+    assert 0 < first["bf16_frac"] < 1.2 and 0 < last["bf16_frac"] < 1.2
+    assert last["attention_share_of_flops"] > first["attention_share_of_flops"]
