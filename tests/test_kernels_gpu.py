@@ -441,6 +441,30 @@ def test_a_far_key_decides_for_a_long_portion_behind_a_long_context():
     torch.testing.assert_close(got, want, **tol(torch.bfloat16))
 
 
+def test_a_short_portion_behind_thirty_thousand_tokens():
+    # 130 tokens of a prompt behind 30 000 in the cache: each softmax group of the tcgen05 kernel walks
+    # some 235 tiles of keys when the range is left whole (its barriers change phase hundreds of times), and
+    # the tiles of several tokens are cut into splits whose partial rows the reduction combines when the
+    # launch wants more CTAs.  A key near the start decides for one row; a later row also sees a marked key of the portion itself.
+    nh, nkv, hd, page = 4, 1, 128, 16
+    assert ops.attention_prefill_uses_tcgen05(torch.bfloat16, nh, nkv, hd, page, 0)
+
+    def craft(r, q, k, v):
+        k[:, :, 5] = 0
+        for row, far, mark in ((3, 41, 30.0), (129, 30100, -20.0)):
+            q[row] = 0; q[row, :, 5] = 9.0 * hd ** 0.5
+            k[far, :, 5] = 9.0; v[far] = mark
+    for target, splits in ((1, False), (296, True)):
+        res, n_red = run_attention(torch.bfloat16, [(30000, 130)], nh, nkv, hd, page, None, target, craft=craft, kinds=2,
+                                   min_split_keys=attention_plan.MIN_SPLIT_KEYS,
+                                   multi_min_split_keys=attention_plan.MULTI_MIN_SPLIT_KEYS)
+        assert (n_red > 0) == splits
+        got, want = res[0]
+        assert (got[3] - 30.0).abs().max() < 0.5            # position 30003 sees the marked key at 41 and not the one at 30100
+        assert (got[129] - 5.0).abs().max() < 0.5           # position 30129 sees both marked keys, which score alike
+        torch.testing.assert_close(got, want, **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_window_edge(dtype):
     # window 24: the query at position p sees keys p-23..p.  The key at p-23 carries the
