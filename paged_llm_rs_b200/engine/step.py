@@ -90,11 +90,12 @@ class StepPacker:
         layout depends on them alone, so a captured graph can be fed any step
         that fits."""
         cache = self.cache
-        toks: List[int] = []
-        pos: List[int] = []
+        tok_parts: List[np.ndarray] = []      # (arrays a request, joined once: a portion has thousands of tokens)
+        pos_parts: List[np.ndarray] = []
         rows: List[int] = []
         segs: List[Tuple[int, int, int, int]] = []
         rcs: List[RequestCache] = []
+        T = 0
         for e in entries:
             n = len(e.tokens)
             if n == 0:
@@ -104,21 +105,19 @@ class StepPacker:
             for w in e.want:
                 if not 0 <= w < n:
                     raise ConfigError(f"request {e.request_id!r} wants place {w} among {n} tokens")
-                rows.append(len(toks) + w)
-            segs.append((len(toks), n, p0, rc.state_slot))
+                rows.append(T + w)
+            segs.append((T, n, p0, rc.state_slot))
             rcs.append(rc)
-            if n == 1:
-                toks.append(int(e.tokens[0]))
-                pos.append(p0)
-            else:
-                toks.extend(int(t) for t in e.tokens)
-                pos.extend(range(p0, p0 + n))
-        T, n_want, n_seg = len(toks), len(rows), len(segs)
-        tok_a = np.asarray(toks, dtype=np.int64)
-        if T and (tok_a.min() < 0 or tok_a.max() >= self.vocab_size):
+            tok_parts.append(np.asarray(e.tokens, dtype=np.int64))
+            pos_parts.append(np.arange(p0, p0 + n, dtype=np.int64))
+            T += n
+        n_want, n_seg = len(rows), len(segs)
+        toks = np.concatenate(tok_parts) if tok_parts else np.zeros(0, np.int64)
+        pos = np.concatenate(pos_parts) if pos_parts else np.zeros(0, np.int64)
+        if T and (toks.min() < 0 or toks.max() >= self.vocab_size):
             raise ConfigError(f"a token id lies outside the vocabulary of {self.vocab_size}")
-        if T and max(pos) >= self.max_positions:
-            raise ConfigError(f"position {max(pos)} reaches past max_position_embeddings {self.max_positions}")
+        if T and int(pos.max()) >= self.max_positions:
+            raise ConfigError(f"position {int(pos.max())} reaches past max_position_embeddings {self.max_positions}")
 
         ps = cache.page_size
         Tc = caps.tokens if caps else T
