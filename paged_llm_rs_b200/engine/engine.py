@@ -212,6 +212,12 @@ class Engine:
                     [StepEntry(s.id, [t], [0]) for s, t in zip(seqs, tokens)])
         return plan, (seqs, logits, tokens_dev, self.runner.tokens_host, [])
 
+    def warm_up(self) -> int:
+        """Capture the steps this engine replays (decode steps up to ``max_batch`` requests, the token budget's
+        steps) now instead of when the first requests need them.  Returns how many captures were made."""
+        ahead = getattr(self.runner, "capture_ahead", None)
+        return ahead(self.scheduler.max_batch) if ahead is not None else 0
+
     # -- whole generations -----------------------------------------------------------------
     def run_until_done(self) -> None:
         while self.scheduler.has_work():

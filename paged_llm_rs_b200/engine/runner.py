@@ -405,6 +405,27 @@ class ModelRunner:
             self._graphs[key] = g
         return g
 
+    def capture_ahead(self, max_batch: int, table_width: int = 64) -> int:
+        """Capture, before the first request needs them, the steps the engine replays: decode steps of 1, 2, 4, ...
+        up to ``max_batch`` requests and, under a token budget, the budget's steps of as many requests, for block
+        tables of up to ``table_width`` pages (wider ones are captured when a request first grows that long).
+        A capture takes some 40 ms; without this the first requests pay for them.  Returns how many were made."""
+        if not self.use_graphs:
+            return 0
+        made, B = 0, 1
+        while True:
+            b = min(B, self.max_graph_batch)
+            if (b, table_width) not in self._graphs:
+                self._graphs[(b, table_width)] = _DecodeGraph(self, b, table_width)
+                made += 1
+            cap = self.graph_step_tokens
+            if cap and b <= cap and (cap, table_width, b) not in self._graphs:
+                self._graphs[(cap, table_width, b)] = _DecodeGraph(self, cap, table_width, segments=b)
+                made += 1
+            if B >= max_batch or b >= self.max_graph_batch:
+                return made
+            B *= 2
+
     def check_status(self) -> None:
         code = int(self.rt.status.item())
         if code:

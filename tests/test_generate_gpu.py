@@ -153,6 +153,24 @@ def test_greedy_many_requests_decoding_beside_prompt_portions(tmp_path):
     assert outs[True] == outs[False]
 
 
+def test_warming_up_captures_the_steps_and_changes_no_token(tmp_path):
+    # the steps captured ahead of time are the ones the requests then replay: no capture is made while they
+    # run, and the tokens are those of an engine that captured as it went
+    from paged_llm_rs_b200 import Engine
+    cfg, seed = CONFIGS["D"]
+    model = write_model(tmp_path, "D", decisive=True)
+    prompts = prompts_for(cfg["vocab_size"], [70, 66, 90, 64, 130, 75], 31)
+    cold = Engine(model, dtype="bfloat16", block_size=16, blocks=160, chunk=96, max_batch=8)
+    want = cold.generate(prompts, max_tokens=24)
+    warm = Engine(model, dtype="bfloat16", block_size=16, blocks=160, chunk=96, max_batch=8)
+    made = warm.warm_up()
+    assert made == 8 and warm.warm_up() == 0            # 1, 2, 4 and 8 requests: decode steps and the budget's steps
+    held = len(warm.runner._graphs)
+    assert warm.generate(prompts, max_tokens=24) == want
+    assert len(warm.runner._graphs) == held
+    check_greedy(model, prompts, want, 24, "bfloat16")
+
+
 def vocab_order_choice(logits64, temperature, u):
     """The engine's device draw: ids upward, the first id whose running sum reaches u * total."""
     p = torch.softmax(logits64 / temperature, -1)
