@@ -12,7 +12,9 @@ next token.  One JSON line is printed:
                timed on the device with CUDA events
   e2e          the same through the Python entry point (Engine.submit / Engine.step):
                host token ids in, host token ids out, every step with its copy of
-               the packed step from pinned memory and its copy of the tokens back
+               the packed step from pinned memory and its copy of the tokens back; five
+               timed rounds of K steps, the last of which (the K positions before the
+               context) is the one reported and the others its spread
   prefill      one prompt of 2048 tokens through the step function (frac: of the library product's burst rate;
                frac_sustained: of its rate in a seconds-long loop under the power cap)
   roofline     bytes the decode step has to read (every weight once and the live
@@ -775,7 +777,10 @@ def main(argv=None) -> int:
             eng.step()
         torch.cuda.synchronize()
         per = []
-        for k in range(rounds):                      # the first round is the one reported; the others give its spread
+        # (the prompts end so that the LAST round's steps run at the last positions before the bench's context, and
+        #  that round is the one reported: the rounds before it, a little shorter in context, give the spread; a
+        #  round past the context would need wider block tables and a capture of its own)
+        for k in range(rounds):
             h2d = d2h = 0
             t0 = time.time()
             for _ in range(steps):
@@ -787,7 +792,7 @@ def main(argv=None) -> int:
             t1 = time.time()
             clocks.region(t0, t1)
             per.append((t1 - t0) / steps * 1e3)
-            if k == 0:
+            if k == rounds - 1:
                 e2e = dict(value=round(B * steps / (t1 - t0), 1), unit="tokens/s", h2d_bytes_per_step=h2d // steps,
                            d2h_bytes_per_step=d2h // steps, ms_per_step=round((t1 - t0) / steps * 1e3, 4))
         e2e.update(n=rounds, median_ms=round(statistics.median(per), 4), min_ms=round(min(per), 4), max_ms=round(max(per), 4))
