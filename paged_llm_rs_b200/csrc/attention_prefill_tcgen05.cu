@@ -47,8 +47,10 @@
 // a group and the exponentials by turns; 255.1 (1077 TFLOP/s) with the scores buffered twice.  2048 tokens:
 // 28.7 -> 26.1 us with the reduction's launch.  What bounds it now is the chain from a tile's weights to
 // the scores of the tile after next (a wake-up, four products and a commit, a wake-up, eight products and
-// a commit, a wake-up: some 2100 clocks for a group's turn): without the maximum it takes 246, with half of
-// the exponentials 251.
+// a commit, a wake-up: some 2450 clocks).  A buffer's next scores wait for that chain and the chain for the
+// group's turn on the buffer's tile (1750 clocks from the scores to the weights), so two of a group's tiles
+// take turn + chain = 4200 clocks, a tile of the CTA 1050: what shortens either by x gains x / 4 a tile
+// (without the maximum the 8192 tokens take 246 us, with half of the exponentials 251).
 // Tried and no faster: three groups; rings of 2, 3 or 6 tiles; Q in tensor memory; polling with test_wait
 // or with a time to stay suspended (319); the issuing loops run by their whole warps with an elected lane;
 // one issuing thread a group for scores and sums (293); four issuing threads, each issuing a tile's sums
